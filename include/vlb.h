@@ -1,0 +1,172 @@
+/* vlb.h -- C ABI of the B200 engine behind MatConvNet's operator classes.
+ *
+ * Every entry point takes DEVICE pointers to single-precision tensors in
+ * MATLAB order H x W x C x N (H fastest; element (h,w,c,n) at
+ * h + H*(w + W*(c + C*n)), reference matlab/src/bits/data.cu:498-505) and
+ * enqueues hand-written sm_100a kernels on the context's stream without
+ * synchronising, as the reference's GPU functors do.  There is no CPU
+ * fallback: host pointers are not accepted and a build without the CUDA
+ * kernels does not exist.
+ *
+ * Return value: the numeric value of vl::ErrorCode (reference
+ * matlab/src/bits/data.hpp:38-52); 0 = VLE_Success.  On failure
+ * vlb_ctx_last_error() holds a message chain like the reference's
+ * Context::getLastErrorMessage() (bits/data.cu:332-377).
+ *
+ * A NULL output pointer means "null tensor: skip this output", as the
+ * reference's `if (derInput)` tests do (bits/nnconv.cu:190-212).
+ */
+#ifndef VLB_H
+#define VLB_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* vl::ErrorCode, bits/data.hpp:38-52 (spelling of OutOfGPUMemeory kept). */
+enum {
+  VLB_Success = 0, VLB_Unsupported, VLB_Cuda, VLB_Cudnn, VLB_Cublas, VLB_OutOfMemory,
+  VLB_OutOfGPUMemeory, VLB_IllegalArgument, VLB_Unknown, VLB_Timeout, VLB_NoData,
+  VLB_IllegalMessage, VLB_Interrupted
+};
+
+/* Arithmetic of the convolution / fully-connected contractions. */
+enum {
+  VLB_PRECISION_3XTF32 = 0, /* tcgen05 kind::tf32, hi/lo split, 3 MMAs per product: fp32-faithful (default) */
+  VLB_PRECISION_TF32 = 1,   /* tcgen05 kind::tf32, single pass: fast path, about 1e-3 relative error */
+  VLB_PRECISION_FP32 = 2    /* CUDA-core FMA implicit GEMM: exact fp32 products, slow; also the path for
+                               strides / dilations / groups the tensor-core kernels do not cover */
+};
+
+/* ---- context: replaces vl::Context (bits/data.hpp:150-179) and the stream part of
+ *      vl::CudaHelper (bits/datacu.hpp:60-158; setStream bits/datacu.cu:70-93) ---- */
+typedef struct vlb_ctx vlb_ctx;
+
+int vlb_ctx_create(vlb_ctx** out);               /* binds to the current CUDA device */
+int vlb_ctx_destroy(vlb_ctx* ctx);               /* frees scratch; Context::clear, bits/data.cu:288-301 */
+int vlb_ctx_set_stream(vlb_ctx* ctx, void* cuda_stream);  /* CudaHelper::setStream; NULL = legacy default stream */
+void* vlb_ctx_get_stream(vlb_ctx* ctx);
+int vlb_ctx_set_precision(vlb_ctx* ctx, int precision);
+int vlb_ctx_get_precision(vlb_ctx* ctx);
+char const* vlb_ctx_last_error(vlb_ctx* ctx);    /* Context::getLastErrorMessage, bits/data.cu:372-377 */
+void vlb_ctx_reset_error(vlb_ctx* ctx);          /* Context::resetLastError */
+int vlb_ctx_reserve_workspace(vlb_ctx* ctx, size_t bytes); /* grow-only scratch, Context::getWorkspace bits/data.cu:395-404 */
+size_t vlb_ctx_workspace_bytes(vlb_ctx* ctx);
+int vlb_ctx_clear_workspace(vlb_ctx* ctx);       /* Context::clearWorkspace, bits/data.cu:406-410 */
+long long vlb_ctx_launch_count(vlb_ctx* ctx);    /* kernels enqueued through this context so far */
+char const* vlb_error_message(int code);         /* vl::getErrorMessage, bits/data.cu:83-100 (all 13 codes named) */
+int vlb_version(void);
+
+/* ---- convolution: vl::nn::Convolution (bits/nnconv.hpp:23-52) -------------------------------- */
+typedef struct {
+  int H, W, C, N;            /* input  H x W x C x N */
+  int FH, FW, FC, K;         /* filter FH x FW x FC x K; groups = C / FC (bits/nnconv.cu:89-90) */
+  int strideY, strideX;
+  int padTop, padBottom, padLeft, padRight;
+  int dilateY, dilateX;
+} vlb_conv_desc;
+
+/* Output extent (matlab/src/vl_nnconv.cu:324-331, bits/impl/im2row_cpu.cpp:70-73). */
+int vlb_conv_output_shape(vlb_conv_desc const* d, int* Ho, int* Wo);
+
+/* Convolution::forward (bits/nnconv.cu:71-157): Y = outMult*Y + inMult*conv(X,F) + b.
+ * b may be NULL.  Y is read only when outMult != 0. */
+int vlb_conv_forward(vlb_ctx* ctx, float* Y, double outMult, float const* X, double inMult,
+                     float const* F, float const* b, vlb_conv_desc const* d);
+
+/* Convolution::backward (bits/nnconv.cu:163-317).  dX, dF, db are overwritten; any may be NULL. */
+int vlb_conv_backward(vlb_ctx* ctx, float* dX, float* dF, float* db, float const* X,
+                      float const* F, float const* dY, vlb_conv_desc const* d);
+
+/* ---- fully connected: vl::nn::FullyConnected (bits/nnfullyconnected.hpp:20-37) ---------------
+ * The gateway routes here when the output is 1x1, stride 1, no pad, no dilation, one group
+ * (matlab/src/vl_nnconv.cu:351-361).  d->FH==d->H, d->FW==d->W, d->FC==d->C.  F == NULL copies. */
+int vlb_fc_forward(vlb_ctx* ctx, float* Y, float const* X, float const* F, float const* b,
+                   vlb_conv_desc const* d);
+int vlb_fc_backward(vlb_ctx* ctx, float* dX, float* dF, float* db, float const* X, float const* F,
+                    float const* dY, vlb_conv_desc const* d);
+
+/* ---- bias: vl::nn::Bias (bits/nnbias.hpp:20-35) ---------------------------------------------- */
+/* Bias::forward (bits/nnbias.cu:37-96): with b != NULL and bMult != 0, Y = yMult*Y + bMult*b
+ * (broadcast over H,W,N); otherwise Y = 0 whatever yMult is; then Y += xMult*X if X != NULL. */
+int vlb_bias_forward(vlb_ctx* ctx, float* Y, double yMult, float const* X, double xMult,
+                     float const* b, double bMult, int H, int W, int K, int N);
+/* Bias::backward (bits/nnbias.cu:102-175): db = dbMult*db + bMult*sum_{h,w,n} dY;
+ * dX = dXMult*dX + xMult*dY.  A multiplier of exactly 0 means "overwrite" (the old value is not
+ * read), where the reference would multiply uninitialised memory by zero. */
+int vlb_bias_backward(vlb_ctx* ctx, float* dX, double dXMult, float* db, double dbMult, double xMult,
+                      double bMult, float const* dY, int H, int W, int K, int N);
+
+/* ---- batch normalisation: vl::nn::BatchNorm (bits/nnbnorm.hpp:22-59) --------------------------
+ * moments = 2*C floats [mean(0..C-1), sigma(C..2C-1)], sigma = sqrt(var + eps)
+ * (matlab/src/vl_nnbnorm.cu:210-213, bits/nnbnorm.cu:65-70). */
+int vlb_bnorm_forward(vlb_ctx* ctx, float* Y, float* moments /* may be NULL */, float const* X,
+                      float const* g, float const* b, int H, int W, int C, int N, double eps);
+int vlb_bnorm_forward_moment(vlb_ctx* ctx, float* Y, float const* moments, float const* X,
+                             float const* g, float const* b, int H, int W, int C, int N, double eps);
+int vlb_bnorm_backward(vlb_ctx* ctx, float* dX, float* dG, float* dB, float* moments /* may be NULL */,
+                       float const* X, float const* g, float const* b, float const* dY,
+                       int H, int W, int C, int N, double eps);
+int vlb_bnorm_backward_moment(vlb_ctx* ctx, float* dX, float* dG, float* dB, float const* moments,
+                              float const* X, float const* g, float const* b, float const* dY,
+                              int H, int W, int C, int N, double eps);
+
+/* ---- pooling: vl::nn::Pooling (bits/nnpooling.hpp:21-49) ------------------------------------- */
+enum { VLB_POOL_MAX = 0, VLB_POOL_AVG = 1 };
+typedef struct {
+  int H, W, C, N;
+  int poolH, poolW, strideY, strideX;
+  int padTop, padBottom, padLeft, padRight;
+  int method;
+} vlb_pool_desc;
+int vlb_pool_output_shape(vlb_pool_desc const* d, int* Ho, int* Wo); /* matlab/src/vl_nnpool.cu:240-247 */
+int vlb_pool_forward(vlb_ctx* ctx, float* Y, float const* X, vlb_pool_desc const* d);
+/* Pooling::backward (bits/nnpooling.cu:170-214).  The reference accumulates into a dX the gateway
+ * has zero-filled (matlab/src/vl_nnpool.cu:255-259); here dX is OVERWRITTEN with "0 + contributions",
+ * contributions added in the reference's window order, so the result is the same bit for bit and the
+ * caller's zero fill is harmless but unnecessary. */
+int vlb_pool_backward(vlb_ctx* ctx, float* dX, float const* X, float const* dY, vlb_pool_desc const* d);
+
+/* ---- ROI pooling: vl::nn::ROIPooling (bits/nnroipooling.hpp:23-45) ----------------------------
+ * rois: 5 x numROIs floats [image(1-based); u1; v1; u2; v2]; transform: 6 doubles, 2x3 column-major.
+ * Y / dY: S0 x S1 x C x numROIs.  dX is overwritten (zeroed, then accumulated with atomics because
+ * ROIs overlap), matching the reference CPU's memset (bits/nnroipooling.cu:237). */
+int vlb_roipool_forward(vlb_ctx* ctx, float* Y, float const* X, float const* rois, int H, int W, int C,
+                        int N, int numROIs, int S0, int S1, double const* transform, int method);
+int vlb_roipool_backward(vlb_ctx* ctx, float* dX, float const* X, float const* rois, float const* dY,
+                         int H, int W, int C, int N, int numROIs, int S0, int S1,
+                         double const* transform, int method);
+/* Bin geometry alone (bits/nnroipooling.cu:120-165), for checking it bit for bit:
+ * bounds[4*(ph + S0*(pw + S1*roi)) + {0,1,2,3}] = hstart,hend,wstart,wend; images[roi] = 0-based image. */
+int vlb_roipool_bounds(vlb_ctx* ctx, int* bounds, int* images, float const* rois, int H, int W, int N,
+                       int numROIs, int S0, int S1, double const* transform);
+
+/* ---- bilinear sampler: vl::nn::BilinearSampler (bits/nnbilinearsampler.hpp:21-36) -------------
+ * X: H x W x C x N; grid: 2 x Ho x Wo x Ng (y first), Ng a multiple of N; Y, dY: Ho x Wo x C x Ng.
+ * dX and dGrid are overwritten (either may be NULL). */
+int vlb_sampler_forward(vlb_ctx* ctx, float* Y, float const* X, float const* grid, int H, int W, int C,
+                        int N, int Ho, int Wo, int Ng);
+int vlb_sampler_backward(vlb_ctx* ctx, float* dX, float* dGrid, float const* X, float const* grid,
+                         float const* dY, int H, int W, int C, int N, int Ho, int Wo, int Ng);
+
+/* ---- blocks the reference implements in MATLAB, needed to run whole networks on the device ---- */
+/* matlab/vl_nnrelu.m:43-48 (leak 0). */
+int vlb_relu_forward(vlb_ctx* ctx, float* Y, float const* X, size_t n);
+int vlb_relu_backward(vlb_ctx* ctx, float* dX, float const* X, float const* dY, size_t n);
+/* matlab/vl_nnsoftmaxloss.m:56-84, one 1-based class label (as float) per image.
+ * loss: one float on the device. */
+int vlb_softmaxloss_forward(vlb_ctx* ctx, float* loss, float const* X, float const* labels,
+                            int H, int W, int C, int N);
+int vlb_softmaxloss_backward(vlb_ctx* ctx, float* dX, float const* X, float const* labels, double dzdy,
+                             int H, int W, int C, int N);
+/* matlab/+dagnn/Sum.m:11-23: Y = A + B (Y may alias A). */
+int vlb_sum(vlb_ctx* ctx, float* Y, float const* A, float const* B, size_t n);
+/* x *= alpha: the 1/numWorkers scaling of an all-reduced gradient (examples/cnn_train.m:482-483). */
+int vlb_scale(vlb_ctx* ctx, float* x, double alpha, size_t n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VLB_H */

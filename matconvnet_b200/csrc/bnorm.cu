@@ -1,0 +1,331 @@
+// Batch normalisation (vl::nn::BatchNorm, reference bits/nnbnorm.hpp:22-59;
+// CPU definition bits/nnbnorm.cu:46-164).
+//
+// HBM-bound, two passes:
+//   1. reduce: per channel sum(x), sum(x^2) [, sum(dy*x), sum(dy)].  A channel is split
+//      across a thread-block CLUSTER of kCluster CTAs (C alone would leave most of the
+//      148 SMs idle: the reference launches exactly C blocks, bits/nnbnorm_gpu.cu:1113).
+//      Each CTA sweeps its share with 128-bit loads, reduces with warp shuffles, and the
+//      cluster's rank-0 CTA gathers the kCluster partials through distributed shared
+//      memory in rank order and finishes the per-channel arithmetic in the reference's
+//      order (bits/nnbnorm.cu:126-133).  No scratch memory, no atomics, deterministic.
+//   2. apply: y or dx, element-wise with the per-channel coefficients.
+// Algorithmic traffic of backward: 8*m*C bytes (pass 1) + 12*m*C bytes (pass 2), m = H*W*N.
+#include "common.cuh"
+#include <cooperative_groups.h>
+#include <math.h>
+
+namespace cg = cooperative_groups;
+
+namespace {
+
+constexpr int kCluster = 8;
+constexpr int kThreads = 256;
+
+// stats layout handed from pass 1 to pass 2 (device memory, 4*C floats):
+// [0,C) mean, [C,2C) sigma, [2C,3C) dgamma, [3C,4C) dbeta
+
+template <int kSums>
+__device__ __forceinline__ void accumulate(float (&acc)[4], float x, float dy)
+{
+  acc[0] += x;
+  acc[1] = fmaf(x, x, acc[1]);
+  if (kSums == 4) { acc[2] = fmaf(dy, x, acc[2]); acc[3] += dy; }
+}
+
+// kMode 0: moments only (forward).  1: moments + ders (backward).  2: ders only, moments given.
+template <int kMode, bool kVec>
+__global__ void __cluster_dims__(1, kCluster, 1) __launch_bounds__(kThreads)
+bnorm_reduce_kernel(float* __restrict__ momentsOut,   // 2*C or nullptr
+                    float* __restrict__ dgOut, float* __restrict__ dbOut,
+                    float const* __restrict__ momentsIn,  // mode 2
+                    float const* __restrict__ x, float const* __restrict__ dy,
+                    int WH, int C, int N, float eps)
+{
+  cg::cluster_group cluster = cg::this_cluster();
+  __shared__ float part[4];
+  __shared__ float warpRed[kThreads / 32][4];
+  int c = blockIdx.x;
+  int rank = (int)cluster.block_rank();   // the cluster spans grid y
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+
+  // Work items: (image n, chunk of the plane).  Item i of this channel goes to CTA i % kCluster.
+  if (kVec) {
+    int WH4 = WH >> 2;
+    long long items = (long long)N * WH4;
+    for (long long i = (long long)rank * kThreads + threadIdx.x; i < items; i += (long long)kCluster * kThreads) {
+      int n = (int)(i / WH4);
+      int q = (int)(i - (long long)n * WH4);
+      size_t off = ((size_t)n * C + c) * (size_t)WH + 4 * (size_t)q;
+      float4 xv = *reinterpret_cast<float4 const*>(x + off);
+      float4 dv = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (kMode != 0) dv = *reinterpret_cast<float4 const*>(dy + off);
+      if (kMode == 2) {
+        acc[2] = fmaf(dv.x, xv.x, acc[2]); acc[2] = fmaf(dv.y, xv.y, acc[2]);
+        acc[2] = fmaf(dv.z, xv.z, acc[2]); acc[2] = fmaf(dv.w, xv.w, acc[2]);
+        acc[3] += (dv.x + dv.y) + (dv.z + dv.w);
+      } else {
+        accumulate<kMode == 0 ? 2 : 4>(acc, xv.x, dv.x);
+        accumulate<kMode == 0 ? 2 : 4>(acc, xv.y, dv.y);
+        accumulate<kMode == 0 ? 2 : 4>(acc, xv.z, dv.z);
+        accumulate<kMode == 0 ? 2 : 4>(acc, xv.w, dv.w);
+      }
+    }
+  } else {
+    long long items = (long long)N * WH;
+    for (long long i = (long long)rank * kThreads + threadIdx.x; i < items; i += (long long)kCluster * kThreads) {
+      int n = (int)(i / WH);
+      int q = (int)(i - (long long)n * WH);
+      size_t off = ((size_t)n * C + c) * (size_t)WH + q;
+      float xv = x[off];
+      float dv = (kMode != 0) ? dy[off] : 0.f;
+      if (kMode == 2) { acc[2] = fmaf(dv, xv, acc[2]); acc[3] += dv; }
+      else accumulate<kMode == 0 ? 2 : 4>(acc, xv, dv);
+    }
+  }
+
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    for (int o = 16; o > 0; o >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) { for (int j = 0; j < 4; ++j) warpRed[warp][j] = acc[j]; }
+  __syncthreads();
+  if (threadIdx.x < 4) {
+    float s = 0.f;
+    for (int w = 0; w < kThreads / 32; ++w) s += warpRed[w][threadIdx.x];
+    part[threadIdx.x] = s;
+  }
+  cluster.sync();
+  if (rank == 0 && threadIdx.x == 0) {
+    float tot[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < kCluster; ++r) {
+      float const* remote = cluster.map_shared_rank(part, r);
+      for (int j = 0; j < 4; ++j) tot[j] += remote[j];
+    }
+    float mass = (float)((long long)WH * N);
+    float mean, sigma;
+    if (kMode == 2) { mean = momentsIn[c]; sigma = momentsIn[c + C]; }
+    else {
+      // reference bits/nnbnorm.cu:65-70
+      mean = __fdiv_rn(tot[0], mass);
+      float s2 = __fadd_rn(__fdiv_rn(tot[1], mass), -__fmul_rn(mean, mean));
+      s2 = fmaxf(s2, 0.f);
+      sigma = __fsqrt_rn(__fadd_rn(s2, eps));
+      if (momentsOut) { momentsOut[c] = mean; momentsOut[c + C] = sigma; }
+    }
+    if (kMode != 0) {
+      // reference bits/nnbnorm.cu:94-98
+      dbOut[c] = tot[3];
+      dgOut[c] = __fdiv_rn(__fadd_rn(tot[2], -__fmul_rn(mean, tot[3])), sigma);
+    }
+  }
+  cluster.sync();   // keep every CTA's shared memory alive until rank 0 has read it
+}
+
+// Per-channel coefficients, computed once so that pass 2 is pure multiply/add.
+// forward: cf = {mean, g/sigma, b, -}   (reference bits/nnbnorm.cu:192-196)
+// backward: cf = {mean, db/m, G1 = g/sigma, G2 = G1*dg/(m*sigma)}   (bits/nnbnorm.cu:148-153)
+__global__ void bnorm_coef_kernel(float4* __restrict__ cf, float const* __restrict__ moments,
+                                  float const* __restrict__ g, float const* __restrict__ b,
+                                  float const* __restrict__ dg, float const* __restrict__ db, int C, float mass)
+{
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float mean = moments[c], sigma = moments[c + C];
+  float G1 = __fdiv_rn(g[c], sigma);
+  if (dg) {
+    float muz = __fdiv_rn(db[c], mass);
+    float G2 = __fdiv_rn(__fmul_rn(G1, dg[c]), __fmul_rn(mass, sigma));
+    cf[c] = make_float4(mean, muz, G1, G2);
+  } else {
+    cf[c] = make_float4(mean, G1, b[c], 0.f);
+  }
+}
+
+// y = g/sigma * (x - mean) + b (reference bits/nnbnorm.cu:192-203)
+template <bool kVec>
+__global__ void bnorm_fwd_apply_kernel(float* __restrict__ y, float const* __restrict__ x,
+                                       float4 const* __restrict__ cf, int WH, int C, size_t total)
+{
+  size_t stride = (size_t)gridDim.x * blockDim.x;
+  if (kVec) {
+    size_t total4 = total >> 2;
+    int WH4 = WH >> 2;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += stride) {
+      int c = (int)((i / WH4) % C);
+      float4 k = __ldg(cf + c);
+      float4 v = reinterpret_cast<float4 const*>(x)[i];
+      v.x = __fadd_rn(__fmul_rn(k.y, __fadd_rn(v.x, -k.x)), k.z);
+      v.y = __fadd_rn(__fmul_rn(k.y, __fadd_rn(v.y, -k.x)), k.z);
+      v.z = __fadd_rn(__fmul_rn(k.y, __fadd_rn(v.z, -k.x)), k.z);
+      v.w = __fadd_rn(__fmul_rn(k.y, __fadd_rn(v.w, -k.x)), k.z);
+      reinterpret_cast<float4*>(y)[i] = v;
+    }
+  } else {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+      int c = (int)((i / WH) % C);
+      float4 k = __ldg(cf + c);
+      y[i] = __fadd_rn(__fmul_rn(k.y, __fadd_rn(x[i], -k.x)), k.z);
+    }
+  }
+}
+
+// dx = G1*(dy - db/m) - G2*(x - mean) (reference bits/nnbnorm.cu:136-164)
+template <bool kVec>
+__global__ void bnorm_bwd_apply_kernel(float* __restrict__ dx, float const* __restrict__ x,
+                                       float const* __restrict__ dy, float4 const* __restrict__ cf,
+                                       int WH, int C, size_t total)
+{
+  size_t stride = (size_t)gridDim.x * blockDim.x;
+  if (kVec) {
+    size_t total4 = total >> 2;
+    int WH4 = WH >> 2;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += stride) {
+      int c = (int)((i / WH4) % C);
+      float4 k = __ldg(cf + c);
+      float4 xv = reinterpret_cast<float4 const*>(x)[i];
+      float4 dv = reinterpret_cast<float4 const*>(dy)[i];
+      float4 o;
+      o.x = __fadd_rn(__fmul_rn(k.z, __fadd_rn(dv.x, -k.y)), -__fmul_rn(k.w, __fadd_rn(xv.x, -k.x)));
+      o.y = __fadd_rn(__fmul_rn(k.z, __fadd_rn(dv.y, -k.y)), -__fmul_rn(k.w, __fadd_rn(xv.y, -k.x)));
+      o.z = __fadd_rn(__fmul_rn(k.z, __fadd_rn(dv.z, -k.y)), -__fmul_rn(k.w, __fadd_rn(xv.z, -k.x)));
+      o.w = __fadd_rn(__fmul_rn(k.z, __fadd_rn(dv.w, -k.y)), -__fmul_rn(k.w, __fadd_rn(xv.w, -k.x)));
+      reinterpret_cast<float4*>(dx)[i] = o;
+    }
+  } else {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+      int c = (int)((i / WH) % C);
+      float4 k = __ldg(cf + c);
+      dx[i] = __fadd_rn(__fmul_rn(k.z, __fadd_rn(dy[i], -k.y)), -__fmul_rn(k.w, __fadd_rn(x[i], -k.x)));
+    }
+  }
+}
+
+bool vec_ok(int WH, void const* a, void const* b, void const* c)
+{
+  uintptr_t bits = (uintptr_t)a | (uintptr_t)b | (uintptr_t)c;
+  return (WH % 4 == 0) && (bits & 15) == 0;
+}
+
+int validate(vlb_ctx* ctx, int H, int W, int C, int N)
+{
+  VLB_REQUIRE(ctx, H > 0 && W > 0 && C > 0 && N > 0, "bnorm: empty input");
+  VLB_REQUIRE(ctx, (long long)H * W * N < (1LL << 31), "bnorm: H*W*N too large");
+  return VLB_Success;
+}
+
+template <int kMode>
+void launch_reduce(vlb_ctx* ctx, bool vec, float* momOut, float* dg, float* db, float const* momIn,
+                   float const* x, float const* dy, int WH, int C, int N, float eps)
+{
+  dim3 grid(C, kCluster);
+  if (vec) bnorm_reduce_kernel<kMode, true><<<grid, kThreads, 0, ctx->stream>>>(momOut, dg, db, momIn, x, dy, WH, C, N, eps);
+  else     bnorm_reduce_kernel<kMode, false><<<grid, kThreads, 0, ctx->stream>>>(momOut, dg, db, momIn, x, dy, WH, C, N, eps);
+  VLB_LAUNCHED(ctx, 1);
+}
+
+// Scratch layout (context workspace): [0, 2C) moments when the caller passes none,
+// then 4C floats of per-channel coefficients (16-byte aligned).
+static float* scratch(vlb_ctx* ctx, int C, float4** cf)
+{
+  size_t momBytes = ((sizeof(float) * 2 * (size_t)C + 255) / 256) * 256;
+  char* ws = (char*)vlb::workspace(ctx, momBytes + sizeof(float4) * (size_t)C);
+  if (!ws) return nullptr;
+  *cf = (float4*)(ws + momBytes);
+  return (float*)ws;
+}
+
+static int forward_common(vlb_ctx* ctx, float* Y, float* momOut, float const* momIn, float const* X, float const* g,
+                          float const* b, int H, int W, int C, int N, double eps, char const* where)
+{
+  int rc = validate(ctx, H, W, C, N);
+  if (rc) return rc;
+  VLB_REQUIRE(ctx, Y && X && g && b, "bnorm_forward: null tensor");
+  float4* cf = nullptr;
+  float* ownMom = scratch(ctx, C, &cf);
+  if (!ownMom) return vlb::pass_error(ctx, ctx->lastError, where);
+  int WH = H * W;
+  float const* mom = momIn;
+  if (!momIn) {
+    // reference: moments computed into the context workspace when not asked for (bits/nnbnorm.cu:233-240)
+    float* m = momOut ? momOut : ownMom;
+    launch_reduce<0>(ctx, vec_ok(WH, X, X, X), m, nullptr, nullptr, nullptr, X, nullptr, WH, C, N, (float)eps);
+    mom = m;
+  }
+  bnorm_coef_kernel<<<vlb::ceil_div(C, 256), 256, 0, ctx->stream>>>(cf, mom, g, b, nullptr, nullptr, C, 0.f);
+  size_t total = (size_t)WH * C * N;
+  bool vec = vec_ok(WH, Y, X, X);
+  unsigned grid = vlb::grid_for(vec ? total / 4 : total, kThreads, ctx->smCount * 16);
+  if (vec) bnorm_fwd_apply_kernel<true><<<grid, kThreads, 0, ctx->stream>>>(Y, X, cf, WH, C, total);
+  else     bnorm_fwd_apply_kernel<false><<<grid, kThreads, 0, ctx->stream>>>(Y, X, cf, WH, C, total);
+  VLB_LAUNCHED(ctx, 2);
+  return vlb::check_launch(ctx, where);
+}
+
+static int backward_common(vlb_ctx* ctx, float* dX, float* dG, float* dB, float* momOut, float const* momIn,
+                           float const* X, float const* g, float const* dY, int H, int W, int C, int N,
+                           double eps, char const* where)
+{
+  int rc = validate(ctx, H, W, C, N);
+  if (rc) return rc;
+  VLB_REQUIRE(ctx, dX && dG && dB && X && g && dY, "bnorm_backward: null tensor");
+  float4* cf = nullptr;
+  float* ownMom = scratch(ctx, C, &cf);
+  if (!ownMom) return vlb::pass_error(ctx, ctx->lastError, where);
+  int WH = H * W;
+  float const* mom = momIn;
+  bool vec = vec_ok(WH, X, dY, dX);
+  if (!momIn) {
+    float* m = momOut ? momOut : ownMom;
+    launch_reduce<1>(ctx, vec, m, dG, dB, nullptr, X, dY, WH, C, N, (float)eps);
+    mom = m;
+  } else {
+    launch_reduce<2>(ctx, vec, nullptr, dG, dB, momIn, X, dY, WH, C, N, (float)eps);
+  }
+  float mass = (float)((long long)WH * N);
+  bnorm_coef_kernel<<<vlb::ceil_div(C, 256), 256, 0, ctx->stream>>>(cf, mom, g, nullptr, dG, dB, C, mass);
+  size_t total = (size_t)WH * C * N;
+  unsigned grid = vlb::grid_for(vec ? total / 4 : total, kThreads, ctx->smCount * 16);
+  if (vec) bnorm_bwd_apply_kernel<true><<<grid, kThreads, 0, ctx->stream>>>(dX, X, dY, cf, WH, C, total);
+  else     bnorm_bwd_apply_kernel<false><<<grid, kThreads, 0, ctx->stream>>>(dX, X, dY, cf, WH, C, total);
+  VLB_LAUNCHED(ctx, 2);
+  return vlb::check_launch(ctx, where);
+}
+
+}  // namespace
+
+extern "C" {
+
+int vlb_bnorm_forward_moment(vlb_ctx* ctx, float* Y, float const* moments, float const* X, float const* g,
+                             float const* b, int H, int W, int C, int N, double eps)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  VLB_REQUIRE(ctx, moments, "bnorm_forward_moment: null moments");
+  return forward_common(ctx, Y, nullptr, moments, X, g, b, H, W, C, N, eps, "vlb_bnorm_forward_moment");
+}
+
+int vlb_bnorm_forward(vlb_ctx* ctx, float* Y, float* moments, float const* X, float const* g, float const* b,
+                      int H, int W, int C, int N, double eps)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  return forward_common(ctx, Y, moments, nullptr, X, g, b, H, W, C, N, eps, "vlb_bnorm_forward");
+}
+
+int vlb_bnorm_backward(vlb_ctx* ctx, float* dX, float* dG, float* dB, float* moments, float const* X,
+                       float const* g, float const* b, float const* dY, int H, int W, int C, int N, double eps)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  (void)b;
+  return backward_common(ctx, dX, dG, dB, moments, nullptr, X, g, dY, H, W, C, N, eps, "vlb_bnorm_backward");
+}
+
+int vlb_bnorm_backward_moment(vlb_ctx* ctx, float* dX, float* dG, float* dB, float const* moments, float const* X,
+                              float const* g, float const* b, float const* dY, int H, int W, int C, int N, double eps)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  (void)b;
+  VLB_REQUIRE(ctx, moments, "bnorm_backward_moment: null moments");
+  return backward_common(ctx, dX, dG, dB, nullptr, moments, X, g, dY, H, W, C, N, eps, "vlb_bnorm_backward_moment");
+}
+
+}  // extern "C"

@@ -1,0 +1,48 @@
+// Shared declarations for the engine's translation units.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string>
+#include "../../include/vlb.h"
+
+// The context: stream, grow-only scratch, sticky error message chain.
+// Mirrors the parts of vl::Context / vl::CudaHelper the operators use
+// (reference bits/data.hpp:150-179, bits/datacu.hpp:60-158).
+struct vlb_ctx {
+  int device = 0;
+  cudaStream_t stream = 0;
+  int precision = VLB_PRECISION_3XTF32;
+  void* workspace = nullptr;
+  size_t workspaceBytes = 0;
+  int lastError = VLB_Success;
+  std::string lastErrorMessage;
+  long long launches = 0;
+  int smCount = 148;
+};
+
+namespace vlb {
+
+int set_error(vlb_ctx* ctx, int code, char const* msg);
+int pass_error(vlb_ctx* ctx, int code, char const* where);
+// Scratch of at least `bytes`; contents belong to whichever op asked last
+// (reference Context::getWorkspace, bits/data.cu:395-404).  nullptr on failure.
+void* workspace(vlb_ctx* ctx, size_t bytes);
+// cudaPeekAtLastError after a launch, as the reference does (bits/datacu.cu:356-371).
+int check_launch(vlb_ctx* ctx, char const* where);
+
+inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
+inline unsigned grid_for(size_t n, int threads, int maxBlocks = 148 * 16)
+{
+  size_t b = (n + threads - 1) / threads;
+  if (b > (size_t)maxBlocks) b = maxBlocks;
+  if (b == 0) b = 1;
+  return (unsigned)b;
+}
+
+}  // namespace vlb
+
+#define VLB_REQUIRE(ctx, cond, msg) \
+  do { if (!(cond)) return vlb::set_error((ctx), VLB_IllegalArgument, (msg)); } while (0)
+
+#define VLB_LAUNCHED(ctx, n) do { (ctx)->launches += (n); } while (0)

@@ -1,0 +1,131 @@
+// Context management and error reporting of the C ABI.
+#include "common.cuh"
+
+namespace vlb {
+
+static char const* const kMessages[] = {
+  "success", "unsupported feature", "CUDA error", "cuDNN error", "cuBLAS error", "out of memory",
+  "out of GPU memory", "illegal argument", "unknown error", "timeout", "no data", "illegal message",
+  "interrupted"};
+
+int set_error(vlb_ctx* ctx, int code, char const* msg)
+{
+  if (!ctx) return code;
+  if (code != VLB_Success) {
+    ctx->lastError = code;
+    ctx->lastErrorMessage = std::string(vlb_error_message(code));
+    if (msg) { ctx->lastErrorMessage += " ["; ctx->lastErrorMessage += msg; ctx->lastErrorMessage += "]"; }
+  }
+  return code;
+}
+
+int pass_error(vlb_ctx* ctx, int code, char const* where)
+{
+  if (ctx && code != VLB_Success && where) {
+    ctx->lastErrorMessage = std::string(where) + ": " + ctx->lastErrorMessage;
+  }
+  return code;
+}
+
+void* workspace(vlb_ctx* ctx, size_t bytes)
+{
+  if (bytes <= ctx->workspaceBytes && ctx->workspace) return ctx->workspace;
+  if (bytes == 0) bytes = 256;
+  if (ctx->workspace) {
+    // Work enqueued earlier may still be using the old buffer.
+    cudaStreamSynchronize(ctx->stream);
+    cudaFree(ctx->workspace);
+    ctx->workspace = nullptr;
+    ctx->workspaceBytes = 0;
+  }
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    set_error(ctx, VLB_OutOfGPUMemeory, cudaGetErrorString(e));
+    return nullptr;
+  }
+  ctx->workspace = p;
+  ctx->workspaceBytes = bytes;
+  return p;
+}
+
+int check_launch(vlb_ctx* ctx, char const* where)
+{
+  cudaError_t e = cudaPeekAtLastError();
+  if (e == cudaSuccess) return VLB_Success;
+  set_error(ctx, VLB_Cuda, cudaGetErrorString(e));
+  return pass_error(ctx, VLB_Cuda, where);
+}
+
+}  // namespace vlb
+
+extern "C" {
+
+int vlb_version(void) { return 100; }
+
+char const* vlb_error_message(int code)
+{
+  if (code < 0 || code > VLB_Interrupted) code = VLB_Unknown;
+  return vlb::kMessages[code];
+}
+
+int vlb_ctx_create(vlb_ctx** out)
+{
+  if (!out) return VLB_IllegalArgument;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) { cudaGetLastError(); return VLB_Cuda; }
+  cudaDeviceProp prop;
+  e = cudaGetDeviceProperties(&prop, dev);
+  if (e != cudaSuccess) { cudaGetLastError(); return VLB_Cuda; }
+  if (prop.major != 10) {
+    // The kernels are built for sm_100a only; refuse anything else up front.
+    return VLB_Unsupported;
+  }
+  vlb_ctx* c = new vlb_ctx();
+  c->device = dev;
+  c->smCount = prop.multiProcessorCount;
+  *out = c;
+  return VLB_Success;
+}
+
+int vlb_ctx_destroy(vlb_ctx* ctx)
+{
+  if (!ctx) return VLB_Success;
+  if (ctx->workspace) { cudaStreamSynchronize(ctx->stream); cudaFree(ctx->workspace); }
+  delete ctx;
+  return VLB_Success;
+}
+
+int vlb_ctx_set_stream(vlb_ctx* ctx, void* s) { if (!ctx) return VLB_IllegalArgument; ctx->stream = (cudaStream_t)s; return VLB_Success; }
+void* vlb_ctx_get_stream(vlb_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+
+int vlb_ctx_set_precision(vlb_ctx* ctx, int p)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  if (p < VLB_PRECISION_3XTF32 || p > VLB_PRECISION_FP32) return vlb::set_error(ctx, VLB_IllegalArgument, "precision");
+  ctx->precision = p;
+  return VLB_Success;
+}
+int vlb_ctx_get_precision(vlb_ctx* ctx) { return ctx ? ctx->precision : -1; }
+
+char const* vlb_ctx_last_error(vlb_ctx* ctx) { return ctx ? ctx->lastErrorMessage.c_str() : "null context"; }
+void vlb_ctx_reset_error(vlb_ctx* ctx) { if (ctx) { ctx->lastError = VLB_Success; ctx->lastErrorMessage.clear(); } }
+
+int vlb_ctx_reserve_workspace(vlb_ctx* ctx, size_t bytes)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  return vlb::workspace(ctx, bytes) ? VLB_Success : ctx->lastError;
+}
+size_t vlb_ctx_workspace_bytes(vlb_ctx* ctx) { return ctx ? ctx->workspaceBytes : 0; }
+int vlb_ctx_clear_workspace(vlb_ctx* ctx)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  if (ctx->workspace) { cudaStreamSynchronize(ctx->stream); cudaFree(ctx->workspace); }
+  ctx->workspace = nullptr; ctx->workspaceBytes = 0;
+  return VLB_Success;
+}
+long long vlb_ctx_launch_count(vlb_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+}  // extern "C"

@@ -1,0 +1,310 @@
+// Element-wise and small reduction kernels: ReLU, Sum, scale, Bias, softmax-loss.
+// All are HBM-bound: 128-bit accesses where alignment allows, grid-stride loops
+// sized from the SM count.
+#include "common.cuh"
+#include <math.h>
+
+namespace {
+
+constexpr int kThreads = 256;
+
+inline bool aligned16(void const* p) { return (((uintptr_t)p) & 15) == 0; }
+
+// ---------------------------------------------------------------- ReLU / sum / scale
+// y = max(x, 0) (reference matlab/vl_nnrelu.m:45)
+__global__ void relu_fwd_kernel(float* __restrict__ y, float const* __restrict__ x, size_t n, bool vec)
+{
+  size_t stride = (size_t)gridDim.x * blockDim.x, i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (vec) {
+    size_t n4 = n >> 2;
+    for (size_t i = i0; i < n4; i += stride) {
+      float4 v = reinterpret_cast<float4 const*>(x)[i];
+      v.x = v.x > 0.f ? v.x : 0.f; v.y = v.y > 0.f ? v.y : 0.f;
+      v.z = v.z > 0.f ? v.z : 0.f; v.w = v.w > 0.f ? v.w : 0.f;
+      reinterpret_cast<float4*>(y)[i] = v;
+    }
+    for (size_t i = (n4 << 2) + i0; i < n; i += stride) y[i] = x[i] > 0.f ? x[i] : 0.f;
+  } else {
+    for (size_t i = i0; i < n; i += stride) y[i] = x[i] > 0.f ? x[i] : 0.f;
+  }
+}
+
+// dx = dy .* (x > 0) (reference matlab/vl_nnrelu.m:47)
+__global__ void relu_bwd_kernel(float* __restrict__ dx, float const* __restrict__ x,
+                                float const* __restrict__ dy, size_t n, bool vec)
+{
+  size_t stride = (size_t)gridDim.x * blockDim.x, i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (vec) {
+    size_t n4 = n >> 2;
+    for (size_t i = i0; i < n4; i += stride) {
+      float4 v = reinterpret_cast<float4 const*>(x)[i];
+      float4 d = reinterpret_cast<float4 const*>(dy)[i];
+      d.x = v.x > 0.f ? d.x : 0.f; d.y = v.y > 0.f ? d.y : 0.f;
+      d.z = v.z > 0.f ? d.z : 0.f; d.w = v.w > 0.f ? d.w : 0.f;
+      reinterpret_cast<float4*>(dx)[i] = d;
+    }
+    for (size_t i = (n4 << 2) + i0; i < n; i += stride) dx[i] = x[i] > 0.f ? dy[i] : 0.f;
+  } else {
+    for (size_t i = i0; i < n; i += stride) dx[i] = x[i] > 0.f ? dy[i] : 0.f;
+  }
+}
+
+__global__ void sum_kernel(float* y, float const* a, float const* b, size_t n, bool vec)
+{
+  size_t stride = (size_t)gridDim.x * blockDim.x, i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (vec) {
+    size_t n4 = n >> 2;
+    for (size_t i = i0; i < n4; i += stride) {
+      float4 u = reinterpret_cast<float4 const*>(a)[i], v = reinterpret_cast<float4 const*>(b)[i];
+      u.x += v.x; u.y += v.y; u.z += v.z; u.w += v.w;
+      reinterpret_cast<float4*>(y)[i] = u;
+    }
+    for (size_t i = (n4 << 2) + i0; i < n; i += stride) y[i] = a[i] + b[i];
+  } else {
+    for (size_t i = i0; i < n; i += stride) y[i] = a[i] + b[i];
+  }
+}
+
+__global__ void scale_kernel(float* x, float alpha, size_t n, bool vec)
+{
+  size_t stride = (size_t)gridDim.x * blockDim.x, i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (vec) {
+    size_t n4 = n >> 2;
+    for (size_t i = i0; i < n4; i += stride) {
+      float4 u = reinterpret_cast<float4*>(x)[i];
+      u.x *= alpha; u.y *= alpha; u.z *= alpha; u.w *= alpha;
+      reinterpret_cast<float4*>(x)[i] = u;
+    }
+    for (size_t i = (n4 << 2) + i0; i < n; i += stride) x[i] *= alpha;
+  } else {
+    for (size_t i = i0; i < n; i += stride) x[i] *= alpha;
+  }
+}
+
+// ---------------------------------------------------------------- Bias
+// One block row per (k, n) plane of P = H*W elements.
+// mode 0: y = bv (+ xm*x); mode 1: y = bv + ym*y (+ xm*x); mode 2: y = 0 (+ xm*x)
+__global__ void bias_fwd_kernel(float* __restrict__ y, float ym, float const* __restrict__ x, float xm,
+                                float const* __restrict__ b, float bm, int P, int K, size_t planes, int mode)
+{
+  for (size_t plane = blockIdx.y; plane < planes; plane += gridDim.y) {
+    int k = (int)(plane % K);
+    float bv = (mode == 2) ? 0.f : __fmul_rn(bm, b[k]);
+    float* yp = y + plane * (size_t)P;
+    float const* xp = x ? x + plane * (size_t)P : nullptr;
+    for (int p = blockIdx.x * blockDim.x + threadIdx.x; p < P; p += gridDim.x * blockDim.x) {
+      float v = bv;
+      if (mode == 1) v = __fadd_rn(bv, __fmul_rn(ym, yp[p]));
+      if (xp) v = __fadd_rn(v, __fmul_rn(xm, xp[p]));
+      yp[p] = v;
+    }
+  }
+}
+
+// db[k] = beta*db[k] + bm * sum over (p, n) of dy; one block per k, fixed-order tree.
+__global__ void bias_bwd_db_kernel(float* __restrict__ db, float beta, float bm, float const* __restrict__ dy,
+                                   int P, int K, int N)
+{
+  __shared__ float red[32];
+  int k = blockIdx.x;
+  float s = 0.f;
+  size_t total = (size_t)P * N;
+  for (size_t i = threadIdx.x; i < total; i += blockDim.x) {
+    size_t n = i / P, p = i - n * P;
+    s += dy[p + (size_t)P * (k + (size_t)K * n)];
+  }
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    s = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (threadIdx.x == 0) db[k] = (beta == 0.f) ? bm * s : bm * s + beta * db[k];
+  }
+}
+
+// dx = dxm*dx + xm*dy ; dxm == 0 means overwrite
+__global__ void axpby_kernel(float* dx, float dxm, float xm, float const* dy, size_t n)
+{
+  size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    float v = __fmul_rn(xm, dy[i]);
+    if (dxm != 0.f) v = __fadd_rn(__fmul_rn(dxm, dx[i]), v);
+    dx[i] = v;
+  }
+}
+
+// ---------------------------------------------------------------- softmax loss
+// One block per (pixel, image): max-shifted log-sum-exp over C channels
+// (reference matlab/vl_nnsoftmaxloss.m:72-84).  `terms` gets one loss term per block
+// (forward) or dx gets (softmax - onehot) * scale (backward).
+__device__ float block_reduce(float v, bool isMax, float* red)
+{
+  for (int o = 16; o > 0; o >>= 1) {
+    float u = __shfl_xor_sync(0xffffffffu, v, o);
+    v = isMax ? fmaxf(v, u) : v + u;
+  }
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  int nw = blockDim.x >> 5;
+  v = (int)threadIdx.x < nw ? red[threadIdx.x] : (isMax ? -INFINITY : 0.f);
+  if (threadIdx.x < 32) {
+    for (int o = 16; o > 0; o >>= 1) {
+      float u = __shfl_xor_sync(0xffffffffu, v, o);
+      v = isMax ? fmaxf(v, u) : v + u;
+    }
+    if (threadIdx.x == 0) red[0] = v;
+  }
+  __syncthreads();
+  v = red[0];
+  __syncthreads();
+  return v;
+}
+
+__global__ void softmaxloss_kernel(float* __restrict__ terms, float* __restrict__ dx, float const* __restrict__ x,
+                                   float const* __restrict__ labels, float scale, int P, int C)
+{
+  __shared__ float red[32];
+  int p = blockIdx.x, n = blockIdx.y;
+  float const* xp = x + p + (size_t)P * C * n;
+  float m = -INFINITY;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) m = fmaxf(m, xp[(size_t)P * c]);
+  m = block_reduce(m, true, red);
+  float s = 0.f;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) s += expf(xp[(size_t)P * c] - m);
+  s = block_reduce(s, false, red);
+  int lab = (int)labels[n] - 1;
+  if (dx) {
+    float* dp = dx + p + (size_t)P * C * n;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+      float v = expf(xp[(size_t)P * c] - m) / s;
+      if (c == lab) v -= 1.f;
+      dp[(size_t)P * c] = v * scale;
+    }
+  } else if (threadIdx.x == 0) {
+    terms[p + (size_t)P * n] = m + logf(s) - xp[(size_t)P * lab];
+  }
+}
+
+// loss = (sum of terms) / N, one block, fixed order.
+__global__ void loss_finish_kernel(float* loss, float const* terms, int count, float invN)
+{
+  __shared__ float red[32];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < count; i += blockDim.x) s += terms[i];
+  s = block_reduce(s, false, red);
+  if (threadIdx.x == 0) *loss = s * invN;
+}
+
+}  // namespace
+
+extern "C" {
+
+int vlb_relu_forward(vlb_ctx* ctx, float* Y, float const* X, size_t n)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  VLB_REQUIRE(ctx, Y && X, "relu_forward: null tensor");
+  if (n == 0) return VLB_Success;
+  bool vec = aligned16(Y) && aligned16(X);
+  relu_fwd_kernel<<<vlb::grid_for(vec ? n / 4 + 1 : n, kThreads, ctx->smCount * 8), kThreads, 0, ctx->stream>>>(Y, X, n, vec);
+  VLB_LAUNCHED(ctx, 1);
+  return vlb::check_launch(ctx, "vlb_relu_forward");
+}
+
+int vlb_relu_backward(vlb_ctx* ctx, float* dX, float const* X, float const* dY, size_t n)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  VLB_REQUIRE(ctx, dX && X && dY, "relu_backward: null tensor");
+  if (n == 0) return VLB_Success;
+  bool vec = aligned16(dX) && aligned16(X) && aligned16(dY);
+  relu_bwd_kernel<<<vlb::grid_for(vec ? n / 4 + 1 : n, kThreads, ctx->smCount * 8), kThreads, 0, ctx->stream>>>(dX, X, dY, n, vec);
+  VLB_LAUNCHED(ctx, 1);
+  return vlb::check_launch(ctx, "vlb_relu_backward");
+}
+
+int vlb_sum(vlb_ctx* ctx, float* Y, float const* A, float const* B, size_t n)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  VLB_REQUIRE(ctx, Y && A && B, "sum: null tensor");
+  if (n == 0) return VLB_Success;
+  bool vec = aligned16(Y) && aligned16(A) && aligned16(B);
+  sum_kernel<<<vlb::grid_for(vec ? n / 4 + 1 : n, kThreads, ctx->smCount * 8), kThreads, 0, ctx->stream>>>(Y, A, B, n, vec);
+  VLB_LAUNCHED(ctx, 1);
+  return vlb::check_launch(ctx, "vlb_sum");
+}
+
+int vlb_scale(vlb_ctx* ctx, float* x, double alpha, size_t n)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  VLB_REQUIRE(ctx, x, "scale: null tensor");
+  if (n == 0) return VLB_Success;
+  bool vec = aligned16(x);
+  scale_kernel<<<vlb::grid_for(vec ? n / 4 + 1 : n, kThreads, ctx->smCount * 8), kThreads, 0, ctx->stream>>>(x, (float)alpha, n, vec);
+  VLB_LAUNCHED(ctx, 1);
+  return vlb::check_launch(ctx, "vlb_scale");
+}
+
+int vlb_bias_forward(vlb_ctx* ctx, float* Y, double yMult, float const* X, double xMult, float const* b,
+                     double bMult, int H, int W, int K, int N)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  VLB_REQUIRE(ctx, Y, "bias_forward: null output");
+  VLB_REQUIRE(ctx, H > 0 && W > 0 && K > 0 && N > 0, "bias_forward: empty tensor");
+  int P = H * W;
+  int mode = (b && bMult != 0) ? ((float)yMult == 0.f ? 0 : 1) : 2;
+  float const* xin = (X && xMult != 0) ? X : nullptr;
+  size_t planes = (size_t)K * N;
+  dim3 grid(vlb::ceil_div(P, kThreads) > 64 ? 64 : vlb::ceil_div(P, kThreads), (unsigned)(planes > 32768 ? 32768 : planes));
+  bias_fwd_kernel<<<grid, kThreads, 0, ctx->stream>>>(Y, (float)yMult, xin, (float)xMult, b, (float)bMult, P, K, planes, mode);
+  VLB_LAUNCHED(ctx, 1);
+  return vlb::check_launch(ctx, "vlb_bias_forward");
+}
+
+int vlb_bias_backward(vlb_ctx* ctx, float* dX, double dXMult, float* db, double dbMult, double xMult,
+                      double bMult, float const* dY, int H, int W, int K, int N)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  VLB_REQUIRE(ctx, dY, "bias_backward: null derOutput");
+  VLB_REQUIRE(ctx, H > 0 && W > 0 && K > 0 && N > 0, "bias_backward: empty tensor");
+  int P = H * W;
+  if (db) {
+    bias_bwd_db_kernel<<<K, 256, 0, ctx->stream>>>(db, (float)dbMult, (float)bMult, dY, P, K, N);
+    VLB_LAUNCHED(ctx, 1);
+  }
+  if (dX) {
+    size_t n = (size_t)P * K * N;
+    axpby_kernel<<<vlb::grid_for(n, kThreads, ctx->smCount * 8), kThreads, 0, ctx->stream>>>(dX, (float)dXMult, (float)xMult, dY, n);
+    VLB_LAUNCHED(ctx, 1);
+  }
+  return vlb::check_launch(ctx, "vlb_bias_backward");
+}
+
+int vlb_softmaxloss_forward(vlb_ctx* ctx, float* loss, float const* X, float const* labels, int H, int W, int C, int N)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  VLB_REQUIRE(ctx, loss && X && labels, "softmaxloss_forward: null tensor");
+  VLB_REQUIRE(ctx, H > 0 && W > 0 && C > 0 && N > 0 && N <= 65535, "softmaxloss_forward: bad shape");
+  int P = H * W;
+  float* terms = (float*)vlb::workspace(ctx, sizeof(float) * (size_t)P * N);
+  if (!terms) return vlb::pass_error(ctx, ctx->lastError, "vlb_softmaxloss_forward");
+  int threads = C >= 256 ? 256 : (C >= 64 ? 64 : 32);
+  softmaxloss_kernel<<<dim3(P, N), threads, 0, ctx->stream>>>(terms, nullptr, X, labels, 0.f, P, C);
+  loss_finish_kernel<<<1, 256, 0, ctx->stream>>>(loss, terms, P * N, 1.f / (float)N);
+  VLB_LAUNCHED(ctx, 2);
+  return vlb::check_launch(ctx, "vlb_softmaxloss_forward");
+}
+
+int vlb_softmaxloss_backward(vlb_ctx* ctx, float* dX, float const* X, float const* labels, double dzdy,
+                             int H, int W, int C, int N)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  VLB_REQUIRE(ctx, dX && X && labels, "softmaxloss_backward: null tensor");
+  VLB_REQUIRE(ctx, H > 0 && W > 0 && C > 0 && N > 0 && N <= 65535, "softmaxloss_backward: bad shape");
+  int P = H * W;
+  int threads = C >= 256 ? 256 : (C >= 64 ? 64 : 32);
+  softmaxloss_kernel<<<dim3(P, N), threads, 0, ctx->stream>>>(nullptr, dX, X, labels, (float)dzdy / (float)N, P, C);
+  VLB_LAUNCHED(ctx, 1);
+  return vlb::check_launch(ctx, "vlb_softmaxloss_backward");
+}
+
+}  // extern "C"

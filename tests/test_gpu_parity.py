@@ -1,0 +1,255 @@
+"""CUDA kernels, called through the C ABI, against the CPU checker on the same seeded inputs
+and against the golden vectors of the reference's compiled CPU backend.
+
+Bars: bit-exact for max-pool routing, pooling values, ROI bin geometry and (with
+integer-valued gradients, whose sums are exact in any order) ROI / sampler scatter;
+relative L2 <= 1e-5 for convolution, fully-connected and batch-norm results in the default
+(3xTF32) arithmetic and for the CUDA-core fp32 path; <= 2e-3 for the plain-TF32 fast path.
+"""
+import numpy as np
+import pytest
+
+from conftest import bit_equal, cases_of, load_golden, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+TOL_FAITHFUL = 1e-5     # 3xTF32 and fp32 paths
+TOL_TF32 = 2e-3         # single-pass TF32 path
+
+
+def _up(mat, *arrays):
+    return [None if a is None else mat.from_numpy(a) for a in arrays]
+
+
+# ------------------------------------------------------------------ pooling
+def test_pool_golden(gpu):
+    nn, mat, _ = gpu
+    g = load_golden("pool")
+    for c in cases_of(g):
+        if c == "ties":
+            continue
+        prm = g[c + ".prm"]
+        kw = dict(stride=tuple(prm[2:4]), pad=tuple(prm[4:8]))
+        (x,) = _up(mat, g[c + ".x"])
+        for m in ("max", "avg"):
+            y = nn.vl_nnpool(x, tuple(prm[0:2]), method=m, **kw)
+            assert bit_equal(mat.to_numpy(y), g["%s.%s.y" % (c, m)]), (c, m, "y")
+            (dy,) = _up(mat, g["%s.%s.dy" % (c, m)])
+            dx = nn.vl_nnpool(x, tuple(prm[0:2]), dy, method=m, **kw)
+            assert bit_equal(mat.to_numpy(dx), g["%s.%s.dx" % (c, m)]), (c, m, "dx")
+    x, dy = _up(mat, g["ties.x"], g["ties.dy"])
+    assert bit_equal(mat.to_numpy(nn.vl_nnpool(x, (2, 2), stride=2)), g["ties.max.y"])
+    assert bit_equal(mat.to_numpy(nn.vl_nnpool(x, (2, 2), dy, stride=2)), g["ties.max.dx"])
+
+
+@pytest.mark.parametrize("shape,pool,stride,pad", [
+    ((224, 224, 4, 2), (2, 2), (2, 2), (0, 0, 0, 0)),       # VGG pool1 geometry
+    ((14, 14, 64, 3), (2, 2), (2, 2), (0, 0, 0, 0)),        # VGG pool5 geometry (H % 4 != 0)
+    ((32, 32, 8, 5), (3, 3), (2, 2), (0, 1, 0, 1)),         # CIFAR overlapping, asymmetric pad
+    ((24, 24, 20, 10), (2, 2), (2, 2), (0, 0, 0, 0)),       # LeNet
+    ((13, 17, 3, 2), (4, 3), (3, 2), (1, 2, 2, 0)),
+    ((5, 5, 2, 2), (5, 5), (1, 1), (0, 0, 0, 0)),           # one window = whole map
+])
+@pytest.mark.parametrize("method", ["max", "avg"])
+def test_pool_vs_oracle(gpu, oracle, shape, pool, stride, pad, method):
+    nn, mat, _ = gpu
+    rng = np.random.default_rng(11)
+    x = np.asfortranarray(rng.standard_normal(shape).astype(np.float32))
+    y_ref = oracle.pool_forward(x, pool, stride, pad, method)
+    dy = np.asfortranarray(rng.standard_normal(y_ref.shape).astype(np.float32))
+    xd, dyd = _up(mat, x, dy)
+    assert bit_equal(mat.to_numpy(nn.vl_nnpool(xd, pool, stride=stride, pad=pad, method=method)), y_ref)
+    dx = nn.vl_nnpool(xd, pool, dyd, stride=stride, pad=pad, method=method)
+    assert bit_equal(mat.to_numpy(dx), oracle.pool_backward(x, dy, pool, stride, pad, method))
+
+
+def test_pool_rejects_bad_arguments(gpu):
+    nn, mat, _ = gpu
+    from matconvnet_b200.capi import VlbError
+    x = mat.zeros((8, 8, 1, 1))
+    with pytest.raises(VlbError):
+        nn.vl_nnpool(x, (2, 2), pad=2)            # padding >= window
+    with pytest.raises(VlbError):
+        nn.vl_nnpool(x, (9, 9))                   # window larger than input
+
+
+# ------------------------------------------------------------------ batch normalisation
+def test_bnorm_golden(gpu):
+    nn, mat, _ = gpu
+    g = load_golden("bnorm")
+    for c in cases_of(g):
+        x, gg, b, dy = _up(mat, g[c + ".x"], g[c + ".g"], g[c + ".b"], g[c + ".dy"])
+        eps = float(g[c + ".eps"])
+        y, mom = nn.vl_nnbnorm(x, gg, b, epsilon=eps)
+        assert rel_l2(mat.to_numpy(y), g[c + ".y64"]) < TOL_FAITHFUL, c
+        assert rel_l2(mat.to_numpy(mom), g[c + ".mom64"]) < TOL_FAITHFUL, c
+        assert rel_l2(mat.to_numpy(y), g[c + ".y"]) < TOL_FAITHFUL, c
+        dx, dg, db, mom2 = nn.vl_nnbnorm(x, gg, b, dy, epsilon=eps)
+        for got, name in ((dx, "dx"), (dg, "dg"), (db, "db")):
+            assert rel_l2(mat.to_numpy(got).ravel(), g[c + "." + name + "64"].ravel()) < TOL_FAITHFUL, (c, name)
+            assert rel_l2(mat.to_numpy(got).ravel(), g[c + "." + name].ravel()) < TOL_FAITHFUL, (c, name)
+        assert rel_l2(mat.to_numpy(mom2), g[c + ".mom64"]) < TOL_FAITHFUL, c
+        (momd,) = _up(mat, g[c + ".mom"])
+        dxm, dgm, dbm, _ = nn.vl_nnbnorm(x, gg, b, dy, epsilon=eps, moments=momd)
+        for got, name in ((dxm, "dxm"), (dgm, "dgm"), (dbm, "dbm")):
+            assert rel_l2(mat.to_numpy(got).ravel(), g[c + "." + name].ravel()) < TOL_FAITHFUL, (c, name)
+        ym, _ = nn.vl_nnbnorm(x, gg, b, epsilon=eps, moments=momd)
+        assert bit_equal(mat.to_numpy(ym), g[c + ".ym"]), c       # same arithmetic, element-wise
+
+
+@pytest.mark.parametrize("shape", [(28, 28, 128, 8), (28, 28, 512, 2), (7, 7, 33, 5), (1, 1, 10, 3), (64, 64, 32, 4)])
+def test_bnorm_vs_oracle(gpu, oracle, shape):
+    nn, mat, _ = gpu
+    rng = np.random.default_rng(12)
+    x = np.asfortranarray((rng.standard_normal(shape) * 1.5 + 0.3).astype(np.float32))
+    dy = np.asfortranarray(rng.standard_normal(shape).astype(np.float32))
+    g = (rng.standard_normal(shape[2]) + 1).astype(np.float32)
+    b = rng.standard_normal(shape[2]).astype(np.float32)
+    x64, dy64, g64, b64 = (a.astype(np.float64) for a in (x, dy, g, b))
+    ref = oracle.bnorm_backward(x64, g64, b64, dy64, 1e-5)          # double instantiation
+    xd, dyd, gd, bd = _up(mat, x, dy, g, b)
+    got = nn.vl_nnbnorm(xd, gd, bd, dyd, epsilon=1e-5)
+    for a, r, name in zip(got, ref, ("dx", "dg", "db", "moments")):
+        assert rel_l2(mat.to_numpy(a).ravel(), r.ravel()) < TOL_FAITHFUL, name
+    # given moments == computed moments (reference xtest/suite/nnbnorm.m:53-79)
+    got2 = nn.vl_nnbnorm(xd, gd, bd, dyd, epsilon=1e-5, moments=got[3])
+    for a, r in zip(got2[:3], got[:3]):
+        assert rel_l2(mat.to_numpy(a).ravel(), mat.to_numpy(r).ravel()) < 1e-6
+    # run-to-run determinism: no atomics anywhere in this block
+    again = nn.vl_nnbnorm(xd, gd, bd, dyd, epsilon=1e-5)
+    for a, r in zip(again, got):
+        assert bit_equal(mat.to_numpy(a), mat.to_numpy(r))
+    y, mom = nn.vl_nnbnorm(xd, gd, bd, epsilon=1e-5)
+    yr, momr = oracle.bnorm_forward(x64, g64, b64, 1e-5)
+    assert rel_l2(mat.to_numpy(y), yr) < TOL_FAITHFUL and rel_l2(mat.to_numpy(mom), momr) < TOL_FAITHFUL
+
+
+# ------------------------------------------------------------------ bias, relu, loss
+def test_bias_golden(gpu):
+    nn, mat, ctx = gpu
+    g = load_golden("bias")
+    H, W, K, N = g["y0"].shape
+    lib = ctx.lib
+    for i, (ym, hx, xm, hb, bm) in enumerate(g["fwd_args"]):
+        y, x, b = _up(mat, g["y0"], g["x"] if hx else None, g["b"] if hb else None)
+        ctx.check(lib.vlb_bias_forward(ctx.handle, mat.ptr(y), ym, mat.ptr(x), xm, mat.ptr(b), bm, H, W, K, N))
+        assert bit_equal(mat.to_numpy(y), g["fwd%d" % i]), i
+    for i, (dxm, dbm, xm, bm) in enumerate(g["bwd_args"]):
+        dx, db, dy = _up(mat, g["dx0"], g["db0"], g["dy"])
+        ctx.check(lib.vlb_bias_backward(ctx.handle, mat.ptr(dx), dxm, mat.ptr(db), dbm, xm, bm, mat.ptr(dy), H, W, K, N))
+        assert bit_equal(mat.to_numpy(dx), g["bwd%d.dx" % i]), i
+        assert rel_l2(mat.to_numpy(db), g["bwd%d.db" % i]) < 1e-6, i
+
+
+def test_relu_and_loss(gpu, oracle):
+    nn, mat, _ = gpu
+    rng = np.random.default_rng(13)
+    for shape in [(7, 5, 3, 2), (16, 16, 8, 4), (1, 1, 1000, 64)]:
+        x = np.asfortranarray(rng.standard_normal(shape).astype(np.float32))
+        x.reshape(-1, order="F")[::7] = 0.0
+        dy = np.asfortranarray(rng.standard_normal(shape).astype(np.float32))
+        xd, dyd = _up(mat, x, dy)
+        assert bit_equal(mat.to_numpy(nn.vl_nnrelu(xd)), oracle.relu_forward(x))
+        assert bit_equal(mat.to_numpy(nn.vl_nnrelu(xd, dyd)), oracle.relu_backward(x, dy))
+    for shape in [(1, 1, 1000, 64), (1, 1, 10, 100), (3, 2, 5, 4)]:
+        x = np.asfortranarray((rng.standard_normal(shape) * 3).astype(np.float32))
+        lab = rng.integers(1, shape[2] + 1, size=shape[3]).astype(np.float32)
+        xd, labd = _up(mat, x, lab)
+        loss = float(nn.vl_nnsoftmaxloss(xd, labd).cpu()[0])
+        ref = float(oracle.softmaxloss_forward(x.astype(np.float64), lab.astype(np.float64)))
+        assert abs(loss - ref) <= 1e-5 * abs(ref)
+        dx = nn.vl_nnsoftmaxloss(xd, labd, 1.0)
+        assert rel_l2(mat.to_numpy(dx), oracle.softmaxloss_backward(x.astype(np.float64), lab.astype(np.float64), 1.0)) < TOL_FAITHFUL
+
+
+# ------------------------------------------------------------------ ROI pooling
+def test_roipool_golden(gpu):
+    nn, mat, _ = gpu
+    g = load_golden("roipool")
+    (x,) = _up(mat, g["x"])
+    keys = sorted({k[:-2] for k in g if k.endswith(".y")})
+    for key in keys:
+        tname, sub, method = key.split(".")
+        sub = tuple(int(v) for v in sub.split("x"))
+        (rois,) = _up(mat, g["rois." + tname])
+        tf = g["tf." + tname]
+        y = nn.vl_nnroipool(x, rois, subdivisions=sub, transform=tf, method=method)
+        assert bit_equal(mat.to_numpy(y), g[key + ".y"]), key
+        (dyi,) = _up(mat, g[key + ".dyi"])
+        dxi = nn.vl_nnroipool(x, rois, dyi, subdivisions=sub, transform=tf, method=method)
+        if method == "max":
+            # integer gradients: sums are exact whatever the order of the atomics => routing is bit-exact
+            assert bit_equal(mat.to_numpy(dxi), g[key + ".dxi"]), key
+        else:
+            assert rel_l2(mat.to_numpy(dxi), g[key + ".dxi"]) < 1e-6, key
+        (dy,) = _up(mat, g[key + ".dy"])
+        dx = nn.vl_nnroipool(x, rois, dy, subdivisions=sub, transform=tf, method=method)
+        assert rel_l2(mat.to_numpy(dx), g[key + ".dx"]) < 1e-6, key
+
+
+def test_roipool_bins_bit_exact(gpu, oracle):
+    """Every (roi, ph, pw) bin of the Fast R-CNN head geometry, feature-map and image coordinates."""
+    nn, mat, _ = gpu
+    rng = np.random.default_rng(14)
+    H, W, N, K = 38, 50, 2, 256
+    for transform, scale in ((1.0, 1.0), (1.0 / 16, 16.0), ([0.97, 0.02, -0.03, 1.04, 0.4, -0.6], 1.0)):
+        u1 = rng.uniform(1, W - 2, K); v1 = rng.uniform(1, H - 2, K)
+        u2 = u1 + rng.uniform(2, W, K); v2 = v1 + rng.uniform(2, H, K)
+        rois = np.stack([rng.integers(1, N + 1, K), u1 * scale, v1 * scale, np.minimum(u2, W) * scale,
+                         np.minimum(v2, H) * scale]).astype(np.float32)
+        rois = np.asfortranarray(rois)
+        for sub in [(7, 7), (6, 6), (1, 1), (16, 16)]:
+            bref, iref = oracle.roipool_bounds(rois, (H, W, 512, N), sub, transform)
+            (rd,) = _up(mat, rois)
+            b, im = nn.roipool_bounds(rd, (H, W, 512, N), sub, transform)
+            assert np.array_equal(mat.to_numpy(b), bref), (transform, sub)
+            assert np.array_equal(im.cpu().numpy(), iref)
+
+
+def test_roipool_identity(gpu):
+    nn, mat, _ = gpu
+    x = np.asfortranarray((np.arange(2, 11)[:, None] * np.arange(1, 11)[None, :]).astype(np.float32)).reshape(9, 10, 1, 1, order="F")
+    rois = np.array([[1, 1, 1, 9, 10]], np.float32).T
+    xd, rd = _up(mat, x, rois)
+    for m in ("max", "avg"):
+        y = nn.vl_nnroipool(xd, rd, subdivisions=(9, 10), transform=np.array([[0, 1, 0], [1, 0, 0]], float), method=m)
+        assert np.array_equal(mat.to_numpy(y), x)
+
+
+# ------------------------------------------------------------------ bilinear sampler
+def test_sampler_golden(gpu):
+    nn, mat, _ = gpu
+    g = load_golden("sampler")
+    for c in cases_of(g):
+        x, grid, dy = _up(mat, g[c + ".x"], g[c + ".grid"], g[c + ".dy"])
+        assert bit_equal(mat.to_numpy(nn.vl_nnbilinearsampler(x, grid)), g[c + ".y"]), c
+        dx, dgrid = nn.vl_nnbilinearsampler(x, grid, dy)
+        assert bit_equal(mat.to_numpy(dgrid), g[c + ".dgrid"]), c
+        assert rel_l2(mat.to_numpy(dx), g[c + ".dx"]) < 1e-6, c
+
+
+def test_sampler_affine_vs_oracle(gpu, oracle):
+    """Small rotations and scales through the affine-grid formula of the reference
+    (matlab/+dagnn/AffineGridGenerator.m:36-57,106-118), two grids per image."""
+    nn, mat, _ = gpu
+    rng = np.random.default_rng(15)
+    H = W = 16; C = 5; N = 3; Ng = 6
+    xi = np.linspace(-1, 1, H); yi = np.linspace(-1, 1, W)
+    yy, xx = np.meshgrid(xi, yi)
+    base = np.stack([yy.ravel(), xx.ravel()], 1)                    # (Wo*Ho) x 2
+    grid = np.zeros((2, H, W, Ng), np.float32, order="F")
+    for n in range(Ng):
+        th, s = rng.uniform(-0.2, 0.2), rng.uniform(0.8, 1.2)
+        A = s * np.array([[np.cos(th), -np.sin(th)], [np.sin(th), np.cos(th)]])
+        t = rng.uniform(-0.1, 0.1, 2)
+        gpts = base @ A + t
+        grid[:, :, :, n] = gpts.reshape(W, H, 2).transpose(2, 1, 0)
+    x = np.asfortranarray(rng.standard_normal((H, W, C, N)).astype(np.float32))
+    y_ref = oracle.sampler_forward(x, grid)
+    dy = np.asfortranarray(rng.integers(-4, 5, y_ref.shape).astype(np.float32))
+    xd, gd, dyd = _up(mat, x, grid, dy)
+    assert bit_equal(mat.to_numpy(nn.vl_nnbilinearsampler(xd, gd)), y_ref)
+    dx, dgrid = nn.vl_nnbilinearsampler(xd, gd, dyd)
+    dxr, dgr = oracle.sampler_backward(x, grid, dy)
+    assert bit_equal(mat.to_numpy(dgrid), dgr)
+    assert rel_l2(mat.to_numpy(dx), dxr) < 1e-6
