@@ -56,6 +56,10 @@ int vlb_ctx_reserve_workspace(vlb_ctx* ctx, size_t bytes); /* grow-only scratch,
 size_t vlb_ctx_workspace_bytes(vlb_ctx* ctx);
 int vlb_ctx_clear_workspace(vlb_ctx* ctx);       /* Context::clearWorkspace, bits/data.cu:406-410 */
 long long vlb_ctx_launch_count(vlb_ctx* ctx);    /* kernels enqueued through this context so far */
+/* Synchronises the stream and reads the status word that the tensor-core kernels set when one of
+ * their bounded pipeline waits expires (0 = none did).  Returns VLE_Timeout, as the reference's own
+ * waits do (matlab/src/vl_tmove.cu:1344-1359), when the word is non-zero, and clears it. */
+int vlb_ctx_device_status(vlb_ctx* ctx, int* status);
 char const* vlb_error_message(int code);         /* vl::getErrorMessage, bits/data.cu:83-100 (all 13 codes named) */
 int vlb_version(void);
 

@@ -53,6 +53,7 @@ SIGNATURES = {
     "vlb_ctx_workspace_bytes": (_Z, [_P]),
     "vlb_ctx_clear_workspace": (_I, [_P]),
     "vlb_ctx_launch_count": (C.c_longlong, [_P]),
+    "vlb_ctx_device_status": (_I, [_P, C.POINTER(_I)]),
     "vlb_conv_output_shape": (_I, [C.POINTER(ConvDesc), C.POINTER(_I), C.POINTER(_I)]),
     "vlb_conv_forward": (_I, [_P, _P, _D, _P, _D, _P, _P, C.POINTER(ConvDesc)]),
     "vlb_conv_backward": (_I, [_P, _P, _P, _P, _P, _P, _P, C.POINTER(ConvDesc)]),
@@ -146,6 +147,12 @@ class Context:
 
     def reserve_workspace(self, nbytes):
         self.check(self.lib.vlb_ctx_reserve_workspace(self.handle, int(nbytes)))
+
+    def device_status(self):
+        """Synchronises and raises VlbError(VLE_Timeout) if a tensor-core kernel gave up a wait."""
+        st = C.c_int(0)
+        self.check(self.lib.vlb_ctx_device_status(self.handle, C.byref(st)))
+        return st.value
 
     def last_error(self):
         return self.lib.vlb_ctx_last_error(self.handle).decode()

@@ -19,6 +19,7 @@ struct vlb_ctx {
   std::string lastErrorMessage;
   long long launches = 0;
   int smCount = 148;
+  int* deviceStatus = nullptr;   // one word the tensor-core kernels set when a bounded wait expires
 };
 
 namespace vlb {

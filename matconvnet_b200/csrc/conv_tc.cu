@@ -1,11 +1,712 @@
-// tcgen05 implicit-GEMM convolution (placeholder until the tensor-core kernels land).
+// Tensor-core contractions for vl::nn::Convolution and vl::nn::FullyConnected
+// (reference bits/nnconv.cu:71-317, bits/nnfullyconnected.cu:30-185) on tcgen05 / TMEM.
+//
+// Every contraction on the path is D[m][n] = sum_r A(m,r) * B(n,r) with fp32 accumulation
+// in tensor memory.  One kernel template, 128 x BN output tile per CTA, reduction in blocks
+// of 32, warp-specialised:
+//   warps 0-3   epilogue: tcgen05.ld the accumulator (one TMEM lane = one output row per
+//               thread) and store to global memory, coalesced along m;
+//   warp  4     allocates TMEM and issues tcgen05.mma (kind::tf32, cta_group::1) from one
+//               lane; tcgen05.commit releases a stage / publishes the accumulator;
+//   warps 5-12  producers: gather the operand tiles from the MATLAB-order tensors
+//               (no patch matrix: the reference writes one per image, bits/nnconv.cu:109-117),
+//               split every value into a TF32 "hi" part and an exactly representable
+//               remainder "lo", and write both as 128-byte-swizzled UMMA tiles.
+// The split is what makes the result fp32-faithful: x*y ~ hi*hi + hi*lo + lo*hi, three
+// MMAs per product ("3xTF32"); the dropped lo*lo term is below 2^-22 relative.  The
+// single-pass TF32 mode issues only hi*hi.
+// Stages are handed over with mbarriers; every wait is bounded (about a second) and on
+// expiry records a status word and unwinds, releasing TMEM, instead of spinning forever.
+//
+// Operand layouts in shared memory (canonical UMMA layouts, 128-byte swizzle):
+//   K-major  tile[rows][32]: row r at r*128 bytes, 16-byte chunk c stored at chunk c ^ (r & 7);
+//            descriptor SBO = 1024 (8 rows), advance 32 bytes per MMA (K = 8).
+//   MN-major tile[32][cols]: 32-bit operands that are contiguous along the row index must use the
+//            "128-byte swizzle with 32-byte base" layout (type 1): atoms of 4 k x 32 cols (512 bytes),
+//            row k & 3 at 128 bytes, 32-byte chunk q of a row stored at chunk q ^ (k & 3); atom
+//            (ci, kq) at (kq * cols/32 + ci) * 512; LBO = 512 between column atoms, SBO =
+//            cols/32 * 512 between k quads, advance 2 * SBO per MMA.
 #include "conv_internal.cuh"
+#include <cuda.h>
+#include <stdlib.h>
+
+namespace {
+
+using vlb::ConvGeom;
+
+constexpr int BM = 128;          // output rows per CTA (TMEM lanes)
+constexpr int BK = 32;           // reduction elements per stage (one 128-byte swizzle row)
+constexpr int kEpilogueWarps = 4;
+constexpr int kProducerWarps = 8;
+constexpr int kProducerThreads = kProducerWarps * 32;
+constexpr int kThreads = (kEpilogueWarps + 1 + kProducerWarps) * 32;   // 416
+constexpr int kMaxStages = 8;
+constexpr long long kWaitCycles = 2000000000LL;   // bound on any single barrier wait
+
+enum OperandMode {
+  OP_DENSE_K = 0,    // addr(i, r) = (r / P) * bs + i * ld + (r % P)      (reduction contiguous)
+  OP_DENSE_MN = 1,   // addr(i, r) = r * ld + i                           (row index contiguous)
+  OP_IM2COL = 2,     // i = output pixel (ho,wo,n), r = (fh,fw,c): shifted input, MN-major
+  OP_WGATHER = 3     // i = (fh,fw,c), r = output pixel (ho,wo,n): shifted input, K-major
+};
+
+enum EpilogueMode {
+  EPI_PLAIN = 0,     // out[m + n*ldd] (+ bias[m]); with splits: out + split*splitStride
+  EPI_CONV = 1       // m = (pixel, image): out[(image*Ktot + n)*P + pixel] = inMult*acc + bias[n] + outMult*old
+};
+
+struct Operand {
+  float const* ptr;
+  long long ld, bs;
+  int P;               // run length of contiguous reduction indices (DENSE_K, batched); 0 = unbatched
+  int rows;            // valid extent of the row (M or N) index
+  int vec;             // 1 when 16-byte loads are legal for this operand
+  // convolution geometry (IM2COL, WGATHER)
+  int H, W, C, FH, FW, Ho, Wo, sy, sx, pt, pl, dy, dx;
+  long long imgStride;   // H*W*Ctotal
+};
+
+struct Epilogue {
+  float* out;
+  float const* bias;
+  long long ldd;
+  long long splitStride;
+  float inMult, outMult;
+  int P, Ktot;
+};
+
+struct Params {
+  Operand a, b;
+  Epilogue e;
+  int M, N, R;
+  int BN;                 // tile columns: 16, 32, 64 or 128
+  int numKb, kbPerSplit;
+  int stages;
+  int* status;
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(void const* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{ asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory"); }
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{ asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.shared::cta.b64 st, [%0];\n}" ::"r"(bar) : "memory"); }
+
+// Bounded wait: false when the phase did not complete within kWaitCycles.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+{
+  long long t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
+    if ((it & 255u) == 255u) {
+      long long now = clock64();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitCycles) return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dstSmem, uint32_t cols)
+{
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dstSmem), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols)
+{ asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory"); }
+
+__device__ __forceinline__ void umma_tf32(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc, uint32_t iDesc, uint32_t accumulate)
+{
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
+               ::"r"(dTmem), "l"(aDesc), "l"(bDesc), "r"(iDesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar)
+{ asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory"); }
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16])
+{
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor (sm_100 format): start address, LBO, SBO in 16-byte
+// units, version 1 at bit 46, layout type at bits 61-63: 2 = 128-byte swizzle (K-major tiles),
+// 1 = 128-byte swizzle with 32-byte base (MN-major tiles of 32-bit elements).
+__device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lboBytes, uint32_t sboBytes, uint32_t layoutType = 2)
+{
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lboBytes >> 4) << 16) | ((uint64_t)(sboBytes >> 4) << 32) |
+         (1ull << 46) | ((uint64_t)layoutType << 61);
+}
+
+// kind::tf32 instruction descriptor: D = F32 (bits 4-5 = 1), A and B = TF32 (bits 7-9, 10-12 = 2),
+// major-ness bits 15 / 16 (1 = MN-major), N >> 3 at bits 17-22, M >> 4 at bits 24-28.
+__device__ __forceinline__ uint32_t make_idesc(bool aMN, bool bMN, int n)
+{
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((aMN ? 1u : 0u) << 15) | ((bMN ? 1u : 0u) << 16) |
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+// ------------------------------------------------------------------ hi / lo split and tile stores
+__device__ __forceinline__ float tf32_hi(float x)
+{
+  uint32_t u;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+  return __uint_as_float(u);
+}
+
+template <bool kSplit>
+__device__ __forceinline__ void store_chunk(uint8_t* hiTile, uint8_t* loTile, uint32_t off, float const (&v)[4])
+{
+  if (kSplit) {
+    float4 h, l;
+    h.x = tf32_hi(v[0]); h.y = tf32_hi(v[1]); h.z = tf32_hi(v[2]); h.w = tf32_hi(v[3]);
+    l.x = v[0] - h.x; l.y = v[1] - h.y; l.z = v[2] - h.z; l.w = v[3] - h.w;
+    *reinterpret_cast<float4*>(hiTile + off) = h;
+    *reinterpret_cast<float4*>(loTile + off) = l;
+  } else {
+    *reinterpret_cast<float4*>(hiTile + off) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+}
+
+__device__ __forceinline__ uint32_t kmajor_off(int row, int kc) { return (uint32_t)row * 128u + (uint32_t)((kc ^ (row & 7)) << 4); }
+__device__ __forceinline__ uint32_t mnmajor_off(int chunk, int k, int atomsPerRow)
+{
+  // chunk = 16-byte chunk along the row index (4 values); 32-byte chunk index (chunk & 7) >> 1 is swizzled with k & 3
+  return (uint32_t)(((k >> 2) * atomsPerRow + (chunk >> 3)) * 512 + (k & 3) * 128 +
+                    (((((chunk & 7) >> 1) ^ (k & 3)) << 5) | ((chunk & 1) << 4)));
+}
+
+// ------------------------------------------------------------------ operand gathers
+// Each returns four values: for MN-major modes the row indices i..i+3 at reduction index r,
+// for K-major modes row i at reduction indices r..r+3.  Out-of-range positions read as zero.
+
+__device__ __forceinline__ void load_dense_k(Operand const& o, int i, int r, int R, float (&v)[4])
+{
+  v[0] = v[1] = v[2] = v[3] = 0.f;
+  if (i >= o.rows || r >= R) return;
+  if (o.vec && r + 3 < R) {
+    long long a = o.P ? (long long)(r / o.P) * o.bs + (long long)i * o.ld + (r % o.P) : (long long)i * o.ld + r;
+    float4 t = *reinterpret_cast<float4 const*>(o.ptr + a);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    return;
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    int rr = r + e;
+    if (rr < R) {
+      long long a = o.P ? (long long)(rr / o.P) * o.bs + (long long)i * o.ld + (rr % o.P) : (long long)i * o.ld + rr;
+      v[e] = o.ptr[a];
+    }
+  }
+}
+
+__device__ __forceinline__ void load_dense_mn(Operand const& o, int i, int r, int R, float (&v)[4])
+{
+  v[0] = v[1] = v[2] = v[3] = 0.f;
+  if (i >= o.rows || r >= R) return;
+  long long a = (long long)r * o.ld + i;
+  if (o.vec && i + 3 < o.rows) {
+    float4 t = *reinterpret_cast<float4 const*>(o.ptr + a);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    return;
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e)
+    if (i + e < o.rows) v[e] = o.ptr[a + e];
+}
+
+// Pixel context of one output position, fixed for a producer thread in IM2COL mode.
+struct PixCtx { int hs, ws; long long base; bool valid; };
+
+__device__ __forceinline__ PixCtx pix_ctx(Operand const& o, int m)
+{
+  PixCtx c;
+  c.valid = m < o.rows;
+  int ho = m % o.Ho, t = m / o.Ho, wo = t % o.Wo, n = t / o.Wo;
+  c.hs = ho * o.sy - o.pt; c.ws = wo * o.sx - o.pl;
+  c.base = (long long)n * o.imgStride;
+  return c;
+}
+
+__device__ __forceinline__ void load_im2col(Operand const& o, PixCtx const (&px)[4], int r, int R, float (&v)[4])
+{
+  v[0] = v[1] = v[2] = v[3] = 0.f;
+  if (r >= R) return;
+  int fh = r % o.FH, t = r / o.FH, fw = t % o.FW, c = t / o.FW;
+  int dh = fh * o.dy, dw = fw * o.dx;
+  long long coff = (long long)c * o.H * o.W;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    int h = px[e].hs + dh, w = px[e].ws + dw;
+    if (px[e].valid && h >= 0 && h < o.H && w >= 0 && w < o.W) v[e] = o.ptr[px[e].base + coff + (long long)w * o.H + h];
+  }
+}
+
+// Filter-tap context of one row (fh,fw,c), fixed for a producer thread in WGATHER mode.
+struct TapCtx { int dh, dw; long long coff; bool valid; };
+
+__device__ __forceinline__ TapCtx tap_ctx(Operand const& o, int i)
+{
+  TapCtx c;
+  c.valid = i < o.rows;
+  int fh = i % o.FH, t = i / o.FH, fw = t % o.FW, ch = t / o.FW;
+  c.dh = fh * o.dy - o.pt; c.dw = fw * o.dx - o.pl;
+  c.coff = (long long)ch * o.H * o.W;
+  return c;
+}
+
+__device__ __forceinline__ void load_wgather(Operand const& o, TapCtx const& tc, int r, int R, float (&v)[4])
+{
+  v[0] = v[1] = v[2] = v[3] = 0.f;
+  if (!tc.valid || r >= R) return;
+  int ho = r % o.Ho, t = r / o.Ho, wo = t % o.Wo, n = t / o.Wo;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    if (r + e < R) {
+      int h = ho * o.sy + tc.dh, w = wo * o.sx + tc.dw;
+      if (h >= 0 && h < o.H && w >= 0 && w < o.W) v[e] = o.ptr[(long long)n * o.imgStride + tc.coff + (long long)w * o.H + h];
+    }
+    if (++ho == o.Ho) { ho = 0; if (++wo == o.Wo) { wo = 0; ++n; } }
+  }
+}
+
+// ------------------------------------------------------------------ the kernel
+template <int kAMode, int kBMode, int kEpi, bool kSplit>
+__global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
+{
+  extern __shared__ uint8_t smemRaw[];
+  __shared__ __align__(8) uint64_t fullBar[kMaxStages];
+  __shared__ __align__(8) uint64_t emptyBar[kMaxStages];
+  __shared__ __align__(8) uint64_t accumBar;
+  __shared__ uint32_t tmemBase;
+
+  constexpr bool kAMN = (kAMode == OP_DENSE_MN || kAMode == OP_IM2COL);
+  constexpr bool kBMN = (kBMode == OP_DENSE_MN);
+
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smemRaw + 1023) & ~(uintptr_t)1023);   // swizzle atoms need 1024-byte alignment
+  int const BN = p.BN;
+  uint32_t const aTileBytes = BM * BK * 4;                  // 16 KB
+  uint32_t const bTileBytes = (uint32_t)BN * BK * 4;
+  uint32_t const stageBytes = (kSplit ? 2u : 1u) * (aTileBytes + bTileBytes);
+  // Accumulator sets.  The tensor core adds each MMA's result to the fp32 accumulator with
+  // truncation, so the error of a long accumulation chain grows linearly with its length.  In the
+  // split mode the products of the small terms (lo*hi, hi*lo) therefore go to their own accumulator
+  // ("small", about 2^-11 of the result, where truncation no longer matters), and the k-blocks are
+  // dealt round-robin to numSets independent (big, small) pairs, which the epilogue adds in fp32.
+  int const numSets = kSplit ? min(8, 512 / (2 * BN)) : 1;
+  uint32_t const tmemCols = kSplit ? (uint32_t)(numSets * 2 * BN) : (BN < 32 ? 32u : (uint32_t)BN);
+
+  int const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int const m0 = blockIdx.x * BM, n0 = blockIdx.y * BN, split = blockIdx.z;
+  int const kbBeg = split * p.kbPerSplit;
+  int const kbEnd = min(p.numKb, kbBeg + p.kbPerSplit);
+  int const numIter = max(kbEnd - kbBeg, 0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) { mbar_init(smem_u32(&fullBar[s]), kProducerThreads); mbar_init(smem_u32(&emptyBar[s]), 1); }
+    mbar_init(smem_u32(&accumBar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kEpilogueWarps) tmem_alloc(smem_u32(&tmemBase), tmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t const tmemAcc = tmemBase;
+
+  if (warp < kEpilogueWarps) {
+    // ============================== epilogue ==============================
+    bool ok = mbar_wait(smem_u32(&accumBar), 0);
+    tc_fence_after();
+    if (!ok) { if (lane == 0) atomicExch(p.status, 3); }
+    else if (numIter > 0) {
+      int m = m0 + warp * 32 + lane;
+      long long rowBase = 0;
+      if (kEpi == EPI_CONV) { int pix = m % p.e.P, img = m / p.e.P; rowBase = (long long)img * p.e.Ktot * p.e.P + pix; }
+      else rowBase = m + (long long)split * p.e.splitStride;
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        uint32_t r[16];
+        uint32_t const laneBase = tmemAcc + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
+        tmem_ld16(laneBase, r);
+        if (kSplit) {
+          // sum the accumulator sets: all "small" parts first, then the "big" ones
+          int const used = min(numSets, numIter);
+          float sum[16];
+          uint32_t t[16];
+          tmem_ld16(laneBase + (uint32_t)BN, t);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) sum[j] = __uint_as_float(t[j]);
+          for (int q = 1; q < used; ++q) {
+            tmem_ld16(laneBase + (uint32_t)(q * 2 * BN + BN), t);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) sum[j] += __uint_as_float(t[j]);
+          }
+          for (int q = 1; q < used; ++q) {
+            tmem_ld16(laneBase + (uint32_t)(q * 2 * BN), t);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) sum[j] += __uint_as_float(t[j]);
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(sum[j] + __uint_as_float(r[j]));
+        }
+        if (m < p.M) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            int n = n0 + c0 + j;
+            if (n < p.N) {
+              float acc = __uint_as_float(r[j]);
+              if (kEpi == EPI_CONV) {
+                float* dst = p.e.out + rowBase + (long long)n * p.e.P;
+                float o = p.e.inMult * acc;
+                if (p.e.bias) o += p.e.bias[n];
+                if (p.e.outMult != 0.f) o += p.e.outMult * *dst;
+                *dst = o;
+              } else {
+                float o = acc;
+                if (p.e.bias) o += p.e.bias[m];
+                p.e.out[rowBase + (long long)n * p.e.ldd] = o;
+              }
+            }
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  } else if (warp == kEpilogueWarps) {
+    // ============================== MMA issue ==============================
+    if (lane == 0) {
+      uint32_t const idesc = make_idesc(kAMN, kBMN, BN);
+      uint32_t aLbo = 512, aSbo = (BM / 32) * 512, bLbo = 512, bSbo = (uint32_t)(BN / 32) * 512;
+      bool ok = true;
+      for (int it = 0; it < numIter && ok; ++it) {
+        int s = it % p.stages;
+        ok = mbar_wait(smem_u32(&fullBar[s]), (uint32_t)((it / p.stages) & 1));
+        if (!ok) { atomicExch(p.status, 2); break; }
+        tc_fence_after();
+        uint32_t base = smem_u32(smem + (size_t)s * stageBytes);
+        uint32_t aHi = base, aLo = base + aTileBytes;
+        uint32_t bHi = base + (kSplit ? 2u : 1u) * aTileBytes, bLo = bHi + bTileBytes;
+#pragma unroll
+        for (int k4 = 0; k4 < BK / 8; ++k4) {
+          uint32_t aAdv = kAMN ? (uint32_t)k4 * (BM / 32) * 1024u : (uint32_t)k4 * 32u;     // two k quads per MMA
+          uint32_t bAdv = kBMN ? (uint32_t)k4 * (uint32_t)(BN / 32) * 1024u : (uint32_t)k4 * 32u;
+          uint64_t dAh = kAMN ? make_desc(aHi + aAdv, aLbo, aSbo, 1) : make_desc(aHi + aAdv, 16, 1024);
+          uint64_t dBh = kBMN ? make_desc(bHi + bAdv, bLbo, bSbo, 1) : make_desc(bHi + bAdv, 16, 1024);
+          uint32_t first = (it >= numSets || k4 > 0) ? 1u : 0u;     // 0 = overwrite: first MMA into this set
+          uint32_t const tmemBig = tmemAcc + (uint32_t)((it % numSets) * 2 * BN), tmemSmall = tmemBig + (uint32_t)BN;
+          if (kSplit) {
+            uint64_t dAl = kAMN ? make_desc(aLo + aAdv, aLbo, aSbo, 1) : make_desc(aLo + aAdv, 16, 1024);
+            uint64_t dBl = kBMN ? make_desc(bLo + bAdv, bLbo, bSbo, 1) : make_desc(bLo + bAdv, 16, 1024);
+            umma_tf32(tmemSmall, dAl, dBh, idesc, first);
+            umma_tf32(tmemSmall, dAh, dBl, idesc, 1u);
+            umma_tf32(tmemBig, dAh, dBh, idesc, first);
+          } else {
+            umma_tf32(tmemBig, dAh, dBh, idesc, first);
+          }
+        }
+        umma_commit(smem_u32(&emptyBar[s]));    // frees the stage once these MMAs have read it
+      }
+      umma_commit(smem_u32(&accumBar));         // accumulator complete (or nothing was issued)
+    }
+    __syncwarp();
+    tc_fence_before();
+  } else {
+    // ============================== producers ==============================
+    int const t = threadIdx.x - (kEpilogueWarps + 1) * 32;      // 0..255
+    // MN-major tiles: chunk column t % 32, k rows t / 32 + 8 j.  K-major tiles: chunk t % 8, rows t / 8 + 32 j.
+    int const mnChunk = t & 31, mnK = t >> 5, kmChunk = t & 7, kmRow = t >> 3;
+    PixCtx px[4];
+    TapCtx tap[4];
+    if (kAMode == OP_IM2COL) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) px[e] = pix_ctx(p.a, m0 + 4 * mnChunk + e);
+    }
+    if (kAMode == OP_WGATHER) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) tap[j] = tap_ctx(p.a, m0 + kmRow + 32 * j);
+    }
+    bool ok = true;
+    for (int it = 0; it < numIter && ok; ++it) {
+      int s = it % p.stages;
+      int const r0 = (kbBeg + it) * BK;
+      float va[4][4], vb[4][4];
+      // global loads first, so that all of them are in flight before the first use
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (kAMode == OP_IM2COL) load_im2col(p.a, px, r0 + mnK + 8 * j, p.R, va[j]);
+        else if (kAMode == OP_DENSE_MN) load_dense_mn(p.a, m0 + 4 * mnChunk, r0 + mnK + 8 * j, p.R, va[j]);
+        else if (kAMode == OP_WGATHER) load_wgather(p.a, tap[j], r0 + 4 * kmChunk, p.R, va[j]);
+        else load_dense_k(p.a, m0 + kmRow + 32 * j, r0 + 4 * kmChunk, p.R, va[j]);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (kBMN) {
+          if (4 * mnChunk < BN) load_dense_mn(p.b, n0 + 4 * mnChunk, r0 + mnK + 8 * j, p.R, vb[j]);
+        } else {
+          if (kmRow + 32 * j < BN) load_dense_k(p.b, n0 + kmRow + 32 * j, r0 + 4 * kmChunk, p.R, vb[j]);
+        }
+      }
+      ok = mbar_wait(smem_u32(&emptyBar[s]), (uint32_t)(((it / p.stages) & 1) ^ 1));
+      if (!ok) { atomicExch(p.status, 1); break; }
+      uint8_t* base = smem + (size_t)s * stageBytes;
+      uint8_t* aHi = base;
+      uint8_t* aLo = base + aTileBytes;
+      uint8_t* bHi = base + (kSplit ? 2u : 1u) * aTileBytes;
+      uint8_t* bLo = bHi + bTileBytes;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t off = kAMN ? mnmajor_off(mnChunk, mnK + 8 * j, BM / 32) : kmajor_off(kmRow + 32 * j, kmChunk);
+        store_chunk<kSplit>(aHi, aLo, off, va[j]);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (kBMN) {
+          if (4 * mnChunk < BN) store_chunk<kSplit>(bHi, bLo, mnmajor_off(mnChunk, mnK + 8 * j, BN / 32), vb[j]);
+        } else {
+          if (kmRow + 32 * j < BN) store_chunk<kSplit>(bHi, bLo, kmajor_off(kmRow + 32 * j, kmChunk), vb[j]);
+        }
+      }
+      fence_async_smem();                     // generic-proxy writes -> visible to the tensor core's async proxy
+      mbar_arrive(smem_u32(&fullBar[s]));
+    }
+  }
+
+  __syncthreads();
+  tc_fence_after();
+  if (warp == kEpilogueWarps) tmem_dealloc(tmemAcc, tmemCols);
+}
+
+// out[e] = sum over splits (ascending) of part[s*stride + e]
+__global__ void tc_splitk_reduce_kernel(float* __restrict__ out, float const* __restrict__ part, size_t n, size_t stride, int splits)
+{
+  size_t step = (size_t)gridDim.x * blockDim.x;
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += step) {
+    float s = part[e];
+    for (int k = 1; k < splits; ++k) s += part[(size_t)k * stride + e];
+    out[e] = s;
+  }
+}
+
+// Ft[fh', fw', k, c] = F[FH-1-fh', FW-1-fw', c, k]: the filter bank whose forward convolution
+// over dY is the data gradient of a stride-1 convolution.
+__global__ void flip_filters_kernel(float* __restrict__ ft, float const* __restrict__ f, int FH, int FW, int C, int K)
+{
+  size_t total = (size_t)FH * FW * C * K;
+  size_t step = (size_t)gridDim.x * blockDim.x;
+  for (size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x; o < total; o += step) {
+    int fh = (int)(o % FH); size_t t = o / FH;
+    int fw = (int)(t % FW); t /= FW;
+    int k = (int)(t % K); int c = (int)(t / K);
+    ft[o] = f[(FH - 1 - fh) + (size_t)FH * ((FW - 1 - fw) + (size_t)FW * (c + (size_t)C * k))];
+  }
+}
+
+// ------------------------------------------------------------------ host side
+int pick_bn(int N) { return N > 64 ? 128 : (N > 32 ? 64 : (N > 16 ? 32 : 16)); }
+
+bool aligned16(void const* p) { return (((uintptr_t)p) & 15) == 0; }
+
+template <int kAMode, int kBMode, int kEpi>
+int launch(vlb_ctx* ctx, Params& p, int splits, char const* where)
+{
+  bool split3 = ctx->precision == VLB_PRECISION_3XTF32;
+  uint32_t stageBytes = (split3 ? 2u : 1u) * (BM * BK * 4 + (uint32_t)p.BN * BK * 4);
+  int stages = (int)((200u * 1024u) / stageBytes);
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages > 6) stages = 6;
+  p.stages = stages;
+  p.status = ctx->deviceStatus;
+  size_t smemBytes = (size_t)stages * stageBytes + 1024;
+  dim3 grid(vlb::ceil_div(p.M, BM), vlb::ceil_div(p.N, p.BN), splits);
+  if (grid.y > 65535u || grid.z > 65535u) return VLB_Unsupported;
+  cudaError_t e;
+  if (split3) {
+    auto k = tc_gemm_kernel<kAMode, kBMode, kEpi, true>;
+    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smemBytes);
+    if (e == cudaSuccess) k<<<grid, kThreads, smemBytes, ctx->stream>>>(p);
+  } else {
+    auto k = tc_gemm_kernel<kAMode, kBMode, kEpi, false>;
+    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smemBytes);
+    if (e == cudaSuccess) k<<<grid, kThreads, smemBytes, ctx->stream>>>(p);
+  }
+  if (e != cudaSuccess) { cudaGetLastError(); return vlb::set_error(ctx, VLB_Cuda, cudaGetErrorString(e)); }
+  VLB_LAUNCHED(ctx, 1);
+  return vlb::check_launch(ctx, where);
+}
+
+// Splits of the reduction so that the grid fills the machine; each split gets whole k-blocks.
+int pick_splits(vlb_ctx* ctx, int tiles, int numKb, int minKbPerSplit)
+{
+  int target = 2 * ctx->smCount;
+  if (tiles >= target || numKb < 2 * minKbPerSplit) return 1;
+  int s = (target + tiles - 1) / tiles;
+  int maxS = numKb / minKbPerSplit;
+  if (s > maxS) s = maxS;
+  if (s > 512) s = 512;
+  return s < 1 ? 1 : s;
+}
+
+void conv_operand(Operand& o, ConvGeom const& g, float const* ptr, int channels)
+{
+  o.ptr = ptr;
+  o.H = g.H; o.W = g.W; o.C = channels; o.FH = g.FH; o.FW = g.FW; o.Ho = g.Ho; o.Wo = g.Wo;
+  o.sy = g.sy; o.sx = g.sx; o.pt = g.pt; o.pl = g.pl; o.dy = g.dy; o.dx = g.dx;
+  o.imgStride = (long long)g.H * g.W * channels;
+  o.ld = 0; o.bs = 0; o.P = 0; o.vec = 0;
+}
+
+bool fits32(ConvGeom const& g)
+{
+  long long in = (long long)g.H * g.W * g.C * g.N, out = (long long)g.Ho * g.Wo * g.K * g.N;
+  return in < (1LL << 31) - 256 && out < (1LL << 31) - 256 && (long long)g.FH * g.FW * g.FC * g.K < (1LL << 31);
+}
+
+bool is_fc(ConvGeom const& g)
+{
+  return g.Ho == 1 && g.Wo == 1 && g.FH == g.H && g.FW == g.W && g.FC == g.C && g.sy == 1 && g.sx == 1 && g.pt == 0 &&
+         g.pb == 0 && g.pl == 0 && g.pr == 0 && g.dy == 1 && g.dx == 1;
+}
+
+}  // namespace
 
 namespace vlb {
 
-int conv_fprop_tc(vlb_ctx*, ConvGeom const&, float*, float, float const*, float, float const*, float const*)
-{ return VLB_Unsupported; }
-int conv_dgrad_tc(vlb_ctx*, ConvGeom const&, float*, float const*, float const*) { return VLB_Unsupported; }
-int conv_wgrad_tc(vlb_ctx*, ConvGeom const&, float*, float*, float const*, float const*, bool*) { return VLB_Unsupported; }
+int conv_fprop_tc(vlb_ctx* ctx, ConvGeom const& g, float* Y, float outMult, float const* X, float inMult,
+                  float const* F, float const* b)
+{
+  if (g.G != 1 || !fits32(g)) return VLB_Unsupported;
+  int const V = g.FH * g.FW * g.FC;
+  Params p = {};
+  if (is_fc(g)) {
+    // Y(K x N) = F'(K x V) X(V x N) + b 1'  (reference bits/nnfullyconnected.cu:45-70): rows = filters
+    if (outMult != 0.f || inMult != 1.f) return VLB_Unsupported;
+    p.M = g.K; p.N = g.N; p.R = V;
+    p.a = Operand{}; p.a.ptr = F; p.a.ld = V; p.a.rows = g.K; p.a.vec = (V % 4 == 0) && aligned16(F);
+    p.b = Operand{}; p.b.ptr = X; p.b.ld = V; p.b.rows = g.N; p.b.vec = (V % 4 == 0) && aligned16(X);
+    p.BN = pick_bn(p.N);
+    p.numKb = ceil_div(p.R, BK);
+    int tiles = ceil_div(p.M, BM) * ceil_div(p.N, p.BN);
+    int splits = pick_splits(ctx, tiles, p.numKb, 8);
+    p.kbPerSplit = ceil_div(p.numKb, splits);
+    splits = ceil_div(p.numKb, p.kbPerSplit);
+    p.e = Epilogue{}; p.e.ldd = g.K;
+    if (splits == 1) {
+      p.e.out = Y; p.e.bias = b;
+      return launch<OP_DENSE_K, OP_DENSE_K, EPI_PLAIN>(ctx, p, 1, "fc_fprop_tc");
+    }
+    size_t nOut = (size_t)g.K * g.N;
+    float* part = (float*)workspace(ctx, sizeof(float) * nOut * splits);
+    if (!part) return ctx->lastError;
+    p.e.out = part; p.e.splitStride = (long long)nOut;
+    int rc = launch<OP_DENSE_K, OP_DENSE_K, EPI_PLAIN>(ctx, p, splits, "fc_fprop_tc");
+    if (rc) return rc;
+    tc_splitk_reduce_kernel<<<grid_for(nOut, 256, ctx->smCount * 8), 256, 0, ctx->stream>>>(Y, part, nOut, nOut, splits);
+    VLB_LAUNCHED(ctx, 1);
+    if (b) return vlb_bias_forward(ctx, Y, 1.0, nullptr, 0.0, b, 1.0, 1, 1, g.K, g.N);
+    return check_launch(ctx, "fc_fprop_tc");
+  }
+  long long M = (long long)g.Ho * g.Wo * g.N;
+  p.M = (int)M; p.N = g.K; p.R = V;
+  conv_operand(p.a, g, X, g.C);
+  p.a.rows = p.M;
+  p.b = Operand{}; p.b.ptr = F; p.b.ld = V; p.b.rows = g.K; p.b.vec = (V % 4 == 0) && aligned16(F);
+  p.BN = pick_bn(p.N);
+  p.numKb = ceil_div(p.R, BK); p.kbPerSplit = p.numKb;
+  p.e = Epilogue{}; p.e.out = Y; p.e.bias = b; p.e.inMult = inMult; p.e.outMult = outMult; p.e.P = g.Ho * g.Wo; p.e.Ktot = g.K;
+  return launch<OP_IM2COL, OP_DENSE_K, EPI_CONV>(ctx, p, 1, "conv_fprop_tc");
+}
+
+int conv_dgrad_tc(vlb_ctx* ctx, ConvGeom const& g, float* dX, float const* F, float const* dY)
+{
+  if (g.G != 1 || !fits32(g)) return VLB_Unsupported;
+  Params p = {};
+  if (is_fc(g)) {
+    // dX(V x N) = F(V x K) dY(K x N)  (reference bits/nnfullyconnected.cu:139-151): rows = input elements
+    int const V = g.FH * g.FW * g.FC;
+    p.M = V; p.N = g.N; p.R = g.K;
+    p.a = Operand{}; p.a.ptr = F; p.a.ld = V; p.a.rows = V; p.a.vec = (V % 4 == 0) && aligned16(F);
+    p.b = Operand{}; p.b.ptr = dY; p.b.ld = g.K; p.b.rows = g.N; p.b.vec = (g.K % 4 == 0) && aligned16(dY);
+    p.BN = pick_bn(p.N);
+    p.numKb = ceil_div(p.R, BK); p.kbPerSplit = p.numKb;
+    p.e = Epilogue{}; p.e.out = dX; p.e.ldd = V;
+    return launch<OP_DENSE_MN, OP_DENSE_K, EPI_PLAIN>(ctx, p, 1, "fc_dgrad_tc");
+  }
+  if (g.sy != 1 || g.sx != 1) return VLB_Unsupported;
+  // dX = conv(dY, flipped and transposed filters) with padding (F-1)*dilate - pad
+  size_t nF = (size_t)g.FH * g.FW * g.FC * g.K;
+  float* ft = (float*)workspace(ctx, sizeof(float) * nF);
+  if (!ft) return ctx->lastError;
+  flip_filters_kernel<<<grid_for(nF, 256, ctx->smCount * 8), 256, 0, ctx->stream>>>(ft, F, g.FH, g.FW, g.C, g.K);
+  VLB_LAUNCHED(ctx, 1);
+  ConvGeom t = g;
+  t.H = g.Ho; t.W = g.Wo; t.C = g.K; t.FC = g.K; t.K = g.C; t.Ho = g.H; t.Wo = g.W;
+  t.pt = (g.FH - 1) * g.dy - g.pt; t.pl = (g.FW - 1) * g.dx - g.pl;
+  long long M = (long long)g.H * g.W * g.N;
+  int const V = g.FH * g.FW * g.K;
+  p.M = (int)M; p.N = g.C; p.R = V;
+  conv_operand(p.a, t, dY, g.K);
+  p.a.rows = p.M;
+  p.b = Operand{}; p.b.ptr = ft; p.b.ld = V; p.b.rows = g.C; p.b.vec = (V % 4 == 0);
+  p.BN = pick_bn(p.N);
+  p.numKb = ceil_div(p.R, BK); p.kbPerSplit = p.numKb;
+  p.e = Epilogue{}; p.e.out = dX; p.e.inMult = 1.f; p.e.P = g.H * g.W; p.e.Ktot = g.C;
+  return launch<OP_IM2COL, OP_DENSE_K, EPI_CONV>(ctx, p, 1, "conv_dgrad_tc");
+}
+
+int conv_wgrad_tc(vlb_ctx* ctx, ConvGeom const& g, float* dF, float* db, float const* X, float const* dY, bool* dbDone)
+{
+  (void)db;
+  *dbDone = false;
+  if (g.G != 1 || !fits32(g)) return VLB_Unsupported;
+  int const V = g.FH * g.FW * g.FC;
+  Params p = {};
+  if (is_fc(g)) {
+    // dF(V x K) = X(V x N) dY'(N x K)  (reference bits/nnfullyconnected.cu:126-137): reduction over the batch
+    p.M = V; p.N = g.K; p.R = g.N;
+    p.a = Operand{}; p.a.ptr = X; p.a.ld = V; p.a.rows = V; p.a.vec = (V % 4 == 0) && aligned16(X);
+    p.b = Operand{}; p.b.ptr = dY; p.b.ld = g.K; p.b.rows = g.K; p.b.vec = (g.K % 4 == 0) && aligned16(dY);
+    p.BN = p.N > 64 ? 128 : (p.N > 32 ? 64 : 32);     // MN-major tiles are built from 32-column atoms
+    p.numKb = ceil_div(p.R, BK); p.kbPerSplit = p.numKb;
+    p.e = Epilogue{}; p.e.out = dF; p.e.ldd = V;
+    return launch<OP_DENSE_MN, OP_DENSE_MN, EPI_PLAIN>(ctx, p, 1, "fc_wgrad_tc");
+  }
+  long long R = (long long)g.Ho * g.Wo * g.N;
+  p.M = V; p.N = g.K; p.R = (int)R;
+  conv_operand(p.a, g, X, g.C);
+  p.a.rows = V;
+  int const P = g.Ho * g.Wo;
+  p.b = Operand{}; p.b.ptr = dY; p.b.ld = P; p.b.bs = (long long)P * g.K; p.b.P = P; p.b.rows = g.K;
+  p.b.vec = (P % 4 == 0) && aligned16(dY);
+  p.BN = pick_bn(p.N);
+  p.numKb = ceil_div(p.R, BK);
+  int tiles = ceil_div(p.M, BM) * ceil_div(p.N, p.BN);
+  int splits = pick_splits(ctx, tiles, p.numKb, 8);
+  p.kbPerSplit = ceil_div(p.numKb, splits);
+  splits = ceil_div(p.numKb, p.kbPerSplit);
+  p.e = Epilogue{}; p.e.ldd = V;
+  if (splits == 1) {
+    p.e.out = dF;
+    return launch<OP_WGATHER, OP_DENSE_K, EPI_PLAIN>(ctx, p, 1, "conv_wgrad_tc");
+  }
+  size_t nF = (size_t)V * g.K;
+  float* part = (float*)workspace(ctx, sizeof(float) * nF * splits);
+  if (!part) return ctx->lastError;
+  p.e.out = part; p.e.splitStride = (long long)nF;
+  int rc = launch<OP_WGATHER, OP_DENSE_K, EPI_PLAIN>(ctx, p, splits, "conv_wgrad_tc");
+  if (rc) return rc;
+  tc_splitk_reduce_kernel<<<grid_for(nF, 256, ctx->smCount * 8), 256, 0, ctx->stream>>>(dF, part, nF, nF, splits);
+  VLB_LAUNCHED(ctx, 1);
+  return check_launch(ctx, "conv_wgrad_tc");
+}
 
 }  // namespace vlb

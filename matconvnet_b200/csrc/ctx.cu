@@ -86,6 +86,11 @@ int vlb_ctx_create(vlb_ctx** out)
   vlb_ctx* c = new vlb_ctx();
   c->device = dev;
   c->smCount = prop.multiProcessorCount;
+  if (cudaMalloc((void**)&c->deviceStatus, 256) != cudaSuccess || cudaMemset(c->deviceStatus, 0, 256) != cudaSuccess) {
+    cudaGetLastError();
+    delete c;
+    return VLB_OutOfGPUMemeory;
+  }
   *out = c;
   return VLB_Success;
 }
@@ -94,6 +99,7 @@ int vlb_ctx_destroy(vlb_ctx* ctx)
 {
   if (!ctx) return VLB_Success;
   if (ctx->workspace) { cudaStreamSynchronize(ctx->stream); cudaFree(ctx->workspace); }
+  if (ctx->deviceStatus) cudaFree(ctx->deviceStatus);
   delete ctx;
   return VLB_Success;
 }
@@ -127,5 +133,18 @@ int vlb_ctx_clear_workspace(vlb_ctx* ctx)
   return VLB_Success;
 }
 long long vlb_ctx_launch_count(vlb_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+int vlb_ctx_device_status(vlb_ctx* ctx, int* status)
+{
+  if (!ctx || !status) return VLB_IllegalArgument;
+  cudaError_t e = cudaStreamSynchronize(ctx->stream);
+  if (e == cudaSuccess) e = cudaMemcpy(status, ctx->deviceStatus, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return vlb::set_error(ctx, VLB_Cuda, cudaGetErrorString(e));
+  if (*status != 0) {
+    cudaMemset(ctx->deviceStatus, 0, sizeof(int));
+    return vlb::set_error(ctx, VLB_Timeout, "a tensor-core kernel gave up waiting on a pipeline barrier");
+  }
+  return VLB_Success;
+}
 
 }  // extern "C"

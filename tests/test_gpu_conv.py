@@ -28,6 +28,7 @@ def precision(gpu):
     _, _, ctx = gpu
     yield ctx
     ctx.set_precision(0)
+    assert ctx.device_status() == 0      # no tensor-core kernel gave up a pipeline wait
 
 
 @pytest.mark.parametrize("mode,prec,tol", MODES)
