@@ -60,6 +60,12 @@ long long vlb_ctx_launch_count(vlb_ctx* ctx);    /* kernels enqueued through thi
  * their bounded pipeline waits expires (0 = none did).  Returns VLE_Timeout, as the reference's own
  * waits do (matlab/src/vl_tmove.cu:1344-1359), when the word is non-zero, and clears it. */
 int vlb_ctx_device_status(vlb_ctx* ctx, int* status);
+/* Measurement aid: between begin and end every tensor-core contraction launch is bracketed by CUDA
+ * events on the context's stream.  end synchronises and returns the summed kernel time, the summed
+ * algorithmic flops (2*M*N*K of each contraction, counted once whatever the arithmetic mode) and the
+ * number of launches.  (The reference times whole layers with tic/toc, matlab/simplenn/vl_simplenn.m:297,397.) */
+int vlb_ctx_profile_begin(vlb_ctx* ctx);
+int vlb_ctx_profile_end(vlb_ctx* ctx, double* ms, double* flops, long long* launches);
 char const* vlb_error_message(int code);         /* vl::getErrorMessage, bits/data.cu:83-100 (all 13 codes named) */
 int vlb_version(void);
 

@@ -54,6 +54,8 @@ SIGNATURES = {
     "vlb_ctx_clear_workspace": (_I, [_P]),
     "vlb_ctx_launch_count": (C.c_longlong, [_P]),
     "vlb_ctx_device_status": (_I, [_P, C.POINTER(_I)]),
+    "vlb_ctx_profile_begin": (_I, [_P]),
+    "vlb_ctx_profile_end": (_I, [_P, C.POINTER(_D), C.POINTER(_D), C.POINTER(C.c_longlong)]),
     "vlb_conv_output_shape": (_I, [C.POINTER(ConvDesc), C.POINTER(_I), C.POINTER(_I)]),
     "vlb_conv_forward": (_I, [_P, _P, _D, _P, _D, _P, _P, C.POINTER(ConvDesc)]),
     "vlb_conv_backward": (_I, [_P, _P, _P, _P, _P, _P, _P, C.POINTER(ConvDesc)]),
@@ -153,6 +155,15 @@ class Context:
         st = C.c_int(0)
         self.check(self.lib.vlb_ctx_device_status(self.handle, C.byref(st)))
         return st.value
+
+    def profile_begin(self):
+        self.check(self.lib.vlb_ctx_profile_begin(self.handle))
+
+    def profile_end(self):
+        """(milliseconds, algorithmic flops, launches) of the tensor-core kernels since profile_begin."""
+        ms, fl, n = C.c_double(), C.c_double(), C.c_longlong()
+        self.check(self.lib.vlb_ctx_profile_end(self.handle, C.byref(ms), C.byref(fl), C.byref(n)))
+        return ms.value, fl.value, n.value
 
     def last_error(self):
         return self.lib.vlb_ctx_last_error(self.handle).decode()

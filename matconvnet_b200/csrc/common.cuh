@@ -4,6 +4,7 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <string>
+#include <vector>
 #include "../../include/vlb.h"
 
 // The context: stream, grow-only scratch, sticky error message chain.
@@ -20,6 +21,10 @@ struct vlb_ctx {
   long long launches = 0;
   int smCount = 148;
   int* deviceStatus = nullptr;   // one word the tensor-core kernels set when a bounded wait expires
+  // optional timing of the tensor-core launches with events on the launching stream
+  struct ProfRec { cudaEvent_t start, stop; double flops; };
+  bool profiling = false;
+  std::vector<ProfRec> prof;
 };
 
 namespace vlb {

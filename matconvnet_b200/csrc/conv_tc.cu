@@ -530,6 +530,12 @@ int launch(vlb_ctx* ctx, Params& p, int splits, char const* where)
   dim3 grid(vlb::ceil_div(p.M, BM), vlb::ceil_div(p.N, p.BN), splits);
   if (grid.y > 65535u || grid.z > 65535u) return VLB_Unsupported;
   cudaError_t e;
+  vlb_ctx::ProfRec rec;
+  if (ctx->profiling) {
+    cudaEventCreate(&rec.start); cudaEventCreate(&rec.stop);
+    rec.flops = 2.0 * (double)p.M * (double)p.N * (double)p.R;
+    cudaEventRecord(rec.start, ctx->stream);
+  }
   if (split3) {
     auto k = tc_gemm_kernel<kAMode, kBMode, kEpi, true>;
     e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smemBytes);
@@ -539,6 +545,7 @@ int launch(vlb_ctx* ctx, Params& p, int splits, char const* where)
     e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smemBytes);
     if (e == cudaSuccess) k<<<grid, kThreads, smemBytes, ctx->stream>>>(p);
   }
+  if (ctx->profiling) { cudaEventRecord(rec.stop, ctx->stream); ctx->prof.push_back(rec); }
   if (e != cudaSuccess) { cudaGetLastError(); return vlb::set_error(ctx, VLB_Cuda, cudaGetErrorString(e)); }
   VLB_LAUNCHED(ctx, 1);
   return vlb::check_launch(ctx, where);

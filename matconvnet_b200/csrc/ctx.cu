@@ -134,6 +134,35 @@ int vlb_ctx_clear_workspace(vlb_ctx* ctx)
 }
 long long vlb_ctx_launch_count(vlb_ctx* ctx) { return ctx ? ctx->launches : 0; }
 
+int vlb_ctx_profile_begin(vlb_ctx* ctx)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  for (auto& r : ctx->prof) { cudaEventDestroy(r.start); cudaEventDestroy(r.stop); }
+  ctx->prof.clear();
+  ctx->profiling = true;
+  return VLB_Success;
+}
+
+int vlb_ctx_profile_end(vlb_ctx* ctx, double* ms, double* flops, long long* launches)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  ctx->profiling = false;
+  cudaError_t e = cudaStreamSynchronize(ctx->stream);
+  double tms = 0, tf = 0;
+  for (auto& r : ctx->prof) {
+    float t = 0.f;
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&t, r.start, r.stop);
+    tms += t; tf += r.flops;
+    cudaEventDestroy(r.start); cudaEventDestroy(r.stop);
+  }
+  if (ms) *ms = tms;
+  if (flops) *flops = tf;
+  if (launches) *launches = (long long)ctx->prof.size();
+  ctx->prof.clear();
+  if (e != cudaSuccess) return vlb::set_error(ctx, VLB_Cuda, cudaGetErrorString(e));
+  return VLB_Success;
+}
+
 int vlb_ctx_device_status(vlb_ctx* ctx, int* status)
 {
   if (!ctx || !status) return VLB_IllegalArgument;

@@ -250,6 +250,17 @@ def vl_nnbilinearsampler(x, grid, dzdy=None, ctx=None):
     return dx, dgrid
 
 
+# --------------------------------------------------------------------- gradient scaling
+def scale_(t, alpha, ctx=None):
+    """t *= alpha in place: the division by the number of workers of an all-reduced gradient
+    (examples/cnn_train.m:482-483)."""
+    ctx = _ctx(ctx)
+    if not (t.is_cuda and t.dtype == torch.float32):
+        raise TypeError("CUDA float32 tensor expected")
+    ctx.check(ctx.lib.vlb_scale(ctx.handle, t.data_ptr(), float(alpha), t.numel()))
+    return t
+
+
 # --------------------------------------------------------------------- MATLAB-only blocks
 def vl_nnrelu(x, dzdy=None, ctx=None):
     """matlab/vl_nnrelu.m:43-48 with LEAK = 0."""

@@ -1,0 +1,80 @@
+"""Linear-chain forward/backward in the reference's schedule (matlab/simplenn/vl_simplenn.m).
+
+A network is ``{'layers': [layer, ...]}`` with layers shaped like the reference's structs:
+  {'type': 'conv', 'weights': [f, b], 'stride': s, 'pad': p, 'dilate': d}
+  {'type': 'relu'}   {'type': 'pool', 'method': 'max'|'avg', 'pool': [ph pw], 'stride': s, 'pad': p}
+  {'type': 'bnorm', 'weights': [g, b, moments], 'epsilon': e}   {'type': 'softmaxloss', 'class': c}
+``vl_simplenn(net, x, dzdy)`` runs the forward pass storing every intermediate (res[i]['x'],
+vl_simplenn.m:294-398) and, when dzdy is given, the backward pass in reverse order
+(vl_simplenn.m:404-524), leaving res[i]['dzdx'] and, for parametrised layers, res[i]['dzdw'].
+As in the reference, each layer's parameter derivatives are handed to the gradient exchange
+as soon as they exist (vl_simplenn.m:504-509): ``on_dzdw(i, j, tensor)`` is called right
+after layer i's backward, which is what lets the all-reduce overlap the remaining layers.
+Every block is a call into the C ABI; nothing is computed on the host.
+"""
+from . import nn
+
+
+def _get(l, key, default):
+    return l[key] if key in l and l[key] is not None else default
+
+
+def vl_simplenn(net, x, dzdy=None, res=None, on_dzdw=None, ctx=None, skip_forward=False,
+                back_prop_depth=None):
+    layers = net["layers"]
+    n = len(layers)
+    if res is None:
+        res = [dict(x=None, dzdx=None, dzdw=None, aux=None) for _ in range(n + 1)]
+    if not skip_forward:
+        res[0]["x"] = x
+        for i, l in enumerate(layers):
+            t = l["type"]
+            xi = res[i]["x"]
+            if t == "conv":
+                res[i + 1]["x"] = nn.vl_nnconv(xi, l["weights"][0], l["weights"][1], stride=_get(l, "stride", 1),
+                                               pad=_get(l, "pad", 0), dilate=_get(l, "dilate", 1), ctx=ctx)
+            elif t == "relu":
+                res[i + 1]["x"] = nn.vl_nnrelu(xi, ctx=ctx)
+            elif t == "pool":
+                res[i + 1]["x"] = nn.vl_nnpool(xi, l["pool"], stride=_get(l, "stride", 1), pad=_get(l, "pad", 0),
+                                               method=_get(l, "method", "max"), ctx=ctx)
+            elif t == "bnorm":
+                # training mode: moments from the batch (vl_simplenn.m:345-351)
+                res[i + 1]["x"], res[i]["aux"] = nn.vl_nnbnorm(xi, l["weights"][0], l["weights"][1],
+                                                               epsilon=_get(l, "epsilon", 1e-4), ctx=ctx)
+            elif t == "softmaxloss":
+                res[i + 1]["x"] = nn.vl_nnsoftmaxloss(xi, l["class"], ctx=ctx)
+            else:
+                raise ValueError("Unknown layer type '%s'." % t)
+    if dzdy is None:
+        return res
+    res[n]["dzdx"] = dzdy
+    first = 0 if back_prop_depth is None else max(0, n - back_prop_depth)
+    for i in range(n - 1, first - 1, -1):
+        l = layers[i]
+        t = l["type"]
+        xi, d = res[i]["x"], res[i + 1]["dzdx"]
+        if t == "conv":
+            dx, df, db = nn.vl_nnconv(xi, l["weights"][0], l["weights"][1], d, stride=_get(l, "stride", 1),
+                                      pad=_get(l, "pad", 0), dilate=_get(l, "dilate", 1), ctx=ctx)
+            res[i]["dzdx"], res[i]["dzdw"] = dx, [df, db]
+        elif t == "relu":
+            res[i]["dzdx"] = nn.vl_nnrelu(xi, d, ctx=ctx)
+        elif t == "pool":
+            res[i]["dzdx"] = nn.vl_nnpool(xi, l["pool"], d, stride=_get(l, "stride", 1), pad=_get(l, "pad", 0),
+                                          method=_get(l, "method", "max"), ctx=ctx)
+        elif t == "bnorm":
+            dx, dg, db, mom = nn.vl_nnbnorm(xi, l["weights"][0], l["weights"][1], d,
+                                            epsilon=_get(l, "epsilon", 1e-4), ctx=ctx)
+            res[i]["dzdx"], res[i]["dzdw"] = dx, [dg, db, mom]
+        elif t == "softmaxloss":
+            res[i]["dzdx"] = nn.vl_nnsoftmaxloss(xi, l["class"], d, ctx=ctx)
+        else:
+            raise ValueError("Unknown layer type '%s'." % t)
+        if on_dzdw is not None and res[i]["dzdw"] is not None:
+            for j, w in enumerate(res[i]["dzdw"]):
+                if w is not None:
+                    on_dzdw(i, j, w)
+        if i + 1 < n:
+            res[i + 1]["dzdx"] = None      # conserveMemory (vl_simplenn.m:512-514)
+    return res
