@@ -123,6 +123,24 @@ int vlb_bnorm_backward_moment(vlb_ctx* ctx, float* dX, float* dG, float* dB, flo
                               float const* X, float const* g, float const* b, float const* dY,
                               int H, int W, int C, int N, double eps);
 
+/* Batch-norm backward (moments computed from the batch, like vlb_bnorm_backward) for callers that may
+ * not allocate device memory: a host whose own allocator owns the whole GPU, or a loop that cannot
+ * afford the device-wide synchronisation of cudaMalloc.  It has no counterpart in the reference.
+ * It needs no vlb_ctx and calls no cudaMalloc, cudaFree or other allocating routine: the per-channel
+ * scratch (moments when `moments` is NULL, and the dx coefficients) is a fixed 96 KB array inside the
+ * library image, which every GPU that loads the library holds until the process exits.
+ *   - C may be at most 4096 channels; more is refused with VLE_IllegalArgument and a message.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress); make
+ *     that first call before any stream capture begins.
+ *   - All calls on a device share the one array, so two calls whose kernels overlap on the GPU (different
+ *     streams, no dependency) race on it; serialise them.  Nothing in it needs clearing between calls:
+ *     each call rewrites the entries of channels [0, C) before reading them.
+ * cudaStream: the stream to enqueue on (NULL = default stream).  errbuf/errlen: optional buffer that
+ * receives a message when the return value is not 0.  Tensors and results are those of vlb_bnorm_backward. */
+int vlb_bnorm_backward_noalloc(void* cudaStream, float* dX, float* dG, float* dB, float* moments /* may be NULL */,
+                               float const* X, float const* g, float const* dY, int H, int W, int C, int N,
+                               double eps, char* errbuf, size_t errlen);
+
 /* ---- pooling: vl::nn::Pooling (bits/nnpooling.hpp:21-49) ------------------------------------- */
 enum { VLB_POOL_MAX = 0, VLB_POOL_AVG = 1 };
 typedef struct {

@@ -67,6 +67,7 @@ SIGNATURES = {
     "vlb_bnorm_forward_moment": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _D]),
     "vlb_bnorm_backward": (_I, [_P] * 9 + [_I, _I, _I, _I, _D]),
     "vlb_bnorm_backward_moment": (_I, [_P] * 9 + [_I, _I, _I, _I, _D]),
+    "vlb_bnorm_backward_noalloc": (_I, [_P] * 8 + [_I, _I, _I, _I, _D, C.c_char_p, _Z]),
     "vlb_pool_output_shape": (_I, [C.POINTER(PoolDesc), C.POINTER(_I), C.POINTER(_I)]),
     "vlb_pool_forward": (_I, [_P, _P, _P, C.POINTER(PoolDesc)]),
     "vlb_pool_backward": (_I, [_P, _P, _P, _P, C.POINTER(PoolDesc)]),

@@ -329,3 +329,81 @@ int vlb_bnorm_backward_moment(vlb_ctx* ctx, float* dX, float* dG, float* dB, flo
 }
 
 }  // extern "C"
+
+// ====================================================================================
+// Batch-norm backward for callers that must not allocate
+// ====================================================================================
+// Some hosts hand the whole device to an allocator of their own (MATLAB's gpuArray pool, a
+// serving process with a fixed arena) or run inside a latency budget that a cudaMalloc --
+// which synchronises the whole device -- would break.  Such callers cannot create a vlb_ctx
+// (it allocates) nor let the scratch buffer grow.  For them the two per-channel scratch arrays
+// of the backward pass live in a fixed array inside the library image: moments (2*C floats,
+// used when the caller passes none) and the coefficients {mean, db/m, G1, G2} (4*C floats).
+constexpr int kNoAllocMaxChannels = 4096;
+static __device__ __align__(256) float g_bnormNoAllocScratch[6 * kNoAllocMaxChannels];   // 96 KB per GPU that loads the library
+
+namespace {
+
+// Device address of the array above, one per device.  The array's name is only a stand-in in
+// host code; the address a kernel can use comes from cudaGetSymbolAddress, asked once per
+// device with that device current.
+constexpr int kMaxDevices = 64;
+float* g_noAllocPtr[kMaxDevices] = {};
+
+void report(char* errbuf, size_t errlen, char const* msg)
+{
+  if (errbuf && errlen) snprintf(errbuf, errlen, "%s", msg);
+}
+
+}  // namespace
+
+extern "C" int vlb_bnorm_backward_noalloc(void* cudaStream, float* dX, float* dG, float* dB, float* moments,
+                                          float const* X, float const* g, float const* dY, int H, int W, int C,
+                                          int N, double eps, char* errbuf, size_t errlen)
+{
+  if (!dX || !dG || !dB || !X || !g || !dY) { report(errbuf, errlen, "bnorm_backward_noalloc: null tensor"); return VLB_IllegalArgument; }
+  if (H <= 0 || W <= 0 || C <= 0 || N <= 0 || (long long)H * W * N >= (1LL << 31)) {
+    report(errbuf, errlen, "bnorm_backward_noalloc: empty or oversized input");
+    return VLB_IllegalArgument;
+  }
+  if (C > kNoAllocMaxChannels) {
+    report(errbuf, errlen, "bnorm_backward_noalloc: more than 4096 channels do not fit the built-in scratch array; "
+                           "use vlb_bnorm_backward with a context");
+    return VLB_IllegalArgument;
+  }
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) { report(errbuf, errlen, "bnorm_backward_noalloc: no usable current device"); return VLB_Cuda; }
+  if (!g_noAllocPtr[dev]) {
+    // first call on this device: resolve the array's device address (no allocation takes place)
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_bnormNoAllocScratch);
+    if (e != cudaSuccess || !p) {
+      cudaGetLastError();
+      report(errbuf, errlen, cudaGetErrorString(e));
+      return VLB_Cuda;
+    }
+    g_noAllocPtr[dev] = p;
+  }
+  cudaStream_t stream = (cudaStream_t)cudaStream;
+  float* ownMom = g_noAllocPtr[dev];
+  float4* cf = reinterpret_cast<float4*>(g_noAllocPtr[dev] + 2 * kNoAllocMaxChannels);
+  float* mom = moments ? moments : ownMom;
+  // Nothing in the scratch has to start from zero: pass 1 writes every moment and pass 1b every
+  // coefficient of channels [0, C) before pass 2 reads them; entries beyond C keep an earlier call's
+  // values and are never read.
+  int WH = H * W;
+  bool vec = vec_ok(WH, X, dY, dX);
+  dim3 grid(C, kCluster);
+  if (vec) bnorm_reduce_kernel<1, true><<<grid, kThreads, 0, stream>>>(mom, dG, dB, nullptr, X, dY, WH, C, N, (float)eps);
+  else     bnorm_reduce_kernel<1, false><<<grid, kThreads, 0, stream>>>(mom, dG, dB, nullptr, X, dY, WH, C, N, (float)eps);
+  float mass = (float)((long long)WH * N);
+  bnorm_coef_kernel<<<vlb::ceil_div(C, 256), 256, 0, stream>>>(cf, mom, g, nullptr, dG, dB, C, mass);
+  size_t total = (size_t)WH * C * N;
+  unsigned blocks = vlb::grid_for(vec ? total / 4 : total, kThreads, 148 * 16);
+  if (vec) bnorm_bwd_apply_kernel<true><<<blocks, kThreads, 0, stream>>>(dX, X, dY, cf, WH, C, total);
+  else     bnorm_bwd_apply_kernel<false><<<blocks, kThreads, 0, stream>>>(dX, X, dY, cf, WH, C, total);
+  e = cudaPeekAtLastError();
+  if (e != cudaSuccess) { report(errbuf, errlen, cudaGetErrorString(e)); return VLB_Cuda; }
+  return VLB_Success;
+}
