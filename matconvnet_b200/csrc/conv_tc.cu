@@ -61,6 +61,7 @@ struct Operand {
   int P;               // run length of contiguous reduction indices (DENSE_K, batched); 0 = unbatched
   int rows;            // valid extent of the row (M or N) index
   int vec;             // 1 when 16-byte loads are legal for this operand
+  int fast;            // 1 when the aligned-window gather applies (IM2COL, WGATHER; see load_shifted)
   // convolution geometry (IM2COL, WGATHER)
   int H, W, C, FH, FW, Ho, Wo, sy, sx, pt, pl, dy, dx;
   long long imgStride;   // H*W*Ctotal
@@ -82,6 +83,8 @@ struct Params {
   int BN;                 // tile columns: 16, 32, 64 or 128
   int numKb, kbPerSplit;
   int stages;
+  int pipelined;          // 1: producers prefetch one stage ahead in registers (aligned gathers only)
+  float const* bTiles;    // when non-null: B pre-split into shared-memory tile images, fetched with bulk copies
   int* status;
 };
 
@@ -109,6 +112,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
       else if (now - t0 > kWaitCycles) return false;
     }
   }
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{ asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes) : "memory"); }
+
+// Bulk asynchronous copy global -> shared (both 16-byte aligned, size a multiple of 16); completion is
+// signalled on the mbarrier as transaction bytes.  Source is always this GPU's own memory.
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dstSmem, void const* src, uint32_t bytes, uint32_t bar)
+{
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dstSmem), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -281,6 +295,98 @@ __device__ __forceinline__ void load_wgather(Operand const& o, TapCtx const& tc,
   }
 }
 
+// ---- fast gathers.  Preconditions (Operand::fast): stride 1, H % 4 == 0, Ho % 4 == 0, base 16-byte
+// aligned, fewer than 2^31 elements.  Then four consecutive output pixels lie in one column, and
+// every 16-byte-aligned group of four input rows is wholly inside the image or wholly padding, so a
+// shifted window of four rows is two aligned 128-bit loads and a funnel shift.
+struct FastPix { int base, ho0, wo; bool valid; };   // base = image*imgStride + wo*H + ho0, in elements
+
+__device__ __forceinline__ FastPix fast_pix(Operand const& o, int m, int limit)
+{
+  FastPix c;
+  c.valid = m < limit;
+  int ho = m % o.Ho, t = m / o.Ho;
+  c.wo = t % o.Wo;
+  c.ho0 = ho;
+  c.base = (t / o.Wo) * (int)o.imgStride + c.wo * o.H + ho;
+  return c;
+}
+
+// v[e] = x[row ho0 + s + e, column wo + dw, plane offset coff] (zero outside the image), e = 0..3
+__device__ __forceinline__ void load_shifted(float const* __restrict__ ptr, int H, int W, FastPix const& px, int s, int dw,
+                                             int coff, bool on, float (&v)[4])
+{
+  int const o = s & 3;
+  int const h0 = px.ho0 + s - o;
+  int const w = px.wo + dw;
+  bool const wok = on && px.valid && w >= 0 && w < W;
+  float const* a0 = ptr + (px.base + coff + dw * H + (s - o));
+  float4 c0 = make_float4(0.f, 0.f, 0.f, 0.f), c1 = c0;
+  if (wok && h0 >= 0 && h0 < H) c0 = *reinterpret_cast<float4 const*>(a0);
+  if (wok && o != 0 && h0 + 4 >= 0 && h0 + 4 < H) c1 = *reinterpret_cast<float4 const*>(a0 + 4);
+  bool const s2 = (o & 2) != 0, s1 = (o & 1) != 0;
+  float t0 = s2 ? c0.z : c0.x, t1 = s2 ? c0.w : c0.y, t2 = s2 ? c1.x : c0.z, t3 = s2 ? c1.y : c0.w, t4 = s2 ? c1.z : c1.x;
+  v[0] = s1 ? t1 : t0; v[1] = s1 ? t2 : t1; v[2] = s1 ? t3 : t2; v[3] = s1 ? t4 : t3;
+}
+
+// One row of a reduction-contiguous operand whose 16-byte loads are legal: p points at (row, batch) start.
+__device__ __forceinline__ void load_row4(float const* __restrict__ p, int r, int R, bool ok, float (&v)[4])
+{
+  v[0] = v[1] = v[2] = v[3] = 0.f;
+  if (!ok || r >= R) return;
+  if (r + 3 < R) {
+    float4 t = *reinterpret_cast<float4 const*>(p + r);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  } else {
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      if (r + e < R) v[e] = p[r + e];
+  }
+}
+
+// ------------------------------------------------------------------ pipelined producer
+// Register image of one stage's global loads for one producer thread.  Shifted gathers keep both
+// aligned 128-bit words per chunk until the data is used (the funnel shift happens at store time).
+template <int kAMode, int kBMode>
+struct RawStage {
+  float4 a0[4];
+  float4 a1[4];     // second aligned word of a shifted window (IM2COL, WGATHER); unused members cost no registers
+  float4 b0[4];     // B rows when B is gathered by the threads rather than bulk-copied
+  int ao[4];        // funnel shift per chunk (IM2COL: depends on the tap of that k)
+};
+
+__device__ __forceinline__ void funnel(float4 c0, float4 c1, int o, float (&v)[4])
+{
+  bool const s2 = (o & 2) != 0, s1 = (o & 1) != 0;
+  float t0 = s2 ? c0.z : c0.x, t1 = s2 ? c0.w : c0.y, t2 = s2 ? c1.x : c0.z, t3 = s2 ? c1.y : c0.w, t4 = s2 ? c1.z : c1.x;
+  v[0] = s1 ? t1 : t0; v[1] = s1 ? t2 : t1; v[2] = s1 ? t3 : t2; v[3] = s1 ? t4 : t3;
+}
+
+// Issues the two aligned loads of a shifted four-row window (see load_shifted) without using them.
+__device__ __forceinline__ void issue_shifted(float const* __restrict__ ptr, int H, int W, FastPix const& px, int s, int dw,
+                                              int coff, bool on, float4& c0, float4& c1)
+{
+  int const o = s & 3;
+  int const h0 = px.ho0 + s - o;
+  int const w = px.wo + dw;
+  bool const wok = on && px.valid && w >= 0 && w < W;
+  float const* a0 = ptr + (px.base + coff + dw * H + (s - o));
+  c0 = make_float4(0.f, 0.f, 0.f, 0.f); c1 = c0;
+  if (wok && h0 >= 0 && h0 < H) c0 = *reinterpret_cast<float4 const*>(a0);
+  if (wok && o != 0 && h0 + 4 >= 0 && h0 + 4 < H) c1 = *reinterpret_cast<float4 const*>(a0 + 4);
+}
+
+__device__ __forceinline__ float4 issue_row4(float const* __restrict__ p, int r, int R, bool ok)
+{
+  float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (!ok || r >= R) return t;
+  if (r + 3 < R) return *reinterpret_cast<float4 const*>(p + r);
+  t.x = p[r];
+  if (r + 1 < R) t.y = p[r + 1];
+  if (r + 2 < R) t.z = p[r + 2];
+  return t;
+}
+
 // ------------------------------------------------------------------ the kernel
 template <int kAMode, int kBMode, int kEpi, bool kSplit>
 __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
@@ -425,35 +531,178 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
     int const t = threadIdx.x - (kEpilogueWarps + 1) * 32;      // 0..255
     // MN-major tiles: chunk column t % 32, k rows t / 32 + 8 j.  K-major tiles: chunk t % 8, rows t / 8 + 32 j.
     int const mnChunk = t & 31, mnK = t >> 5, kmChunk = t & 7, kmRow = t >> 3;
+    bool const aFast = p.a.fast != 0;
     PixCtx px[4];
     TapCtx tap[4];
+    // fast IM2COL: this thread's four pixels, and its reduction index (fh,fw,c), which advances by 8 per step
+    FastPix fpx = {0, 0, 0, false};
+    int fFh = 0, fFw = 0, fC = 0, fR = 0, d8fh = 0, d8fw = 0, d8c = 0;
+    // fast WGATHER: this thread's four filter taps
+    int tapS[4], tapDw[4], tapCoff[4];
+    bool tapOk[4];
+    int const HW = p.a.H * p.a.W;
     if (kAMode == OP_IM2COL) {
+      if (aFast) {
+        fpx = fast_pix(p.a, m0 + 4 * mnChunk, p.a.rows);
+        fR = kbBeg * BK + mnK;
+        fFh = fR % p.a.FH; int q = fR / p.a.FH; fFw = q % p.a.FW; fC = q / p.a.FW;
+        d8fh = 8 % p.a.FH; q = 8 / p.a.FH; d8fw = q % p.a.FW; d8c = q / p.a.FW;
+      } else {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) px[e] = pix_ctx(p.a, m0 + 4 * mnChunk + e);
+        for (int e = 0; e < 4; ++e) px[e] = pix_ctx(p.a, m0 + 4 * mnChunk + e);
+      }
     }
     if (kAMode == OP_WGATHER) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) tap[j] = tap_ctx(p.a, m0 + kmRow + 32 * j);
+      for (int j = 0; j < 4; ++j) {
+        tap[j] = tap_ctx(p.a, m0 + kmRow + 32 * j);
+        tapS[j] = tap[j].dh; tapDw[j] = tap[j].dw; tapCoff[j] = (int)tap[j].coff; tapOk[j] = tap[j].valid;
+      }
     }
+    // reduction-contiguous dense operands: row pointers are fixed for the thread
+    float const* aRow[4];
+    float const* bRow[4];
+    bool aRowOk[4], bRowOk[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      int ia = m0 + kmRow + 32 * j, ib = n0 + kmRow + 32 * j;
+      aRowOk[j] = (kAMode == OP_DENSE_K) && ia < p.a.rows;
+      aRow[j] = p.a.ptr + (aRowOk[j] ? (long long)ia * p.a.ld : 0);
+      bRowOk[j] = (kBMode == OP_DENSE_K) && ib < p.b.rows && kmRow + 32 * j < BN;
+      bRow[j] = p.b.ptr + (bRowOk[j] ? (long long)ib * p.b.ld : 0);
+    }
+    if (p.pipelined && kAMode != OP_DENSE_MN && kBMode == OP_DENSE_K) {
+      // ---- pipelined: the loads of stage it+1 are issued before stage it is written to shared
+      // memory, so a full stage of global loads is always in flight per thread.
+      typedef RawStage<kAMode, kBMode> Raw;
+      bool const bBulk = p.bTiles != nullptr;
+      uint32_t const bBytes = (kSplit ? 2u : 1u) * bTileBytes;
+      auto issue = [&](int it, Raw& R) {
+        int const r0 = (kbBeg + it) * BK;
+        if (kAMode == OP_IM2COL) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            int const sft = fFh * p.a.dy - p.a.pt;
+            R.ao[j] = sft & 3;
+            issue_shifted(p.a.ptr, p.a.H, p.a.W, fpx, sft, fFw * p.a.dx - p.a.pl, fC * HW, fR < p.R, R.a0[j], R.a1[j]);
+            fR += 8; fFh += d8fh; fFw += d8fw; fC += d8c;
+            if (fFh >= p.a.FH) { fFh -= p.a.FH; ++fFw; }
+            if (fFw >= p.a.FW) { fFw -= p.a.FW; ++fC; }
+          }
+        } else if (kAMode == OP_WGATHER) {
+          FastPix rp = fast_pix(p.a, r0 + 4 * kmChunk, p.R);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            issue_shifted(p.a.ptr, p.a.H, p.a.W, rp, tapS[j], tapDw[j], tapCoff[j], tapOk[j], R.a0[j], R.a1[j]);
+        } else {
+          int const r = r0 + 4 * kmChunk;
+          long long boff = 0;
+          if (p.a.P) { int nb = r / p.a.P; boff = (long long)nb * p.a.bs - (long long)nb * p.a.P; }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) R.a0[j] = issue_row4(aRow[j] + boff, r, p.R, aRowOk[j]);
+        }
+        if (!bBulk) {
+          int const r = r0 + 4 * kmChunk;
+          long long boff = 0;
+          if (p.b.P) { int nb = r / p.b.P; boff = (long long)nb * p.b.bs - (long long)nb * p.b.P; }
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (kmRow + 32 * j < BN) R.b0[j] = issue_row4(bRow[j] + boff, r, p.R, bRowOk[j]);
+        }
+      };
+      auto commit = [&](int it, Raw& R) -> bool {
+        int const s = it % p.stages;
+        if (!mbar_wait(smem_u32(&emptyBar[s]), (uint32_t)(((it / p.stages) & 1) ^ 1))) { atomicExch(p.status, 1); return false; }
+        uint8_t* base = smem + (size_t)s * stageBytes;
+        uint8_t* aHi = base;
+        uint8_t* aLo = base + aTileBytes;
+        uint8_t* bHi = base + (kSplit ? 2u : 1u) * aTileBytes;
+        uint8_t* bLo = bHi + bTileBytes;
+        if (bBulk && t == 0) {
+          // the whole pre-split B tile (hi then lo) of this k-block in one bulk copy
+          mbar_expect_tx(smem_u32(&fullBar[s]), bBytes);
+          bulk_copy_g2s(smem_u32(bHi), p.bTiles + ((size_t)blockIdx.y * p.numKb + (size_t)(kbBeg + it)) * (bBytes / 4), bBytes,
+                        smem_u32(&fullBar[s]));
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float v[4];
+          if (kAMode == OP_IM2COL) funnel(R.a0[j], R.a1[j], R.ao[j], v);
+          else if (kAMode == OP_WGATHER) funnel(R.a0[j], R.a1[j], tapS[j] & 3, v);
+          else { v[0] = R.a0[j].x; v[1] = R.a0[j].y; v[2] = R.a0[j].z; v[3] = R.a0[j].w; }
+          uint32_t off = kAMN ? mnmajor_off(mnChunk, mnK + 8 * j, BM / 32) : kmajor_off(kmRow + 32 * j, kmChunk);
+          store_chunk<kSplit>(aHi, aLo, off, v);
+        }
+        if (!bBulk) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (kmRow + 32 * j < BN) {
+              float v[4] = {R.b0[j].x, R.b0[j].y, R.b0[j].z, R.b0[j].w};
+              store_chunk<kSplit>(bHi, bLo, kmajor_off(kmRow + 32 * j, kmChunk), v);
+            }
+        }
+        fence_async_smem();
+        mbar_arrive(smem_u32(&fullBar[s]));
+        return true;
+      };
+      Raw ra, rb;
+      if (numIter > 0) issue(0, ra);
+      for (int it = 0; it < numIter; it += 2) {
+        if (it + 1 < numIter) issue(it + 1, rb);
+        if (!commit(it, ra)) break;
+        if (it + 1 >= numIter) break;
+        if (it + 2 < numIter) issue(it + 2, ra);
+        if (!commit(it + 1, rb)) break;
+      }
+    } else {
     bool ok = true;
     for (int it = 0; it < numIter && ok; ++it) {
       int s = it % p.stages;
       int const r0 = (kbBeg + it) * BK;
       float va[4][4], vb[4][4];
       // global loads first, so that all of them are in flight before the first use
+      if (kAMode == OP_IM2COL && aFast) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (kAMode == OP_IM2COL) load_im2col(p.a, px, r0 + mnK + 8 * j, p.R, va[j]);
-        else if (kAMode == OP_DENSE_MN) load_dense_mn(p.a, m0 + 4 * mnChunk, r0 + mnK + 8 * j, p.R, va[j]);
-        else if (kAMode == OP_WGATHER) load_wgather(p.a, tap[j], r0 + 4 * kmChunk, p.R, va[j]);
-        else load_dense_k(p.a, m0 + kmRow + 32 * j, r0 + 4 * kmChunk, p.R, va[j]);
+        for (int j = 0; j < 4; ++j) {
+          load_shifted(p.a.ptr, p.a.H, p.a.W, fpx, fFh * p.a.dy - p.a.pt, fFw * p.a.dx - p.a.pl, fC * HW, fR < p.R, va[j]);
+          fR += 8; fFh += d8fh; fFw += d8fw; fC += d8c;
+          if (fFh >= p.a.FH) { fFh -= p.a.FH; ++fFw; }
+          if (fFw >= p.a.FW) { fFw -= p.a.FW; ++fC; }
+        }
+      } else if (kAMode == OP_WGATHER && aFast) {
+        FastPix rp = fast_pix(p.a, r0 + 4 * kmChunk, p.R);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) load_shifted(p.a.ptr, p.a.H, p.a.W, rp, tapS[j], tapDw[j], tapCoff[j], tapOk[j], va[j]);
+      } else if (kAMode == OP_DENSE_K && p.a.vec) {
+        int const r = r0 + 4 * kmChunk;
+        long long boff = 0;
+        if (p.a.P) { int nb = r / p.a.P; boff = (long long)nb * p.a.bs - (long long)nb * p.a.P; }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) load_row4(aRow[j] + boff, r, p.R, aRowOk[j], va[j]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (kAMode == OP_IM2COL) load_im2col(p.a, px, r0 + mnK + 8 * j, p.R, va[j]);
+          else if (kAMode == OP_DENSE_MN) load_dense_mn(p.a, m0 + 4 * mnChunk, r0 + mnK + 8 * j, p.R, va[j]);
+          else if (kAMode == OP_WGATHER) load_wgather(p.a, tap[j], r0 + 4 * kmChunk, p.R, va[j]);
+          else load_dense_k(p.a, m0 + kmRow + 32 * j, r0 + 4 * kmChunk, p.R, va[j]);
+        }
       }
+      if (kBMode == OP_DENSE_K && p.b.vec) {
+        int const r = r0 + 4 * kmChunk;
+        long long boff = 0;
+        if (p.b.P) { int nb = r / p.b.P; boff = (long long)nb * p.b.bs - (long long)nb * p.b.P; }
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (kBMN) {
-          if (4 * mnChunk < BN) load_dense_mn(p.b, n0 + 4 * mnChunk, r0 + mnK + 8 * j, p.R, vb[j]);
-        } else {
-          if (kmRow + 32 * j < BN) load_dense_k(p.b, n0 + kmRow + 32 * j, r0 + 4 * kmChunk, p.R, vb[j]);
+        for (int j = 0; j < 4; ++j)
+          if (kmRow + 32 * j < BN) load_row4(bRow[j] + boff, r, p.R, bRowOk[j], vb[j]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (kBMN) {
+            if (4 * mnChunk < BN) load_dense_mn(p.b, n0 + 4 * mnChunk, r0 + mnK + 8 * j, p.R, vb[j]);
+          } else {
+            if (kmRow + 32 * j < BN) load_dense_k(p.b, n0 + kmRow + 32 * j, r0 + 4 * kmChunk, p.R, vb[j]);
+          }
         }
       }
       ok = mbar_wait(smem_u32(&emptyBar[s]), (uint32_t)(((it / p.stages) & 1) ^ 1));
@@ -478,6 +727,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
       }
       fence_async_smem();                     // generic-proxy writes -> visible to the tensor core's async proxy
       mbar_arrive(smem_u32(&fullBar[s]));
+    }
     }
   }
 
@@ -509,6 +759,56 @@ __global__ void flip_filters_kernel(float* __restrict__ ft, float const* __restr
     int k = (int)(t % K); int c = (int)(t / K);
     ft[o] = f[(FH - 1 - fh) + (size_t)FH * ((FW - 1 - fw) + (size_t)FW * (c + (size_t)C * k))];
   }
+}
+
+// The B operand of fprop / dgrad is the filter bank: small, and the same for every CTA.  It is split
+// into hi / lo once and laid out as ready-made shared-memory tile images -- for n-tile t and k-block
+// kb: [hi tile BN x 32][lo tile BN x 32], K-major with the 128-byte swizzle -- so that a producer
+// fetches a whole stage of B with one bulk copy.
+// mode 0: B(n, r) = F[n*R + r].  mode 1 (data gradient of a stride-1 convolution): n = channel c,
+// r = fh' + FH*(fw' + FW*k), B = F[FH-1-fh', FW-1-fw', c, k].
+template <bool kSplit>
+__global__ void prep_b_tiles_kernel(float* __restrict__ out, float const* __restrict__ f, int N, int R, int BN, int numKb,
+                                    int mode, int FH, int FW, int C, int K)
+{
+  size_t const Rp = (size_t)numKb * 32;
+  size_t const total = (size_t)((N + BN - 1) / BN) * BN * Rp;
+  size_t const step = (size_t)gridDim.x * blockDim.x;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += step) {
+    int const r = (int)(idx % Rp), n = (int)(idx / Rp);
+    float val = 0.f;
+    if (n < N && r < R) {
+      if (mode == 0) val = f[(size_t)n * R + r];
+      else {
+        int fh = r % FH, t = r / FH, fw = t % FW, k = t / FW;
+        val = f[(FH - 1 - fh) + (size_t)FH * ((FW - 1 - fw) + (size_t)FW * (n + (size_t)C * k))];
+      }
+    }
+    int const tile = n / BN, row = n % BN, kb = r >> 5, kk = r & 31;
+    size_t const base = ((size_t)tile * numKb + kb) * (kSplit ? 2 : 1) * (size_t)BN * 32;
+    size_t const off = (size_t)row * 32 + ((((kk >> 2) ^ (row & 7)) << 2) | (kk & 3));
+    if (kSplit) {
+      float hi = tf32_hi(val);
+      out[base + off] = hi;
+      out[base + (size_t)BN * 32 + off] = val - hi;
+    } else {
+      out[base + off] = val;
+    }
+  }
+}
+
+// Builds the tile images in the context's scratch; returns nullptr (error set) on failure.
+float const* prep_b_tiles(vlb_ctx* ctx, float const* f, int N, int R, int BN, int numKb, int mode, vlb::ConvGeom const& g)
+{
+  bool split3 = ctx->precision == VLB_PRECISION_3XTF32;
+  size_t total = (size_t)vlb::ceil_div(N, BN) * BN * (size_t)numKb * 32;
+  float* tiles = (float*)vlb::workspace(ctx, sizeof(float) * total * (split3 ? 2 : 1));
+  if (!tiles) return nullptr;
+  unsigned grid = vlb::grid_for(total, 256, ctx->smCount * 8);
+  if (split3) prep_b_tiles_kernel<true><<<grid, 256, 0, ctx->stream>>>(tiles, f, N, R, BN, numKb, mode, g.FH, g.FW, g.C, g.K);
+  else        prep_b_tiles_kernel<false><<<grid, 256, 0, ctx->stream>>>(tiles, f, N, R, BN, numKb, mode, g.FH, g.FW, g.C, g.K);
+  VLB_LAUNCHED(ctx, 1);
+  return tiles;
 }
 
 // ------------------------------------------------------------------ host side
@@ -570,6 +870,7 @@ void conv_operand(Operand& o, ConvGeom const& g, float const* ptr, int channels)
   o.sy = g.sy; o.sx = g.sx; o.pt = g.pt; o.pl = g.pl; o.dy = g.dy; o.dx = g.dx;
   o.imgStride = (long long)g.H * g.W * channels;
   o.ld = 0; o.bs = 0; o.P = 0; o.vec = 0;
+  o.fast = (g.sy == 1 && g.sx == 1 && g.H % 4 == 0 && g.Ho % 4 == 0 && aligned16(ptr)) ? 1 : 0;
 }
 
 bool fits32(ConvGeom const& g)
@@ -607,6 +908,7 @@ int conv_fprop_tc(vlb_ctx* ctx, ConvGeom const& g, float* Y, float outMult, floa
     p.kbPerSplit = ceil_div(p.numKb, splits);
     splits = ceil_div(p.numKb, p.kbPerSplit);
     p.e = Epilogue{}; p.e.ldd = g.K;
+    p.pipelined = (p.a.vec && p.b.vec) ? 1 : 0;
     if (splits == 1) {
       p.e.out = Y; p.e.bias = b;
       return launch<OP_DENSE_K, OP_DENSE_K, EPI_PLAIN>(ctx, p, 1, "fc_fprop_tc");
@@ -630,6 +932,11 @@ int conv_fprop_tc(vlb_ctx* ctx, ConvGeom const& g, float* Y, float outMult, floa
   p.BN = pick_bn(p.N);
   p.numKb = ceil_div(p.R, BK); p.kbPerSplit = p.numKb;
   p.e = Epilogue{}; p.e.out = Y; p.e.bias = b; p.e.inMult = inMult; p.e.outMult = outMult; p.e.P = g.Ho * g.Wo; p.e.Ktot = g.K;
+  if (p.a.fast) {
+    p.bTiles = prep_b_tiles(ctx, F, g.K, V, p.BN, p.numKb, 0, g);
+    if (!p.bTiles) return ctx->lastError;
+    p.pipelined = 1;
+  }
   return launch<OP_IM2COL, OP_DENSE_K, EPI_CONV>(ctx, p, 1, "conv_fprop_tc");
 }
 
@@ -650,11 +957,6 @@ int conv_dgrad_tc(vlb_ctx* ctx, ConvGeom const& g, float* dX, float const* F, fl
   }
   if (g.sy != 1 || g.sx != 1) return VLB_Unsupported;
   // dX = conv(dY, flipped and transposed filters) with padding (F-1)*dilate - pad
-  size_t nF = (size_t)g.FH * g.FW * g.FC * g.K;
-  float* ft = (float*)workspace(ctx, sizeof(float) * nF);
-  if (!ft) return ctx->lastError;
-  flip_filters_kernel<<<grid_for(nF, 256, ctx->smCount * 8), 256, 0, ctx->stream>>>(ft, F, g.FH, g.FW, g.C, g.K);
-  VLB_LAUNCHED(ctx, 1);
   ConvGeom t = g;
   t.H = g.Ho; t.W = g.Wo; t.C = g.K; t.FC = g.K; t.K = g.C; t.Ho = g.H; t.Wo = g.W;
   t.pt = (g.FH - 1) * g.dy - g.pt; t.pl = (g.FW - 1) * g.dx - g.pl;
@@ -663,9 +965,22 @@ int conv_dgrad_tc(vlb_ctx* ctx, ConvGeom const& g, float* dX, float const* F, fl
   p.M = (int)M; p.N = g.C; p.R = V;
   conv_operand(p.a, t, dY, g.K);
   p.a.rows = p.M;
-  p.b = Operand{}; p.b.ptr = ft; p.b.ld = V; p.b.rows = g.C; p.b.vec = (V % 4 == 0);
   p.BN = pick_bn(p.N);
   p.numKb = ceil_div(p.R, BK); p.kbPerSplit = p.numKb;
+  p.b = Operand{}; p.b.ld = V; p.b.rows = g.C;
+  if (p.a.fast) {
+    p.bTiles = prep_b_tiles(ctx, F, g.C, V, p.BN, p.numKb, 1, g);
+    if (!p.bTiles) return ctx->lastError;
+    p.b.ptr = p.bTiles;          // not read by the pipelined producers
+    p.pipelined = 1;
+  } else {
+    size_t nF = (size_t)g.FH * g.FW * g.FC * g.K;
+    float* ft = (float*)workspace(ctx, sizeof(float) * nF);
+    if (!ft) return ctx->lastError;
+    flip_filters_kernel<<<grid_for(nF, 256, ctx->smCount * 8), 256, 0, ctx->stream>>>(ft, F, g.FH, g.FW, g.C, g.K);
+    VLB_LAUNCHED(ctx, 1);
+    p.b.ptr = ft; p.b.vec = (V % 4 == 0);
+  }
   p.e = Epilogue{}; p.e.out = dX; p.e.inMult = 1.f; p.e.P = g.H * g.W; p.e.Ktot = g.C;
   return launch<OP_IM2COL, OP_DENSE_K, EPI_CONV>(ctx, p, 1, "conv_dgrad_tc");
 }
@@ -694,6 +1009,7 @@ int conv_wgrad_tc(vlb_ctx* ctx, ConvGeom const& g, float* dF, float* db, float c
   int const P = g.Ho * g.Wo;
   p.b = Operand{}; p.b.ptr = dY; p.b.ld = P; p.b.bs = (long long)P * g.K; p.b.P = P; p.b.rows = g.K;
   p.b.vec = (P % 4 == 0) && aligned16(dY);
+  p.pipelined = (p.a.fast && p.b.vec) ? 1 : 0;
   p.BN = pick_bn(p.N);
   p.numKb = ceil_div(p.R, BK);
   int tiles = ceil_div(p.M, BM) * ceil_div(p.N, p.BN);

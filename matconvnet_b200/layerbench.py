@@ -1,0 +1,134 @@
+"""Per-layer timing of the hot-path kernels through the C ABI.
+
+    python -m matconvnet_b200.layerbench [--net vgg16] [--batch 64] [--precision 3xtf32] [--layers conv3_1,fc6]
+    python -m matconvnet_b200.layerbench --kind bnorm|pool|roipool|sampler
+
+Each row is one block of the network at the given batch: forward, data-gradient and
+filter-gradient times from CUDA events on the launching stream (median of --iters after warm-up, the
+L2 flushed between iterations by writing a 256 MB buffer), and the algorithmic rate they imply:
+2*M*N*K flops for contractions, the compulsory bytes for the bandwidth-bound blocks.
+"""
+import argparse
+import json
+
+import numpy as np
+import torch
+
+from . import mat, nn
+
+VGG = [("conv1_1", 224, 3, 64, 3, 1), ("conv1_2", 224, 64, 64, 3, 1), ("conv2_1", 112, 64, 128, 3, 1),
+       ("conv2_2", 112, 128, 128, 3, 1), ("conv3_1", 56, 128, 256, 3, 1), ("conv3_2", 56, 256, 256, 3, 1),
+       ("conv4_1", 28, 256, 512, 3, 1), ("conv4_2", 28, 512, 512, 3, 1), ("conv5_1", 14, 512, 512, 3, 1),
+       ("fc6", 7, 512, 4096, 7, 0), ("fc7", 1, 4096, 4096, 1, 0), ("fc8", 1, 4096, 1000, 1, 0)]
+RESNET = [("res_1x1_a", 28, 512, 128, 1, 0), ("res_3x3", 28, 128, 128, 3, 1), ("res_1x1_b", 28, 128, 512, 1, 0)]
+
+
+def timed(fn, iters, flush):
+    times = []
+    for it in range(iters + 2):
+        if flush is not None:
+            flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        if it >= 2:
+            times.append(e0.elapsed_time(e1))
+    return float(np.median(times))
+
+
+def conv_rows(layers, batch, iters, flush, which):
+    rows = []
+    for name, hw, cin, cout, fs, pad in layers:
+        if which and name not in which:
+            continue
+        x = mat.as_mat(torch.randn(hw, hw, cin, batch, device="cuda"))
+        f = mat.as_mat(torch.randn(fs, fs, cin, cout, device="cuda") * (2.0 / (fs * fs * cin)) ** 0.5)
+        b = mat.zeros((1, cout))
+        y = nn.vl_nnconv(x, f, b, pad=pad)
+        dy = mat.as_mat(torch.randn(*y.shape, device="cuda"))
+        flops = 2.0 * y.shape[0] * y.shape[1] * batch * cout * fs * fs * cin
+        t_f = timed(lambda: nn.vl_nnconv(x, f, b, pad=pad), iters, flush)
+        t_d = timed(lambda: nn.vl_nnconv(x, f, b, dy, pad=pad, no_der_filters=True, no_der_biases=True), iters, flush)
+        t_w = timed(lambda: nn.vl_nnconv(x, f, b, dy, pad=pad, no_der_data=True), iters, flush)
+        rows.append({"layer": name, "gflop": flops / 1e9, "fprop_ms": t_f, "dgrad_ms": t_d, "wgrad_dbias_ms": t_w,
+                     "fprop_tflops": flops / t_f / 1e9, "dgrad_tflops": flops / t_d / 1e9,
+                     "wgrad_tflops": flops / t_w / 1e9})
+    return rows
+
+
+def bandwidth_rows(kind, iters, flush):
+    rows = []
+    if kind == "bnorm":
+        for shape in [(28, 28, 128, 64), (28, 28, 512, 64), (56, 56, 64, 64)]:
+            x, dy = mat.as_mat(torch.randn(*shape, device="cuda")), mat.as_mat(torch.randn(*shape, device="cuda"))
+            g, b = mat.as_mat(torch.rand(shape[2], 1, device="cuda") + 0.5), mat.zeros((shape[2], 1))
+            n = float(np.prod(shape))
+            t_b = timed(lambda: nn.vl_nnbnorm(x, g, b, dy, epsilon=1e-5), iters, flush)
+            t_f = timed(lambda: nn.vl_nnbnorm(x, g, b, epsilon=1e-5), iters, flush)
+            rows.append({"block": "bnorm %s" % (shape,), "bwd_ms": t_b, "bwd_GBs_20B": 20 * n / t_b / 1e6,
+                         "bwd_GBs_12B": 12 * n / t_b / 1e6, "fwd_ms": t_f, "fwd_GBs_16B": 16 * n / t_f / 1e6})
+    elif kind == "pool":
+        for hw, c in [(224, 64), (112, 128), (56, 256), (28, 512), (14, 512)]:
+            x = mat.as_mat(torch.randn(hw, hw, c, 64, device="cuda"))
+            y = nn.vl_nnpool(x, (2, 2), stride=2)
+            dy = mat.as_mat(torch.randn(*y.shape, device="cuda"))
+            nin, nout = float(x.numel()), float(y.numel())
+            t_f = timed(lambda: nn.vl_nnpool(x, (2, 2), stride=2), iters, flush)
+            t_b = timed(lambda: nn.vl_nnpool(x, (2, 2), dy, stride=2), iters, flush)
+            rows.append({"block": "maxpool2x2 %dx%dx%dx64" % (hw, hw, c), "fwd_ms": t_f, "fwd_GBs": 4 * (nin + nout) / t_f / 1e6,
+                         "bwd_ms": t_b, "bwd_GBs": 4 * (2 * nin + nout) / t_b / 1e6})
+    elif kind == "roipool":
+        g = torch.Generator(device="cuda").manual_seed(0)
+        H, W, Cc, N, K = 38, 50, 512, 2, 256
+        x = mat.as_mat(torch.randn(H, W, Cc, N, device="cuda", generator=g))
+        u1 = torch.rand(K, device="cuda", generator=g) * (W - 3) + 1
+        v1 = torch.rand(K, device="cuda", generator=g) * (H - 3) + 1
+        u2 = torch.minimum(u1 + 2 + torch.rand(K, device="cuda", generator=g) * W, torch.tensor(float(W), device="cuda"))
+        v2 = torch.minimum(v1 + 2 + torch.rand(K, device="cuda", generator=g) * H, torch.tensor(float(H), device="cuda"))
+        rois = mat.as_mat(torch.stack([torch.arange(K, device="cuda") % N + 1.0, u1, v1, u2, v2]))
+        y = nn.vl_nnroipool(x, rois, subdivisions=(7, 7))
+        dy = mat.as_mat(torch.randn(*y.shape, device="cuda"))
+        t_f = timed(lambda: nn.vl_nnroipool(x, rois, subdivisions=(7, 7)), iters, flush)
+        t_b = timed(lambda: nn.vl_nnroipool(x, rois, dy, subdivisions=(7, 7)), iters, flush)
+        nbytes = 4.0 * (2 * x.numel() + y.numel())
+        rows.append({"block": "roipool 38x50x512x2, 256 rois, 7x7", "fwd_ms": t_f, "bwd_ms": t_b, "bwd_GBs": nbytes / t_b / 1e6})
+    elif kind == "sampler":
+        x = mat.as_mat(torch.randn(64, 64, 32, 256, device="cuda"))
+        grid = mat.as_mat(torch.rand(2, 64, 64, 256, device="cuda") * 2 - 1)
+        dy = mat.as_mat(torch.randn(64, 64, 32, 256, device="cuda"))
+        t_f = timed(lambda: nn.vl_nnbilinearsampler(x, grid), iters, flush)
+        t_b = timed(lambda: nn.vl_nnbilinearsampler(x, grid, dy), iters, flush)
+        nbytes = 4.0 * (3 * x.numel() + 2 * grid.numel())
+        rows.append({"block": "sampler 64x64x32x256", "fwd_ms": t_f, "bwd_ms": t_b, "bwd_GBs": nbytes / t_b / 1e6})
+    return rows
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--net", default="vgg16", choices=["vgg16", "resnet"])
+    ap.add_argument("--kind", default="conv", choices=["conv", "bnorm", "pool", "roipool", "sampler"])
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--precision", default="3xtf32", choices=["3xtf32", "tf32", "fp32"])
+    ap.add_argument("--layers", default="")
+    ap.add_argument("--no-flush", action="store_true")
+    args = ap.parse_args()
+    torch.cuda.set_device(0)
+    ctx = nn.default_context()
+    ctx.set_precision({"3xtf32": 0, "tf32": 1, "fp32": 2}[args.precision])
+    ctx.reserve_workspace(1 << 30)
+    flush = None if args.no_flush else torch.empty(64 << 20, device="cuda")
+    if args.kind == "conv":
+        which = [s for s in args.layers.split(",") if s]
+        rows = conv_rows(VGG if args.net == "vgg16" else RESNET, args.batch, args.iters, flush, which)
+    else:
+        rows = bandwidth_rows(args.kind, args.iters, flush)
+    ctx.device_status()
+    for r in rows:
+        print(json.dumps({k: (round(v, 3) if isinstance(v, float) else v) for k, v in r.items()}))
+
+
+if __name__ == "__main__":
+    main()
