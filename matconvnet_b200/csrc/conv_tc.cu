@@ -8,7 +8,7 @@
 //               thread) and store to global memory, coalesced along m;
 //   warp  4     allocates TMEM and issues tcgen05.mma (kind::tf32, cta_group::1) from one
 //               lane; tcgen05.commit releases a stage / publishes the accumulator;
-//   warps 5-12  producers: gather the operand tiles from the MATLAB-order tensors
+//   warps 5-20  producers: gather the operand tiles from the MATLAB-order tensors
 //               (no patch matrix: the reference writes one per image, bits/nnconv.cu:109-117),
 //               split every value into a TF32 "hi" part and an exactly representable
 //               remainder "lo", and write both as 128-byte-swizzled UMMA tiles.
@@ -37,9 +37,12 @@ using vlb::ConvGeom;
 constexpr int BM = 128;          // output rows per CTA (TMEM lanes)
 constexpr int BK = 32;           // reduction elements per stage (one 128-byte swizzle row)
 constexpr int kEpilogueWarps = 4;
-constexpr int kProducerWarps = 8;
+constexpr int kProducerWarps = 16;
 constexpr int kProducerThreads = kProducerWarps * 32;
-constexpr int kThreads = (kEpilogueWarps + 1 + kProducerWarps) * 32;   // 416
+constexpr int kThreads = (kEpilogueWarps + 1 + kProducerWarps) * 32;   // 672
+constexpr int CH = (BM * 8) / kProducerThreads;   // 16-byte chunks per producer thread per 128 x 32 operand tile (2)
+constexpr int KSTEP = 32 / CH;                    // MN-major tiles: k rows between a thread's consecutive chunks
+constexpr int RSTEP = BM / CH;                    // K-major tiles: rows between a thread's consecutive chunks
 constexpr int kMaxStages = 8;
 constexpr long long kWaitCycles = 2000000000LL;   // bound on any single barrier wait
 
@@ -349,10 +352,10 @@ __device__ __forceinline__ void load_row4(float const* __restrict__ p, int r, in
 // aligned 128-bit words per chunk until the data is used (the funnel shift happens at store time).
 template <int kAMode, int kBMode>
 struct RawStage {
-  float4 a0[4];
-  float4 a1[4];     // second aligned word of a shifted window (IM2COL, WGATHER); unused members cost no registers
-  float4 b0[4];     // B rows when B is gathered by the threads rather than bulk-copied
-  int ao[4];        // funnel shift per chunk (IM2COL: depends on the tap of that k)
+  float4 a0[CH];
+  float4 a1[CH];     // second aligned word of a shifted window (IM2COL, WGATHER); unused members cost no registers
+  float4 b0[CH];     // B rows when B is gathered by the threads rather than bulk-copied
+  int ao[CH];        // funnel shift per chunk (IM2COL: depends on the tap of that k)
 };
 
 __device__ __forceinline__ void funnel(float4 c0, float4 c1, int o, float (&v)[4])
@@ -528,25 +531,25 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
     tc_fence_before();
   } else {
     // ============================== producers ==============================
-    int const t = threadIdx.x - (kEpilogueWarps + 1) * 32;      // 0..255
-    // MN-major tiles: chunk column t % 32, k rows t / 32 + 8 j.  K-major tiles: chunk t % 8, rows t / 8 + 32 j.
+    int const t = threadIdx.x - (kEpilogueWarps + 1) * 32;      // 0..kProducerThreads-1
+    // MN-major tiles: chunk column t % 32, k rows t / 32 + KSTEP j.  K-major tiles: chunk t % 8, rows t / 8 + RSTEP j.
     int const mnChunk = t & 31, mnK = t >> 5, kmChunk = t & 7, kmRow = t >> 3;
     bool const aFast = p.a.fast != 0;
     PixCtx px[4];
-    TapCtx tap[4];
-    // fast IM2COL: this thread's four pixels, and its reduction index (fh,fw,c), which advances by 8 per step
+    TapCtx tap[CH];
+    // fast IM2COL: this thread's four pixels, and its reduction index (fh,fw,c), which advances by KSTEP per step
     FastPix fpx = {0, 0, 0, false};
     int fFh = 0, fFw = 0, fC = 0, fR = 0, d8fh = 0, d8fw = 0, d8c = 0;
     // fast WGATHER: this thread's four filter taps
-    int tapS[4], tapDw[4], tapCoff[4];
-    bool tapOk[4];
+    int tapS[CH], tapDw[CH], tapCoff[CH];
+    bool tapOk[CH];
     int const HW = p.a.H * p.a.W;
     if (kAMode == OP_IM2COL) {
       if (aFast) {
         fpx = fast_pix(p.a, m0 + 4 * mnChunk, p.a.rows);
         fR = kbBeg * BK + mnK;
         fFh = fR % p.a.FH; int q = fR / p.a.FH; fFw = q % p.a.FW; fC = q / p.a.FW;
-        d8fh = 8 % p.a.FH; q = 8 / p.a.FH; d8fw = q % p.a.FW; d8c = q / p.a.FW;
+        d8fh = KSTEP % p.a.FH; q = KSTEP / p.a.FH; d8fw = q % p.a.FW; d8c = q / p.a.FW;
       } else {
 #pragma unroll
         for (int e = 0; e < 4; ++e) px[e] = pix_ctx(p.a, m0 + 4 * mnChunk + e);
@@ -554,21 +557,21 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
     }
     if (kAMode == OP_WGATHER) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        tap[j] = tap_ctx(p.a, m0 + kmRow + 32 * j);
+      for (int j = 0; j < CH; ++j) {
+        tap[j] = tap_ctx(p.a, m0 + kmRow + RSTEP * j);
         tapS[j] = tap[j].dh; tapDw[j] = tap[j].dw; tapCoff[j] = (int)tap[j].coff; tapOk[j] = tap[j].valid;
       }
     }
     // reduction-contiguous dense operands: row pointers are fixed for the thread
-    float const* aRow[4];
-    float const* bRow[4];
-    bool aRowOk[4], bRowOk[4];
+    float const* aRow[CH];
+    float const* bRow[CH];
+    bool aRowOk[CH], bRowOk[CH];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      int ia = m0 + kmRow + 32 * j, ib = n0 + kmRow + 32 * j;
+    for (int j = 0; j < CH; ++j) {
+      int ia = m0 + kmRow + RSTEP * j, ib = n0 + kmRow + RSTEP * j;
       aRowOk[j] = (kAMode == OP_DENSE_K) && ia < p.a.rows;
       aRow[j] = p.a.ptr + (aRowOk[j] ? (long long)ia * p.a.ld : 0);
-      bRowOk[j] = (kBMode == OP_DENSE_K) && ib < p.b.rows && kmRow + 32 * j < BN;
+      bRowOk[j] = (kBMode == OP_DENSE_K) && ib < p.b.rows && kmRow + RSTEP * j < BN;
       bRow[j] = p.b.ptr + (bRowOk[j] ? (long long)ib * p.b.ld : 0);
     }
     if (p.pipelined && kAMode != OP_DENSE_MN && kBMode == OP_DENSE_K) {
@@ -581,33 +584,33 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
         int const r0 = (kbBeg + it) * BK;
         if (kAMode == OP_IM2COL) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
+          for (int j = 0; j < CH; ++j) {
             int const sft = fFh * p.a.dy - p.a.pt;
             R.ao[j] = sft & 3;
             issue_shifted(p.a.ptr, p.a.H, p.a.W, fpx, sft, fFw * p.a.dx - p.a.pl, fC * HW, fR < p.R, R.a0[j], R.a1[j]);
-            fR += 8; fFh += d8fh; fFw += d8fw; fC += d8c;
+            fR += KSTEP; fFh += d8fh; fFw += d8fw; fC += d8c;
             if (fFh >= p.a.FH) { fFh -= p.a.FH; ++fFw; }
             if (fFw >= p.a.FW) { fFw -= p.a.FW; ++fC; }
           }
         } else if (kAMode == OP_WGATHER) {
           FastPix rp = fast_pix(p.a, r0 + 4 * kmChunk, p.R);
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
+          for (int j = 0; j < CH; ++j)
             issue_shifted(p.a.ptr, p.a.H, p.a.W, rp, tapS[j], tapDw[j], tapCoff[j], tapOk[j], R.a0[j], R.a1[j]);
         } else {
           int const r = r0 + 4 * kmChunk;
           long long boff = 0;
           if (p.a.P) { int nb = r / p.a.P; boff = (long long)nb * p.a.bs - (long long)nb * p.a.P; }
 #pragma unroll
-          for (int j = 0; j < 4; ++j) R.a0[j] = issue_row4(aRow[j] + boff, r, p.R, aRowOk[j]);
+          for (int j = 0; j < CH; ++j) R.a0[j] = issue_row4(aRow[j] + boff, r, p.R, aRowOk[j]);
         }
         if (!bBulk) {
           int const r = r0 + 4 * kmChunk;
           long long boff = 0;
           if (p.b.P) { int nb = r / p.b.P; boff = (long long)nb * p.b.bs - (long long)nb * p.b.P; }
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            if (kmRow + 32 * j < BN) R.b0[j] = issue_row4(bRow[j] + boff, r, p.R, bRowOk[j]);
+          for (int j = 0; j < CH; ++j)
+            if (kmRow + RSTEP * j < BN) R.b0[j] = issue_row4(bRow[j] + boff, r, p.R, bRowOk[j]);
         }
       };
       auto commit = [&](int it, Raw& R) -> bool {
@@ -625,20 +628,20 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
                         smem_u32(&fullBar[s]));
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < CH; ++j) {
           float v[4];
           if (kAMode == OP_IM2COL) funnel(R.a0[j], R.a1[j], R.ao[j], v);
           else if (kAMode == OP_WGATHER) funnel(R.a0[j], R.a1[j], tapS[j] & 3, v);
           else { v[0] = R.a0[j].x; v[1] = R.a0[j].y; v[2] = R.a0[j].z; v[3] = R.a0[j].w; }
-          uint32_t off = kAMN ? mnmajor_off(mnChunk, mnK + 8 * j, BM / 32) : kmajor_off(kmRow + 32 * j, kmChunk);
+          uint32_t off = kAMN ? mnmajor_off(mnChunk, mnK + KSTEP * j, BM / 32) : kmajor_off(kmRow + RSTEP * j, kmChunk);
           store_chunk<kSplit>(aHi, aLo, off, v);
         }
         if (!bBulk) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            if (kmRow + 32 * j < BN) {
+          for (int j = 0; j < CH; ++j)
+            if (kmRow + RSTEP * j < BN) {
               float v[4] = {R.b0[j].x, R.b0[j].y, R.b0[j].z, R.b0[j].w};
-              store_chunk<kSplit>(bHi, bLo, kmajor_off(kmRow + 32 * j, kmChunk), v);
+              store_chunk<kSplit>(bHi, bLo, kmajor_off(kmRow + RSTEP * j, kmChunk), v);
             }
         }
         fence_async_smem();
@@ -659,33 +662,33 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
     for (int it = 0; it < numIter && ok; ++it) {
       int s = it % p.stages;
       int const r0 = (kbBeg + it) * BK;
-      float va[4][4], vb[4][4];
+      float va[CH][4], vb[CH][4];
       // global loads first, so that all of them are in flight before the first use
       if (kAMode == OP_IM2COL && aFast) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < CH; ++j) {
           load_shifted(p.a.ptr, p.a.H, p.a.W, fpx, fFh * p.a.dy - p.a.pt, fFw * p.a.dx - p.a.pl, fC * HW, fR < p.R, va[j]);
-          fR += 8; fFh += d8fh; fFw += d8fw; fC += d8c;
+          fR += KSTEP; fFh += d8fh; fFw += d8fw; fC += d8c;
           if (fFh >= p.a.FH) { fFh -= p.a.FH; ++fFw; }
           if (fFw >= p.a.FW) { fFw -= p.a.FW; ++fC; }
         }
       } else if (kAMode == OP_WGATHER && aFast) {
         FastPix rp = fast_pix(p.a, r0 + 4 * kmChunk, p.R);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) load_shifted(p.a.ptr, p.a.H, p.a.W, rp, tapS[j], tapDw[j], tapCoff[j], tapOk[j], va[j]);
+        for (int j = 0; j < CH; ++j) load_shifted(p.a.ptr, p.a.H, p.a.W, rp, tapS[j], tapDw[j], tapCoff[j], tapOk[j], va[j]);
       } else if (kAMode == OP_DENSE_K && p.a.vec) {
         int const r = r0 + 4 * kmChunk;
         long long boff = 0;
         if (p.a.P) { int nb = r / p.a.P; boff = (long long)nb * p.a.bs - (long long)nb * p.a.P; }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) load_row4(aRow[j] + boff, r, p.R, aRowOk[j], va[j]);
+        for (int j = 0; j < CH; ++j) load_row4(aRow[j] + boff, r, p.R, aRowOk[j], va[j]);
       } else {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (kAMode == OP_IM2COL) load_im2col(p.a, px, r0 + mnK + 8 * j, p.R, va[j]);
-          else if (kAMode == OP_DENSE_MN) load_dense_mn(p.a, m0 + 4 * mnChunk, r0 + mnK + 8 * j, p.R, va[j]);
+        for (int j = 0; j < CH; ++j) {
+          if (kAMode == OP_IM2COL) load_im2col(p.a, px, r0 + mnK + KSTEP * j, p.R, va[j]);
+          else if (kAMode == OP_DENSE_MN) load_dense_mn(p.a, m0 + 4 * mnChunk, r0 + mnK + KSTEP * j, p.R, va[j]);
           else if (kAMode == OP_WGATHER) load_wgather(p.a, tap[j], r0 + 4 * kmChunk, p.R, va[j]);
-          else load_dense_k(p.a, m0 + kmRow + 32 * j, r0 + 4 * kmChunk, p.R, va[j]);
+          else load_dense_k(p.a, m0 + kmRow + RSTEP * j, r0 + 4 * kmChunk, p.R, va[j]);
         }
       }
       if (kBMode == OP_DENSE_K && p.b.vec) {
@@ -693,15 +696,15 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
         long long boff = 0;
         if (p.b.P) { int nb = r / p.b.P; boff = (long long)nb * p.b.bs - (long long)nb * p.b.P; }
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (kmRow + 32 * j < BN) load_row4(bRow[j] + boff, r, p.R, bRowOk[j], vb[j]);
+        for (int j = 0; j < CH; ++j)
+          if (kmRow + RSTEP * j < BN) load_row4(bRow[j] + boff, r, p.R, bRowOk[j], vb[j]);
       } else {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < CH; ++j) {
           if (kBMN) {
-            if (4 * mnChunk < BN) load_dense_mn(p.b, n0 + 4 * mnChunk, r0 + mnK + 8 * j, p.R, vb[j]);
+            if (4 * mnChunk < BN) load_dense_mn(p.b, n0 + 4 * mnChunk, r0 + mnK + KSTEP * j, p.R, vb[j]);
           } else {
-            if (kmRow + 32 * j < BN) load_dense_k(p.b, n0 + kmRow + 32 * j, r0 + 4 * kmChunk, p.R, vb[j]);
+            if (kmRow + RSTEP * j < BN) load_dense_k(p.b, n0 + kmRow + RSTEP * j, r0 + 4 * kmChunk, p.R, vb[j]);
           }
         }
       }
@@ -713,16 +716,16 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
       uint8_t* bHi = base + (kSplit ? 2u : 1u) * aTileBytes;
       uint8_t* bLo = bHi + bTileBytes;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        uint32_t off = kAMN ? mnmajor_off(mnChunk, mnK + 8 * j, BM / 32) : kmajor_off(kmRow + 32 * j, kmChunk);
+      for (int j = 0; j < CH; ++j) {
+        uint32_t off = kAMN ? mnmajor_off(mnChunk, mnK + KSTEP * j, BM / 32) : kmajor_off(kmRow + RSTEP * j, kmChunk);
         store_chunk<kSplit>(aHi, aLo, off, va[j]);
       }
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < CH; ++j) {
         if (kBMN) {
-          if (4 * mnChunk < BN) store_chunk<kSplit>(bHi, bLo, mnmajor_off(mnChunk, mnK + 8 * j, BN / 32), vb[j]);
+          if (4 * mnChunk < BN) store_chunk<kSplit>(bHi, bLo, mnmajor_off(mnChunk, mnK + KSTEP * j, BN / 32), vb[j]);
         } else {
-          if (kmRow + 32 * j < BN) store_chunk<kSplit>(bHi, bLo, kmajor_off(kmRow + 32 * j, kmChunk), vb[j]);
+          if (kmRow + RSTEP * j < BN) store_chunk<kSplit>(bHi, bLo, kmajor_off(kmRow + RSTEP * j, kmChunk), vb[j]);
         }
       }
       fence_async_smem();                     // generic-proxy writes -> visible to the tensor core's async proxy
@@ -856,7 +859,7 @@ int pick_splits(vlb_ctx* ctx, int tiles, int numKb, int minKbPerSplit)
 {
   int target = 2 * ctx->smCount;
   if (tiles >= target || numKb < 2 * minKbPerSplit) return 1;
-  int s = (target + tiles - 1) / tiles;
+  int s = target / tiles;           // tiles * s <= two full waves
   int maxS = numKb / minKbPerSplit;
   if (s > maxS) s = maxS;
   if (s > 512) s = 512;
