@@ -171,7 +171,7 @@ def main():
 
     ctx = nn.default_context()
     ctx.set_precision({"3xtf32": 0, "tf32": 1, "fp32": 2}[args.precision])
-    ctx.reserve_workspace(1 << 30)          # split-K partials and flipped filters; grown once, up front
+    ctx.reserve_workspace(3 << 30)          # operand tile images and split-K partials; grown once, up front
 
     net = models.vgg16(seed=0)              # identical replica on every rank
     B = args.batch

@@ -148,6 +148,15 @@ __device__ __forceinline__ void umma_tf32(uint32_t dTmem, uint64_t aDesc, uint64
 __device__ __forceinline__ void umma_commit(uint32_t bar)
 { asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory"); }
 
+__device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t (&r)[16])
+{
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16])
 {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
@@ -348,46 +357,35 @@ __device__ __forceinline__ void load_row4(float const* __restrict__ p, int r, in
 }
 
 // ------------------------------------------------------------------ pipelined producer
-// Register image of one stage's global loads for one producer thread.  Shifted gathers keep both
-// aligned 128-bit words per chunk until the data is used (the funnel shift happens at store time).
-template <int kAMode, int kBMode>
-struct RawStage {
-  float4 a0[CH];
-  float4 a1[CH];     // second aligned word of a shifted window (IM2COL, WGATHER); unused members cost no registers
-  float4 b0[CH];     // B rows when B is gathered by the threads rather than bulk-copied
-  int ao[CH];        // funnel shift per chunk (IM2COL: depends on the tap of that k)
-};
+constexpr int kPrefetch = 3;     // stages of global loads in flight per producer thread
 
-__device__ __forceinline__ void funnel(float4 c0, float4 c1, int o, float (&v)[4])
-{
-  bool const s2 = (o & 2) != 0, s1 = (o & 1) != 0;
-  float t0 = s2 ? c0.z : c0.x, t1 = s2 ? c0.w : c0.y, t2 = s2 ? c1.x : c0.z, t3 = s2 ? c1.y : c0.w, t4 = s2 ? c1.z : c1.x;
-  v[0] = s1 ? t1 : t0; v[1] = s1 ? t2 : t1; v[2] = s1 ? t3 : t2; v[3] = s1 ? t4 : t3;
-}
-
-// Issues the two aligned loads of a shifted four-row window (see load_shifted) without using them.
-__device__ __forceinline__ void issue_shifted(float const* __restrict__ ptr, int H, int W, FastPix const& px, int s, int dw,
-                                              int coff, bool on, float4& c0, float4& c1)
+// Four consecutive rows ho0+s .. ho0+s+3 of one input column, loaded straight into their final
+// registers.  The window straddles at most two aligned groups of four rows, each wholly inside the
+// image or wholly padding, so every load has a single predicate; the load widths follow the
+// alignment of the window start (s & 3): 128 | 32+64+32 | 64+64 | 32+64+32 bits.
+__device__ __forceinline__ void issue_window(float const* __restrict__ ptr, int H, int W, FastPix const& px, int s, int dw,
+                                             int coff, bool on, float4& v)
 {
   int const o = s & 3;
-  int const h0 = px.ho0 + s - o;
+  int const h0 = px.ho0 + s - o;            // first row of the aligned group that holds the window start
   int const w = px.wo + dw;
   bool const wok = on && px.valid && w >= 0 && w < W;
-  float const* a0 = ptr + (px.base + coff + dw * H + (s - o));
-  c0 = make_float4(0.f, 0.f, 0.f, 0.f); c1 = c0;
-  if (wok && h0 >= 0 && h0 < H) c0 = *reinterpret_cast<float4 const*>(a0);
-  if (wok && o != 0 && h0 + 4 >= 0 && h0 + 4 < H) c1 = *reinterpret_cast<float4 const*>(a0 + 4);
-}
-
-__device__ __forceinline__ float4 issue_row4(float const* __restrict__ p, int r, int R, bool ok)
-{
-  float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (!ok || r >= R) return t;
-  if (r + 3 < R) return *reinterpret_cast<float4 const*>(p + r);
-  t.x = p[r];
-  if (r + 1 < R) t.y = p[r + 1];
-  if (r + 2 < R) t.z = p[r + 2];
-  return t;
+  bool const g0 = wok && h0 >= 0 && h0 < H;
+  bool const g1 = wok && h0 + 4 >= 0 && h0 + 4 < H;
+  float const* a = ptr + (px.base + coff + dw * H + s);
+  v = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (o == 0) {
+    if (g0) v = *reinterpret_cast<float4 const*>(a);
+  } else if (o == 2) {
+    if (g0) { float2 t = *reinterpret_cast<float2 const*>(a); v.x = t.x; v.y = t.y; }
+    if (g1) { float2 t = *reinterpret_cast<float2 const*>(a + 2); v.z = t.x; v.w = t.y; }
+  } else {
+    // o == 1: rows 0..2 lie in the first group, row 3 in the second; o == 3: row 0 | rows 1..3
+    bool const gm = (o == 1) ? g0 : g1;
+    if (g0) v.x = a[0];
+    if (gm) { float2 t = *reinterpret_cast<float2 const*>(a + 1); v.y = t.x; v.z = t.y; }
+    if (g1) v.w = a[3];
+  }
 }
 
 // ------------------------------------------------------------------ the kernel
@@ -434,63 +432,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
   uint32_t const tmemAcc = tmemBase;
 
   if (warp < kEpilogueWarps) {
-    // ============================== epilogue ==============================
-    bool ok = mbar_wait(smem_u32(&accumBar), 0);
-    tc_fence_after();
-    if (!ok) { if (lane == 0) atomicExch(p.status, 3); }
-    else if (numIter > 0) {
-      int m = m0 + warp * 32 + lane;
-      long long rowBase = 0;
-      if (kEpi == EPI_CONV) { int pix = m % p.e.P, img = m / p.e.P; rowBase = (long long)img * p.e.Ktot * p.e.P + pix; }
-      else rowBase = m + (long long)split * p.e.splitStride;
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        uint32_t r[16];
-        uint32_t const laneBase = tmemAcc + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
-        tmem_ld16(laneBase, r);
-        if (kSplit) {
-          // sum the accumulator sets: all "small" parts first, then the "big" ones
-          int const used = min(numSets, numIter);
-          float sum[16];
-          uint32_t t[16];
-          tmem_ld16(laneBase + (uint32_t)BN, t);
-#pragma unroll
-          for (int j = 0; j < 16; ++j) sum[j] = __uint_as_float(t[j]);
-          for (int q = 1; q < used; ++q) {
-            tmem_ld16(laneBase + (uint32_t)(q * 2 * BN + BN), t);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) sum[j] += __uint_as_float(t[j]);
-          }
-          for (int q = 1; q < used; ++q) {
-            tmem_ld16(laneBase + (uint32_t)(q * 2 * BN), t);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) sum[j] += __uint_as_float(t[j]);
-          }
-#pragma unroll
-          for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(sum[j] + __uint_as_float(r[j]));
-        }
-        if (m < p.M) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            int n = n0 + c0 + j;
-            if (n < p.N) {
-              float acc = __uint_as_float(r[j]);
-              if (kEpi == EPI_CONV) {
-                float* dst = p.e.out + rowBase + (long long)n * p.e.P;
-                float o = p.e.inMult * acc;
-                if (p.e.bias) o += p.e.bias[n];
-                if (p.e.outMult != 0.f) o += p.e.outMult * *dst;
-                *dst = o;
-              } else {
-                float o = acc;
-                if (p.e.bias) o += p.e.bias[m];
-                p.e.out[rowBase + (long long)n * p.e.ldd] = o;
-              }
-            }
-          }
-        }
-      }
-    }
-    tc_fence_before();
+    // warps 0-3 take no part in the main loop; they join the epilogue below
   } else if (warp == kEpilogueWarps) {
     // ============================== MMA issue ==============================
     if (lane == 0) {
@@ -574,88 +516,62 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
       bRowOk[j] = (kBMode == OP_DENSE_K) && ib < p.b.rows && kmRow + RSTEP * j < BN;
       bRow[j] = p.b.ptr + (bRowOk[j] ? (long long)ib * p.b.ld : 0);
     }
-    if (p.pipelined && kAMode != OP_DENSE_MN && kBMode == OP_DENSE_K) {
-      // ---- pipelined: the loads of stage it+1 are issued before stage it is written to shared
-      // memory, so a full stage of global loads is always in flight per thread.
-      typedef RawStage<kAMode, kBMode> Raw;
-      bool const bBulk = p.bTiles != nullptr;
+    if (p.pipelined && p.bTiles != nullptr && (kAMode == OP_IM2COL || kAMode == OP_WGATHER)) {
+      // ---- pipelined: kPrefetch stages of this thread's global loads are in flight at any time; B
+      // arrives as a ready-made tile image through one bulk copy per stage.
       uint32_t const bBytes = (kSplit ? 2u : 1u) * bTileBytes;
-      auto issue = [&](int it, Raw& R) {
-        int const r0 = (kbBeg + it) * BK;
+      auto issue = [&](int it, float4 (&R)[CH]) {
         if (kAMode == OP_IM2COL) {
 #pragma unroll
           for (int j = 0; j < CH; ++j) {
-            int const sft = fFh * p.a.dy - p.a.pt;
-            R.ao[j] = sft & 3;
-            issue_shifted(p.a.ptr, p.a.H, p.a.W, fpx, sft, fFw * p.a.dx - p.a.pl, fC * HW, fR < p.R, R.a0[j], R.a1[j]);
+            issue_window(p.a.ptr, p.a.H, p.a.W, fpx, fFh * p.a.dy - p.a.pt, fFw * p.a.dx - p.a.pl, fC * HW, fR < p.R, R[j]);
             fR += KSTEP; fFh += d8fh; fFw += d8fw; fC += d8c;
             if (fFh >= p.a.FH) { fFh -= p.a.FH; ++fFw; }
             if (fFw >= p.a.FW) { fFw -= p.a.FW; ++fC; }
           }
-        } else if (kAMode == OP_WGATHER) {
-          FastPix rp = fast_pix(p.a, r0 + 4 * kmChunk, p.R);
-#pragma unroll
-          for (int j = 0; j < CH; ++j)
-            issue_shifted(p.a.ptr, p.a.H, p.a.W, rp, tapS[j], tapDw[j], tapCoff[j], tapOk[j], R.a0[j], R.a1[j]);
         } else {
-          int const r = r0 + 4 * kmChunk;
-          long long boff = 0;
-          if (p.a.P) { int nb = r / p.a.P; boff = (long long)nb * p.a.bs - (long long)nb * p.a.P; }
-#pragma unroll
-          for (int j = 0; j < CH; ++j) R.a0[j] = issue_row4(aRow[j] + boff, r, p.R, aRowOk[j]);
-        }
-        if (!bBulk) {
-          int const r = r0 + 4 * kmChunk;
-          long long boff = 0;
-          if (p.b.P) { int nb = r / p.b.P; boff = (long long)nb * p.b.bs - (long long)nb * p.b.P; }
+          FastPix rp = fast_pix(p.a, (kbBeg + it) * BK + 4 * kmChunk, p.R);
 #pragma unroll
           for (int j = 0; j < CH; ++j)
-            if (kmRow + RSTEP * j < BN) R.b0[j] = issue_row4(bRow[j] + boff, r, p.R, bRowOk[j]);
+            issue_window(p.a.ptr, p.a.H, p.a.W, rp, tapS[j], tapDw[j], tapCoff[j], tapOk[j], R[j]);
         }
       };
-      auto commit = [&](int it, Raw& R) -> bool {
+      auto commit = [&](int it, float4 (&R)[CH]) -> bool {
         int const s = it % p.stages;
         if (!mbar_wait(smem_u32(&emptyBar[s]), (uint32_t)(((it / p.stages) & 1) ^ 1))) { atomicExch(p.status, 1); return false; }
         uint8_t* base = smem + (size_t)s * stageBytes;
         uint8_t* aHi = base;
         uint8_t* aLo = base + aTileBytes;
         uint8_t* bHi = base + (kSplit ? 2u : 1u) * aTileBytes;
-        uint8_t* bLo = bHi + bTileBytes;
-        if (bBulk && t == 0) {
-          // the whole pre-split B tile (hi then lo) of this k-block in one bulk copy
+        if (t == 0) {
           mbar_expect_tx(smem_u32(&fullBar[s]), bBytes);
           bulk_copy_g2s(smem_u32(bHi), p.bTiles + ((size_t)blockIdx.y * p.numKb + (size_t)(kbBeg + it)) * (bBytes / 4), bBytes,
                         smem_u32(&fullBar[s]));
         }
 #pragma unroll
         for (int j = 0; j < CH; ++j) {
-          float v[4];
-          if (kAMode == OP_IM2COL) funnel(R.a0[j], R.a1[j], R.ao[j], v);
-          else if (kAMode == OP_WGATHER) funnel(R.a0[j], R.a1[j], tapS[j] & 3, v);
-          else { v[0] = R.a0[j].x; v[1] = R.a0[j].y; v[2] = R.a0[j].z; v[3] = R.a0[j].w; }
+          float v[4] = {R[j].x, R[j].y, R[j].z, R[j].w};
           uint32_t off = kAMN ? mnmajor_off(mnChunk, mnK + KSTEP * j, BM / 32) : kmajor_off(kmRow + RSTEP * j, kmChunk);
           store_chunk<kSplit>(aHi, aLo, off, v);
-        }
-        if (!bBulk) {
-#pragma unroll
-          for (int j = 0; j < CH; ++j)
-            if (kmRow + RSTEP * j < BN) {
-              float v[4] = {R.b0[j].x, R.b0[j].y, R.b0[j].z, R.b0[j].w};
-              store_chunk<kSplit>(bHi, bLo, kmajor_off(kmRow + RSTEP * j, kmChunk), v);
-            }
         }
         fence_async_smem();
         mbar_arrive(smem_u32(&fullBar[s]));
         return true;
       };
-      Raw ra, rb;
-      if (numIter > 0) issue(0, ra);
-      for (int it = 0; it < numIter; it += 2) {
-        if (it + 1 < numIter) issue(it + 1, rb);
-        if (!commit(it, ra)) break;
-        if (it + 1 >= numIter) break;
-        if (it + 2 < numIter) issue(it + 2, ra);
-        if (!commit(it + 1, rb)) break;
+      float4 q[kPrefetch][CH];
+#pragma unroll
+      for (int u = 0; u < kPrefetch; ++u)
+        if (u < numIter) issue(u, q[u]);
+      bool live = true;
+      for (int it = 0; it < numIter && live; it += kPrefetch) {
+#pragma unroll
+        for (int u = 0; u < kPrefetch; ++u) {
+          int const i = it + u;
+          if (i < numIter && live) {
+            live = commit(i, q[u]);
+            if (live && i + kPrefetch < numIter) issue(i + kPrefetch, q[u]);
+          }
+        }
       }
     } else {
     bool ok = true;
@@ -734,6 +650,71 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
     }
   }
 
+  // ============================== epilogue ==============================
+  // Every warp but the MMA issuer drains the accumulator: a warp may read only the TMEM lanes of its
+  // quarter (warp % 4), so the five warps of a quarter (one of warps 0-3 and four producers, which
+  // have finished by now) share that quarter's 32 output rows and split the columns in chunks of 16.
+  if (warp != kEpilogueWarps) {
+    bool ok = mbar_wait(smem_u32(&accumBar), 0);
+    ok = __all_sync(0xffffffffu, ok);
+    tc_fence_after();
+    if (!ok) { if (lane == 0) atomicExch(p.status, 3); }
+    else if (numIter > 0) {
+      int const quarter = warp & 3;
+      int const rank = warp < kEpilogueWarps ? 0 : 1 + (warp - (kEpilogueWarps + 1)) / 4;
+      int const group = 1 + kProducerWarps / 4;
+      int const m = m0 + quarter * 32 + lane;
+      long long rowBase = 0;
+      if (kEpi == EPI_CONV) { int pix = m % p.e.P, img = m / p.e.P; rowBase = (long long)img * p.e.Ktot * p.e.P + pix; }
+      else rowBase = m + (long long)split * p.e.splitStride;
+      int const used = min(numSets, numIter);
+      for (int c0 = 16 * rank; c0 < BN; c0 += 16 * group) {
+        uint32_t const laneBase = tmemAcc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
+        float big[16], small[16];
+        {
+          uint32_t t0[16], t1[16];
+          tmem_ld16_issue(laneBase, t0);
+          if (kSplit) tmem_ld16_issue(laneBase + (uint32_t)BN, t1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) { big[j] = __uint_as_float(t0[j]); small[j] = kSplit ? __uint_as_float(t1[j]) : 0.f; }
+        }
+        if (kSplit) {
+          // add the other accumulator sets: the "small" parts among themselves, the "big" parts among themselves
+          for (int q = 1; q < used; ++q) {
+            uint32_t t0[16], t1[16];
+            tmem_ld16_issue(laneBase + (uint32_t)(q * 2 * BN), t0);
+            tmem_ld16_issue(laneBase + (uint32_t)(q * 2 * BN + BN), t1);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) { big[j] += __uint_as_float(t0[j]); small[j] += __uint_as_float(t1[j]); }
+          }
+        }
+        if (m < p.M) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            int n = n0 + c0 + j;
+            if (n < p.N) {
+              float acc = big[j] + small[j];
+              if (kEpi == EPI_CONV) {
+                float* dst = p.e.out + rowBase + (long long)n * p.e.P;
+                float o = p.e.inMult * acc;
+                if (p.e.bias) o += p.e.bias[n];
+                if (p.e.outMult != 0.f) o += p.e.outMult * *dst;
+                *dst = o;
+              } else {
+                float o = acc;
+                if (p.e.bias) o += p.e.bias[m];
+                p.e.out[rowBase + (long long)n * p.e.ldd] = o;
+              }
+            }
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+
   __syncthreads();
   tc_fence_after();
   if (warp == kEpilogueWarps) tmem_dealloc(tmemAcc, tmemCols);
@@ -768,7 +749,7 @@ __global__ void flip_filters_kernel(float* __restrict__ ft, float const* __restr
 // into hi / lo once and laid out as ready-made shared-memory tile images -- for n-tile t and k-block
 // kb: [hi tile BN x 32][lo tile BN x 32], K-major with the 128-byte swizzle -- so that a producer
 // fetches a whole stage of B with one bulk copy.
-// mode 0: B(n, r) = F[n*R + r].  mode 1 (data gradient of a stride-1 convolution): n = channel c,
+// mode 0: B(n, r) = F[n*R + r].  mode 2: B(n, r) = dY[pixel, n, image] with r = pixel + P*image.  mode 1 (data gradient of a stride-1 convolution): n = channel c,
 // r = fh' + FH*(fw' + FW*k), B = F[FH-1-fh', FW-1-fw', c, k].
 template <bool kSplit>
 __global__ void prep_b_tiles_kernel(float* __restrict__ out, float const* __restrict__ f, int N, int R, int BN, int numKb,
@@ -782,7 +763,11 @@ __global__ void prep_b_tiles_kernel(float* __restrict__ out, float const* __rest
     float val = 0.f;
     if (n < N && r < R) {
       if (mode == 0) val = f[(size_t)n * R + r];
-      else {
+      else if (mode == 2) {
+        // filter gradient: n = filter, r = pixel + P*image of dY (FH carries P here)
+        int img = r / FH, pix = r - img * FH;
+        val = f[((size_t)img * N + n) * FH + pix];
+      } else {
         int fh = r % FH, t = r / FH, fw = t % FW, k = t / FW;
         val = f[(FH - 1 - fh) + (size_t)FH * ((FW - 1 - fw) + (size_t)FW * (n + (size_t)C * k))];
       }
@@ -801,12 +786,28 @@ __global__ void prep_b_tiles_kernel(float* __restrict__ out, float const* __rest
 }
 
 // Builds the tile images in the context's scratch; returns nullptr (error set) on failure.
-float const* prep_b_tiles(vlb_ctx* ctx, float const* f, int N, int R, int BN, int numKb, int mode, vlb::ConvGeom const& g)
+size_t b_tiles_bytes(vlb_ctx* ctx, int N, int BN, int numKb)
+{
+  bool split3 = ctx->precision == VLB_PRECISION_3XTF32;
+  size_t bytes = sizeof(float) * (size_t)vlb::ceil_div(N, BN) * BN * (size_t)numKb * 32 * (split3 ? 2 : 1);
+  return (bytes + 255) & ~(size_t)255;
+}
+
+// `extraBytes` of scratch are reserved behind the tiles for the caller (split-K partials).
+float const* prep_b_tiles(vlb_ctx* ctx, float const* f, int N, int R, int BN, int numKb, int mode, vlb::ConvGeom const& g,
+                          size_t extraBytes = 0, int P = 0)
 {
   bool split3 = ctx->precision == VLB_PRECISION_3XTF32;
   size_t total = (size_t)vlb::ceil_div(N, BN) * BN * (size_t)numKb * 32;
-  float* tiles = (float*)vlb::workspace(ctx, sizeof(float) * total * (split3 ? 2 : 1));
+  float* tiles = (float*)vlb::workspace(ctx, b_tiles_bytes(ctx, N, BN, numKb) + extraBytes);
   if (!tiles) return nullptr;
+  if (mode == 2) {
+    unsigned grid2 = vlb::grid_for(total, 256, ctx->smCount * 16);
+    if (split3) prep_b_tiles_kernel<true><<<grid2, 256, 0, ctx->stream>>>(tiles, f, N, R, BN, numKb, 2, P, 0, 0, 0);
+    else        prep_b_tiles_kernel<false><<<grid2, 256, 0, ctx->stream>>>(tiles, f, N, R, BN, numKb, 2, P, 0, 0, 0);
+    VLB_LAUNCHED(ctx, 1);
+    return tiles;
+  }
   unsigned grid = vlb::grid_for(total, 256, ctx->smCount * 8);
   if (split3) prep_b_tiles_kernel<true><<<grid, 256, 0, ctx->stream>>>(tiles, f, N, R, BN, numKb, mode, g.FH, g.FW, g.C, g.K);
   else        prep_b_tiles_kernel<false><<<grid, 256, 0, ctx->stream>>>(tiles, f, N, R, BN, numKb, mode, g.FH, g.FW, g.C, g.K);
@@ -911,7 +912,6 @@ int conv_fprop_tc(vlb_ctx* ctx, ConvGeom const& g, float* Y, float outMult, floa
     p.kbPerSplit = ceil_div(p.numKb, splits);
     splits = ceil_div(p.numKb, p.kbPerSplit);
     p.e = Epilogue{}; p.e.ldd = g.K;
-    p.pipelined = (p.a.vec && p.b.vec) ? 1 : 0;
     if (splits == 1) {
       p.e.out = Y; p.e.bias = b;
       return launch<OP_DENSE_K, OP_DENSE_K, EPI_PLAIN>(ctx, p, 1, "fc_fprop_tc");
@@ -1012,7 +1012,6 @@ int conv_wgrad_tc(vlb_ctx* ctx, ConvGeom const& g, float* dF, float* db, float c
   int const P = g.Ho * g.Wo;
   p.b = Operand{}; p.b.ptr = dY; p.b.ld = P; p.b.bs = (long long)P * g.K; p.b.P = P; p.b.rows = g.K;
   p.b.vec = (P % 4 == 0) && aligned16(dY);
-  p.pipelined = (p.a.fast && p.b.vec) ? 1 : 0;
   p.BN = pick_bn(p.N);
   p.numKb = ceil_div(p.R, BK);
   int tiles = ceil_div(p.M, BM) * ceil_div(p.N, p.BN);
@@ -1020,12 +1019,22 @@ int conv_wgrad_tc(vlb_ctx* ctx, ConvGeom const& g, float* dF, float* db, float c
   p.kbPerSplit = ceil_div(p.numKb, splits);
   splits = ceil_div(p.numKb, p.kbPerSplit);
   p.e = Epilogue{}; p.e.ldd = V;
+  size_t nF = (size_t)V * g.K;
+  size_t partBytes = splits > 1 ? sizeof(float) * nF * splits : 0;
+  size_t tileBytes = 0;
+  if (p.a.fast) {
+    // dY is split into hi / lo once and laid out as tile images, like the filters of fprop
+    tileBytes = b_tiles_bytes(ctx, g.K, p.BN, p.numKb);
+    p.bTiles = prep_b_tiles(ctx, dY, g.K, p.R, p.BN, p.numKb, 2, g, partBytes, P);
+    if (!p.bTiles) return ctx->lastError;
+    p.pipelined = 1;
+  }
   if (splits == 1) {
     p.e.out = dF;
     return launch<OP_WGATHER, OP_DENSE_K, EPI_PLAIN>(ctx, p, 1, "conv_wgrad_tc");
   }
-  size_t nF = (size_t)V * g.K;
-  float* part = (float*)workspace(ctx, sizeof(float) * nF * splits);
+  char* ws = (char*)workspace(ctx, tileBytes + partBytes);
+  float* part = ws ? (float*)(ws + tileBytes) : nullptr;
   if (!part) return ctx->lastError;
   p.e.out = part; p.e.splitStride = (long long)nF;
   int rc = launch<OP_WGATHER, OP_DENSE_K, EPI_PLAIN>(ctx, p, splits, "conv_wgrad_tc");

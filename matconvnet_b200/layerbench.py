@@ -118,7 +118,7 @@ def main():
     torch.cuda.set_device(0)
     ctx = nn.default_context()
     ctx.set_precision({"3xtf32": 0, "tf32": 1, "fp32": 2}[args.precision])
-    ctx.reserve_workspace(1 << 30)
+    ctx.reserve_workspace(3 << 30)
     flush = None if args.no_flush else torch.empty(64 << 20, device="cuda")
     if args.kind == "conv":
         which = [s for s in args.layers.split(",") if s]
