@@ -8,7 +8,7 @@
 //               thread) and store to global memory, coalesced along m;
 //   warp  4     allocates TMEM and issues tcgen05.mma (kind::tf32, cta_group::1) from one
 //               lane; tcgen05.commit releases a stage / publishes the accumulator;
-//   warps 5-20  producers: gather the operand tiles from the MATLAB-order tensors
+//   warps 5-16  producers: gather the operand tiles from the MATLAB-order tensors
 //               (no patch matrix: the reference writes one per image, bits/nnconv.cu:109-117),
 //               split every value into a TF32 "hi" part and an exactly representable
 //               remainder "lo", and write both as 128-byte-swizzled UMMA tiles.
@@ -37,10 +37,12 @@ using vlb::ConvGeom;
 constexpr int BM = 128;          // output rows per CTA (TMEM lanes)
 constexpr int BK = 32;           // reduction elements per stage (one 128-byte swizzle row)
 constexpr int kEpilogueWarps = 4;
-constexpr int kProducerWarps = 16;
+constexpr int kProducerWarps = 12;
 constexpr int kProducerThreads = kProducerWarps * 32;
-constexpr int kThreads = (kEpilogueWarps + 1 + kProducerWarps) * 32;   // 672
-constexpr int CH = (BM * 8) / kProducerThreads;   // 16-byte chunks per producer thread per 128 x 32 operand tile (2)
+constexpr int kThreads = (kEpilogueWarps + 1 + kProducerWarps) * 32;   // 544
+constexpr int kGenericWarps = 8;                   // the general-purpose producer loop uses the first 8 producer warps
+constexpr int kGenericThreads = kGenericWarps * 32;
+constexpr int CH = (BM * 8) / kGenericThreads;    // 16-byte chunks per thread per 128 x 32 operand tile in that loop (4)
 constexpr int KSTEP = 32 / CH;                    // MN-major tiles: k rows between a thread's consecutive chunks
 constexpr int RSTEP = BM / CH;                    // K-major tiles: rows between a thread's consecutive chunks
 constexpr int kMaxStages = 8;
@@ -106,10 +108,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
   long long t0 = 0;
   for (uint32_t it = 0;; ++it) {
     uint32_t ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    // the thread is suspended by the hardware until the phase completes or the time hint (ns) runs out
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(100000u) : "memory");
     if (ok) return true;
-    if ((it & 255u) == 255u) {
+    if ((it & 15u) == 15u) {
       long long now = clock64();
       if (t0 == 0) t0 = now;
       else if (now - t0 > kWaitCycles) return false;
@@ -357,7 +360,17 @@ __device__ __forceinline__ void load_row4(float const* __restrict__ p, int r, in
 }
 
 // ------------------------------------------------------------------ pipelined producer
-constexpr int kPrefetch = 3;     // stages of global loads in flight per producer thread
+// Pipelined producers work in kGroups independent groups of warps; group g fills the stages
+// it = g, g + kGroups, ...  A warp stalls for the full latency of its own stage's global loads, but
+// the other groups are then busy with other stages, so kGroups stages of loads are in flight per SM
+// without relying on how the compiler tracks outstanding loads inside one thread.
+// A group must not lap the MMA warp by more than the number of shared-memory stages, or the parity
+// test of an mbarrier wait would alias: kGroups <= stages (at least 3) is required.
+constexpr int kGroups = 3;
+constexpr int kGroupThreads = kProducerThreads / kGroups;       // 128
+constexpr int CHG = (BM * 8) / kGroupThreads;                    // chunks per thread per stage (8)
+constexpr int KSTEPG = 32 / CHG;                                 // MN-major: k rows between a thread's chunks (4)
+constexpr int RSTEPG = BM / CHG;                                 // K-major: rows between a thread's chunks (16)
 
 // Four consecutive rows ho0+s .. ho0+s+3 of one input column, loaded straight into their final
 // registers.  The window straddles at most two aligned groups of four rows, each wholly inside the
@@ -388,6 +401,29 @@ __device__ __forceinline__ void issue_window(float const* __restrict__ ptr, int 
   }
 }
 
+// The same window load with everything precomputed: a = address of the window start, o = its
+// alignment (s & 3), g0 / g1 = whether the first / second aligned group of rows is inside the image.
+// The window start is aligned to o = s & 3 elements only, so the four rows are fetched as four
+// independent predicated 32-bit loads: straight-line code (a load inside a branch makes the compiler
+// wait for it before the paths rejoin) and one destination register per load (two loads that may
+// write the same register are serialised by the scoreboard even when one is predicated off).  Both
+// effects were measured at about 5000 cycles per stage; this form keeps a stage's 32 loads in flight.
+__device__ __forceinline__ void ldg32_if(float& x, float const* a, bool pred)
+{
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %2, 0;\n @p ld.global.nc.f32 %0, [%1];\n}" : "+f"(x) : "l"(a), "r"((int)pred));
+}
+
+// a = address of the window start, o = its alignment (s & 3), g0 / g1 = whether the first / second
+// aligned group of four rows is inside the image; row e of the window lies in the first group iff e < 4 - o.
+__device__ __forceinline__ void issue_window2(float const* __restrict__ a, int o, bool g0, bool g1, float4& v)
+{
+  v = make_float4(0.f, 0.f, 0.f, 0.f);
+  ldg32_if(v.x, a, g0);
+  ldg32_if(v.y, a + 1, o < 3 ? g0 : g1);
+  ldg32_if(v.z, a + 2, o < 2 ? g0 : g1);
+  ldg32_if(v.w, a + 3, o < 1 ? g0 : g1);
+}
+
 // ------------------------------------------------------------------ the kernel
 template <int kAMode, int kBMode, int kEpi, bool kSplit>
 __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
@@ -397,11 +433,13 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
   __shared__ __align__(8) uint64_t emptyBar[kMaxStages];
   __shared__ __align__(8) uint64_t accumBar;
   __shared__ uint32_t tmemBase;
+  __shared__ int2 tapLut[64];       // IM2COL, pipelined: per filter tap fh + FH*fw {element offset of the tap, fh | fw<<5 | (s&3)<<10}
+  __shared__ int4 tapTab[BM];       // WGATHER, pipelined: per tile row (fh,fw,c) {element offset, row shift s, column shift dw, valid}
 
   constexpr bool kAMN = (kAMode == OP_DENSE_MN || kAMode == OP_IM2COL);
   constexpr bool kBMN = (kBMode == OP_DENSE_MN);
 
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smemRaw + 1023) & ~(uintptr_t)1023);   // swizzle atoms need 1024-byte alignment
+  uint8_t* smem = smemRaw + ((1024u - (smem_u32(smemRaw) & 1023u)) & 1023u);   // swizzle atoms need 1024-byte alignment
   int const BN = p.BN;
   uint32_t const aTileBytes = BM * BK * 4;                  // 16 KB
   uint32_t const bTileBytes = (uint32_t)BN * BK * 4;
@@ -421,11 +459,20 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
   int const numIter = max(kbEnd - kbBeg, 0);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < p.stages; ++s) { mbar_init(smem_u32(&fullBar[s]), kProducerThreads); mbar_init(smem_u32(&emptyBar[s]), 1); }
+    for (int s = 0; s < p.stages; ++s) { mbar_init(smem_u32(&fullBar[s]), p.pipelined ? kProducerWarps / kGroups : kGenericWarps); mbar_init(smem_u32(&emptyBar[s]), 1); }
     mbar_init(smem_u32(&accumBar), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == kEpilogueWarps) tmem_alloc(smem_u32(&tmemBase), tmemCols);
+  if (kAMode == OP_IM2COL && p.pipelined && (int)threadIdx.x < p.a.FH * p.a.FW) {
+    int const fh = (int)threadIdx.x % p.a.FH, fw = (int)threadIdx.x / p.a.FH;
+    int const sft = fh * p.a.dy - p.a.pt;
+    tapLut[threadIdx.x] = make_int2((fw * p.a.dx - p.a.pl) * p.a.H + sft, fh | (fw << 5) | ((sft & 3) << 10));
+  }
+  if (kAMode == OP_WGATHER && p.pipelined && threadIdx.x < BM) {
+    TapCtx tc = tap_ctx(p.a, m0 + (int)threadIdx.x);
+    tapTab[threadIdx.x] = make_int4((int)tc.coff + tc.dw * p.a.H + tc.dh, tc.dh, tc.dw, tc.valid ? 1 : 0);
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -482,6 +529,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
     // fast IM2COL: this thread's four pixels, and its reduction index (fh,fw,c), which advances by KSTEP per step
     FastPix fpx = {0, 0, 0, false};
     int fFh = 0, fFw = 0, fC = 0, fR = 0, d8fh = 0, d8fw = 0, d8c = 0;
+    uint32_t g0mask = 0, g1mask = 0, wmask = 0;    // per tap row fh / column fw: is the aligned row group / the column inside the image
     // fast WGATHER: this thread's four filter taps
     int tapS[CH], tapDw[CH], tapCoff[CH];
     bool tapOk[CH];
@@ -492,6 +540,17 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
         fR = kbBeg * BK + mnK;
         fFh = fR % p.a.FH; int q = fR / p.a.FH; fFw = q % p.a.FW; fC = q / p.a.FW;
         d8fh = KSTEP % p.a.FH; q = KSTEP / p.a.FH; d8fw = q % p.a.FW; d8c = q / p.a.FW;
+        if (fpx.valid) {
+          for (int fh = 0; fh < p.a.FH; ++fh) {
+            int sft = fh * p.a.dy - p.a.pt, h0 = fpx.ho0 + sft - (sft & 3);
+            if (h0 >= 0 && h0 < p.a.H) g0mask |= 1u << fh;
+            if (h0 + 4 >= 0 && h0 + 4 < p.a.H) g1mask |= 1u << fh;
+          }
+          for (int fw = 0; fw < p.a.FW; ++fw) {
+            int w = fpx.wo + fw * p.a.dx - p.a.pl;
+            if (w >= 0 && w < p.a.W) wmask |= 1u << fw;
+          }
+        }
       } else {
 #pragma unroll
         for (int e = 0; e < 4; ++e) px[e] = pix_ctx(p.a, m0 + 4 * mnChunk + e);
@@ -517,63 +576,86 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
       bRow[j] = p.b.ptr + (bRowOk[j] ? (long long)ib * p.b.ld : 0);
     }
     if (p.pipelined && p.bTiles != nullptr && (kAMode == OP_IM2COL || kAMode == OP_WGATHER)) {
-      // ---- pipelined: kPrefetch stages of this thread's global loads are in flight at any time; B
-      // arrives as a ready-made tile image through one bulk copy per stage.
+      // ---- pipelined: group-per-stage producers; B arrives as a ready-made tile image through one
+      // bulk copy per stage.
+      int const grp = t / kGroupThreads, tg = t % kGroupThreads;
+      int const gChunk = tg & 31, gK = tg >> 5;          // MN-major: chunk column, first k row
+      int const gKc = tg & 7, gRow = tg >> 3;            // K-major: 16-byte chunk within the row, first row
       uint32_t const bBytes = (kSplit ? 2u : 1u) * bTileBytes;
-      auto issue = [&](int it, float4 (&R)[CH]) {
-        if (kAMode == OP_IM2COL) {
-#pragma unroll
-          for (int j = 0; j < CH; ++j) {
-            issue_window(p.a.ptr, p.a.H, p.a.W, fpx, fFh * p.a.dy - p.a.pt, fFw * p.a.dx - p.a.pl, fC * HW, fR < p.R, R[j]);
-            fR += KSTEP; fFh += d8fh; fFw += d8fw; fC += d8c;
-            if (fFh >= p.a.FH) { fFh -= p.a.FH; ++fFw; }
-            if (fFw >= p.a.FW) { fFw -= p.a.FW; ++fC; }
+      FastPix gpx = {0, 0, 0, false};
+      uint32_t g0m = 0, g1m = 0, wm = 0;
+      if (kAMode == OP_IM2COL) {
+        gpx = fast_pix(p.a, m0 + 4 * gChunk, p.a.rows);
+        if (gpx.valid) {
+          for (int fh = 0; fh < p.a.FH; ++fh) {
+            int sft = fh * p.a.dy - p.a.pt, h0 = gpx.ho0 + sft - (sft & 3);
+            if (h0 >= 0 && h0 < p.a.H) g0m |= 1u << fh;
+            if (h0 + 4 >= 0 && h0 + 4 < p.a.H) g1m |= 1u << fh;
           }
-        } else {
-          FastPix rp = fast_pix(p.a, (kbBeg + it) * BK + 4 * kmChunk, p.R);
-#pragma unroll
-          for (int j = 0; j < CH; ++j)
-            issue_window(p.a.ptr, p.a.H, p.a.W, rp, tapS[j], tapDw[j], tapCoff[j], tapOk[j], R[j]);
-        }
-      };
-      auto commit = [&](int it, float4 (&R)[CH]) -> bool {
-        int const s = it % p.stages;
-        if (!mbar_wait(smem_u32(&emptyBar[s]), (uint32_t)(((it / p.stages) & 1) ^ 1))) { atomicExch(p.status, 1); return false; }
-        uint8_t* base = smem + (size_t)s * stageBytes;
-        uint8_t* aHi = base;
-        uint8_t* aLo = base + aTileBytes;
-        uint8_t* bHi = base + (kSplit ? 2u : 1u) * aTileBytes;
-        if (t == 0) {
-          mbar_expect_tx(smem_u32(&fullBar[s]), bBytes);
-          bulk_copy_g2s(smem_u32(bHi), p.bTiles + ((size_t)blockIdx.y * p.numKb + (size_t)(kbBeg + it)) * (bBytes / 4), bBytes,
-                        smem_u32(&fullBar[s]));
-        }
-#pragma unroll
-        for (int j = 0; j < CH; ++j) {
-          float v[4] = {R[j].x, R[j].y, R[j].z, R[j].w};
-          uint32_t off = kAMN ? mnmajor_off(mnChunk, mnK + KSTEP * j, BM / 32) : kmajor_off(kmRow + RSTEP * j, kmChunk);
-          store_chunk<kSplit>(aHi, aLo, off, v);
-        }
-        fence_async_smem();
-        mbar_arrive(smem_u32(&fullBar[s]));
-        return true;
-      };
-      float4 q[kPrefetch][CH];
-#pragma unroll
-      for (int u = 0; u < kPrefetch; ++u)
-        if (u < numIter) issue(u, q[u]);
-      bool live = true;
-      for (int it = 0; it < numIter && live; it += kPrefetch) {
-#pragma unroll
-        for (int u = 0; u < kPrefetch; ++u) {
-          int const i = it + u;
-          if (i < numIter && live) {
-            live = commit(i, q[u]);
-            if (live && i + kPrefetch < numIter) issue(i + kPrefetch, q[u]);
+          for (int fw = 0; fw < p.a.FW; ++fw) {
+            int w = gpx.wo + fw * p.a.dx - p.a.pl;
+            if (w >= 0 && w < p.a.W) wm |= 1u << fw;
           }
         }
       }
-    } else {
+      float const* const xb = p.a.ptr + gpx.base;
+      // reduction index of this thread's first chunk in its group's current stage, as (tap, channel);
+      // it advances by KSTEPG per chunk and by kGroups * BK per stage, with carries instead of divisions
+      int const taps = p.a.FH * p.a.FW;
+      int tap0 = 0, ch0 = 0;
+      if (kAMode == OP_IM2COL) { int r = (kbBeg + grp) * BK + gK; tap0 = r % taps; ch0 = r / taps; }
+      int const dTapJ = KSTEPG % taps, dChJ = KSTEPG / taps, dTapIt = (kGroups * BK) % taps, dChIt = (kGroups * BK) / taps;
+      uint32_t aOff[CHG];
+#pragma unroll
+      for (int j = 0; j < CHG; ++j) aOff[j] = kAMN ? mnmajor_off(gChunk, gK + KSTEPG * j, BM / 32) : kmajor_off(gRow + RSTEPG * j, gKc);
+      for (int it = grp; it < numIter; it += kGroups) {
+        float4 R[CHG];
+        if (kAMode == OP_IM2COL) {
+          int tap = tap0, ch = ch0, r = (kbBeg + it) * BK + gK;
+#pragma unroll
+          for (int j = 0; j < CHG; ++j) {
+            int2 const te = tapLut[tap];
+            uint32_t const e = (uint32_t)te.y;
+            uint32_t const wv = (r < p.R ? 1u : 0u) & (wm >> ((e >> 5) & 31u));
+            bool const g0 = (wv & (g0m >> (e & 31u)) & 1u) != 0, g1 = (wv & (g1m >> (e & 31u)) & 1u) != 0;
+            issue_window2(xb + (ch * HW + te.x), (int)((e >> 10) & 3u), g0, g1, R[j]);
+            r += KSTEPG; tap += dTapJ; ch += dChJ;
+            if (tap >= taps) { tap -= taps; ++ch; }
+          }
+          tap0 += dTapIt; ch0 += dChIt;
+          if (tap0 >= taps) { tap0 -= taps; ++ch0; }
+        } else {
+          FastPix rp = fast_pix(p.a, (kbBeg + it) * BK + 4 * gKc, p.R);
+          float const* const rb = p.a.ptr + rp.base;
+#pragma unroll
+          for (int j = 0; j < CHG; ++j) {
+            int4 const e = tapTab[gRow + RSTEPG * j];
+            int const o = e.y & 3, h0 = rp.ho0 + e.y - o, w = rp.wo + e.z;
+            bool const wv = rp.valid && e.w != 0 && w >= 0 && w < p.a.W;
+            bool const g0 = wv && h0 >= 0 && h0 < p.a.H, g1 = wv && h0 + 4 >= 0 && h0 + 4 < p.a.H;
+            issue_window2(rb + e.x, o, g0, g1, R[j]);
+          }
+        }
+        int const s = it % p.stages;
+        if (!mbar_wait(smem_u32(&emptyBar[s]), (uint32_t)(((it / p.stages) & 1) ^ 1))) { atomicExch(p.status, 1); break; }
+        uint8_t* base = smem + (size_t)s * stageBytes;
+        uint8_t* aHi = base;
+        uint8_t* aLo = base + aTileBytes;
+        if (tg == 0) {
+          mbar_expect_tx(smem_u32(&fullBar[s]), bBytes);
+          bulk_copy_g2s(smem_u32(base + (kSplit ? 2u : 1u) * aTileBytes),
+                        p.bTiles + ((size_t)blockIdx.y * p.numKb + (size_t)(kbBeg + it)) * (bBytes / 4), bBytes, smem_u32(&fullBar[s]));
+        }
+#pragma unroll
+        for (int j = 0; j < CHG; ++j) {
+          float v[4] = {R[j].x, R[j].y, R[j].z, R[j].w};
+          store_chunk<kSplit>(aHi, aLo, aOff[j], v);
+        }
+        fence_async_smem();
+        __syncwarp();                         // every lane's stores and proxy fence precede the warp's single arrival
+        if (lane == 0) mbar_arrive(smem_u32(&fullBar[s]));
+      }
+    } else if (t < kGenericThreads) {
     bool ok = true;
     for (int it = 0; it < numIter && ok; ++it) {
       int s = it % p.stages;
@@ -645,7 +727,8 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
         }
       }
       fence_async_smem();                     // generic-proxy writes -> visible to the tensor core's async proxy
-      mbar_arrive(smem_u32(&fullBar[s]));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&fullBar[s]));
     }
     }
   }
@@ -874,7 +957,7 @@ void conv_operand(Operand& o, ConvGeom const& g, float const* ptr, int channels)
   o.sy = g.sy; o.sx = g.sx; o.pt = g.pt; o.pl = g.pl; o.dy = g.dy; o.dx = g.dx;
   o.imgStride = (long long)g.H * g.W * channels;
   o.ld = 0; o.bs = 0; o.P = 0; o.vec = 0;
-  o.fast = (g.sy == 1 && g.sx == 1 && g.H % 4 == 0 && g.Ho % 4 == 0 && aligned16(ptr)) ? 1 : 0;
+  o.fast = (g.sy == 1 && g.sx == 1 && g.H % 4 == 0 && g.Ho % 4 == 0 && g.FH <= 32 && g.FW <= 32 && g.FH * g.FW <= 64 && aligned16(ptr)) ? 1 : 0;
 }
 
 bool fits32(ConvGeom const& g)
