@@ -113,7 +113,7 @@ def cpu_vgg16(batch, steps, warmup, threads):
     times = []
     for it in range(warmup + steps):
         t0 = time.perf_counter()
-        res = cpu_net.simplenn(backend, glue, layers, x, np.float32(1.0))
+        res = cpu_net.simplenn(backend, glue, layers, x, np.float32(1.0), conserve_memory=True)
         dt = time.perf_counter() - t0
         if it >= warmup:
             times.append(dt)
@@ -186,7 +186,8 @@ def main():
     exchange = dataparallel.GradientExchange(world, scale_fn=lambda t, a: nn.scale_(t, a, ctx=ctx))
 
     def step():
-        res = simplenn.vl_simplenn(net, x, one, on_dzdw=lambda i, j, w: exchange.push("l%d_%d" % (i, j), w), ctx=ctx)
+        res = simplenn.vl_simplenn(net, x, one, on_dzdw=lambda i, j, w: exchange.push("l%d_%d" % (i, j), w), ctx=ctx,
+                                   conserve_memory=True)
         exchange.pull_all()
         return res
 

@@ -66,7 +66,7 @@ struct Operand {
   int P;               // run length of contiguous reduction indices (DENSE_K, batched); 0 = unbatched
   int rows;            // valid extent of the row (M or N) index
   int vec;             // 1 when 16-byte loads are legal for this operand
-  int fast;            // 1 when the aligned-window gather applies (IM2COL, WGATHER; see load_shifted)
+  int fast;            // pipelined gather: 1 aligned windows, 2 element-wise (any geometry), 0 none (IM2COL, WGATHER)
   // convolution geometry (IM2COL, WGATHER)
   int H, W, C, FH, FW, Ho, Wo, sy, sx, pt, pl, dy, dx;
   long long imgStride;   // H*W*Ctotal
@@ -523,7 +523,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
     int const t = threadIdx.x - (kEpilogueWarps + 1) * 32;      // 0..kProducerThreads-1
     // MN-major tiles: chunk column t % 32, k rows t / 32 + KSTEP j.  K-major tiles: chunk t % 8, rows t / 8 + RSTEP j.
     int const mnChunk = t & 31, mnK = t >> 5, kmChunk = t & 7, kmRow = t >> 3;
-    bool const aFast = p.a.fast != 0;
+    bool const aFast = p.a.fast == 1;
     PixCtx px[4];
     TapCtx tap[CH];
     // fast IM2COL: this thread's four pixels, and its reduction index (fh,fw,c), which advances by KSTEP per step
@@ -585,7 +585,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
       FastPix gpx = {0, 0, 0, false};
       uint32_t g0m = 0, g1m = 0, wm = 0;
       if (kAMode == OP_IM2COL) {
-        gpx = fast_pix(p.a, m0 + 4 * gChunk, p.a.rows);
+        if (p.a.fast == 1) gpx = fast_pix(p.a, m0 + 4 * gChunk, p.a.rows);
         if (gpx.valid) {
           for (int fh = 0; fh < p.a.FH; ++fh) {
             int sft = fh * p.a.dy - p.a.pt, h0 = gpx.ho0 + sft - (sft & 3);
@@ -595,6 +595,24 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
           for (int fw = 0; fw < p.a.FW; ++fw) {
             int w = gpx.wo + fw * p.a.dx - p.a.pl;
             if (w >= 0 && w < p.a.W) wm |= 1u << fw;
+          }
+        }
+      }
+      // general gather (p.a.fast == 2: any extent, stride or dilation): the four pixels of a chunk are
+      // tracked one by one -- element offset of the pixel's window origin, and which tap rows / columns
+      // fall inside the image
+      bool const aligned = p.a.fast == 1;
+      int eBase[4] = {0, 0, 0, 0};
+      uint32_t eHm[4] = {0, 0, 0, 0}, eWm[4] = {0, 0, 0, 0};
+      if (kAMode == OP_IM2COL && !aligned) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          int const m = m0 + 4 * gChunk + e;
+          if (m < p.a.rows) {
+            int ho = m % p.a.Ho, q = m / p.a.Ho, wo = q % p.a.Wo, n = q / p.a.Wo;
+            eBase[e] = n * (int)p.a.imgStride + wo * p.a.sx * p.a.H + ho * p.a.sy;
+            for (int fh = 0; fh < p.a.FH; ++fh) { int h = ho * p.a.sy + fh * p.a.dy - p.a.pt; if (h >= 0 && h < p.a.H) eHm[e] |= 1u << fh; }
+            for (int fw = 0; fw < p.a.FW; ++fw) { int w = wo * p.a.sx + fw * p.a.dx - p.a.pl; if (w >= 0 && w < p.a.W) eWm[e] |= 1u << fw; }
           }
         }
       }
@@ -617,23 +635,58 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
             int2 const te = tapLut[tap];
             uint32_t const e = (uint32_t)te.y;
             uint32_t const wv = (r < p.R ? 1u : 0u) & (wm >> ((e >> 5) & 31u));
-            bool const g0 = (wv & (g0m >> (e & 31u)) & 1u) != 0, g1 = (wv & (g1m >> (e & 31u)) & 1u) != 0;
-            issue_window2(xb + (ch * HW + te.x), (int)((e >> 10) & 3u), g0, g1, R[j]);
+            if (aligned) {
+              bool const g0 = (wv & (g0m >> (e & 31u)) & 1u) != 0, g1 = (wv & (g1m >> (e & 31u)) & 1u) != 0;
+              issue_window2(xb + (ch * HW + te.x), (int)((e >> 10) & 3u), g0, g1, R[j]);
+            } else {
+              uint32_t const rv = r < p.R ? 1u : 0u, fh = e & 31u, fw = (e >> 5) & 31u;
+              float const* const q = p.a.ptr + (ch * HW + te.x);
+              R[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+              ldg32_if(R[j].x, q + eBase[0], (rv & (eHm[0] >> fh) & (eWm[0] >> fw) & 1u) != 0);
+              ldg32_if(R[j].y, q + eBase[1], (rv & (eHm[1] >> fh) & (eWm[1] >> fw) & 1u) != 0);
+              ldg32_if(R[j].z, q + eBase[2], (rv & (eHm[2] >> fh) & (eWm[2] >> fw) & 1u) != 0);
+              ldg32_if(R[j].w, q + eBase[3], (rv & (eHm[3] >> fh) & (eWm[3] >> fw) & 1u) != 0);
+            }
             r += KSTEPG; tap += dTapJ; ch += dChJ;
             if (tap >= taps) { tap -= taps; ++ch; }
           }
           tap0 += dTapIt; ch0 += dChIt;
           if (tap0 >= taps) { tap0 -= taps; ++ch0; }
         } else {
-          FastPix rp = fast_pix(p.a, (kbBeg + it) * BK + 4 * gKc, p.R);
-          float const* const rb = p.a.ptr + rp.base;
+          if (aligned) {
+            FastPix rp = fast_pix(p.a, (kbBeg + it) * BK + 4 * gKc, p.R);
+            float const* const rb = p.a.ptr + rp.base;
 #pragma unroll
-          for (int j = 0; j < CHG; ++j) {
-            int4 const e = tapTab[gRow + RSTEPG * j];
-            int const o = e.y & 3, h0 = rp.ho0 + e.y - o, w = rp.wo + e.z;
-            bool const wv = rp.valid && e.w != 0 && w >= 0 && w < p.a.W;
-            bool const g0 = wv && h0 >= 0 && h0 < p.a.H, g1 = wv && h0 + 4 >= 0 && h0 + 4 < p.a.H;
-            issue_window2(rb + e.x, o, g0, g1, R[j]);
+            for (int j = 0; j < CHG; ++j) {
+              int4 const e = tapTab[gRow + RSTEPG * j];
+              int const o = e.y & 3, h0 = rp.ho0 + e.y - o, w = rp.wo + e.z;
+              bool const wv = rp.valid && e.w != 0 && w >= 0 && w < p.a.W;
+              bool const g0 = wv && h0 >= 0 && h0 < p.a.H, g1 = wv && h0 + 4 >= 0 && h0 + 4 < p.a.H;
+              issue_window2(rb + e.x, o, g0, g1, R[j]);
+            }
+          } else {
+            // the four reduction pixels of this thread's chunk, one by one
+            int const r = (kbBeg + it) * BK + 4 * gKc;
+            int ho = r % p.a.Ho, q = r / p.a.Ho, wo = q % p.a.Wo, n = q / p.a.Wo;
+            int pb[4], ph[4], pw[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              ph[e] = (r + e < p.R) ? ho * p.a.sy : -(1 << 28);      // an invalid pixel fails every row test
+              pw[e] = wo * p.a.sx;
+              pb[e] = n * (int)p.a.imgStride + pw[e] * p.a.H + ho * p.a.sy;
+              if (++ho == p.a.Ho) { ho = 0; if (++wo == p.a.Wo) { wo = 0; ++n; } }
+            }
+#pragma unroll
+            for (int j = 0; j < CHG; ++j) {
+              int4 const e = tapTab[gRow + RSTEPG * j];
+              float const* const qp = p.a.ptr + e.x;
+              bool const on = e.w != 0;
+              R[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+              ldg32_if(R[j].x, qp + pb[0], on && (unsigned)(ph[0] + e.y) < (unsigned)p.a.H && (unsigned)(pw[0] + e.z) < (unsigned)p.a.W);
+              ldg32_if(R[j].y, qp + pb[1], on && (unsigned)(ph[1] + e.y) < (unsigned)p.a.H && (unsigned)(pw[1] + e.z) < (unsigned)p.a.W);
+              ldg32_if(R[j].z, qp + pb[2], on && (unsigned)(ph[2] + e.y) < (unsigned)p.a.H && (unsigned)(pw[2] + e.z) < (unsigned)p.a.W);
+              ldg32_if(R[j].w, qp + pb[3], on && (unsigned)(ph[3] + e.y) < (unsigned)p.a.H && (unsigned)(pw[3] + e.z) < (unsigned)p.a.W);
+            }
           }
         }
         int const s = it % p.stages;
@@ -957,7 +1010,9 @@ void conv_operand(Operand& o, ConvGeom const& g, float const* ptr, int channels)
   o.sy = g.sy; o.sx = g.sx; o.pt = g.pt; o.pl = g.pl; o.dy = g.dy; o.dx = g.dx;
   o.imgStride = (long long)g.H * g.W * channels;
   o.ld = 0; o.bs = 0; o.P = 0; o.vec = 0;
-  o.fast = (g.sy == 1 && g.sx == 1 && g.H % 4 == 0 && g.Ho % 4 == 0 && g.FH <= 32 && g.FW <= 32 && g.FH * g.FW <= 64 && aligned16(ptr)) ? 1 : 0;
+  // 1: aligned windows (stride 1, extents multiples of 4); 2: element-wise gather, any geometry; 0: no pipelined path
+  bool const lut = g.FH <= 32 && g.FW <= 32 && g.FH * g.FW <= 64;
+  o.fast = !lut ? 0 : ((g.sy == 1 && g.sx == 1 && g.H % 4 == 0 && g.Ho % 4 == 0 && aligned16(ptr)) ? 1 : 2);
 }
 
 bool fits32(ConvGeom const& g)

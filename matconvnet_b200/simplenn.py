@@ -20,7 +20,7 @@ def _get(l, key, default):
 
 
 def vl_simplenn(net, x, dzdy=None, res=None, on_dzdw=None, ctx=None, skip_forward=False,
-                back_prop_depth=None):
+                back_prop_depth=None, conserve_memory=False):
     layers = net["layers"]
     n = len(layers)
     if res is None:
@@ -75,6 +75,6 @@ def vl_simplenn(net, x, dzdy=None, res=None, on_dzdw=None, ctx=None, skip_forwar
             for j, w in enumerate(res[i]["dzdw"]):
                 if w is not None:
                     on_dzdw(i, j, w)
-        if i + 1 < n:
-            res[i + 1]["dzdx"] = None      # conserveMemory (vl_simplenn.m:512-514)
+        if conserve_memory and i + 1 < n:
+            res[i + 1]["dzdx"] = None      # opts.conserveMemory (vl_simplenn.m:512-514)
     return res
