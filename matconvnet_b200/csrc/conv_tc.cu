@@ -46,6 +46,7 @@ constexpr int CH = (BM * 8) / kGenericThreads;    // 16-byte chunks per thread p
 constexpr int KSTEP = 32 / CH;                    // MN-major tiles: k rows between a thread's consecutive chunks
 constexpr int RSTEP = BM / CH;                    // K-major tiles: rows between a thread's consecutive chunks
 constexpr int kMaxStages = 8;
+constexpr int kDrainEvery = 8;                    // 3xTF32: k-blocks (of 32) accumulated by the tensor core before the fp32 drain
 constexpr long long kWaitCycles = 2000000000LL;   // bound on any single barrier wait
 
 enum OperandMode {
@@ -88,6 +89,7 @@ struct Params {
   int BN;                 // tile columns: 16, 32, 64 or 128
   int numKb, kbPerSplit;
   int stages;
+  int drainEvery;         // 3xTF32: k-blocks per tensor-core accumulation chain
   int pipelined;          // 1: producers prefetch one stage ahead in registers (aligned gathers only)
   float const* bTiles;    // when non-null: B pre-split into shared-memory tile images, fetched with bulk copies
   int* status;
@@ -159,6 +161,14 @@ __device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t (&r)[16
                : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, uint32_t const (&r)[16])
+{
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                 "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16])
 {
@@ -432,6 +442,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
   __shared__ __align__(8) uint64_t fullBar[kMaxStages];
   __shared__ __align__(8) uint64_t emptyBar[kMaxStages];
   __shared__ __align__(8) uint64_t accumBar;
+  __shared__ __align__(8) uint64_t drainFull[2], drainEmpty[2], sumBar;   // T0/T1 hand-over; P complete
   __shared__ uint32_t tmemBase;
   __shared__ int2 tapLut[64];       // IM2COL, pipelined: per filter tap fh + FH*fw {element offset of the tap, fh | fw<<5 | (s&3)<<10}
   __shared__ int4 tapTab[BM];       // WGATHER, pipelined: per tile row (fh,fw,c) {element offset, row shift s, column shift dw, valid}
@@ -444,23 +455,29 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
   uint32_t const aTileBytes = BM * BK * 4;                  // 16 KB
   uint32_t const bTileBytes = (uint32_t)BN * BK * 4;
   uint32_t const stageBytes = (kSplit ? 2u : 1u) * (aTileBytes + bTileBytes);
-  // Accumulator sets.  The tensor core adds each MMA's result to the fp32 accumulator with
-  // truncation, so the error of a long accumulation chain grows linearly with its length.  In the
-  // split mode the products of the small terms (lo*hi, hi*lo) therefore go to their own accumulator
-  // ("small", about 2^-11 of the result, where truncation no longer matters), and the k-blocks are
-  // dealt round-robin to numSets independent (big, small) pairs, which the epilogue adds in fp32.
-  int const numSets = kSplit ? min(8, 512 / (2 * BN)) : 1;
-  uint32_t const tmemCols = kSplit ? (uint32_t)(numSets * 2 * BN) : (BN < 32 ? 32u : (uint32_t)BN);
+  // Accumulators.  The tensor core adds each MMA's result to the fp32 accumulator with truncation,
+  // so the error of an accumulation chain is a bias that grows linearly with its length (3e-5
+  // relative after a few thousand steps).  In the split mode the chain is therefore kept short:
+  //   T0, T1  hi*hi products of p.drainEvery consecutive k-blocks (8: 32 MMAs), used alternately;
+  //   P       the running sum: warps 0-3 add a finished T to it in fp32 with round-to-nearest
+  //           (tcgen05.ld, add, tcgen05.st) while the tensor core fills the other T;
+  //   S       the small terms lo*hi + hi*lo (about 2^-11 of the result, where the bias no longer
+  //           matters) of the whole reduction.
+  // The epilogue returns P + T(last) + S.  Columns: T0 | T1 | P | S, BN each.
+  uint32_t const tmemCols = kSplit ? (uint32_t)(4 * BN) : (BN < 32 ? 32u : (uint32_t)BN);
 
   int const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int const m0 = blockIdx.x * BM, n0 = blockIdx.y * BN, split = blockIdx.z;
   int const kbBeg = split * p.kbPerSplit;
   int const kbEnd = min(p.numKb, kbBeg + p.kbPerSplit);
   int const numIter = max(kbEnd - kbBeg, 0);
+  int const numChunks = kSplit ? (numIter + p.drainEvery - 1) / p.drainEvery : 1;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) { mbar_init(smem_u32(&fullBar[s]), p.pipelined ? kProducerWarps / kGroups : kGenericWarps); mbar_init(smem_u32(&emptyBar[s]), 1); }
     mbar_init(smem_u32(&accumBar), 1);
+    for (int b = 0; b < 2; ++b) { mbar_init(smem_u32(&drainFull[b]), 1); mbar_init(smem_u32(&drainEmpty[b]), kEpilogueWarps); }
+    mbar_init(smem_u32(&sumBar), kEpilogueWarps);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == kEpilogueWarps) tmem_alloc(smem_u32(&tmemBase), tmemCols);
@@ -479,7 +496,48 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
   uint32_t const tmemAcc = tmemBase;
 
   if (warp < kEpilogueWarps) {
-    // warps 0-3 take no part in the main loop; they join the epilogue below
+    // ============================== fp32 drain (3xTF32 only) ==============================
+    // Chunk c (k-blocks c*p.drainEvery ...) was accumulated in T[c & 1]; all chunks but the last are
+    // added to P here.  Warp w owns TMEM lanes 32w .. 32w+31.
+    if (kSplit) {
+      uint32_t const lanes = tmemAcc + ((uint32_t)(warp * 32) << 16);
+      bool ok = true;
+      for (int c = 0; c + 1 < numChunks && ok; ++c) {
+        int const b = c & 1;
+        ok = mbar_wait(smem_u32(&drainFull[b]), (uint32_t)((c >> 1) & 1));
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) { if (lane == 0) atomicExch(p.status, 5); break; }
+        tc_fence_after();
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t t0[16], t1[16], p0[16], p1[16];
+          bool const two = c0 + 16 < BN;
+          tmem_ld16_issue(lanes + (uint32_t)(b * BN + c0), t0);
+          if (two) tmem_ld16_issue(lanes + (uint32_t)(b * BN + c0 + 16), t1);
+          if (c > 0) {
+            tmem_ld16_issue(lanes + (uint32_t)(2 * BN + c0), p0);
+            if (two) tmem_ld16_issue(lanes + (uint32_t)(2 * BN + c0 + 16), p1);
+          }
+          tmem_ld_wait();
+          if (c > 0) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              t0[j] = __float_as_uint(__uint_as_float(t0[j]) + __uint_as_float(p0[j]));
+              if (two) t1[j] = __float_as_uint(__uint_as_float(t1[j]) + __uint_as_float(p1[j]));
+            }
+          }
+          tmem_st16(lanes + (uint32_t)(2 * BN + c0), t0);
+          if (two) tmem_st16(lanes + (uint32_t)(2 * BN + c0 + 16), t1);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&drainEmpty[b]));     // T[b] may be overwritten
+      }
+      // P is complete (its stores have been waited for): publish it to the warps of the epilogue
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sumBar));
+    }
   } else if (warp == kEpilogueWarps) {
     // ============================== MMA issue ==============================
     if (lane == 0) {
@@ -488,6 +546,13 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
       bool ok = true;
       for (int it = 0; it < numIter && ok; ++it) {
         int s = it % p.stages;
+        int const chunk = it / p.drainEvery, tb = kSplit ? (chunk & 1) : 0;
+        bool const chunkStart = it % p.drainEvery == 0;
+        if (kSplit && chunkStart && chunk >= 2) {      // T[tb] is reused: its previous contents must have been added to P
+          ok = mbar_wait(smem_u32(&drainEmpty[tb]), (uint32_t)(((chunk >> 1) - 1) & 1));
+          if (!ok) { atomicExch(p.status, 6); break; }
+          tc_fence_after();
+        }
         ok = mbar_wait(smem_u32(&fullBar[s]), (uint32_t)((it / p.stages) & 1));
         if (!ok) { atomicExch(p.status, 2); break; }
         tc_fence_after();
@@ -500,19 +565,20 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
           uint32_t bAdv = kBMN ? (uint32_t)k4 * (uint32_t)(BN / 32) * 1024u : (uint32_t)k4 * 32u;
           uint64_t dAh = kAMN ? make_desc(aHi + aAdv, aLbo, aSbo, 1) : make_desc(aHi + aAdv, 16, 1024);
           uint64_t dBh = kBMN ? make_desc(bHi + bAdv, bLbo, bSbo, 1) : make_desc(bHi + bAdv, 16, 1024);
-          uint32_t first = (it >= numSets || k4 > 0) ? 1u : 0u;     // 0 = overwrite: first MMA into this set
-          uint32_t const tmemBig = tmemAcc + (uint32_t)((it % numSets) * 2 * BN), tmemSmall = tmemBig + (uint32_t)BN;
           if (kSplit) {
+            uint32_t const tmemBig = tmemAcc + (uint32_t)(tb * BN), tmemSmall = tmemAcc + (uint32_t)(3 * BN);
             uint64_t dAl = kAMN ? make_desc(aLo + aAdv, aLbo, aSbo, 1) : make_desc(aLo + aAdv, 16, 1024);
             uint64_t dBl = kBMN ? make_desc(bLo + bAdv, bLbo, bSbo, 1) : make_desc(bLo + bAdv, 16, 1024);
-            umma_tf32(tmemSmall, dAl, dBh, idesc, first);
+            umma_tf32(tmemSmall, dAl, dBh, idesc, (it > 0 || k4 > 0) ? 1u : 0u);     // 0 = overwrite
             umma_tf32(tmemSmall, dAh, dBl, idesc, 1u);
-            umma_tf32(tmemBig, dAh, dBh, idesc, first);
+            umma_tf32(tmemBig, dAh, dBh, idesc, (!chunkStart || k4 > 0) ? 1u : 0u);
           } else {
-            umma_tf32(tmemBig, dAh, dBh, idesc, first);
+            umma_tf32(tmemAcc, dAh, dBh, idesc, (it > 0 || k4 > 0) ? 1u : 0u);
           }
         }
         umma_commit(smem_u32(&emptyBar[s]));    // frees the stage once these MMAs have read it
+        if (kSplit && chunk + 1 < numChunks && it % p.drainEvery == p.drainEvery - 1)
+          umma_commit(smem_u32(&drainFull[tb]));   // this chunk's T is complete: hand it to the drain warps
       }
       umma_commit(smem_u32(&accumBar));         // accumulator complete (or nothing was issued)
     }
@@ -792,6 +858,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
   // have finished by now) share that quarter's 32 output rows and split the columns in chunks of 16.
   if (warp != kEpilogueWarps) {
     bool ok = mbar_wait(smem_u32(&accumBar), 0);
+    if (kSplit && ok) ok = mbar_wait(smem_u32(&sumBar), 0);
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
     if (!ok) { if (lane == 0) atomicExch(p.status, 3); }
@@ -803,27 +870,21 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
       long long rowBase = 0;
       if (kEpi == EPI_CONV) { int pix = m % p.e.P, img = m / p.e.P; rowBase = (long long)img * p.e.Ktot * p.e.P + pix; }
       else rowBase = m + (long long)split * p.e.splitStride;
-      int const used = min(numSets, numIter);
+      uint32_t const lastT = (uint32_t)(((numChunks - 1) & 1) * BN);
       for (int c0 = 16 * rank; c0 < BN; c0 += 16 * group) {
         uint32_t const laneBase = tmemAcc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
         float big[16], small[16];
         {
-          uint32_t t0[16], t1[16];
-          tmem_ld16_issue(laneBase, t0);
-          if (kSplit) tmem_ld16_issue(laneBase + (uint32_t)BN, t1);
+          uint32_t t0[16], t1[16], t2[16];
+          tmem_ld16_issue(laneBase + lastT, t0);
+          if (kSplit) tmem_ld16_issue(laneBase + (uint32_t)(3 * BN), t1);
+          if (kSplit && numChunks > 1) tmem_ld16_issue(laneBase + (uint32_t)(2 * BN), t2);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) { big[j] = __uint_as_float(t0[j]); small[j] = kSplit ? __uint_as_float(t1[j]) : 0.f; }
-        }
-        if (kSplit) {
-          // add the other accumulator sets: the "small" parts among themselves, the "big" parts among themselves
-          for (int q = 1; q < used; ++q) {
-            uint32_t t0[16], t1[16];
-            tmem_ld16_issue(laneBase + (uint32_t)(q * 2 * BN), t0);
-            tmem_ld16_issue(laneBase + (uint32_t)(q * 2 * BN + BN), t1);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 16; ++j) { big[j] += __uint_as_float(t0[j]); small[j] += __uint_as_float(t1[j]); }
+          for (int j = 0; j < 16; ++j) {
+            big[j] = __uint_as_float(t0[j]);
+            small[j] = kSplit ? __uint_as_float(t1[j]) : 0.f;
+            if (kSplit && numChunks > 1) big[j] += __uint_as_float(t2[j]);
           }
         }
         if (m < p.M) {
@@ -966,6 +1027,7 @@ int launch(vlb_ctx* ctx, Params& p, int splits, char const* where)
   if (stages > 6) stages = 6;
   p.stages = stages;
   p.status = ctx->deviceStatus;
+  p.drainEvery = kDrainEvery;
   size_t smemBytes = (size_t)stages * stageBytes + 1024;
   dim3 grid(vlb::ceil_div(p.M, BM), vlb::ceil_div(p.N, p.BN), splits);
   if (grid.y > 65535u || grid.z > 65535u) return VLB_Unsupported;
