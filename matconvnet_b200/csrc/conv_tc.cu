@@ -917,6 +917,318 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
   if (warp == kEpilogueWarps) tmem_dealloc(tmemAcc, tmemCols);
 }
 
+// ------------------------------------------------------------------ convolution with the gathered operand in tensor memory
+// fprop and stride-1 dgrad: D[m][n] = sum_r A(m,r) B(n,r), m = output pixel (ho,wo,image), r = (fh,fw,c).
+// In tc_gemm_kernel both operands are read from shared memory by every MMA, and the shared-memory
+// banks (MMA reads + producer stores + bulk-copy writes) are the unit that saturates first.  Here the
+// gathered operand A never touches shared memory: one producer thread per output pixel (= TMEM lane)
+// loads its 32 window elements of a k-block -- for a warp, 32 neighbouring pixels of one (tap,
+// channel), i.e. one coalesced line per k -- splits them into hi / lo and writes them to tensor
+// memory with tcgen05.st; the MMA takes A from tensor memory and only the filter tiles from shared
+// memory (bulk copies of the ready-made tile images).  Any stride, padding and dilation.
+//   warps 0-3   fp32 drain of the short accumulation chains (3xTF32), then epilogue
+//   warp  4     MMA issue (one lane), TMEM allocation
+//   warp  5     filter-tile loader (one lane): bulk copies into kTsBStages shared-memory stages
+//   warp  6     forwarder (one lane): when the filter tile of a k-block has landed it arrives on that
+//               k-block's A-stage barrier, so that the MMA thread waits on a single barrier per k-block
+//   warps 7-14  producers: two groups of four warps (one warp per TMEM lane quarter); group g owns
+//               A stage g and fills it for the k-blocks g, g+2, ...; a producer that finds its A stage
+//               free again also knows that the filter stage of the same k-block is free and says so
+//               to the loader, so that the MMA thread commits to a single barrier per k-block.
+// The MMA thread is the critical resource: the tensor core's queue is about one MMA deep, so every
+// cycle that thread spends on anything but issuing (each barrier wait costs it about 100 cycles even
+// when the barrier is already complete, each commit about 50) is a cycle the tensor core idles.
+// Tensor memory columns: T0 | T1 | P (BN each; 3xTF32: chain accumulators and fp32 running sum; the
+// small terms lo*hi + hi*lo go to T as well) | A stage g at 3*BN + 64*g: 32 columns hi, 32 columns lo.
+constexpr int kTsGroups = 2;
+constexpr int kTsLoaderWarp = kEpilogueWarps + 1;
+constexpr int kTsForwardWarp = kEpilogueWarps + 2;
+constexpr int kTsFirstProducer = kEpilogueWarps + 3;
+constexpr int kTsThreads = (kTsFirstProducer + 4 * kTsGroups) * 32;      // 480
+constexpr int kTsBStages = 6;
+constexpr int kTsDrainEvery = 4;        // k-blocks per accumulation chain: 4 x 4 k-steps x 3 MMAs
+
+__device__ __forceinline__ void umma_tf32_ts(uint32_t dTmem, uint32_t aTmem, uint64_t bDesc, uint32_t iDesc, uint32_t accumulate)
+{
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n}"
+               ::"r"(dTmem), "r"(aTmem), "l"(bDesc), "r"(iDesc), "r"(accumulate) : "memory");
+}
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, uint32_t const (&r)[32])
+{
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+               "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                 "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                 "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                 "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+{ asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n}" ::"r"(bar), "r"(bytes) : "memory"); }
+
+template <bool kSplit>
+__global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
+{
+  extern __shared__ uint8_t smemRaw[];
+  __shared__ __align__(8) uint64_t fullA[kTsGroups], emptyA[kTsGroups], fullB[kTsBStages], emptyB[kTsBStages];
+  __shared__ __align__(8) uint64_t drainFull[2], drainEmpty[2], sumBar, accumBar;
+  __shared__ uint32_t tmemBase;
+  __shared__ int2 tapLut[64];       // per filter tap fh + FH*fw: {element offset of the tap, fh | fw << 5}
+
+  uint8_t* smem = smemRaw + ((1024u - (smem_u32(smemRaw) & 1023u)) & 1023u);
+  int const BN = p.BN;
+  uint32_t const bTileBytes = (uint32_t)BN * BK * 4;
+  uint32_t const bBytes = (kSplit ? 2u : 1u) * bTileBytes;
+  uint32_t const tmemCols = 512;
+  uint32_t const colP = (uint32_t)(2 * BN), colA = (uint32_t)(3 * BN);
+
+  int const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int const m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  int const numIter = p.numKb;
+  int const numChunks = kSplit ? (numIter + kTsDrainEvery - 1) / kTsDrainEvery : 1;
+
+  if (threadIdx.x == 0) {
+    // an A stage is full when its four producer warps and the forwarder (filter tile landed) have arrived
+    for (int s = 0; s < kTsGroups; ++s) { mbar_init(smem_u32(&fullA[s]), 5); mbar_init(smem_u32(&emptyA[s]), 1); }
+    for (int s = 0; s < kTsBStages; ++s) { mbar_init(smem_u32(&fullB[s]), 1); mbar_init(smem_u32(&emptyB[s]), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(smem_u32(&drainFull[b]), 1); mbar_init(smem_u32(&drainEmpty[b]), kEpilogueWarps); }
+    mbar_init(smem_u32(&sumBar), kEpilogueWarps);
+    mbar_init(smem_u32(&accumBar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kEpilogueWarps) tmem_alloc(smem_u32(&tmemBase), tmemCols);
+  if ((int)threadIdx.x < p.a.FH * p.a.FW) {
+    int const fh = (int)threadIdx.x % p.a.FH, fw = (int)threadIdx.x / p.a.FH;
+    tapLut[threadIdx.x] = make_int2((fw * p.a.dx - p.a.pl) * p.a.H + fh * p.a.dy - p.a.pt, fh | (fw << 5));
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t const tmemAcc = tmemBase;
+
+  if (warp < kEpilogueWarps) {
+    // ============================== fp32 drain (3xTF32 only) ==============================
+    // Chain c (k-blocks c*kTsDrainEvery ...) was accumulated in T[c & 1]; all chains but the last are
+    // added to P here.  Warp w owns TMEM lanes 32w .. 32w+31.
+    if (kSplit) {
+      uint32_t const lanes = tmemAcc + ((uint32_t)(warp * 32) << 16);
+      bool ok = true;
+      for (int c = 0; c + 1 < numChunks && ok; ++c) {
+        int const b = c & 1;
+        ok = mbar_wait(smem_u32(&drainFull[b]), (uint32_t)((c >> 1) & 1));
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) { if (lane == 0) atomicExch(p.status, 5); break; }
+        tc_fence_after();
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t t0[16], t1[16], p0[16], p1[16];
+          bool const two = c0 + 16 < BN;
+          tmem_ld16_issue(lanes + (uint32_t)(b * BN + c0), t0);
+          if (two) tmem_ld16_issue(lanes + (uint32_t)(b * BN + c0 + 16), t1);
+          if (c > 0) {
+            tmem_ld16_issue(lanes + colP + (uint32_t)c0, p0);
+            if (two) tmem_ld16_issue(lanes + colP + (uint32_t)(c0 + 16), p1);
+          }
+          tmem_ld_wait();
+          if (c > 0) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              t0[j] = __float_as_uint(__uint_as_float(t0[j]) + __uint_as_float(p0[j]));
+              if (two) t1[j] = __float_as_uint(__uint_as_float(t1[j]) + __uint_as_float(p1[j]));
+            }
+          }
+          tmem_st16(lanes + colP + (uint32_t)c0, t0);
+          if (two) tmem_st16(lanes + colP + (uint32_t)(c0 + 16), t1);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&drainEmpty[b]));     // T[b] may be overwritten
+      }
+      // P is complete (its stores have been waited for): publish it to the warps of the epilogue
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sumBar));
+    }
+  } else if (warp == kEpilogueWarps) {
+    // ============================== MMA issue ==============================
+    // Per k-block: one barrier wait (A written and B landed), twelve MMAs, one commit.  Running counters
+    // instead of divisions; per chain of kTsDrainEvery k-blocks one more wait and one more commit.
+    if (lane == 0) {
+      uint32_t const idesc = make_idesc(false, false, BN);
+      uint64_t const descB0 = make_desc(smem_u32(smem), 16, 1024);
+      uint32_t const stageStep = bBytes >> 4, loStep = bTileBytes >> 4;
+      bool ok = true;
+      int sa = 0, sb = 0, inChunk = 0, chunk = 0;
+      uint32_t phA = 0;
+      for (int it = 0; it < numIter; ++it) {
+        int const tb = chunk & 1;
+        bool const chunkStart = kSplit ? inChunk == 0 : it == 0;
+        if (kSplit && chunkStart && chunk >= 2) {      // T[tb] is reused: its previous contents must have been added to P
+          ok = mbar_wait(smem_u32(&drainEmpty[tb]), (uint32_t)(((chunk >> 1) - 1) & 1));
+          if (!ok) { atomicExch(p.status, 6); break; }
+        }
+        ok = mbar_wait(smem_u32(&fullA[sa]), phA);
+        if (!ok) { atomicExch(p.status, 2); break; }
+        tc_fence_after();
+        uint64_t const dBh = descB0 + (uint64_t)((uint32_t)sb * stageStep), dBl = dBh + loStep;
+        uint32_t const aHi = tmemAcc + colA + (uint32_t)(sa * 64), aLo = aHi + 32u;
+        uint32_t const tAcc = tmemAcc + (uint32_t)(tb * BN);
+#pragma unroll
+        for (int k8 = 0; k8 < BK / 8; ++k8) {
+          uint32_t const acc = (chunkStart && k8 == 0) ? 0u : 1u;      // 0 = overwrite: first MMA of a chain
+          if (kSplit) {
+            asm volatile(
+                "{\n .reg .pred p0, p1;\n setp.ne.b32 p0, %6, 0;\n setp.eq.b32 p1, %6, %6;\n"
+                " tcgen05.mma.cta_group::1.kind::tf32 [%0], [%2], %3, %5, p0;\n"
+                " tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %4, %5, p1;\n"
+                " tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %3, %5, p1;\n}"
+                ::"r"(tAcc), "r"(aHi + 8u * k8), "r"(aLo + 8u * k8), "l"(dBh + 2u * k8), "l"(dBl + 2u * k8), "r"(idesc), "r"(acc) : "memory");
+          } else {
+            umma_tf32_ts(tAcc, aHi + 8u * k8, dBh + 2u * k8, idesc, acc);
+          }
+        }
+        umma_commit(smem_u32(&emptyA[sa]));      // frees the A stage; its producers pass the news on for the B stage
+        if (++sa == kTsGroups) { sa = 0; phA ^= 1u; }
+        if (++sb == kTsBStages) sb = 0;
+        if (kSplit && ++inChunk == kTsDrainEvery) {
+          if (chunk + 1 < numChunks) umma_commit(smem_u32(&drainFull[tb]));   // this chain is complete: hand it to the drain warps
+          inChunk = 0; ++chunk;
+        }
+      }
+      umma_commit(smem_u32(&accumBar));
+    }
+    __syncwarp();
+    tc_fence_before();
+  } else if (warp == kTsLoaderWarp) {
+    // ============================== filter tiles: bulk copies ==============================
+    if (lane == 0) {
+      int sb = 0; uint32_t ph = 1;                       // first use of a stage: nothing to wait for
+      for (int it = 0; it < numIter; ++it) {
+        if (!mbar_wait(smem_u32(&emptyB[sb]), ph)) { atomicExch(p.status, 8); break; }
+        mbar_arrive_expect_tx(smem_u32(&fullB[sb]), bBytes);
+        bulk_copy_g2s(smem_u32(smem + (size_t)sb * bBytes), p.bTiles + ((size_t)blockIdx.y * p.numKb + (size_t)it) * (bBytes / 4),
+                      bBytes, smem_u32(&fullB[sb]));
+        if (++sb == kTsBStages) { sb = 0; ph ^= 1u; }
+      }
+    }
+    __syncwarp();
+  } else if (warp == kTsForwardWarp) {
+    // ============================== forwarder ==============================
+    // k-block it uses A stage it & 1 in that barrier's phase it >> 1.  The arrival for it must fall into
+    // that phase, so the phase of it - 2 has to be complete first (this thread arrived in it as well).
+    if (lane == 0) {
+      int sb = 0; uint32_t phB = 0;
+      for (int it = 0; it < numIter; ++it) {
+        int const sa = it & 1;
+        if (!mbar_wait(smem_u32(&fullB[sb]), phB)) { atomicExch(p.status, 7); break; }
+        if (it >= kTsGroups && !mbar_wait(smem_u32(&fullA[sa]), (uint32_t)(((it >> 1) - 1) & 1))) { atomicExch(p.status, 9); break; }
+        mbar_arrive(smem_u32(&fullA[sa]));
+        if (++sb == kTsBStages) { sb = 0; phB ^= 1u; }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ============================== producers ==============================
+    int const grp = (warp - kTsFirstProducer) >> 2;
+    int const quarter = warp & 3;                       // the TMEM lanes this warp may access
+    bool const herald = (warp - kTsFirstProducer) % 4 == 0 && lane == 0;   // tells the loader about freed filter stages
+    int const m = m0 + quarter * 32 + lane;
+    int const HW = p.a.H * p.a.W, taps = p.a.FH * p.a.FW;
+    uint32_t hm = 0, wm = 0;                            // tap rows / columns inside the image for this pixel
+    float const* xq = p.a.ptr;
+    if (m < p.M) {
+      int const ho = m % p.a.Ho, q = m / p.a.Ho, wo = q % p.a.Wo, n = q / p.a.Wo;
+      xq += (long long)n * p.a.imgStride + (long long)wo * p.a.sx * p.a.H + ho * p.a.sy;
+      for (int fh = 0; fh < p.a.FH; ++fh) { int h = ho * p.a.sy + fh * p.a.dy - p.a.pt; if (h >= 0 && h < p.a.H) hm |= 1u << fh; }
+      for (int fw = 0; fw < p.a.FW; ++fw) { int w = wo * p.a.sx + fw * p.a.dx - p.a.pl; if (w >= 0 && w < p.a.W) wm |= 1u << fw; }
+    }
+    uint32_t const aAddr = tmemAcc + ((uint32_t)(quarter * 32) << 16) + colA + (uint32_t)(grp * 64);
+    uint32_t phE = 1;                                   // first use of the stage: nothing to wait for
+    int sbFree = grp;                                   // filter stage of the k-block whose MMAs this group sees complete next
+    for (int it = grp; it < numIter; it += kTsGroups) {
+      int const r = it * BK;
+      int tap = r % taps, ch = r / taps;
+      float v[32];
+#pragma unroll
+      for (int k = 0; k < 32; ++k) {
+        int2 const te = tapLut[tap];
+        uint32_t const e = (uint32_t)te.y;
+        bool const on = ((r + k < p.R ? 1u : 0u) & (hm >> (e & 31u)) & (wm >> (e >> 5))) != 0;
+        v[k] = 0.f;
+        ldg32_if(v[k], xq + (ch * HW + te.x), on);
+        if (++tap == taps) { tap = 0; ++ch; }
+      }
+      uint32_t hi[32];
+#pragma unroll
+      for (int k = 0; k < 32; ++k) hi[k] = __float_as_uint(tf32_hi(v[k]));
+      if (!mbar_wait(smem_u32(&emptyA[grp]), phE)) { atomicExch(p.status, 1); break; }
+      phE ^= 1u;
+      if (herald && it >= kTsGroups) {                  // the MMAs of k-block it - 2 are complete: its filter stage is free too
+        mbar_arrive(smem_u32(&emptyB[sbFree]));
+        sbFree += kTsGroups; if (sbFree >= kTsBStages) sbFree -= kTsBStages;
+      }
+      tc_fence_after();
+      tmem_st32(aAddr, hi);
+      if (kSplit) {
+#pragma unroll
+        for (int k = 0; k < 32; ++k) hi[k] = __float_as_uint(v[k] - __uint_as_float(hi[k]));
+        tmem_st32(aAddr + 32u, hi);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&fullA[grp]));
+    }
+  }
+
+  // ============================== epilogue ==============================
+  // The drain warp and the two producer warps of each TMEM lane quarter share its 32 output rows and deal the
+  // columns in chunks of 16.
+  if (warp < kEpilogueWarps || warp >= kTsFirstProducer) {
+    bool ok = mbar_wait(smem_u32(&accumBar), 0);
+    if (kSplit && ok) ok = mbar_wait(smem_u32(&sumBar), 0);
+    ok = __all_sync(0xffffffffu, ok);
+    tc_fence_after();
+    if (!ok) { if (lane == 0) atomicExch(p.status, 3); }
+    else if (numIter > 0) {
+      int const quarter = warp & 3;
+      int const rank = warp < kEpilogueWarps ? 0 : 1 + ((warp - kTsFirstProducer) >> 2);
+      int const m = m0 + quarter * 32 + lane;
+      int const pix = m % p.e.P, img = m / p.e.P;
+      long long const rowBase = (long long)img * p.e.Ktot * p.e.P + pix;
+      uint32_t const lastT = (uint32_t)(((numChunks - 1) & 1) * BN);
+      for (int c0 = 16 * rank; c0 < BN; c0 += 16 * (1 + kTsGroups)) {
+        uint32_t const laneBase = tmemAcc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
+        uint32_t t0[16], t2[16];
+        tmem_ld16_issue(laneBase + lastT, t0);
+        if (kSplit && numChunks > 1) tmem_ld16_issue(laneBase + colP, t2);
+        tmem_ld_wait();
+        if (m < p.M) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            int const n = n0 + c0 + j;
+            if (n < p.N) {
+              float acc = __uint_as_float(t0[j]);
+              if (kSplit && numChunks > 1) acc += __uint_as_float(t2[j]);
+              float* dst = p.e.out + rowBase + (long long)n * p.e.P;
+              float o = p.e.inMult * acc;
+              if (p.e.bias) o += p.e.bias[n];
+              if (p.e.outMult != 0.f) o += p.e.outMult * *dst;
+              *dst = o;
+            }
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+
+  __syncthreads();
+  tc_fence_after();
+  if (warp == kEpilogueWarps) tmem_dealloc(tmemAcc, tmemCols);
+}
+
 // out[e] = sum over splits (ascending) of part[s*stride + e]
 __global__ void tc_splitk_reduce_kernel(float* __restrict__ out, float const* __restrict__ part, size_t n, size_t stride, int splits)
 {
@@ -1053,6 +1365,38 @@ int launch(vlb_ctx* ctx, Params& p, int splits, char const* where)
   return vlb::check_launch(ctx, where);
 }
 
+// fprop / stride-1 dgrad with the gathered operand in tensor memory (p.bTiles set, p.a a convolution operand).
+int launch_ts(vlb_ctx* ctx, Params& p, char const* where)
+{
+  bool split3 = ctx->precision == VLB_PRECISION_3XTF32;
+  p.status = ctx->deviceStatus;
+  // at least 120 KB, so that two CTAs (each allocating all 512 TMEM columns) never share an SM
+  size_t smemBytes = (size_t)kTsBStages * (split3 ? 2u : 1u) * (size_t)p.BN * BK * 4 + 1024;
+  if (smemBytes < 120u * 1024u) smemBytes = 120u * 1024u;
+  dim3 grid(vlb::ceil_div(p.M, BM), vlb::ceil_div(p.N, p.BN), 1);
+  if (grid.y > 65535u) return VLB_Unsupported;
+  cudaError_t e;
+  vlb_ctx::ProfRec rec;
+  if (ctx->profiling) {
+    cudaEventCreate(&rec.start); cudaEventCreate(&rec.stop);
+    rec.flops = 2.0 * (double)p.M * (double)p.N * (double)p.R;
+    cudaEventRecord(rec.start, ctx->stream);
+  }
+  if (split3) {
+    auto k = conv_ts_kernel<true>;
+    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smemBytes);
+    if (e == cudaSuccess) k<<<grid, kTsThreads, smemBytes, ctx->stream>>>(p);
+  } else {
+    auto k = conv_ts_kernel<false>;
+    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smemBytes);
+    if (e == cudaSuccess) k<<<grid, kTsThreads, smemBytes, ctx->stream>>>(p);
+  }
+  if (ctx->profiling) { cudaEventRecord(rec.stop, ctx->stream); ctx->prof.push_back(rec); }
+  if (e != cudaSuccess) { cudaGetLastError(); return vlb::set_error(ctx, VLB_Cuda, cudaGetErrorString(e)); }
+  VLB_LAUNCHED(ctx, 1);
+  return vlb::check_launch(ctx, where);
+}
+
 // Splits of the reduction so that the grid fills the machine; each split gets whole k-blocks.
 int pick_splits(vlb_ctx* ctx, int tiles, int numKb, int minKbPerSplit)
 {
@@ -1139,6 +1483,7 @@ int conv_fprop_tc(vlb_ctx* ctx, ConvGeom const& g, float* Y, float outMult, floa
     p.bTiles = prep_b_tiles(ctx, F, g.K, V, p.BN, p.numKb, 0, g);
     if (!p.bTiles) return ctx->lastError;
     p.pipelined = 1;
+    if (!getenv("VLB_CONV_SS")) return launch_ts(ctx, p, "conv_fprop_ts");
   }
   return launch<OP_IM2COL, OP_DENSE_K, EPI_CONV>(ctx, p, 1, "conv_fprop_tc");
 }
@@ -1185,6 +1530,7 @@ int conv_dgrad_tc(vlb_ctx* ctx, ConvGeom const& g, float* dX, float const* F, fl
     p.b.ptr = ft; p.b.vec = (V % 4 == 0);
   }
   p.e = Epilogue{}; p.e.out = dX; p.e.inMult = 1.f; p.e.P = g.H * g.W; p.e.Ktot = g.C;
+  if (p.pipelined && !getenv("VLB_CONV_SS")) return launch_ts(ctx, p, "conv_dgrad_ts");
   return launch<OP_IM2COL, OP_DENSE_K, EPI_CONV>(ctx, p, 1, "conv_dgrad_tc");
 }
 
