@@ -90,6 +90,7 @@ struct Params {
   int numKb, kbPerSplit;
   int stages;
   int drainEvery;         // 3xTF32: k-blocks per tensor-core accumulation chain
+  int chanFast;           // conv_ts_kernel: reduction ordered channel-fastest, r = c + C*(fh + FH*fw); needs C % 32 == 0
   int pipelined;          // 1: producers prefetch one stage ahead in registers (aligned gathers only)
   float const* bTiles;    // when non-null: B pre-split into shared-memory tile images, fetched with bulk copies
   int* status;
@@ -1058,24 +1059,36 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
       uint32_t const idesc = make_idesc(false, false, BN);
       uint64_t const descB0 = make_desc(smem_u32(smem), 16, 1024);
       uint32_t const stageStep = bBytes >> 4, loStep = bTileBytes >> 4;
+      // The waits for k-block it + 1 are issued between the two halves of k-block it: the tensor core's
+      // queue is short, and whatever this thread does between two MMAs for longer than about one MMA idles it.
       bool ok = true;
       int sa = 0, sb = 0, inChunk = 0, chunk = 0;
       uint32_t phA = 0;
-      for (int it = 0; it < numIter; ++it) {
+      if (numIter > 0) {
+        ok = mbar_wait(smem_u32(&fullA[0]), 0);
+        if (!ok) atomicExch(p.status, 2);
+        tc_fence_after();
+      }
+      for (int it = 0; it < numIter && ok; ++it) {
         int const tb = chunk & 1;
         bool const chunkStart = kSplit ? inChunk == 0 : it == 0;
-        if (kSplit && chunkStart && chunk >= 2) {      // T[tb] is reused: its previous contents must have been added to P
-          ok = mbar_wait(smem_u32(&drainEmpty[tb]), (uint32_t)(((chunk >> 1) - 1) & 1));
-          if (!ok) { atomicExch(p.status, 6); break; }
-        }
-        ok = mbar_wait(smem_u32(&fullA[sa]), phA);
-        if (!ok) { atomicExch(p.status, 2); break; }
-        tc_fence_after();
         uint64_t const dBh = descB0 + (uint64_t)((uint32_t)sb * stageStep), dBl = dBh + loStep;
         uint32_t const aHi = tmemAcc + colA + (uint32_t)(sa * 64), aLo = aHi + 32u;
         uint32_t const tAcc = tmemAcc + (uint32_t)(tb * BN);
 #pragma unroll
         for (int k8 = 0; k8 < BK / 8; ++k8) {
+          if (k8 == BK / 16 && it + 1 < numIter) {
+            // ---- between the halves: make sure k-block it + 1 can start right after this one
+            int const nsa = sa + 1 == kTsGroups ? 0 : sa + 1;
+            uint32_t const nph = sa + 1 == kTsGroups ? phA ^ 1u : phA;
+            if (kSplit && inChunk + 1 == kTsDrainEvery && chunk + 1 >= 2) {   // it + 1 starts a chain in T[(chunk+1)&1]
+              ok = mbar_wait(smem_u32(&drainEmpty[(chunk + 1) & 1]), (uint32_t)((((chunk + 1) >> 1) - 1) & 1));
+              if (!ok) { atomicExch(p.status, 6); break; }
+            }
+            ok = mbar_wait(smem_u32(&fullA[nsa]), nph);
+            if (!ok) { atomicExch(p.status, 2); break; }
+            tc_fence_after();
+          }
           uint32_t const acc = (chunkStart && k8 == 0) ? 0u : 1u;      // 0 = overwrite: first MMA of a chain
           if (kSplit) {
             asm volatile(
@@ -1088,6 +1101,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
             umma_tf32_ts(tAcc, aHi + 8u * k8, dBh + 2u * k8, idesc, acc);
           }
         }
+        if (!ok) break;
         umma_commit(smem_u32(&emptyA[sa]));      // frees the A stage; its producers pass the news on for the B stage
         if (++sa == kTsGroups) { sa = 0; phA ^= 1u; }
         if (++sb == kTsBStages) sb = 0;
@@ -1150,6 +1164,16 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
       int const r = it * BK;
       int tap = r % taps, ch = r / taps;
       float v[32];
+      if (p.chanFast) {
+        // the whole k-block is one filter tap and 32 consecutive channels: one validity test, constant stride
+        int const tp = r / p.a.C, c0 = r - tp * p.a.C;
+        int2 const te = tapLut[tp];
+        uint32_t const e = (uint32_t)te.y;
+        bool const on = ((hm >> (e & 31u)) & (wm >> (e >> 5)) & 1u) != 0;
+        float const* const q = xq + ((long long)c0 * HW + te.x);
+#pragma unroll
+        for (int k = 0; k < 32; ++k) { v[k] = 0.f; ldg32_if(v[k], q + (long long)k * HW, on); }
+      } else
 #pragma unroll
       for (int k = 0; k < 32; ++k) {
         int2 const te = tapLut[tap];
@@ -1258,6 +1282,7 @@ __global__ void flip_filters_kernel(float* __restrict__ ft, float const* __restr
 // into hi / lo once and laid out as ready-made shared-memory tile images -- for n-tile t and k-block
 // kb: [hi tile BN x 32][lo tile BN x 32], K-major with the 128-byte swizzle -- so that a producer
 // fetches a whole stage of B with one bulk copy.
+// modes 3 / 4: as 0 / 1 with the reduction index ordered channel-fastest.
 // mode 0: B(n, r) = F[n*R + r].  mode 2: B(n, r) = dY[pixel, n, image] with r = pixel + P*image.  mode 1 (data gradient of a stride-1 convolution): n = channel c,
 // r = fh' + FH*(fw' + FW*k), B = F[FH-1-fh', FW-1-fw', c, k].
 template <bool kSplit>
@@ -1276,6 +1301,14 @@ __global__ void prep_b_tiles_kernel(float* __restrict__ out, float const* __rest
         // filter gradient: n = filter, r = pixel + P*image of dY (FH carries P here)
         int img = r / FH, pix = r - img * FH;
         val = f[((size_t)img * N + n) * FH + pix];
+      } else if (mode == 3) {
+        // forward filters, channel-fastest reduction: r = c + C*tap
+        int c = r % C, tap = r / C;
+        val = f[(size_t)n * R + tap + (size_t)(FH * FW) * c];
+      } else if (mode == 4) {
+        // data gradient, channel-fastest reduction: r = k + K*(fh' + FH*fw')
+        int k = r % K, tap = r / K, fh = tap % FH, fw = tap / FH;
+        val = f[(FH - 1 - fh) + (size_t)FH * ((FW - 1 - fw) + (size_t)FW * (n + (size_t)C * k))];
       } else {
         int fh = r % FH, t = r / FH, fw = t % FW, k = t / FW;
         val = f[(FH - 1 - fh) + (size_t)FH * ((FW - 1 - fw) + (size_t)FW * (n + (size_t)C * k))];
@@ -1480,10 +1513,11 @@ int conv_fprop_tc(vlb_ctx* ctx, ConvGeom const& g, float* Y, float outMult, floa
   p.numKb = ceil_div(p.R, BK); p.kbPerSplit = p.numKb;
   p.e = Epilogue{}; p.e.out = Y; p.e.bias = b; p.e.inMult = inMult; p.e.outMult = outMult; p.e.P = g.Ho * g.Wo; p.e.Ktot = g.K;
   if (p.a.fast) {
-    p.bTiles = prep_b_tiles(ctx, F, g.K, V, p.BN, p.numKb, 0, g);
+    p.chanFast = g.C % 32 == 0;
+    p.bTiles = prep_b_tiles(ctx, F, g.K, V, p.BN, p.numKb, p.chanFast ? 3 : 0, g);
     if (!p.bTiles) return ctx->lastError;
     p.pipelined = 1;
-    if (!getenv("VLB_CONV_SS")) return launch_ts(ctx, p, "conv_fprop_ts");
+    return launch_ts(ctx, p, "conv_fprop_ts");
   }
   return launch<OP_IM2COL, OP_DENSE_K, EPI_CONV>(ctx, p, 1, "conv_fprop_tc");
 }
@@ -1517,7 +1551,8 @@ int conv_dgrad_tc(vlb_ctx* ctx, ConvGeom const& g, float* dX, float const* F, fl
   p.numKb = ceil_div(p.R, BK); p.kbPerSplit = p.numKb;
   p.b = Operand{}; p.b.ld = V; p.b.rows = g.C;
   if (p.a.fast) {
-    p.bTiles = prep_b_tiles(ctx, F, g.C, V, p.BN, p.numKb, 1, g);
+    p.chanFast = g.K % 32 == 0;
+    p.bTiles = prep_b_tiles(ctx, F, g.C, V, p.BN, p.numKb, p.chanFast ? 4 : 1, g);
     if (!p.bTiles) return ctx->lastError;
     p.b.ptr = p.bTiles;          // not read by the pipelined producers
     p.pipelined = 1;
@@ -1530,7 +1565,7 @@ int conv_dgrad_tc(vlb_ctx* ctx, ConvGeom const& g, float* dX, float const* F, fl
     p.b.ptr = ft; p.b.vec = (V % 4 == 0);
   }
   p.e = Epilogue{}; p.e.out = dX; p.e.inMult = 1.f; p.e.P = g.H * g.W; p.e.Ktot = g.C;
-  if (p.pipelined && !getenv("VLB_CONV_SS")) return launch_ts(ctx, p, "conv_dgrad_ts");
+  if (p.pipelined) return launch_ts(ctx, p, "conv_dgrad_ts");
   return launch<OP_IM2COL, OP_DENSE_K, EPI_CONV>(ctx, p, 1, "conv_dgrad_tc");
 }
 

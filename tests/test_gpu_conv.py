@@ -85,6 +85,11 @@ LAYERS = {
     "odd_dilate2": ((15, 13, 4, 2), (3, 3, 4, 8), 1, 2, 2),
     "odd_groups": ((10, 10, 8, 2), (3, 3, 2, 12), 1, 1, 1),
     "odd_nobias_ragged": ((9, 11, 5, 3), (2, 4, 5, 7), (1, 2), (0, 1, 2, 0), 1),
+    # channel counts that are multiples of 32 (one filter tap per 32-deep reduction block) with strides, dilation,
+    # asymmetric padding, a ragged last row tile, and 96 = 3 x 32 channels (not a multiple of 64)
+    "c32_stride2_pad": ((19, 17, 32, 3), (3, 3, 32, 40), 2, (1, 0, 2, 1), 1),
+    "c96_dilate2": ((15, 14, 96, 2), (3, 2, 96, 72), 1, (2, 2, 1, 1), (2, 1)),
+    "c64_5x5_stride_1_2": ((13, 21, 64, 2), (5, 5, 64, 33), (1, 2), 2, 1),
 }
 
 

@@ -110,7 +110,10 @@ def test_c2_cifar_net(gpu, oracle):
     res, ref = _run_both(gpu, oracle, net, x, 1.0)
     loss = float(res[-1]["x"].cpu()[0])
     assert abs(loss - float(ref[-1]["x"])) <= 1e-5 * abs(float(ref[-1]["x"]))
-    _compare(res, ref, mat, net["layers"])
+    # end to end a ReLU / max-pool decision on an activation within rounding of a tie may flip and change the gradients
+    # below it by whole elements: loose bound end to end, the per-layer bound in the replay
+    _compare(res, ref, mat, net["layers"], tol=5e-3)
+    _replay(res, mat, oracle, net["layers"])
 
 
 def test_c3_resnet_bottleneck(gpu, oracle):
