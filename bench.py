@@ -166,6 +166,9 @@ def main():
     assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path in this engine)"
     torch.cuda.set_device(local)
     if world > 1:
+        # NCCL_DEBUG=VERSION makes NCCL print a banner on stdout, where only the JSON line belongs
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     warmup = max(args.warmup, 3)
 
