@@ -544,42 +544,46 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
     if (lane == 0) {
       uint32_t const idesc = make_idesc(kAMN, kBMN, BN);
       uint32_t aLbo = 512, aSbo = (BM / 32) * 512, bLbo = 512, bSbo = (uint32_t)(BN / 32) * 512;
+      // The issuing thread is the critical resource (the tensor core's queue is about one MMA deep, and the
+      // thread shares its scheduler with busy producer warps): running counters instead of divisions, and
+      // descriptors derived from one per-stage base with 64-bit adds.
+      uint64_t const dA0 = kAMN ? make_desc(smem_u32(smem), aLbo, aSbo, 1) : make_desc(smem_u32(smem), 16, 1024);
+      uint64_t const dB0 = kBMN ? make_desc(smem_u32(smem) + (kSplit ? 2u : 1u) * aTileBytes, bLbo, bSbo, 1)
+                                : make_desc(smem_u32(smem) + (kSplit ? 2u : 1u) * aTileBytes, 16, 1024);
+      uint32_t const aAdv = (kAMN ? (uint32_t)(BM / 32) * 1024u : 32u) >> 4, bAdv = (kBMN ? (uint32_t)(BN / 32) * 1024u : 32u) >> 4;
+      uint32_t const stageStep = stageBytes >> 4, aLoStep = aTileBytes >> 4, bLoStep = bTileBytes >> 4;
       bool ok = true;
+      int s = 0, inChunk = 0, chunk = 0;
+      uint32_t ph = 0;
       for (int it = 0; it < numIter && ok; ++it) {
-        int s = it % p.stages;
-        int const chunk = it / p.drainEvery, tb = kSplit ? (chunk & 1) : 0;
-        bool const chunkStart = it % p.drainEvery == 0;
+        int const tb = kSplit ? (chunk & 1) : 0;
+        bool const chunkStart = inChunk == 0;
         if (kSplit && chunkStart && chunk >= 2) {      // T[tb] is reused: its previous contents must have been added to P
           ok = mbar_wait(smem_u32(&drainEmpty[tb]), (uint32_t)(((chunk >> 1) - 1) & 1));
           if (!ok) { atomicExch(p.status, 6); break; }
-          tc_fence_after();
         }
-        ok = mbar_wait(smem_u32(&fullBar[s]), (uint32_t)((it / p.stages) & 1));
+        ok = mbar_wait(smem_u32(&fullBar[s]), ph);
         if (!ok) { atomicExch(p.status, 2); break; }
         tc_fence_after();
-        uint32_t base = smem_u32(smem + (size_t)s * stageBytes);
-        uint32_t aHi = base, aLo = base + aTileBytes;
-        uint32_t bHi = base + (kSplit ? 2u : 1u) * aTileBytes, bLo = bHi + bTileBytes;
+        uint64_t const dAh0 = dA0 + (uint64_t)((uint32_t)s * stageStep), dBh0 = dB0 + (uint64_t)((uint32_t)s * stageStep);
+        uint32_t const tmemBig = tmemAcc + (uint32_t)(tb * BN), tmemSmall = tmemAcc + (uint32_t)(3 * BN);
 #pragma unroll
         for (int k4 = 0; k4 < BK / 8; ++k4) {
-          uint32_t aAdv = kAMN ? (uint32_t)k4 * (BM / 32) * 1024u : (uint32_t)k4 * 32u;     // two k quads per MMA
-          uint32_t bAdv = kBMN ? (uint32_t)k4 * (uint32_t)(BN / 32) * 1024u : (uint32_t)k4 * 32u;
-          uint64_t dAh = kAMN ? make_desc(aHi + aAdv, aLbo, aSbo, 1) : make_desc(aHi + aAdv, 16, 1024);
-          uint64_t dBh = kBMN ? make_desc(bHi + bAdv, bLbo, bSbo, 1) : make_desc(bHi + bAdv, 16, 1024);
+          uint64_t const dAh = dAh0 + (uint64_t)(aAdv * k4), dBh = dBh0 + (uint64_t)(bAdv * k4);
           if (kSplit) {
-            uint32_t const tmemBig = tmemAcc + (uint32_t)(tb * BN), tmemSmall = tmemAcc + (uint32_t)(3 * BN);
-            uint64_t dAl = kAMN ? make_desc(aLo + aAdv, aLbo, aSbo, 1) : make_desc(aLo + aAdv, 16, 1024);
-            uint64_t dBl = kBMN ? make_desc(bLo + bAdv, bLbo, bSbo, 1) : make_desc(bLo + bAdv, 16, 1024);
-            umma_tf32(tmemSmall, dAl, dBh, idesc, (it > 0 || k4 > 0) ? 1u : 0u);     // 0 = overwrite
-            umma_tf32(tmemSmall, dAh, dBl, idesc, 1u);
+            umma_tf32(tmemSmall, dAh + aLoStep, dBh, idesc, (it > 0 || k4 > 0) ? 1u : 0u);     // 0 = overwrite
+            umma_tf32(tmemSmall, dAh, dBh + bLoStep, idesc, 1u);
             umma_tf32(tmemBig, dAh, dBh, idesc, (!chunkStart || k4 > 0) ? 1u : 0u);
           } else {
             umma_tf32(tmemAcc, dAh, dBh, idesc, (it > 0 || k4 > 0) ? 1u : 0u);
           }
         }
         umma_commit(smem_u32(&emptyBar[s]));    // frees the stage once these MMAs have read it
-        if (kSplit && chunk + 1 < numChunks && it % p.drainEvery == p.drainEvery - 1)
-          umma_commit(smem_u32(&drainFull[tb]));   // this chunk's T is complete: hand it to the drain warps
+        if (++s == p.stages) { s = 0; ph ^= 1u; }
+        if (++inChunk == p.drainEvery) {
+          if (kSplit && chunk + 1 < numChunks) umma_commit(smem_u32(&drainFull[tb]));   // this chain's T is complete: hand it to the drain warps
+          inChunk = 0; ++chunk;
+        }
       }
       umma_commit(smem_u32(&accumBar));         // accumulator complete (or nothing was issued)
     }
