@@ -1,7 +1,9 @@
 // Batch normalisation (vl::nn::BatchNorm, reference bits/nnbnorm.hpp:22-59;
 // CPU definition bits/nnbnorm.cu:46-164).
 //
-// HBM-bound, two passes:
+// HBM-bound.  The regular entry points run one fused launch (bnorm_fused_kernel below: reduce, derive the
+// coefficients, apply, all by the cluster that owns the channel); forward with given moments and the
+// allocation-free entry point use the separate passes:
 //   1. reduce: per channel sum(x), sum(x^2) [, sum(dy*x), sum(dy)].  A channel is split
 //      across a thread-block CLUSTER of kCluster CTAs (C alone would leave most of the
 //      148 SMs idle: the reference launches exactly C blocks, bits/nnbnorm_gpu.cu:1113).
@@ -120,6 +122,155 @@ bnorm_reduce_kernel(float* __restrict__ momentsOut,   // 2*C or nullptr
     }
   }
   cluster.sync();   // keep every CTA's shared memory alive until rank 0 has read it
+}
+
+// One launch for the whole operator: the cluster that reduced a channel also applies it.
+// After the reduction rank 0 derives the channel's coefficients into its shared memory, the other
+// CTAs read them through distributed shared memory, and every CTA sweeps the same items again --
+// they are still in L2 (a channel's x and dy, 8*m bytes, times the clusters in flight), so DRAM sees
+// x and dy once and the result once: 12*m*C bytes backward, 8*m*C forward.
+// kMode 0: forward, moments computed.  1: backward, moments computed.  2: backward, moments given.
+template <int kMode, bool kVec>
+__global__ void __cluster_dims__(1, kCluster, 1) __launch_bounds__(kThreads)
+bnorm_fused_kernel(float* __restrict__ out,            // y or dx
+                   float* __restrict__ momentsOut,     // 2*C or nullptr
+                   float* __restrict__ dgOut, float* __restrict__ dbOut,
+                   float const* __restrict__ momentsIn,  // mode 2
+                   float const* __restrict__ x, float const* __restrict__ dy,
+                   float const* __restrict__ g, float const* __restrict__ b,
+                   int WH, int C, int N, float eps)
+{
+  cg::cluster_group cluster = cg::this_cluster();
+  __shared__ float part[4];
+  __shared__ float coef[4];
+  __shared__ float warpRed[kThreads / 32][4];
+  int const c = blockIdx.x;
+  int const rank = (int)cluster.block_rank();   // the cluster spans grid y
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  int const WH4 = WH >> 2;
+  long long const items = kVec ? (long long)N * WH4 : (long long)N * WH;
+  long long const first = (long long)rank * kThreads + threadIdx.x, step = (long long)kCluster * kThreads;
+
+#pragma unroll 4
+  for (long long i = first; i < items; i += step) {
+    if (kVec) {
+      int n = (int)(i / WH4);
+      int q = (int)(i - (long long)n * WH4);
+      size_t off = ((size_t)n * C + c) * (size_t)WH + 4 * (size_t)q;
+      float4 xv = *reinterpret_cast<float4 const*>(x + off);
+      float4 dv = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (kMode != 0) dv = *reinterpret_cast<float4 const*>(dy + off);
+      if (kMode == 2) {
+        acc[2] = fmaf(dv.x, xv.x, acc[2]); acc[2] = fmaf(dv.y, xv.y, acc[2]);
+        acc[2] = fmaf(dv.z, xv.z, acc[2]); acc[2] = fmaf(dv.w, xv.w, acc[2]);
+        acc[3] += (dv.x + dv.y) + (dv.z + dv.w);
+      } else {
+        accumulate<kMode == 0 ? 2 : 4>(acc, xv.x, dv.x);
+        accumulate<kMode == 0 ? 2 : 4>(acc, xv.y, dv.y);
+        accumulate<kMode == 0 ? 2 : 4>(acc, xv.z, dv.z);
+        accumulate<kMode == 0 ? 2 : 4>(acc, xv.w, dv.w);
+      }
+    } else {
+      int n = (int)(i / WH);
+      int q = (int)(i - (long long)n * WH);
+      size_t off = ((size_t)n * C + c) * (size_t)WH + q;
+      float xv = x[off];
+      float dv = (kMode != 0) ? dy[off] : 0.f;
+      if (kMode == 2) { acc[2] = fmaf(dv, xv, acc[2]); acc[3] += dv; }
+      else accumulate<kMode == 0 ? 2 : 4>(acc, xv, dv);
+    }
+  }
+
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    for (int o = 16; o > 0; o >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+  int const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) { for (int j = 0; j < 4; ++j) warpRed[warp][j] = acc[j]; }
+  __syncthreads();
+  if (threadIdx.x < 4) {
+    float s = 0.f;
+    for (int w = 0; w < kThreads / 32; ++w) s += warpRed[w][threadIdx.x];
+    part[threadIdx.x] = s;
+  }
+  cluster.sync();
+  if (rank == 0 && threadIdx.x == 0) {
+    float tot[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < kCluster; ++r) {
+      float const* remote = cluster.map_shared_rank(part, r);
+      for (int j = 0; j < 4; ++j) tot[j] += remote[j];
+    }
+    float const mass = (float)((long long)WH * N);
+    float mean, sigma;
+    if (kMode == 2) { mean = momentsIn[c]; sigma = momentsIn[c + C]; }
+    else {
+      // reference bits/nnbnorm.cu:65-70
+      mean = __fdiv_rn(tot[0], mass);
+      float s2 = __fadd_rn(__fdiv_rn(tot[1], mass), -__fmul_rn(mean, mean));
+      s2 = fmaxf(s2, 0.f);
+      sigma = __fsqrt_rn(__fadd_rn(s2, eps));
+      if (momentsOut) { momentsOut[c] = mean; momentsOut[c + C] = sigma; }
+    }
+    float const G1 = __fdiv_rn(g[c], sigma);
+    if (kMode != 0) {
+      // reference bits/nnbnorm.cu:94-98, 148-153
+      float const dbv = tot[3];
+      float const dgv = __fdiv_rn(__fadd_rn(tot[2], -__fmul_rn(mean, tot[3])), sigma);
+      dbOut[c] = dbv;
+      dgOut[c] = dgv;
+      coef[0] = mean; coef[1] = __fdiv_rn(dbv, mass); coef[2] = G1;
+      coef[3] = __fdiv_rn(__fmul_rn(G1, dgv), __fmul_rn(mass, sigma));
+    } else {
+      // reference bits/nnbnorm.cu:192-196
+      coef[0] = mean; coef[1] = G1; coef[2] = b[c]; coef[3] = 0.f;
+    }
+  }
+  cluster.sync();
+  float k0, k1, k2, k3;
+  {
+    float const* rc = cluster.map_shared_rank(coef, 0);
+    k0 = rc[0]; k1 = rc[1]; k2 = rc[2]; k3 = rc[3];
+  }
+  cluster.sync();   // rank 0's shared memory has been read by everyone
+
+#pragma unroll 4
+  for (long long i = first; i < items; i += step) {
+    if (kVec) {
+      int n = (int)(i / WH4);
+      int q = (int)(i - (long long)n * WH4);
+      size_t off = ((size_t)n * C + c) * (size_t)WH + 4 * (size_t)q;
+      float4 xv = *reinterpret_cast<float4 const*>(x + off);
+      float4 o;
+      if (kMode == 0) {
+        o.x = __fadd_rn(__fmul_rn(k1, __fadd_rn(xv.x, -k0)), k2);
+        o.y = __fadd_rn(__fmul_rn(k1, __fadd_rn(xv.y, -k0)), k2);
+        o.z = __fadd_rn(__fmul_rn(k1, __fadd_rn(xv.z, -k0)), k2);
+        o.w = __fadd_rn(__fmul_rn(k1, __fadd_rn(xv.w, -k0)), k2);
+      } else {
+        float4 dv = *reinterpret_cast<float4 const*>(dy + off);
+        o.x = __fadd_rn(__fmul_rn(k2, __fadd_rn(dv.x, -k1)), -__fmul_rn(k3, __fadd_rn(xv.x, -k0)));
+        o.y = __fadd_rn(__fmul_rn(k2, __fadd_rn(dv.y, -k1)), -__fmul_rn(k3, __fadd_rn(xv.y, -k0)));
+        o.z = __fadd_rn(__fmul_rn(k2, __fadd_rn(dv.z, -k1)), -__fmul_rn(k3, __fadd_rn(xv.z, -k0)));
+        o.w = __fadd_rn(__fmul_rn(k2, __fadd_rn(dv.w, -k1)), -__fmul_rn(k3, __fadd_rn(xv.w, -k0)));
+      }
+      *reinterpret_cast<float4*>(out + off) = o;
+    } else {
+      int n = (int)(i / WH);
+      int q = (int)(i - (long long)n * WH);
+      size_t off = ((size_t)n * C + c) * (size_t)WH + q;
+      if (kMode == 0) out[off] = __fadd_rn(__fmul_rn(k1, __fadd_rn(x[off], -k0)), k2);
+      else out[off] = __fadd_rn(__fmul_rn(k2, __fadd_rn(dy[off], -k1)), -__fmul_rn(k3, __fadd_rn(x[off], -k0)));
+    }
+  }
+}
+
+template <int kMode>
+void launch_fused(vlb_ctx* ctx, bool vec, float* out, float* momOut, float* dg, float* db, float const* momIn,
+                  float const* x, float const* dy, float const* g, float const* b, int WH, int C, int N, float eps)
+{
+  dim3 grid(C, kCluster);
+  if (vec) bnorm_fused_kernel<kMode, true><<<grid, kThreads, 0, ctx->stream>>>(out, momOut, dg, db, momIn, x, dy, g, b, WH, C, N, eps);
+  else     bnorm_fused_kernel<kMode, false><<<grid, kThreads, 0, ctx->stream>>>(out, momOut, dg, db, momIn, x, dy, g, b, WH, C, N, eps);
+  VLB_LAUNCHED(ctx, 1);
 }
 
 // Per-channel coefficients, computed once so that pass 2 is pure multiply/add.
@@ -247,10 +398,10 @@ static int forward_common(vlb_ctx* ctx, float* Y, float* momOut, float const* mo
   int WH = H * W;
   float const* mom = momIn;
   if (!momIn) {
-    // reference: moments computed into the context workspace when not asked for (bits/nnbnorm.cu:233-240)
-    float* m = momOut ? momOut : ownMom;
-    launch_reduce<0>(ctx, vec_ok(WH, X, X, X), m, nullptr, nullptr, nullptr, X, nullptr, WH, C, N, (float)eps);
-    mom = m;
+    // moments computed and applied by the same clusters (the reference computes them into the context
+    // workspace when the caller does not ask for them, bits/nnbnorm.cu:233-240)
+    launch_fused<0>(ctx, vec_ok(WH, Y, X, X), Y, momOut, nullptr, nullptr, nullptr, X, nullptr, g, b, WH, C, N, (float)eps);
+    return vlb::check_launch(ctx, where);
   }
   bnorm_coef_kernel<<<vlb::ceil_div(C, 256), 256, 0, ctx->stream>>>(cf, mom, g, b, nullptr, nullptr, C, 0.f);
   size_t total = (size_t)WH * C * N;
@@ -269,26 +420,10 @@ static int backward_common(vlb_ctx* ctx, float* dX, float* dG, float* dB, float*
   int rc = validate(ctx, H, W, C, N);
   if (rc) return rc;
   VLB_REQUIRE(ctx, dX && dG && dB && X && g && dY, "bnorm_backward: null tensor");
-  float4* cf = nullptr;
-  float* ownMom = scratch(ctx, C, &cf);
-  if (!ownMom) return vlb::pass_error(ctx, ctx->lastError, where);
   int WH = H * W;
-  float const* mom = momIn;
   bool vec = vec_ok(WH, X, dY, dX);
-  if (!momIn) {
-    float* m = momOut ? momOut : ownMom;
-    launch_reduce<1>(ctx, vec, m, dG, dB, nullptr, X, dY, WH, C, N, (float)eps);
-    mom = m;
-  } else {
-    launch_reduce<2>(ctx, vec, nullptr, dG, dB, momIn, X, dY, WH, C, N, (float)eps);
-  }
-  float mass = (float)((long long)WH * N);
-  bnorm_coef_kernel<<<vlb::ceil_div(C, 256), 256, 0, ctx->stream>>>(cf, mom, g, nullptr, dG, dB, C, mass);
-  size_t total = (size_t)WH * C * N;
-  unsigned grid = vlb::grid_for(vec ? total / 4 : total, kThreads, ctx->smCount * 16);
-  if (vec) bnorm_bwd_apply_kernel<true><<<grid, kThreads, 0, ctx->stream>>>(dX, X, dY, cf, WH, C, total);
-  else     bnorm_bwd_apply_kernel<false><<<grid, kThreads, 0, ctx->stream>>>(dX, X, dY, cf, WH, C, total);
-  VLB_LAUNCHED(ctx, 2);
+  if (!momIn) launch_fused<1>(ctx, vec, dX, momOut, dG, dB, nullptr, X, dY, g, nullptr, WH, C, N, (float)eps);
+  else        launch_fused<2>(ctx, vec, dX, nullptr, dG, dB, momIn, X, dY, g, nullptr, WH, C, N, (float)eps);
   return vlb::check_launch(ctx, where);
 }
 
