@@ -20,7 +20,8 @@ struct vlb_ctx {
   std::string lastErrorMessage;
   long long launches = 0;
   int smCount = 148;
-  int* deviceStatus = nullptr;   // one word the tensor-core kernels set when a bounded wait expires
+  int* deviceStatus = nullptr;   // one word the tensor-core kernels set when a bounded wait expires; behind it (byte 256)
+                                 // 4096 zeroed ticket counters for last-block-finishes reductions, left at zero by their users
   // optional timing of the tensor-core launches with events on the launching stream
   struct ProfRec { cudaEvent_t start, stop; double flops; };
   bool profiling = false;

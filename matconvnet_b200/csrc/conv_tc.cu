@@ -1331,6 +1331,75 @@ __global__ void prep_b_tiles_kernel(float* __restrict__ out, float const* __rest
   }
 }
 
+// dY of a filter gradient as tile images (mode 2 of prep_b_tiles_kernel) for planes that are a multiple of
+// four pixels: 16-byte loads along the pixels, 16-byte stores of the swizzled chunks, and -- dY being read
+// anyway -- the bias gradient db[n] = sum of dY over pixels and images (reference bits/nnconv.cu:141-149) on
+// the way: per-block partial sums, and the block that takes a channel's last ticket adds them in block order,
+// so the result does not depend on the scheduling.
+// grid (blocks per channel, channels rounded up to the tile), kPrepThreads threads, kPrepIters float4 per thread.
+constexpr int kPrepThreads = 256, kPrepIters = 4;
+
+template <bool kSplit>
+__global__ void __launch_bounds__(kPrepThreads)
+prep_dy_tiles_kernel(float* __restrict__ out, float const* __restrict__ dy, int N, int R, int P, int BN, int numKb,
+                     float* __restrict__ db, float* __restrict__ dbPart, unsigned* __restrict__ tickets)
+{
+  __shared__ float red[kPrepThreads / 32];
+  __shared__ bool last;
+  int const n = blockIdx.y, tile = n / BN, row = n % BN;
+  int const Rp = numKb * 32;
+  float sum = 0.f;
+#pragma unroll
+  for (int u = 0; u < kPrepIters; ++u) {
+    int const r = ((int)blockIdx.x * kPrepIters + u) * (kPrepThreads * 4) + (int)threadIdx.x * 4;
+    if (r < Rp) {
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (n < N && r < R) {
+        int const img = r / P, pix = r - img * P;
+        v = *reinterpret_cast<float4 const*>(dy + ((size_t)img * N + n) * P + pix);
+      }
+      sum += (v.x + v.y) + (v.z + v.w);
+      int const kb = r >> 5, kk = r & 31;
+      size_t const base = ((size_t)tile * numKb + kb) * (kSplit ? 2 : 1) * (size_t)BN * 32;
+      size_t const off = (size_t)row * 32 + (size_t)((((kk >> 2) ^ (row & 7)) << 2));
+      if (kSplit) {
+        float4 h = make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w));
+        *reinterpret_cast<float4*>(out + base + off) = h;
+        *reinterpret_cast<float4*>(out + base + (size_t)BN * 32 + off) = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
+      } else {
+        *reinterpret_cast<float4*>(out + base + off) = v;
+      }
+    }
+  }
+  if (db == nullptr || n >= N) return;
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+    for (int w = 0; w < kPrepThreads / 32; ++w) s += red[w];
+    dbPart[(size_t)n * gridDim.x + blockIdx.x] = s;
+    __threadfence();
+    last = atomicAdd(&tickets[n], 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  // the channel's partials in block order: strided per-thread sums, then a fixed tree
+  float s = 0.f;
+  for (unsigned i = threadIdx.x; i < gridDim.x; i += kPrepThreads) s += __ldcg(dbPart + (size_t)n * gridDim.x + i);
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < kPrepThreads / 32; ++w) t += red[w];
+    db[n] = t;
+    tickets[n] = 0;      // ready for the next call
+  }
+}
+
 // Builds the tile images in the context's scratch; returns nullptr (error set) on failure.
 size_t b_tiles_bytes(vlb_ctx* ctx, int N, int BN, int numKb)
 {
@@ -1357,6 +1426,28 @@ float const* prep_b_tiles(vlb_ctx* ctx, float const* f, int N, int R, int BN, in
   unsigned grid = vlb::grid_for(total, 256, ctx->smCount * 8);
   if (split3) prep_b_tiles_kernel<true><<<grid, 256, 0, ctx->stream>>>(tiles, f, N, R, BN, numKb, mode, g.FH, g.FW, g.C, g.K);
   else        prep_b_tiles_kernel<false><<<grid, 256, 0, ctx->stream>>>(tiles, f, N, R, BN, numKb, mode, g.FH, g.FW, g.C, g.K);
+  VLB_LAUNCHED(ctx, 1);
+  return tiles;
+}
+
+// dY tile images with 16-byte accesses and, when db is given, the bias gradient from the same sweep.
+// Scratch layout: [tiles][extraBytes for the caller][per-block partial sums of db].
+float const* prep_dy_tiles(vlb_ctx* ctx, float const* dY, int K, int R, int P, int BN, int numKb, size_t extraBytes, float* db)
+{
+  bool split3 = ctx->precision == VLB_PRECISION_3XTF32;
+  size_t const tileBytes = b_tiles_bytes(ctx, K, BN, numKb);
+  int const perBlock = kPrepThreads * 4 * kPrepIters;
+  unsigned const bx = (unsigned)vlb::ceil_div((long long)numKb * 32, perBlock);
+  size_t const partBytes = db ? sizeof(float) * (size_t)K * bx : 0;
+  extraBytes = (extraBytes + 255) & ~(size_t)255;
+  char* ws = (char*)vlb::workspace(ctx, tileBytes + extraBytes + partBytes);
+  if (!ws) return nullptr;
+  float* tiles = (float*)ws;
+  float* dbPart = db ? (float*)(ws + tileBytes + extraBytes) : nullptr;
+  unsigned* tickets = (unsigned*)((char*)ctx->deviceStatus + 256);
+  dim3 grid(bx, (unsigned)(vlb::ceil_div(K, BN) * BN));
+  if (split3) prep_dy_tiles_kernel<true><<<grid, kPrepThreads, 0, ctx->stream>>>(tiles, dY, K, R, P, BN, numKb, db, dbPart, tickets);
+  else        prep_dy_tiles_kernel<false><<<grid, kPrepThreads, 0, ctx->stream>>>(tiles, dY, K, R, P, BN, numKb, db, dbPart, tickets);
   VLB_LAUNCHED(ctx, 1);
   return tiles;
 }
@@ -1575,7 +1666,6 @@ int conv_dgrad_tc(vlb_ctx* ctx, ConvGeom const& g, float* dX, float const* F, fl
 
 int conv_wgrad_tc(vlb_ctx* ctx, ConvGeom const& g, float* dF, float* db, float const* X, float const* dY, bool* dbDone)
 {
-  (void)db;
   *dbDone = false;
   if (g.G != 1 || !fits32(g)) return VLB_Unsupported;
   int const V = g.FH * g.FW * g.FC;
@@ -1610,7 +1700,13 @@ int conv_wgrad_tc(vlb_ctx* ctx, ConvGeom const& g, float* dF, float* db, float c
   if (p.a.fast) {
     // dY is split into hi / lo once and laid out as tile images, like the filters of fprop
     tileBytes = b_tiles_bytes(ctx, g.K, p.BN, p.numKb);
-    p.bTiles = prep_b_tiles(ctx, dY, g.K, p.R, p.BN, p.numKb, 2, g, partBytes, P);
+    partBytes = (partBytes + 255) & ~(size_t)255;
+    if (P % 4 == 0 && aligned16(dY) && g.K <= 4096 && vlb::ceil_div(g.K, p.BN) * p.BN <= 65535) {
+      p.bTiles = prep_dy_tiles(ctx, dY, g.K, p.R, P, p.BN, p.numKb, partBytes, db);
+      *dbDone = db != nullptr;
+    } else {
+      p.bTiles = prep_b_tiles(ctx, dY, g.K, p.R, p.BN, p.numKb, 2, g, partBytes, P);
+    }
     if (!p.bTiles) return ctx->lastError;
     p.pipelined = 1;
   }

@@ -86,7 +86,7 @@ int vlb_ctx_create(vlb_ctx** out)
   vlb_ctx* c = new vlb_ctx();
   c->device = dev;
   c->smCount = prop.multiProcessorCount;
-  if (cudaMalloc((void**)&c->deviceStatus, 256) != cudaSuccess || cudaMemset(c->deviceStatus, 0, 256) != cudaSuccess) {
+  if (cudaMalloc((void**)&c->deviceStatus, 256 + 4 * 4096) != cudaSuccess || cudaMemset(c->deviceStatus, 0, 256 + 4 * 4096) != cudaSuccess) {
     cudaGetLastError();
     delete c;
     return VLB_OutOfGPUMemeory;
