@@ -132,6 +132,8 @@ int vlb_conv_forward(vlb_ctx* ctx, float* Y, double outMult, float const* X, dou
   int rc = make_geom(ctx, d, &g);
   if (rc) return vlb::pass_error(ctx, rc, "vlb_conv_forward");
   VLB_REQUIRE(ctx, Y && X && F, "conv_forward: null tensor");
+  rc = vlb::conv_fprop_small(ctx, g, Y, (float)outMult, X, (float)inMult, F, b);
+  if (rc != VLB_Unsupported) return rc ? vlb::pass_error(ctx, rc, "vlb_conv_forward") : rc;
   if (ctx->precision != VLB_PRECISION_FP32) {
     rc = vlb::conv_fprop_tc(ctx, g, Y, (float)outMult, X, (float)inMult, F, b);
     if (rc != VLB_Unsupported) return rc ? vlb::pass_error(ctx, rc, "vlb_conv_forward") : rc;
@@ -162,7 +164,8 @@ int vlb_conv_backward(vlb_ctx* ctx, float* dX, float* dF, float* db, float const
     if (rc) return vlb::pass_error(ctx, rc, "vlb_conv_backward");
   }
   if (dX) {
-    rc = tc ? vlb::conv_dgrad_tc(ctx, g, dX, F, dY) : VLB_Unsupported;
+    rc = vlb::conv_dgrad_small(ctx, g, dX, F, dY);
+    if (rc == VLB_Unsupported) rc = tc ? vlb::conv_dgrad_tc(ctx, g, dX, F, dY) : VLB_Unsupported;
     if (rc == VLB_Unsupported) rc = vlb::conv_dgrad_simt(ctx, g, dX, F, dY);
     if (rc) return vlb::pass_error(ctx, rc, "vlb_conv_backward");
   }

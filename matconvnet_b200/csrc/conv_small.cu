@@ -1,0 +1,219 @@
+// Direct CUDA-core convolutions for the two shapes at the image end of a network that a 128 x N
+// tensor-core tile serves badly (reference bits/nnconv.cu:71-317 computes them with the same im2row +
+// GEMM as every other layer):
+//   * few input values per output pixel (R = FH*FW*C <= 64, e.g. a 3x3 filter on an RGB image): the
+//     tensor-core kernel would run one k-block per CTA and be all prologue and epilogue;
+//   * few output channels (<= 4, e.g. the data gradient of that first layer): 125 of the tile's 128
+//     columns would be padding.
+// Both are one thread per output pixel, so that loads and stores are coalesced along H (the fastest
+// dimension of the MATLAB layout), with the filters in shared memory read as broadcasts.  Exact fp32 FMAs:
+// the results are at least as accurate as the 3xTF32 arithmetic of the tensor-core path.
+#include "conv_internal.cuh"
+
+namespace {
+
+using vlb::ConvGeom;
+
+constexpr int kThreads = 256;
+
+struct SmallParams {
+  float const* x;       // input (or dY for a data gradient), H x W x Cin x N
+  float const* f;       // filter bank as stored, FH x FW x FC x K
+  float* out;           // Ho x Wo x Kout x N
+  float const* bias;    // per output channel or nullptr
+  float inMult, outMult;
+  int H, W, Cin, N, Ho, Wo, Kout;
+  int FH, FW, sy, sx, pt, pl, dy, dx;
+  int flip;             // 0: forward filters F[fh,fw,c,k]; 1: data gradient, F[FH-1-fh, FW-1-fw, k(out), c(in)]
+  int Cf;               // the filter bank's third extent (channels of the forward input)
+};
+
+// Pixel of this thread, element offset of its window origin and which tap rows / columns are inside the image.
+struct Pix { long long base; uint32_t hm, wm; bool valid; long long outBase; };
+
+__device__ __forceinline__ Pix pixel_of(SmallParams const& p, long long m)
+{
+  Pix q = {0, 0u, 0u, false, 0};
+  long long const M = (long long)p.Ho * p.Wo * p.N;
+  if (m >= M) return q;
+  int const ho = (int)(m % p.Ho);
+  long long const t = m / p.Ho;
+  int const wo = (int)(t % p.Wo), n = (int)(t / p.Wo);
+  q.valid = true;
+  q.base = (long long)n * p.H * p.W * p.Cin + (long long)(wo * p.sx - p.pl) * p.H + (ho * p.sy - p.pt);
+  for (int fh = 0; fh < p.FH; ++fh) { int h = ho * p.sy + fh * p.dy - p.pt; if (h >= 0 && h < p.H) q.hm |= 1u << fh; }
+  for (int fw = 0; fw < p.FW; ++fw) { int w = wo * p.sx + fw * p.dx - p.pl; if (w >= 0 && w < p.W) q.wm |= 1u << fw; }
+  q.outBase = (long long)n * p.Kout * p.Ho * p.Wo + (long long)wo * p.Ho + ho;
+  return q;
+}
+
+__device__ __forceinline__ float filter_at(SmallParams const& p, int fh, int fw, int cin, int kout)
+{
+  if (!p.flip) return p.f[fh + (size_t)p.FH * (fw + (size_t)p.FW * (cin + (size_t)p.Cf * kout))];
+  // data gradient: "input channel" cin is a filter index, "output channel" kout an image channel
+  return p.f[(p.FH - 1 - fh) + (size_t)p.FH * ((p.FW - 1 - fw) + (size_t)p.FW * (kout + (size_t)p.Cf * cin))];
+}
+
+// ---- few inputs per pixel: KC accumulators per thread, filters [r][KC] in shared memory
+template <int KC>
+__global__ void __launch_bounds__(kThreads) conv_small_r_kernel(SmallParams p)
+{
+  extern __shared__ float4 smem4[];
+  float* fs = reinterpret_cast<float*>(smem4);                 // [R][KC]
+  int const taps = p.FH * p.FW, R = taps * p.Cin;
+  int2* lut = reinterpret_cast<int2*>(fs + (size_t)R * KC);     // per r: {element offset, fh | fw << 5}
+  int const k0 = blockIdx.y * KC;
+  for (int i = threadIdx.x; i < R * KC; i += kThreads) {
+    int const r = i / KC, k = i % KC;
+    int const fh = r % p.FH, fw = (r / p.FH) % p.FW, c = r / taps;
+    fs[i] = (k0 + k < p.Kout) ? filter_at(p, fh, fw, c, k0 + k) : 0.f;
+  }
+  for (int r = threadIdx.x; r < R; r += kThreads) {
+    int const fh = r % p.FH, fw = (r / p.FH) % p.FW, c = r / taps;
+    lut[r] = make_int2(c * p.H * p.W + fw * p.dx * p.H + fh * p.dy, fh | (fw << 5));
+  }
+  __syncthreads();
+  long long const m = (long long)blockIdx.x * kThreads + threadIdx.x;
+  Pix const q = pixel_of(p, m);
+  float acc[KC];
+#pragma unroll
+  for (int k = 0; k < KC; ++k) acc[k] = 0.f;
+  float const* xq = p.x + q.base;
+  for (int r = 0; r < R; ++r) {
+    int2 const te = lut[r];
+    bool const on = ((q.hm >> (te.y & 31)) & (q.wm >> (te.y >> 5)) & 1u) != 0;
+    float const xv = on ? __ldg(xq + te.x) : 0.f;
+    float4 const* f4 = reinterpret_cast<float4 const*>(fs + (size_t)r * KC);
+#pragma unroll
+    for (int k4 = 0; k4 < KC / 4; ++k4) {
+      float4 const w = f4[k4];
+      acc[4 * k4 + 0] = fmaf(xv, w.x, acc[4 * k4 + 0]);
+      acc[4 * k4 + 1] = fmaf(xv, w.y, acc[4 * k4 + 1]);
+      acc[4 * k4 + 2] = fmaf(xv, w.z, acc[4 * k4 + 2]);
+      acc[4 * k4 + 3] = fmaf(xv, w.w, acc[4 * k4 + 3]);
+    }
+  }
+  if (!q.valid) return;
+  long long const P = (long long)p.Ho * p.Wo;
+#pragma unroll
+  for (int k = 0; k < KC; ++k) {
+    if (k0 + k < p.Kout) {
+      float* dst = p.out + q.outBase + (long long)(k0 + k) * P;
+      float o = p.inMult * acc[k];
+      if (p.bias) o += p.bias[k0 + k];
+      if (p.outMult != 0.f) o += p.outMult * *dst;
+      *dst = o;
+    }
+  }
+}
+
+// ---- few output channels: NC accumulators per thread, filters [tap][cin][NC] in shared memory
+template <int NC>
+__global__ void __launch_bounds__(kThreads) conv_small_n_kernel(SmallParams p)
+{
+  extern __shared__ float4 smem4[];
+  float* fs = reinterpret_cast<float*>(smem4);                 // [taps][Cin][NC]
+  int const taps = p.FH * p.FW;
+  int2* lut = reinterpret_cast<int2*>(fs + (size_t)taps * p.Cin * NC);      // per tap: {element offset, fh | fw << 5}
+  for (int i = threadIdx.x; i < taps * p.Cin * NC; i += kThreads) {
+    int const k = i % NC, c = (i / NC) % p.Cin, tap = i / (NC * p.Cin);
+    fs[i] = k < p.Kout ? filter_at(p, tap % p.FH, tap / p.FH, c, k) : 0.f;
+  }
+  for (int t = threadIdx.x; t < taps; t += kThreads) {
+    int const fh = t % p.FH, fw = t / p.FH;
+    lut[t] = make_int2(fw * p.dx * p.H + fh * p.dy, fh | (fw << 5));
+  }
+  __syncthreads();
+  long long const m = (long long)blockIdx.x * kThreads + threadIdx.x;
+  Pix const q = pixel_of(p, m);
+  float acc[NC];
+#pragma unroll
+  for (int k = 0; k < NC; ++k) acc[k] = 0.f;
+  int const HW = p.H * p.W;
+  for (int tap = 0; tap < taps; ++tap) {
+    int2 const te = lut[tap];
+    bool const on = ((q.hm >> (te.y & 31)) & (q.wm >> (te.y >> 5)) & 1u) != 0;
+    if (!on) continue;
+    float const* xq = p.x + q.base + te.x;
+    float const* ft = fs + (size_t)tap * p.Cin * NC;
+#pragma unroll 8
+    for (int c = 0; c < p.Cin; ++c) {
+      float const xv = __ldg(xq + (long long)c * HW);
+      if (NC == 4) {
+        float4 const w = *reinterpret_cast<float4 const*>(ft + 4 * c);
+        acc[0] = fmaf(xv, w.x, acc[0]); acc[1] = fmaf(xv, w.y, acc[1]);
+        acc[2] = fmaf(xv, w.z, acc[2]); acc[3] = fmaf(xv, w.w, acc[3]);
+      } else {
+#pragma unroll
+        for (int k = 0; k < NC; ++k) acc[k] = fmaf(xv, ft[NC * c + k], acc[k]);
+      }
+    }
+  }
+  if (!q.valid) return;
+  long long const P = (long long)p.Ho * p.Wo;
+#pragma unroll
+  for (int k = 0; k < NC; ++k) {
+    if (k < p.Kout) {
+      float* dst = p.out + q.outBase + (long long)k * P;
+      float o = p.inMult * acc[k];
+      if (p.bias) o += p.bias[k];
+      if (p.outMult != 0.f) o += p.outMult * *dst;
+      *dst = o;
+    }
+  }
+}
+
+bool fits32(ConvGeom const& g)
+{
+  return (long long)g.H * g.W * g.C * g.N < (1LL << 31) - 256 && (long long)g.Ho * g.Wo * g.K * g.N < (1LL << 31) - 256;
+}
+
+}  // namespace
+
+namespace vlb {
+
+// Forward convolution with at most 64 input values per output pixel.
+int conv_fprop_small(vlb_ctx* ctx, ConvGeom const& g, float* Y, float outMult, float const* X, float inMult,
+                     float const* F, float const* b)
+{
+  int const R = g.FH * g.FW * g.FC;
+  long long const pixels = (long long)g.Ho * g.Wo * g.N;
+  if (g.G != 1 || R > 64 || pixels < 4096 || g.FH > 31 || g.FW > 26 || !fits32(g)) return VLB_Unsupported;
+  SmallParams p = {};
+  p.x = X; p.f = F; p.out = Y; p.bias = b; p.inMult = inMult; p.outMult = outMult;
+  p.H = g.H; p.W = g.W; p.Cin = g.C; p.N = g.N; p.Ho = g.Ho; p.Wo = g.Wo; p.Kout = g.K;
+  p.FH = g.FH; p.FW = g.FW; p.sy = g.sy; p.sx = g.sx; p.pt = g.pt; p.pl = g.pl; p.dy = g.dy; p.dx = g.dx;
+  p.flip = 0; p.Cf = g.FC;
+  long long const M = (long long)g.Ho * g.Wo * g.N;
+  int const KC = g.K > 32 ? 64 : (g.K > 16 ? 32 : 16);
+  dim3 grid((unsigned)ceil_div(M, kThreads), (unsigned)ceil_div(g.K, KC));
+  size_t const smem = sizeof(float) * (size_t)R * KC + sizeof(int2) * (size_t)R;
+  if (KC == 64) conv_small_r_kernel<64><<<grid, kThreads, smem, ctx->stream>>>(p);
+  else if (KC == 32) conv_small_r_kernel<32><<<grid, kThreads, smem, ctx->stream>>>(p);
+  else conv_small_r_kernel<16><<<grid, kThreads, smem, ctx->stream>>>(p);
+  VLB_LAUNCHED(ctx, 1);
+  return check_launch(ctx, "conv_fprop_small");
+}
+
+// Data gradient of a stride-1 convolution whose input has at most 4 channels: a forward convolution of dY
+// with the flipped, transposed filters and padding (F-1)*dilate - pad.
+int conv_dgrad_small(vlb_ctx* ctx, ConvGeom const& g, float* dX, float const* F, float const* dY)
+{
+  if (g.G != 1 || g.C > 4 || g.sy != 1 || g.sx != 1 || (long long)g.H * g.W * g.N < 4096 || g.FH > 31 || g.FW > 26 || !fits32(g))
+    return VLB_Unsupported;
+  int const taps = g.FH * g.FW;
+  size_t const smem = sizeof(float) * (size_t)taps * g.K * 4 + sizeof(int2) * (size_t)taps;
+  if (smem > 48 * 1024) return VLB_Unsupported;
+  SmallParams p = {};
+  p.x = dY; p.f = F; p.out = dX; p.bias = nullptr; p.inMult = 1.f; p.outMult = 0.f;
+  p.H = g.Ho; p.W = g.Wo; p.Cin = g.K; p.N = g.N; p.Ho = g.H; p.Wo = g.W; p.Kout = g.C;
+  p.FH = g.FH; p.FW = g.FW; p.sy = 1; p.sx = 1; p.dy = g.dy; p.dx = g.dx;
+  p.pt = (g.FH - 1) * g.dy - g.pt; p.pl = (g.FW - 1) * g.dx - g.pl;
+  p.flip = 1; p.Cf = g.FC;
+  long long const M = (long long)g.H * g.W * g.N;
+  conv_small_n_kernel<4><<<(unsigned)ceil_div(M, kThreads), kThreads, smem, ctx->stream>>>(p);
+  VLB_LAUNCHED(ctx, 1);
+  return check_launch(ctx, "conv_dgrad_small");
+}
+
+}  // namespace vlb

@@ -90,6 +90,10 @@ LAYERS = {
     "c32_stride2_pad": ((19, 17, 32, 3), (3, 3, 32, 40), 2, (1, 0, 2, 1), 1),
     "c96_dilate2": ((15, 14, 96, 2), (3, 2, 96, 72), 1, (2, 2, 1, 1), (2, 1)),
     "c64_5x5_stride_1_2": ((13, 21, 64, 2), (5, 5, 64, 33), (1, 2), 2, 1),
+    # image-end shapes served by the direct CUDA-core kernels: few inputs per pixel (forward), few channels (dgrad)
+    "small_r_stride": ((41, 37, 2, 5), (3, 5, 2, 20), (2, 1), (1, 0, 2, 1), 1),
+    "small_r_dilate_c1": ((50, 47, 1, 3), (3, 3, 1, 70), 1, (2, 1, 0, 2), 2),
+    "small_n_4ch_5x5": ((36, 40, 4, 4), (5, 5, 4, 24), 1, 2, 1),
 }
 
 
