@@ -90,6 +90,7 @@ struct Params {
   int numKb, kbPerSplit;
   int stages;
   int drainEvery;         // 3xTF32: k-blocks per tensor-core accumulation chain
+  int tilesM, tilesN;     // conv_ts_kernel: the grid of output tiles its persistent CTAs walk
   int chanFast;           // conv_ts_kernel: reduction ordered channel-fastest, r = c + C*(fh + FH*fw); needs C % 32 == 0
   int pipelined;          // 1: producers prefetch one stage ahead in registers (aligned gathers only)
   float const* bTiles;    // when non-null: B pre-split into shared-memory tile images, fetched with bulk copies
@@ -972,12 +973,43 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, uint32_t const (&r)[32
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
 { asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n}" ::"r"(bar), "r"(bytes) : "memory"); }
 
+// Epilogue of conv_ts_kernel: the finished tile sits in the P columns; this warp stores the rows of its TMEM lane
+// quarter for the 32-column groups rank, rank + nranks, ...: out[(image*Ktot + n)*P + pixel] = inMult*acc + bias[n] + outMult*old.
+__device__ __forceinline__ void ts_store_tile(Params const& p, uint32_t lanesP, int quarter, int lane, int rank, int nranks, int m0, int n0)
+{
+  int const BN = p.BN;
+  int const m = m0 + quarter * 32 + lane;
+  int const pix = m % p.e.P, img = m / p.e.P;
+  long long const rowBase = (long long)img * p.e.Ktot * p.e.P + pix;
+  for (int c0 = 32 * rank; c0 < BN; c0 += 32 * nranks) {
+    uint32_t t0[16], t1[16];
+    bool const two = c0 + 16 < BN;
+    tmem_ld16_issue(lanesP + (uint32_t)c0, t0);
+    if (two) tmem_ld16_issue(lanesP + (uint32_t)(c0 + 16), t1);
+    tmem_ld_wait();
+    if (m < p.M) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        int const n = n0 + c0 + j;
+        if ((j < 16 || two) && n < p.N) {
+          float const acc = __uint_as_float(j < 16 ? t0[j & 15] : t1[j & 15]);
+          float* dst = p.e.out + rowBase + (long long)n * p.e.P;
+          float o = p.e.inMult * acc;
+          if (p.e.bias) o += p.e.bias[n];
+          if (p.e.outMult != 0.f) o += p.e.outMult * *dst;
+          *dst = o;
+        }
+      }
+    }
+  }
+}
+
 template <bool kSplit>
 __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
 {
   extern __shared__ uint8_t smemRaw[];
   __shared__ __align__(8) uint64_t fullA[kTsGroups], emptyA[kTsGroups], fullB[kTsBStages], emptyB[kTsBStages];
-  __shared__ __align__(8) uint64_t drainFull[2], drainEmpty[2], sumBar, accumBar;
+  __shared__ __align__(8) uint64_t drainFull[2], drainEmpty[2], tileDone;
   __shared__ uint32_t tmemBase;
   __shared__ int2 tapLut[64];       // per filter tap fh + FH*fw: {element offset of the tap, fh | fw << 5}
 
@@ -989,17 +1021,19 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
   uint32_t const colP = (uint32_t)(2 * BN), colA = (uint32_t)(3 * BN);
 
   int const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int const m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
-  int const numIter = p.numKb;
-  int const numChunks = kSplit ? (numIter + kTsDrainEvery - 1) / kTsDrainEvery : 1;
+  int const numIter = p.numKb;                     // k-blocks per tile
+  int const chunksPerTile = kSplit ? (numIter + kTsDrainEvery - 1) / kTsDrainEvery : 1;
+  int const numTiles = p.tilesM * p.tilesN;
+  // this CTA's tiles: blockIdx.x, blockIdx.x + gridDim.x, ...; tile t = (row tile t / tilesN, column tile t % tilesN)
+  int const myTiles = (int)blockIdx.x < numTiles ? (numTiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  bool const singleTile = (int)gridDim.x == numTiles;      // launched with one CTA per tile (long reductions)
 
   if (threadIdx.x == 0) {
     // an A stage is full when its four producer warps and the forwarder (filter tile landed) have arrived
     for (int s = 0; s < kTsGroups; ++s) { mbar_init(smem_u32(&fullA[s]), 5); mbar_init(smem_u32(&emptyA[s]), 1); }
     for (int s = 0; s < kTsBStages; ++s) { mbar_init(smem_u32(&fullB[s]), 1); mbar_init(smem_u32(&emptyB[s]), 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(smem_u32(&drainFull[b]), 1); mbar_init(smem_u32(&drainEmpty[b]), kEpilogueWarps); }
-    mbar_init(smem_u32(&sumBar), kEpilogueWarps);
-    mbar_init(smem_u32(&accumBar), 1);
+    mbar_init(smem_u32(&tileDone), kEpilogueWarps);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == kEpilogueWarps) tmem_alloc(smem_u32(&tmemBase), tmemCols);
@@ -1013,18 +1047,24 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
   uint32_t const tmemAcc = tmemBase;
 
   if (warp < kEpilogueWarps) {
-    // ============================== fp32 drain (3xTF32 only) ==============================
-    // Chain c (k-blocks c*kTsDrainEvery ...) was accumulated in T[c & 1]; all chains but the last are
-    // added to P here.  Warp w owns TMEM lanes 32w .. 32w+31.
-    if (kSplit) {
-      uint32_t const lanes = tmemAcc + ((uint32_t)(warp * 32) << 16);
-      bool ok = true;
-      for (int c = 0; c + 1 < numChunks && ok; ++c) {
-        int const b = c & 1;
-        ok = mbar_wait(smem_u32(&drainFull[b]), (uint32_t)((c >> 1) & 1));
+    // ============================== fp32 drain and epilogue ==============================
+    // Chains are numbered over the whole life of the CTA: chain gc was accumulated in T[gc & 1].  Every chain
+    // of a tile is added to P and its T released at once; after the last one the tile is stored from P (one
+    // TMEM lane = one output row per thread, stores coalesced along the rows) while the tensor core is already
+    // two chains into the next tile.
+    uint32_t const lanes = tmemAcc + ((uint32_t)(warp * 32) << 16);
+    int gc = 0;
+    bool ok = true;
+    for (int ts = 0; ts < myTiles && ok; ++ts) {
+      int const tile = (int)blockIdx.x + ts * (int)gridDim.x;
+      int const m0 = (tile / p.tilesN) * BM, n0 = (tile % p.tilesN) * BN;
+      for (int c = 0; c < chunksPerTile && ok; ++c, ++gc) {
+        int const b = gc & 1;
+        ok = mbar_wait(smem_u32(&drainFull[b]), (uint32_t)((gc >> 1) & 1));
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) { if (lane == 0) atomicExch(p.status, 5); break; }
         tc_fence_after();
+        // P = T (first chain of the tile) or P += T, then T[b] goes back to the tensor core at once
         for (int c0 = 0; c0 < BN; c0 += 32) {
           uint32_t t0[16], t1[16], p0[16], p1[16];
           bool const two = c0 + 16 < BN;
@@ -1049,44 +1089,55 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&drainEmpty[b]));     // T[b] may be overwritten
+        if (c + 1 == chunksPerTile) {
+          if (singleTile) {
+            // one tile per CTA: the producers have nothing left to do and share the stores
+            if (lane == 0) mbar_arrive(smem_u32(&tileDone));
+            ts_store_tile(p, lanes + colP, warp, lane, 0, 1 + kTsGroups, m0, n0);
+          } else {
+            // the tile is complete in P: store it while the tensor core works on the next tile (whose first
+            // chain is not added to P before this is through)
+            ts_store_tile(p, lanes + colP, warp, lane, 0, 1, m0, n0);
+          }
+          tc_fence_before();
+        }
       }
-      // P is complete (its stores have been waited for): publish it to the warps of the epilogue
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sumBar));
     }
   } else if (warp == kEpilogueWarps) {
     // ============================== MMA issue ==============================
-    // Per k-block: one barrier wait (A written and B landed), twelve MMAs, one commit.  Running counters
-    // instead of divisions; per chain of kTsDrainEvery k-blocks one more wait and one more commit.
+    // Per k-block: one barrier wait (A written and B landed), twelve MMAs, one commit; per chain one more wait
+    // and one more commit.  Running counters instead of divisions.  The waits for the next k-block are issued
+    // between the two halves of the current one: the tensor core's queue is short, and whatever this thread
+    // does between two MMAs for longer than about one MMA idles it.  k-blocks and chains are numbered over the
+    // whole life of the CTA, so the pipeline runs across tile boundaries without draining.
     if (lane == 0) {
       uint32_t const idesc = make_idesc(false, false, BN);
       uint64_t const descB0 = make_desc(smem_u32(smem), 16, 1024);
       uint32_t const stageStep = bBytes >> 4, loStep = bTileBytes >> 4;
-      // The waits for k-block it + 1 are issued between the two halves of k-block it: the tensor core's
-      // queue is short, and whatever this thread does between two MMAs for longer than about one MMA idles it.
+      long long const total = (long long)myTiles * numIter;
       bool ok = true;
-      int sa = 0, sb = 0, inChunk = 0, chunk = 0;
+      int sa = 0, sb = 0, inChunk = 0, it = 0, gc = 0;
       uint32_t phA = 0;
-      if (numIter > 0) {
+      if (total > 0) {
         ok = mbar_wait(smem_u32(&fullA[0]), 0);
         if (!ok) atomicExch(p.status, 2);
         tc_fence_after();
       }
-      for (int it = 0; it < numIter && ok; ++it) {
-        int const tb = chunk & 1;
-        bool const chunkStart = kSplit ? inChunk == 0 : it == 0;
+      for (long long gi = 0; gi < total && ok; ++gi) {
+        int const tb = gc & 1;
+        bool const chunkStart = inChunk == 0;
+        bool const chunkEnd = it + 1 == numIter || (kSplit && inChunk + 1 == kTsDrainEvery);
         uint64_t const dBh = descB0 + (uint64_t)((uint32_t)sb * stageStep), dBl = dBh + loStep;
         uint32_t const aHi = tmemAcc + colA + (uint32_t)(sa * 64), aLo = aHi + 32u;
         uint32_t const tAcc = tmemAcc + (uint32_t)(tb * BN);
 #pragma unroll
         for (int k8 = 0; k8 < BK / 8; ++k8) {
-          if (k8 == BK / 16 && it + 1 < numIter) {
-            // ---- between the halves: make sure k-block it + 1 can start right after this one
+          if (k8 == BK / 16 && gi + 1 < total) {
+            // ---- between the halves: make sure the next k-block can start right after this one
             int const nsa = sa + 1 == kTsGroups ? 0 : sa + 1;
             uint32_t const nph = sa + 1 == kTsGroups ? phA ^ 1u : phA;
-            if (kSplit && inChunk + 1 == kTsDrainEvery && chunk + 1 >= 2) {   // it + 1 starts a chain in T[(chunk+1)&1]
-              ok = mbar_wait(smem_u32(&drainEmpty[(chunk + 1) & 1]), (uint32_t)((((chunk + 1) >> 1) - 1) & 1));
+            if (chunkEnd && gc + 1 >= 2) {      // the next k-block starts a chain in T[(gc+1)&1]: its previous contents must be drained
+              ok = mbar_wait(smem_u32(&drainEmpty[(gc + 1) & 1]), (uint32_t)((((gc + 1) >> 1) - 1) & 1));
               if (!ok) { atomicExch(p.status, 6); break; }
             }
             ok = mbar_wait(smem_u32(&fullA[nsa]), nph);
@@ -1109,12 +1160,10 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
         umma_commit(smem_u32(&emptyA[sa]));      // frees the A stage; its producers pass the news on for the B stage
         if (++sa == kTsGroups) { sa = 0; phA ^= 1u; }
         if (++sb == kTsBStages) sb = 0;
-        if (kSplit && ++inChunk == kTsDrainEvery) {
-          if (chunk + 1 < numChunks) umma_commit(smem_u32(&drainFull[tb]));   // this chain is complete: hand it to the drain warps
-          inChunk = 0; ++chunk;
-        }
+        ++inChunk;
+        if (chunkEnd) { umma_commit(smem_u32(&drainFull[tb])); inChunk = 0; ++gc; }   // chain complete: hand it to the drain warps
+        if (++it == numIter) it = 0;
       }
-      umma_commit(smem_u32(&accumBar));
     }
     __syncwarp();
     tc_fence_before();
@@ -1122,25 +1171,31 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
     // ============================== filter tiles: bulk copies ==============================
     if (lane == 0) {
       int sb = 0; uint32_t ph = 1;                       // first use of a stage: nothing to wait for
-      for (int it = 0; it < numIter; ++it) {
-        if (!mbar_wait(smem_u32(&emptyB[sb]), ph)) { atomicExch(p.status, 8); break; }
-        mbar_arrive_expect_tx(smem_u32(&fullB[sb]), bBytes);
-        bulk_copy_g2s(smem_u32(smem + (size_t)sb * bBytes), p.bTiles + ((size_t)blockIdx.y * p.numKb + (size_t)it) * (bBytes / 4),
-                      bBytes, smem_u32(&fullB[sb]));
-        if (++sb == kTsBStages) { sb = 0; ph ^= 1u; }
+      bool ok = true;
+      for (int ts = 0; ts < myTiles && ok; ++ts) {
+        int const nt = ((int)blockIdx.x + ts * (int)gridDim.x) % p.tilesN;
+        float const* src = p.bTiles + (size_t)nt * p.numKb * (bBytes / 4);
+        for (int it = 0; it < numIter; ++it) {
+          if (!mbar_wait(smem_u32(&emptyB[sb]), ph)) { atomicExch(p.status, 8); ok = false; break; }
+          mbar_arrive_expect_tx(smem_u32(&fullB[sb]), bBytes);
+          bulk_copy_g2s(smem_u32(smem + (size_t)sb * bBytes), src + (size_t)it * (bBytes / 4), bBytes, smem_u32(&fullB[sb]));
+          if (++sb == kTsBStages) { sb = 0; ph ^= 1u; }
+        }
       }
     }
     __syncwarp();
   } else if (warp == kTsForwardWarp) {
     // ============================== forwarder ==============================
-    // k-block it uses A stage it & 1 in that barrier's phase it >> 1.  The arrival for it must fall into
-    // that phase, so the phase of it - 2 has to be complete first (this thread arrived in it as well).
+    // k-block gi (numbered over the CTA's life) uses A stage gi & 1 in that barrier's phase gi >> 1.  The arrival
+    // for gi must fall into that phase, so the phase of gi - 2 has to be complete first (this thread arrived in
+    // it as well).
     if (lane == 0) {
       int sb = 0; uint32_t phB = 0;
-      for (int it = 0; it < numIter; ++it) {
-        int const sa = it & 1;
+      long long const total = (long long)myTiles * numIter;
+      for (long long gi = 0; gi < total; ++gi) {
+        int const sa = (int)(gi & 1);
         if (!mbar_wait(smem_u32(&fullB[sb]), phB)) { atomicExch(p.status, 7); break; }
-        if (it >= kTsGroups && !mbar_wait(smem_u32(&fullA[sa]), (uint32_t)(((it >> 1) - 1) & 1))) { atomicExch(p.status, 9); break; }
+        if (gi >= kTsGroups && !mbar_wait(smem_u32(&fullA[sa]), (uint32_t)(((gi >> 1) - 1) & 1))) { atomicExch(p.status, 9); break; }
         mbar_arrive(smem_u32(&fullA[sa]));
         if (++sb == kTsBStages) { sb = 0; phB ^= 1u; }
       }
@@ -1151,105 +1206,82 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
     int const grp = (warp - kTsFirstProducer) >> 2;
     int const quarter = warp & 3;                       // the TMEM lanes this warp may access
     bool const herald = (warp - kTsFirstProducer) % 4 == 0 && lane == 0;   // tells the loader about freed filter stages
-    int const m = m0 + quarter * 32 + lane;
     int const HW = p.a.H * p.a.W, taps = p.a.FH * p.a.FW;
-    uint32_t hm = 0, wm = 0;                            // tap rows / columns inside the image for this pixel
-    float const* xq = p.a.ptr;
-    if (m < p.M) {
-      int const ho = m % p.a.Ho, q = m / p.a.Ho, wo = q % p.a.Wo, n = q / p.a.Wo;
-      xq += (long long)n * p.a.imgStride + (long long)wo * p.a.sx * p.a.H + ho * p.a.sy;
-      for (int fh = 0; fh < p.a.FH; ++fh) { int h = ho * p.a.sy + fh * p.a.dy - p.a.pt; if (h >= 0 && h < p.a.H) hm |= 1u << fh; }
-      for (int fw = 0; fw < p.a.FW; ++fw) { int w = wo * p.a.sx + fw * p.a.dx - p.a.pl; if (w >= 0 && w < p.a.W) wm |= 1u << fw; }
-    }
     uint32_t const aAddr = tmemAcc + ((uint32_t)(quarter * 32) << 16) + colA + (uint32_t)(grp * 64);
     uint32_t phE = 1;                                   // first use of the stage: nothing to wait for
     int sbFree = grp;                                   // filter stage of the k-block whose MMAs this group sees complete next
-    for (int it = grp; it < numIter; it += kTsGroups) {
-      int const r = it * BK;
-      int tap = r % taps, ch = r / taps;
-      float v[32];
-      if (p.chanFast) {
-        // the whole k-block is one filter tap and 32 consecutive channels: one validity test, constant stride
-        int const tp = r / p.a.C, c0 = r - tp * p.a.C;
-        int2 const te = tapLut[tp];
-        uint32_t const e = (uint32_t)te.y;
-        bool const on = ((hm >> (e & 31u)) & (wm >> (e >> 5)) & 1u) != 0;
-        float const* const q = xq + ((long long)c0 * HW + te.x);
-#pragma unroll
-        for (int k = 0; k < 32; ++k) { v[k] = 0.f; ldg32_if(v[k], q + (long long)k * HW, on); }
-      } else
-#pragma unroll
-      for (int k = 0; k < 32; ++k) {
-        int2 const te = tapLut[tap];
-        uint32_t const e = (uint32_t)te.y;
-        bool const on = ((r + k < p.R ? 1u : 0u) & (hm >> (e & 31u)) & (wm >> (e >> 5))) != 0;
-        v[k] = 0.f;
-        ldg32_if(v[k], xq + (ch * HW + te.x), on);
-        if (++tap == taps) { tap = 0; ++ch; }
+    long long gi = 0;                                   // k-blocks numbered over the CTA's life; this group takes gi % 2 == grp
+    bool ok = true;
+    for (int ts = 0; ts < myTiles && ok; ++ts) {
+      int const tile = (int)blockIdx.x + ts * (int)gridDim.x;
+      int const m = (tile / p.tilesN) * BM + quarter * 32 + lane;
+      uint32_t hm = 0, wm = 0;                          // tap rows / columns inside the image for this pixel
+      float const* xq = p.a.ptr;
+      if (m < p.M) {
+        int const ho = m % p.a.Ho, q = m / p.a.Ho, wo = q % p.a.Wo, n = q / p.a.Wo;
+        xq += (long long)n * p.a.imgStride + (long long)wo * p.a.sx * p.a.H + ho * p.a.sy;
+        for (int fh = 0; fh < p.a.FH; ++fh) { int h = ho * p.a.sy + fh * p.a.dy - p.a.pt; if (h >= 0 && h < p.a.H) hm |= 1u << fh; }
+        for (int fw = 0; fw < p.a.FW; ++fw) { int w = wo * p.a.sx + fw * p.a.dx - p.a.pl; if (w >= 0 && w < p.a.W) wm |= 1u << fw; }
       }
-      uint32_t hi[32];
+      for (int it = (int)((gi ^ grp) & 1); it < numIter; it += kTsGroups) {
+        int const r = it * BK;
+        float v[32];
+        if (p.chanFast) {
+          // the whole k-block is one filter tap and 32 consecutive channels: one validity test, constant stride
+          int const tp = r / p.a.C, c0 = r - tp * p.a.C;
+          int2 const te = tapLut[tp];
+          uint32_t const e = (uint32_t)te.y;
+          bool const on = ((hm >> (e & 31u)) & (wm >> (e >> 5)) & 1u) != 0;
+          float const* const q = xq + ((long long)c0 * HW + te.x);
 #pragma unroll
-      for (int k = 0; k < 32; ++k) hi[k] = __float_as_uint(tf32_hi(v[k]));
-      if (!mbar_wait(smem_u32(&emptyA[grp]), phE)) { atomicExch(p.status, 1); break; }
-      phE ^= 1u;
-      if (herald && it >= kTsGroups) {                  // the MMAs of k-block it - 2 are complete: its filter stage is free too
-        mbar_arrive(smem_u32(&emptyB[sbFree]));
-        sbFree += kTsGroups; if (sbFree >= kTsBStages) sbFree -= kTsBStages;
-      }
-      tc_fence_after();
-      tmem_st32(aAddr, hi);
-      if (kSplit) {
+          for (int k = 0; k < 32; ++k) { v[k] = 0.f; ldg32_if(v[k], q + (long long)k * HW, on); }
+        } else {
+          int tap = r % taps, ch = r / taps;
 #pragma unroll
-        for (int k = 0; k < 32; ++k) hi[k] = __float_as_uint(v[k] - __uint_as_float(hi[k]));
-        tmem_st32(aAddr + 32u, hi);
-      }
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&fullA[grp]));
-    }
-  }
-
-  // ============================== epilogue ==============================
-  // The drain warp and the two producer warps of each TMEM lane quarter share its 32 output rows and deal the
-  // columns in chunks of 16.
-  if (warp < kEpilogueWarps || warp >= kTsFirstProducer) {
-    bool ok = mbar_wait(smem_u32(&accumBar), 0);
-    if (kSplit && ok) ok = mbar_wait(smem_u32(&sumBar), 0);
-    ok = __all_sync(0xffffffffu, ok);
-    tc_fence_after();
-    if (!ok) { if (lane == 0) atomicExch(p.status, 3); }
-    else if (numIter > 0) {
-      int const quarter = warp & 3;
-      int const rank = warp < kEpilogueWarps ? 0 : 1 + ((warp - kTsFirstProducer) >> 2);
-      int const m = m0 + quarter * 32 + lane;
-      int const pix = m % p.e.P, img = m / p.e.P;
-      long long const rowBase = (long long)img * p.e.Ktot * p.e.P + pix;
-      uint32_t const lastT = (uint32_t)(((numChunks - 1) & 1) * BN);
-      for (int c0 = 16 * rank; c0 < BN; c0 += 16 * (1 + kTsGroups)) {
-        uint32_t const laneBase = tmemAcc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
-        uint32_t t0[16], t2[16];
-        tmem_ld16_issue(laneBase + lastT, t0);
-        if (kSplit && numChunks > 1) tmem_ld16_issue(laneBase + colP, t2);
-        tmem_ld_wait();
-        if (m < p.M) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            int const n = n0 + c0 + j;
-            if (n < p.N) {
-              float acc = __uint_as_float(t0[j]);
-              if (kSplit && numChunks > 1) acc += __uint_as_float(t2[j]);
-              float* dst = p.e.out + rowBase + (long long)n * p.e.P;
-              float o = p.e.inMult * acc;
-              if (p.e.bias) o += p.e.bias[n];
-              if (p.e.outMult != 0.f) o += p.e.outMult * *dst;
-              *dst = o;
-            }
+          for (int k = 0; k < 32; ++k) {
+            int2 const te = tapLut[tap];
+            uint32_t const e = (uint32_t)te.y;
+            bool const on = ((r + k < p.R ? 1u : 0u) & (hm >> (e & 31u)) & (wm >> (e >> 5))) != 0;
+            v[k] = 0.f;
+            ldg32_if(v[k], xq + (ch * HW + te.x), on);
+            if (++tap == taps) { tap = 0; ++ch; }
           }
         }
+        uint32_t hi[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) hi[k] = __float_as_uint(tf32_hi(v[k]));
+        if (!mbar_wait(smem_u32(&emptyA[grp]), phE)) { atomicExch(p.status, 1); ok = false; break; }
+        phE ^= 1u;
+        if (herald && gi + it >= kTsGroups) {                      // the MMAs of the k-block two before this one are complete: its filter stage is free too
+          mbar_arrive(smem_u32(&emptyB[sbFree]));
+          sbFree += kTsGroups; if (sbFree >= kTsBStages) sbFree -= kTsBStages;
+        }
+        tc_fence_after();
+        tmem_st32(aAddr, hi);
+        if (kSplit) {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) hi[k] = __float_as_uint(v[k] - __uint_as_float(hi[k]));
+          tmem_st32(aAddr + 32u, hi);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&fullA[grp]));
       }
+      gi += numIter;
     }
-    tc_fence_before();
+    if (singleTile && ok && myTiles > 0) {
+      bool done = mbar_wait(smem_u32(&tileDone), 0);
+      done = __all_sync(0xffffffffu, done);
+      tc_fence_after();
+      if (!done) { if (lane == 0) atomicExch(p.status, 3); }
+      else {
+        int const tile = (int)blockIdx.x;
+        ts_store_tile(p, tmemAcc + ((uint32_t)(quarter * 32) << 16) + colP, quarter, lane, 1 + grp, 1 + kTsGroups,
+                      (tile / p.tilesN) * BM, (tile % p.tilesN) * BN);
+      }
+      tc_fence_before();
+    }
   }
 
   __syncthreads();
@@ -1501,8 +1533,14 @@ int launch_ts(vlb_ctx* ctx, Params& p, char const* where)
   // at least 120 KB, so that two CTAs (each allocating all 512 TMEM columns) never share an SM
   size_t smemBytes = (size_t)kTsBStages * (split3 ? 2u : 1u) * (size_t)p.BN * BK * 4 + 1024;
   if (smemBytes < 120u * 1024u) smemBytes = 120u * 1024u;
-  dim3 grid(vlb::ceil_div(p.M, BM), vlb::ceil_div(p.N, p.BN), 1);
-  if (grid.y > 65535u) return VLB_Unsupported;
+  p.tilesM = vlb::ceil_div(p.M, BM); p.tilesN = vlb::ceil_div(p.N, p.BN);
+  long long const numTiles = (long long)p.tilesM * p.tilesN;
+  if (numTiles >= (1LL << 31)) return VLB_Unsupported;
+  // Short reductions (prologue and epilogue would dominate a CTA's life): persistent, one CTA per SM walks the tiles and
+  // stores a tile while the next is computed.  Long reductions: one CTA per tile, every warp shares the stores at the end
+  // (the overlapped stores of four warps slow the MMA-issuing thread down by more than they hide).
+  bool const persistent = p.BN <= 64 || p.numKb <= 36;
+  dim3 grid((unsigned)(persistent && numTiles > ctx->smCount ? ctx->smCount : numTiles), 1, 1);
   cudaError_t e;
   vlb_ctx::ProfRec rec;
   if (ctx->profiling) {
