@@ -47,7 +47,7 @@ constexpr int KSTEP = 32 / CH;                    // MN-major tiles: k rows betw
 constexpr int RSTEP = BM / CH;                    // K-major tiles: rows between a thread's consecutive chunks
 constexpr int kMaxStages = 8;
 constexpr int kDrainEvery = 8;                    // 3xTF32: k-blocks (of 32) accumulated by the tensor core before the fp32 drain
-constexpr long long kWaitCycles = 2000000000LL;   // bound on any single barrier wait
+constexpr long long kWaitCycles = 200000000LL;    // bound on any single barrier wait (about 0.1 s)
 
 enum OperandMode {
   OP_DENSE_K = 0,    // addr(i, r) = (r / P) * bs + i * ld + (r % P)      (reduction contiguous)
@@ -933,11 +933,11 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
 // memory with tcgen05.st; the MMA takes A from tensor memory and only the filter tiles from shared
 // memory (bulk copies of the ready-made tile images).  Any stride, padding and dilation.
 //   warps 0-3   fp32 drain of the short accumulation chains (3xTF32), then epilogue
-//   warp  4     MMA issue (one lane), TMEM allocation
-//   warp  5     filter-tile loader (one lane): bulk copies into kTsBStages shared-memory stages
-//   warp  6     forwarder (one lane): when the filter tile of a k-block has landed it arrives on that
-//               k-block's A-stage barrier, so that the MMA thread waits on a single barrier per k-block
-//   warps 7-14  producers: two groups of four warps (one warp per TMEM lane quarter); group g owns
+//   warps 4, 5  MMA issue (one lane each; warp 4 also allocates TMEM): issuer q takes every other k-block
+//   warp  6     filter-tile loader (one lane): bulk copies into kTsBStages shared-memory stages
+//   warp  7     forwarder (one lane): when the filter tile of a k-block has landed it arrives on that
+//               k-block's A-stage barrier, so that an MMA thread waits on a single barrier per k-block
+//   warps 8-15  producers: two groups of four warps (one warp per TMEM lane quarter); group g owns
 //               A stage g and fills it for the k-blocks g, g+2, ...; a producer that finds its A stage
 //               free again also knows that the filter stage of the same k-block is free and says so
 //               to the loader, so that the MMA thread commits to a single barrier per k-block.
@@ -947,10 +947,10 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
 // Tensor memory columns: T0 | T1 | P (BN each; 3xTF32: chain accumulators and fp32 running sum; the
 // small terms lo*hi + hi*lo go to T as well) | A stage g at 3*BN + 64*g: 32 columns hi, 32 columns lo.
 constexpr int kTsGroups = 2;
-constexpr int kTsLoaderWarp = kEpilogueWarps + 1;
-constexpr int kTsForwardWarp = kEpilogueWarps + 2;
-constexpr int kTsFirstProducer = kEpilogueWarps + 3;
-constexpr int kTsThreads = (kTsFirstProducer + 4 * kTsGroups) * 32;      // 480
+constexpr int kTsLoaderWarp = kEpilogueWarps + 2;
+constexpr int kTsForwardWarp = kEpilogueWarps + 3;
+constexpr int kTsFirstProducer = kEpilogueWarps + 4;
+constexpr int kTsThreads = (kTsFirstProducer + 4 * kTsGroups) * 32;      // 512
 constexpr int kTsBStages = 6;
 constexpr int kTsDrainEvery = 4;        // k-blocks per accumulation chain: 4 x 4 k-steps x 3 MMAs
 
@@ -1053,116 +1053,122 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
     // TMEM lane = one output row per thread, stores coalesced along the rows) while the tensor core is already
     // two chains into the next tile.
     uint32_t const lanes = tmemAcc + ((uint32_t)(warp * 32) << 16);
-    int gc = 0;
+    int gcq[2] = {0, 0};                              // chains of issuer 0 / 1 drained so far
     bool ok = true;
     for (int ts = 0; ts < myTiles && ok; ++ts) {
       int const tile = (int)blockIdx.x + ts * (int)gridDim.x;
       int const m0 = (tile / p.tilesN) * BM, n0 = (tile % p.tilesN) * BN;
-      for (int c = 0; c < chunksPerTile && ok; ++c, ++gc) {
-        int const b = gc & 1;
-        ok = mbar_wait(smem_u32(&drainFull[b]), (uint32_t)((gc >> 1) & 1));
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) { if (lane == 0) atomicExch(p.status, 5); break; }
-        tc_fence_after();
-        // P = T (first chain of the tile) or P += T, then T[b] goes back to the tensor core at once
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          uint32_t t0[16], t1[16], p0[16], p1[16];
-          bool const two = c0 + 16 < BN;
-          tmem_ld16_issue(lanes + (uint32_t)(b * BN + c0), t0);
-          if (two) tmem_ld16_issue(lanes + (uint32_t)(b * BN + c0 + 16), t1);
-          if (c > 0) {
-            tmem_ld16_issue(lanes + colP + (uint32_t)c0, p0);
-            if (two) tmem_ld16_issue(lanes + colP + (uint32_t)(c0 + 16), p1);
-          }
-          tmem_ld_wait();
-          if (c > 0) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              t0[j] = __float_as_uint(__uint_as_float(t0[j]) + __uint_as_float(p0[j]));
-              if (two) t1[j] = __float_as_uint(__uint_as_float(t1[j]) + __uint_as_float(p1[j]));
+      int const qFirst = (int)(((long long)ts * numIter) & 1);          // the issuer that owns the tile's first k-block
+      int chains[2];
+      for (int q = 0; q < 2; ++q) {
+        int const first = q == qFirst ? 0 : 1, nOwn = numIter > first ? (numIter - first + 1) / 2 : 0;
+        chains[q] = kSplit ? (nOwn + kTsDrainEvery - 1) / kTsDrainEvery : (nOwn > 0 ? 1 : 0);
+      }
+      int const rounds = chains[0] > chains[1] ? chains[0] : chains[1];
+      bool fresh = true;                              // P holds nothing of this tile yet
+      for (int c = 0; c < rounds && ok; ++c) {
+        for (int h = 0; h < 2 && ok; ++h) {
+          int const q = h == 0 ? qFirst : 1 - qFirst;
+          if (c >= chains[q]) continue;
+          ok = mbar_wait(smem_u32(&drainFull[q]), (uint32_t)(gcq[q] & 1));
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) { if (lane == 0) atomicExch(p.status, 5); break; }
+          ++gcq[q];
+          tc_fence_after();
+          // P = T (first chain of the tile) or P += T, then T[q] goes back to its issuer at once
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t t0[16], t1[16], p0[16], p1[16];
+            bool const two = c0 + 16 < BN;
+            tmem_ld16_issue(lanes + (uint32_t)(q * BN + c0), t0);
+            if (two) tmem_ld16_issue(lanes + (uint32_t)(q * BN + c0 + 16), t1);
+            if (!fresh) {
+              tmem_ld16_issue(lanes + colP + (uint32_t)c0, p0);
+              if (two) tmem_ld16_issue(lanes + colP + (uint32_t)(c0 + 16), p1);
             }
+            tmem_ld_wait();
+            if (!fresh) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                t0[j] = __float_as_uint(__uint_as_float(t0[j]) + __uint_as_float(p0[j]));
+                if (two) t1[j] = __float_as_uint(__uint_as_float(t1[j]) + __uint_as_float(p1[j]));
+              }
+            }
+            tmem_st16(lanes + colP + (uint32_t)c0, t0);
+            if (two) tmem_st16(lanes + colP + (uint32_t)(c0 + 16), t1);
           }
-          tmem_st16(lanes + colP + (uint32_t)c0, t0);
-          if (two) tmem_st16(lanes + colP + (uint32_t)(c0 + 16), t1);
-        }
-        tmem_st_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&drainEmpty[b]));     // T[b] may be overwritten
-        if (c + 1 == chunksPerTile) {
-          if (singleTile) {
-            // one tile per CTA: the producers have nothing left to do and share the stores
-            if (lane == 0) mbar_arrive(smem_u32(&tileDone));
-            ts_store_tile(p, lanes + colP, warp, lane, 0, 1 + kTsGroups, m0, n0);
-          } else {
-            // the tile is complete in P: store it while the tensor core works on the next tile (whose first
-            // chain is not added to P before this is through)
-            ts_store_tile(p, lanes + colP, warp, lane, 0, 1, m0, n0);
-          }
+          fresh = false;
+          tmem_st_wait();
           tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&drainEmpty[q]));     // T[q] may be overwritten
         }
       }
+      if (!ok) break;
+      if (singleTile) {
+        // one tile per CTA: the producers have nothing left to do and share the stores
+        if (lane == 0) mbar_arrive(smem_u32(&tileDone));
+        ts_store_tile(p, lanes + colP, warp, lane, 0, 1 + kTsGroups, m0, n0);
+      } else {
+        // the tile is complete in P: store it while the tensor core works on the next tile (neither issuer
+        // gets more than one chain ahead of the drain)
+        ts_store_tile(p, lanes + colP, warp, lane, 0, 1, m0, n0);
+      }
+      tc_fence_before();
     }
-  } else if (warp == kEpilogueWarps) {
+  } else if (warp == kEpilogueWarps || warp == kEpilogueWarps + 1) {
     // ============================== MMA issue ==============================
-    // Per k-block: one barrier wait (A written and B landed), twelve MMAs, one commit; per chain one more wait
-    // and one more commit.  Running counters instead of divisions.  The waits for the next k-block are issued
-    // between the two halves of the current one: the tensor core's queue is short, and whatever this thread
-    // does between two MMAs for longer than about one MMA idles it.  k-blocks and chains are numbered over the
-    // whole life of the CTA, so the pipeline runs across tile boundaries without draining.
+    // Two issuing threads (in two warps, on two schedulers).  The tensor core's queue is about one MMA deep, so
+    // while a thread waits on a barrier or commits, nothing of its own is in flight; with two threads the other
+    // one's MMAs fill the gap.  Issuer q takes the k-blocks gi = q, q+2, ... (numbered over the CTA's life), which
+    // live in A stage q, and accumulates its chains in T[q]; chains of the two issuers never touch the same
+    // tensor-memory columns, so no ordering between the two streams is needed.  Per k-block: one barrier wait
+    // (A written and B landed), twelve MMAs, one commit; per chain: a wait for the drain of T[q] (there is no
+    // second T to switch to) and a commit that hands the chain to the drain warps.  (An issuer cannot wait for its
+    // next k-block ahead of time: that k-block goes into the A stage the current one still occupies.)
     if (lane == 0) {
+      int const q = warp - kEpilogueWarps;
       uint32_t const idesc = make_idesc(false, false, BN);
       uint64_t const descB0 = make_desc(smem_u32(smem), 16, 1024);
       uint32_t const stageStep = bBytes >> 4, loStep = bTileBytes >> 4;
-      long long const total = (long long)myTiles * numIter;
+      uint32_t const aHi = tmemAcc + colA + (uint32_t)(q * 64), aLo = aHi + 32u;
+      uint32_t const tAcc = tmemAcc + (uint32_t)(q * BN);
       bool ok = true;
-      int sa = 0, sb = 0, inChunk = 0, it = 0, gc = 0;
+      int sb = q, gcq = 0;
       uint32_t phA = 0;
-      if (total > 0) {
-        ok = mbar_wait(smem_u32(&fullA[0]), 0);
-        if (!ok) atomicExch(p.status, 2);
-        tc_fence_after();
-      }
-      for (long long gi = 0; gi < total && ok; ++gi) {
-        int const tb = gc & 1;
-        bool const chunkStart = inChunk == 0;
-        bool const chunkEnd = it + 1 == numIter || (kSplit && inChunk + 1 == kTsDrainEvery);
-        uint64_t const dBh = descB0 + (uint64_t)((uint32_t)sb * stageStep), dBl = dBh + loStep;
-        uint32_t const aHi = tmemAcc + colA + (uint32_t)(sa * 64), aLo = aHi + 32u;
-        uint32_t const tAcc = tmemAcc + (uint32_t)(tb * BN);
+      for (int ts = 0; ts < myTiles && ok; ++ts) {
+        int const first = (int)((((long long)ts * numIter) ^ q) & 1);
+        for (int it = first, j = 0; it < numIter; it += 2, ++j) {
+          int const inChunk = kSplit ? j % kTsDrainEvery : j;
+          bool const chunkStart = inChunk == 0;
+          bool const chunkEnd = it + 2 >= numIter || (kSplit && inChunk + 1 == kTsDrainEvery);
+          if (chunkStart && gcq >= 1) {               // the previous chain of T[q] must have been added to P
+            ok = mbar_wait(smem_u32(&drainEmpty[q]), (uint32_t)((gcq - 1) & 1));
+            if (!ok) { atomicExch(p.status, 6); break; }
+          }
+          ok = mbar_wait(smem_u32(&fullA[q]), phA);
+          if (!ok) { atomicExch(p.status, 2); break; }
+          tc_fence_after();
+          uint64_t const dBh = descB0 + (uint64_t)((uint32_t)sb * stageStep), dBl = dBh + loStep;
 #pragma unroll
-        for (int k8 = 0; k8 < BK / 8; ++k8) {
-          if (k8 == BK / 16 && gi + 1 < total) {
-            // ---- between the halves: make sure the next k-block can start right after this one
-            int const nsa = sa + 1 == kTsGroups ? 0 : sa + 1;
-            uint32_t const nph = sa + 1 == kTsGroups ? phA ^ 1u : phA;
-            if (chunkEnd && gc + 1 >= 2) {      // the next k-block starts a chain in T[(gc+1)&1]: its previous contents must be drained
-              ok = mbar_wait(smem_u32(&drainEmpty[(gc + 1) & 1]), (uint32_t)((((gc + 1) >> 1) - 1) & 1));
-              if (!ok) { atomicExch(p.status, 6); break; }
+          for (int k8 = 0; k8 < BK / 8; ++k8) {
+            uint32_t const acc = (chunkStart && k8 == 0) ? 0u : 1u;      // 0 = overwrite: first MMA of a chain
+            if (kSplit) {
+              asm volatile(
+                  "{\n .reg .pred p0, p1;\n setp.ne.b32 p0, %6, 0;\n setp.eq.b32 p1, %6, %6;\n"
+                  " tcgen05.mma.cta_group::1.kind::tf32 [%0], [%2], %3, %5, p0;\n"
+                  " tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %4, %5, p1;\n"
+                  " tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %3, %5, p1;\n}"
+                  ::"r"(tAcc), "r"(aHi + 8u * k8), "r"(aLo + 8u * k8), "l"(dBh + 2u * k8), "l"(dBl + 2u * k8), "r"(idesc), "r"(acc) : "memory");
+            } else {
+              umma_tf32_ts(tAcc, aHi + 8u * k8, dBh + 2u * k8, idesc, acc);
             }
-            ok = mbar_wait(smem_u32(&fullA[nsa]), nph);
-            if (!ok) { atomicExch(p.status, 2); break; }
-            tc_fence_after();
           }
-          uint32_t const acc = (chunkStart && k8 == 0) ? 0u : 1u;      // 0 = overwrite: first MMA of a chain
-          if (kSplit) {
-            asm volatile(
-                "{\n .reg .pred p0, p1;\n setp.ne.b32 p0, %6, 0;\n setp.eq.b32 p1, %6, %6;\n"
-                " tcgen05.mma.cta_group::1.kind::tf32 [%0], [%2], %3, %5, p0;\n"
-                " tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %4, %5, p1;\n"
-                " tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %3, %5, p1;\n}"
-                ::"r"(tAcc), "r"(aHi + 8u * k8), "r"(aLo + 8u * k8), "l"(dBh + 2u * k8), "l"(dBl + 2u * k8), "r"(idesc), "r"(acc) : "memory");
-          } else {
-            umma_tf32_ts(tAcc, aHi + 8u * k8, dBh + 2u * k8, idesc, acc);
-          }
+          if (!ok) break;
+          umma_commit(smem_u32(&emptyA[q]));      // frees the A stage; its producers pass the news on for the B stage
+          phA ^= 1u;
+          sb += 2; if (sb >= kTsBStages) sb -= kTsBStages;
+          if (chunkEnd) { umma_commit(smem_u32(&drainFull[q])); ++gcq; }   // chain complete: hand it to the drain warps
         }
-        if (!ok) break;
-        umma_commit(smem_u32(&emptyA[sa]));      // frees the A stage; its producers pass the news on for the B stage
-        if (++sa == kTsGroups) { sa = 0; phA ^= 1u; }
-        if (++sb == kTsBStages) sb = 0;
-        ++inChunk;
-        if (chunkEnd) { umma_commit(smem_u32(&drainFull[tb])); inChunk = 0; ++gc; }   // chain complete: hand it to the drain warps
-        if (++it == numIter) it = 0;
       }
     }
     __syncwarp();
