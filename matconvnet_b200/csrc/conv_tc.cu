@@ -944,14 +944,15 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
 // The MMA thread is the critical resource: the tensor core's queue is about one MMA deep, so every
 // cycle that thread spends on anything but issuing (each barrier wait costs it about 100 cycles even
 // when the barrier is already complete, each commit about 50) is a cycle the tensor core idles.
-// Tensor memory columns: T0 | T1 | P (BN each; 3xTF32: chain accumulators and fp32 running sum; the
-// small terms lo*hi + hi*lo go to T as well) | A stage g at 3*BN + 64*g: 32 columns hi, 32 columns lo.
+// Tensor memory columns: T0 | T1 | T2 (BN each: chain accumulators, used round-robin by the two issuers; the small
+// terms lo*hi + hi*lo go to T as well) | A stage g at 3*BN + 64*g: 32 columns hi, 32 columns lo.  The fp32 running
+// sum P of a tile lives in shared memory, P[column][row], behind the filter stages.
 constexpr int kTsGroups = 2;
 constexpr int kTsLoaderWarp = kEpilogueWarps + 2;
 constexpr int kTsForwardWarp = kEpilogueWarps + 3;
 constexpr int kTsFirstProducer = kEpilogueWarps + 4;
 constexpr int kTsThreads = (kTsFirstProducer + 4 * kTsGroups) * 32;      // 512
-constexpr int kTsBStages = 6;
+constexpr int kTsBStages = 4;
 constexpr int kTsDrainEvery = 4;        // k-blocks per accumulation chain: 4 x 4 k-steps x 3 MMAs
 
 __device__ __forceinline__ void umma_tf32_ts(uint32_t dTmem, uint32_t aTmem, uint64_t bDesc, uint32_t iDesc, uint32_t accumulate)
@@ -973,34 +974,32 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, uint32_t const (&r)[32
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
 { asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n}" ::"r"(bar), "r"(bytes) : "memory"); }
 
-// Epilogue of conv_ts_kernel: the finished tile sits in the P columns; this warp stores the rows of its TMEM lane
-// quarter for the 32-column groups rank, rank + nranks, ...: out[(image*Ktot + n)*P + pixel] = inMult*acc + bias[n] + outMult*old.
-__device__ __forceinline__ void ts_store_tile(Params const& p, uint32_t lanesP, int quarter, int lane, int rank, int nranks, int m0, int n0)
+// Chains of one issuer in a tile of numIter k-blocks: the issuer that owns the tile's first k-block (second = 0) takes
+// the k-blocks 0, 2, ..., the other one (second = 1) the k-blocks 1, 3, ...; a chain is kTsDrainEvery own k-blocks (3xTF32)
+// or all of them (plain TF32).
+template <bool kSplit>
+__device__ __forceinline__ int ts_chains(int numIter, int second)
 {
-  int const BN = p.BN;
-  int const m = m0 + quarter * 32 + lane;
+  int const nOwn = numIter > second ? (numIter - second + 1) / 2 : 0;
+  return kSplit ? (nOwn + kTsDrainEvery - 1) / kTsDrainEvery : (nOwn > 0 ? 1 : 0);
+}
+
+// Epilogue of conv_ts_kernel: the finished tile sits in shared memory, P[column][row]; this warp stores the rows of its
+// TMEM lane quarter for the columns rank, rank + nranks, ...: out[(image*Ktot + n)*P + pixel] = inMult*acc + bias[n] + outMult*old.
+__device__ __forceinline__ void ts_store_tile(Params const& p, float const* P, int quarter, int lane, int rank, int nranks, int m0, int n0)
+{
+  int const row = quarter * 32 + lane;
+  int const m = m0 + row;
+  if (m >= p.M) return;
   int const pix = m % p.e.P, img = m / p.e.P;
-  long long const rowBase = (long long)img * p.e.Ktot * p.e.P + pix;
-  for (int c0 = 32 * rank; c0 < BN; c0 += 32 * nranks) {
-    uint32_t t0[16], t1[16];
-    bool const two = c0 + 16 < BN;
-    tmem_ld16_issue(lanesP + (uint32_t)c0, t0);
-    if (two) tmem_ld16_issue(lanesP + (uint32_t)(c0 + 16), t1);
-    tmem_ld_wait();
-    if (m < p.M) {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        int const n = n0 + c0 + j;
-        if ((j < 16 || two) && n < p.N) {
-          float const acc = __uint_as_float(j < 16 ? t0[j & 15] : t1[j & 15]);
-          float* dst = p.e.out + rowBase + (long long)n * p.e.P;
-          float o = p.e.inMult * acc;
-          if (p.e.bias) o += p.e.bias[n];
-          if (p.e.outMult != 0.f) o += p.e.outMult * *dst;
-          *dst = o;
-        }
-      }
-    }
+  float* const dst0 = p.e.out + ((long long)img * p.e.Ktot * p.e.P + pix);
+  int const nEnd = min(p.BN, p.N - n0);
+  for (int c = rank; c < nEnd; c += nranks) {
+    float* dst = dst0 + (long long)(n0 + c) * p.e.P;
+    float o = p.e.inMult * P[c * BM + row];
+    if (p.e.bias) o += p.e.bias[n0 + c];
+    if (p.e.outMult != 0.f) o += p.e.outMult * *dst;
+    *dst = o;
   }
 }
 
@@ -1009,7 +1008,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
 {
   extern __shared__ uint8_t smemRaw[];
   __shared__ __align__(8) uint64_t fullA[kTsGroups], emptyA[kTsGroups], fullB[kTsBStages], emptyB[kTsBStages];
-  __shared__ __align__(8) uint64_t drainFull[2], drainEmpty[2], tileDone;
+  __shared__ __align__(8) uint64_t tFull[3], tFree[3], tileDone;
   __shared__ uint32_t tmemBase;
   __shared__ int2 tapLut[64];       // per filter tap fh + FH*fw: {element offset of the tap, fh | fw << 5}
 
@@ -1018,7 +1017,8 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
   uint32_t const bTileBytes = (uint32_t)BN * BK * 4;
   uint32_t const bBytes = (kSplit ? 2u : 1u) * bTileBytes;
   uint32_t const tmemCols = 512;
-  uint32_t const colP = (uint32_t)(2 * BN), colA = (uint32_t)(3 * BN);
+  uint32_t const colA = (uint32_t)(3 * BN);
+  float* const Psm = reinterpret_cast<float*>(smem + (size_t)kTsBStages * bBytes);      // [BN][BM]
 
   int const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int const numIter = p.numKb;                     // k-blocks per tile
@@ -1032,7 +1032,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
     // an A stage is full when its four producer warps and the forwarder (filter tile landed) have arrived
     for (int s = 0; s < kTsGroups; ++s) { mbar_init(smem_u32(&fullA[s]), 5); mbar_init(smem_u32(&emptyA[s]), 1); }
     for (int s = 0; s < kTsBStages; ++s) { mbar_init(smem_u32(&fullB[s]), 1); mbar_init(smem_u32(&emptyB[s]), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(smem_u32(&drainFull[b]), 1); mbar_init(smem_u32(&drainEmpty[b]), kEpilogueWarps); }
+    for (int b = 0; b < 3; ++b) { mbar_init(smem_u32(&tFull[b]), 1); mbar_init(smem_u32(&tFree[b]), kEpilogueWarps); }
     mbar_init(smem_u32(&tileDone), kEpilogueWarps);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -1053,97 +1053,95 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
     // TMEM lane = one output row per thread, stores coalesced along the rows) while the tensor core is already
     // two chains into the next tile.
     uint32_t const lanes = tmemAcc + ((uint32_t)(warp * 32) << 16);
-    int gcq[2] = {0, 0};                              // chains of issuer 0 / 1 drained so far
+    float* const Prow = Psm + warp * 32 + lane;       // this thread's row of P: Prow[column * BM]
+    int g = 0;                                        // chains in the order they are drained, over the CTA's life: chain g sits in T[g % 3]
     bool ok = true;
     for (int ts = 0; ts < myTiles && ok; ++ts) {
       int const tile = (int)blockIdx.x + ts * (int)gridDim.x;
       int const m0 = (tile / p.tilesN) * BM, n0 = (tile % p.tilesN) * BN;
       int const qFirst = (int)(((long long)ts * numIter) & 1);          // the issuer that owns the tile's first k-block
-      int chains[2];
-      for (int q = 0; q < 2; ++q) {
-        int const first = q == qFirst ? 0 : 1, nOwn = numIter > first ? (numIter - first + 1) / 2 : 0;
-        chains[q] = kSplit ? (nOwn + kTsDrainEvery - 1) / kTsDrainEvery : (nOwn > 0 ? 1 : 0);
-      }
-      int const rounds = chains[0] > chains[1] ? chains[0] : chains[1];
+      int const chainsF = ts_chains<kSplit>(numIter, 0), chainsS = ts_chains<kSplit>(numIter, 1);   // of that issuer, of the other
       bool fresh = true;                              // P holds nothing of this tile yet
-      for (int c = 0; c < rounds && ok; ++c) {
+      (void)qFirst;
+      for (int c = 0; c < chainsF && ok; ++c) {
         for (int h = 0; h < 2 && ok; ++h) {
-          int const q = h == 0 ? qFirst : 1 - qFirst;
-          if (c >= chains[q]) continue;
-          ok = mbar_wait(smem_u32(&drainFull[q]), (uint32_t)(gcq[q] & 1));
+          if (h == 1 && c >= chainsS) continue;
+          int const t = g % 3;
+          ok = mbar_wait(smem_u32(&tFull[t]), (uint32_t)((g / 3) & 1));
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) { if (lane == 0) atomicExch(p.status, 5); break; }
-          ++gcq[q];
+          ++g;
           tc_fence_after();
-          // P = T (first chain of the tile) or P += T, then T[q] goes back to its issuer at once
+          // P = T (first chain of the tile) or P += T in fp32, then T[t] goes back to the issuers at once
           for (int c0 = 0; c0 < BN; c0 += 32) {
-            uint32_t t0[16], t1[16], p0[16], p1[16];
+            uint32_t t0[16], t1[16];
             bool const two = c0 + 16 < BN;
-            tmem_ld16_issue(lanes + (uint32_t)(q * BN + c0), t0);
-            if (two) tmem_ld16_issue(lanes + (uint32_t)(q * BN + c0 + 16), t1);
-            if (!fresh) {
-              tmem_ld16_issue(lanes + colP + (uint32_t)c0, p0);
-              if (two) tmem_ld16_issue(lanes + colP + (uint32_t)(c0 + 16), p1);
-            }
+            tmem_ld16_issue(lanes + (uint32_t)(t * BN + c0), t0);
+            if (two) tmem_ld16_issue(lanes + (uint32_t)(t * BN + c0 + 16), t1);
             tmem_ld_wait();
-            if (!fresh) {
+            float* pc = Prow + (size_t)c0 * BM;
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                t0[j] = __float_as_uint(__uint_as_float(t0[j]) + __uint_as_float(p0[j]));
-                if (two) t1[j] = __float_as_uint(__uint_as_float(t1[j]) + __uint_as_float(p1[j]));
-              }
+            for (int j = 0; j < 16; ++j) {
+              float v0 = __uint_as_float(t0[j]), v1 = __uint_as_float(t1[j]);
+              if (!fresh) { v0 += pc[j * BM]; if (two) v1 += pc[(16 + j) * BM]; }
+              pc[j * BM] = v0;
+              if (two) pc[(16 + j) * BM] = v1;
             }
-            tmem_st16(lanes + colP + (uint32_t)c0, t0);
-            if (two) tmem_st16(lanes + colP + (uint32_t)(c0 + 16), t1);
           }
           fresh = false;
-          tmem_st_wait();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&drainEmpty[q]));     // T[q] may be overwritten
+          if (lane == 0) mbar_arrive(smem_u32(&tFree[t]));     // T[t] may be overwritten
         }
       }
       if (!ok) break;
       if (singleTile) {
         // one tile per CTA: the producers have nothing left to do and share the stores
+        __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&tileDone));
-        ts_store_tile(p, lanes + colP, warp, lane, 0, 1 + kTsGroups, m0, n0);
+        ts_store_tile(p, Psm, warp, lane, 0, 1 + kTsGroups, m0, n0);
       } else {
-        // the tile is complete in P: store it while the tensor core works on the next tile (neither issuer
-        // gets more than one chain ahead of the drain)
-        ts_store_tile(p, lanes + colP, warp, lane, 0, 1, m0, n0);
+        // the tile is complete in P: store it while the tensor core works on the next tile (its chains wait in
+        // their T buffers until this is through)
+        ts_store_tile(p, Psm, warp, lane, 0, 1, m0, n0);
       }
-      tc_fence_before();
     }
   } else if (warp == kEpilogueWarps || warp == kEpilogueWarps + 1) {
     // ============================== MMA issue ==============================
     // Two issuing threads (in two warps, on two schedulers).  The tensor core's queue is about one MMA deep, so
     // while a thread waits on a barrier or commits, nothing of its own is in flight; with two threads the other
     // one's MMAs fill the gap.  Issuer q takes the k-blocks gi = q, q+2, ... (numbered over the CTA's life), which
-    // live in A stage q, and accumulates its chains in T[q]; chains of the two issuers never touch the same
-    // tensor-memory columns, so no ordering between the two streams is needed.  Per k-block: one barrier wait
-    // (A written and B landed), twelve MMAs, one commit; per chain: a wait for the drain of T[q] (there is no
-    // second T to switch to) and a commit that hands the chain to the drain warps.  (An issuer cannot wait for its
-    // next k-block ahead of time: that k-block goes into the A stage the current one still occupies.)
+    // live in A stage q.  Chains (kTsDrainEvery own k-blocks) take the three T buffers in turn, in the order the
+    // drain warps will add them to P, so two chains are being accumulated while the third is drained; the two
+    // issuers never touch the same tensor-memory columns, so no ordering between the two streams is needed.
+    // Per k-block: one barrier wait (A written and B landed), twelve MMAs, one commit; per chain: a wait for the T
+    // buffer and a commit that hands the chain to the drain warps.  (An issuer cannot wait for its next k-block
+    // ahead of time: that k-block goes into the A stage the current one still occupies.)
     if (lane == 0) {
       int const q = warp - kEpilogueWarps;
       uint32_t const idesc = make_idesc(false, false, BN);
       uint64_t const descB0 = make_desc(smem_u32(smem), 16, 1024);
       uint32_t const stageStep = bBytes >> 4, loStep = bTileBytes >> 4;
       uint32_t const aHi = tmemAcc + colA + (uint32_t)(q * 64), aLo = aHi + 32u;
-      uint32_t const tAcc = tmemAcc + (uint32_t)(q * BN);
       bool ok = true;
-      int sb = q, gcq = 0;
-      uint32_t phA = 0;
+      int sb = q, gBase = 0, g = 0;
+      uint32_t phA = 0, tAcc = tmemAcc;
       for (int ts = 0; ts < myTiles && ok; ++ts) {
-        int const first = (int)((((long long)ts * numIter) ^ q) & 1);
+        int const first = (int)((((long long)ts * numIter) ^ q) & 1);      // 0: this issuer owns the tile's first k-block
+        int const chainsF = ts_chains<kSplit>(numIter, 0), chainsS = ts_chains<kSplit>(numIter, 1);
         for (int it = first, j = 0; it < numIter; it += 2, ++j) {
           int const inChunk = kSplit ? j % kTsDrainEvery : j;
           bool const chunkStart = inChunk == 0;
           bool const chunkEnd = it + 2 >= numIter || (kSplit && inChunk + 1 == kTsDrainEvery);
-          if (chunkStart && gcq >= 1) {               // the previous chain of T[q] must have been added to P
-            ok = mbar_wait(smem_u32(&drainEmpty[q]), (uint32_t)((gcq - 1) & 1));
-            if (!ok) { atomicExch(p.status, 6); break; }
+          if (chunkStart) {
+            // this chain's place in the drain order (first issuer's chain c, second issuer's chain c, first's c+1, ...)
+            int const c = kSplit ? j / kTsDrainEvery : 0;
+            g = gBase + min(c, chainsF) + min(c, chainsS) + (first == 1 && c < chainsF ? 1 : 0);
+            tAcc = tmemAcc + (uint32_t)((g % 3) * BN);
+            if (g >= 3) {                             // the chain that sat in this T before must have been added to P
+              ok = mbar_wait(smem_u32(&tFree[g % 3]), (uint32_t)(((g / 3) - 1) & 1));
+              if (!ok) { atomicExch(p.status, 6); break; }
+            }
           }
           ok = mbar_wait(smem_u32(&fullA[q]), phA);
           if (!ok) { atomicExch(p.status, 2); break; }
@@ -1167,8 +1165,9 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
           umma_commit(smem_u32(&emptyA[q]));      // frees the A stage; its producers pass the news on for the B stage
           phA ^= 1u;
           sb += 2; if (sb >= kTsBStages) sb -= kTsBStages;
-          if (chunkEnd) { umma_commit(smem_u32(&drainFull[q])); ++gcq; }   // chain complete: hand it to the drain warps
+          if (chunkEnd) umma_commit(smem_u32(&tFull[g % 3]));   // chain complete: hand it to the drain warps
         }
+        gBase += chainsF + chainsS;
       }
     }
     __syncwarp();
@@ -1283,8 +1282,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
       if (!done) { if (lane == 0) atomicExch(p.status, 3); }
       else {
         int const tile = (int)blockIdx.x;
-        ts_store_tile(p, tmemAcc + ((uint32_t)(quarter * 32) << 16) + colP, quarter, lane, 1 + grp, 1 + kTsGroups,
-                      (tile / p.tilesN) * BM, (tile % p.tilesN) * BN);
+        ts_store_tile(p, Psm, quarter, lane, 1 + grp, 1 + kTsGroups, (tile / p.tilesN) * BM, (tile % p.tilesN) * BN);
       }
       tc_fence_before();
     }
@@ -1537,15 +1535,14 @@ int launch_ts(vlb_ctx* ctx, Params& p, char const* where)
   bool split3 = ctx->precision == VLB_PRECISION_3XTF32;
   p.status = ctx->deviceStatus;
   // at least 120 KB, so that two CTAs (each allocating all 512 TMEM columns) never share an SM
-  size_t smemBytes = (size_t)kTsBStages * (split3 ? 2u : 1u) * (size_t)p.BN * BK * 4 + 1024;
+  size_t smemBytes = (size_t)kTsBStages * (split3 ? 2u : 1u) * (size_t)p.BN * BK * 4 + sizeof(float) * (size_t)p.BN * BM + 1024;
   if (smemBytes < 120u * 1024u) smemBytes = 120u * 1024u;
   p.tilesM = vlb::ceil_div(p.M, BM); p.tilesN = vlb::ceil_div(p.N, p.BN);
   long long const numTiles = (long long)p.tilesM * p.tilesN;
   if (numTiles >= (1LL << 31)) return VLB_Unsupported;
-  // Short reductions (prologue and epilogue would dominate a CTA's life): persistent, one CTA per SM walks the tiles and
-  // stores a tile while the next is computed.  Long reductions: one CTA per tile, every warp shares the stores at the end
-  // (the overlapped stores of four warps slow the MMA-issuing thread down by more than they hide).
-  bool const persistent = p.BN <= 64 || p.numKb <= 36;
+  // Persistent: one CTA per SM walks the tiles, so that the pipeline never drains between tiles and a tile is stored
+  // while the next one is computed.  With fewer tiles than SMs every CTA has one tile and all its warps share the stores.
+  bool const persistent = true;
   dim3 grid((unsigned)(persistent && numTiles > ctx->smCount ? ctx->smCount : numTiles), 1, 1);
   cudaError_t e;
   vlb_ctx::ProfRec rec;
