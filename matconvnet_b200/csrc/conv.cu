@@ -58,8 +58,24 @@ conv_dbias_kernel(float* __restrict__ db, float const* __restrict__ dy, int P, i
   cluster.sync();
 }
 
+// The same for 1x1 outputs (fully connected layers): db[k] = sum over images of dy[k + K*n]; one thread per
+// filter, reads coalesced across the filters, images added in order.
+__global__ void conv_dbias_p1_kernel(float* __restrict__ db, float const* __restrict__ dy, int K, int N)
+{
+  int const k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= K) return;
+  float s = 0.f;
+  for (int n = 0; n < N; ++n) s += dy[(size_t)n * K + k];
+  db[k] = s;
+}
+
 int launch_dbias(vlb_ctx* ctx, float* db, float const* dY, int P, int K, int N)
 {
+  if (P == 1) {
+    conv_dbias_p1_kernel<<<vlb::ceil_div(K, 128), 128, 0, ctx->stream>>>(db, dY, K, N);
+    VLB_LAUNCHED(ctx, 1);
+    return vlb::check_launch(ctx, "conv_dbias");
+  }
   bool vec = (P % 4 == 0) && ((((uintptr_t)dY) & 15) == 0);
   dim3 grid(K, kCluster);
   if (vec) conv_dbias_kernel<true><<<grid, kThreads, 0, ctx->stream>>>(db, dY, P, K, N);

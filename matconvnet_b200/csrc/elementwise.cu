@@ -101,6 +101,20 @@ __global__ void bias_fwd_kernel(float* __restrict__ y, float ym, float const* __
   }
 }
 
+// The same for small planes (P < 64, e.g. the 1x1 outputs of a fully connected layer): one thread per element.
+__global__ void bias_fwd_flat_kernel(float* __restrict__ y, float ym, float const* __restrict__ x, float xm,
+                                     float const* __restrict__ b, float bm, int P, int K, size_t total, int mode)
+{
+  size_t const step = (size_t)gridDim.x * blockDim.x;
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += step) {
+    int const k = (int)((e / P) % K);
+    float v = (mode == 2) ? 0.f : __fmul_rn(bm, b[k]);
+    if (mode == 1) v = __fadd_rn(v, __fmul_rn(ym, y[e]));
+    if (x) v = __fadd_rn(v, __fmul_rn(xm, x[e]));
+    y[e] = v;
+  }
+}
+
 // db[k] = beta*db[k] + bm * sum over (p, n) of dy; one block per k, fixed-order tree.
 __global__ void bias_bwd_db_kernel(float* __restrict__ db, float beta, float bm, float const* __restrict__ dy,
                                    int P, int K, int N)
@@ -254,6 +268,13 @@ int vlb_bias_forward(vlb_ctx* ctx, float* Y, double yMult, float const* X, doubl
   int mode = (b && bMult != 0) ? ((float)yMult == 0.f ? 0 : 1) : 2;
   float const* xin = (X && xMult != 0) ? X : nullptr;
   size_t planes = (size_t)K * N;
+  if (P < 64) {
+    size_t total = planes * (size_t)P;
+    bias_fwd_flat_kernel<<<vlb::grid_for(total, kThreads, ctx->smCount * 8), kThreads, 0, ctx->stream>>>(
+        Y, (float)yMult, xin, (float)xMult, b, (float)bMult, P, K, total, mode);
+    VLB_LAUNCHED(ctx, 1);
+    return vlb::check_launch(ctx, "vlb_bias_forward");
+  }
   dim3 grid(vlb::ceil_div(P, kThreads) > 64 ? 64 : vlb::ceil_div(P, kThreads), (unsigned)(planes > 32768 ? 32768 : planes));
   bias_fwd_kernel<<<grid, kThreads, 0, ctx->stream>>>(Y, (float)yMult, xin, (float)xMult, b, (float)bMult, P, K, planes, mode);
   VLB_LAUNCHED(ctx, 1);

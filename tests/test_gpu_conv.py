@@ -138,6 +138,25 @@ def test_conv_layers_vs_oracle(gpu, oracle, precision, layer, mode, prec, tol):
     assert dx3 is None and np.array_equal(mat.to_numpy(df3), mat.to_numpy(df))
 
 
+def test_fused_bias_gradient_is_deterministic_and_matches_the_separate_kernel(gpu):
+    """When the output plane is a multiple of four pixels the bias gradient is summed by the kernel that writes the
+    dY tile images of the filter gradient (per-block partials finished by the last block, in block order): the
+    result must not depend on the scheduling, and must agree with the stand-alone reduction used when only the bias
+    gradient is asked for (reference bits/nnconv.cu:229-244)."""
+    nn, mat, ctx = gpu
+    import torch
+    ctx.set_precision(0)
+    x = mat.as_mat(torch.randn(40, 36, 32, 6, device="cuda"))
+    f = mat.as_mat(torch.randn(3, 3, 32, 48, device="cuda") * 0.05)
+    b = mat.zeros((1, 48))
+    dy = mat.as_mat(torch.randn(40, 36, 48, 6, device="cuda"))
+    runs = [mat.to_numpy(nn.vl_nnconv(x, f, b, dy, pad=1, no_der_data=True)[2]).ravel() for _ in range(3)]
+    assert np.array_equal(runs[0], runs[1]) and np.array_equal(runs[0], runs[2])
+    alone = mat.to_numpy(nn.vl_nnconv(x, f, b, dy, pad=1, no_der_data=True, no_der_filters=True)[2]).ravel()
+    ref = mat.to_numpy(dy).astype(np.float64).sum(axis=(0, 1, 3))
+    assert rel_l2(runs[0], ref) < 1e-6 and rel_l2(alone, ref) < 1e-6
+
+
 def test_conv_identities_on_device(gpu):
     """stride == subsampling, pad == crop, groups == block-diagonal (reference
     xtest/suite/nnconv.m:88-125,144-161), in the default arithmetic."""
