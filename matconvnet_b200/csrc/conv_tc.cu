@@ -91,7 +91,7 @@ struct Params {
   int stages;
   int drainEvery;         // 3xTF32: k-blocks per tensor-core accumulation chain
   int tilesM, tilesN;     // conv_ts_kernel: the grid of output tiles its persistent CTAs walk
-  int chanFast;           // conv_ts_kernel: reduction ordered channel-fastest, r = c + C*(fh + FH*fw); needs C % 32 == 0
+  int chanFast;           // conv_ts_kernel: reduction in blocks of 32 channels, r = c%32 + 32*(tap + taps*(c/32)); needs C % 32 == 0
   int pipelined;          // 1: producers prefetch one stage ahead in registers (aligned gathers only)
   float const* bTiles;    // when non-null: B pre-split into shared-memory tile images, fetched with bulk copies
   int* status;
@@ -1232,8 +1232,9 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
         int const r = it * BK;
         float v[32];
         if (p.chanFast) {
-          // the whole k-block is one filter tap and 32 consecutive channels: one validity test, constant stride
-          int const tp = r / p.a.C, c0 = r - tp * p.a.C;
+          // the whole k-block is one filter tap and 32 consecutive channels: one validity test, constant stride.  The taps
+          // of a channel block follow one another, so that the lines fetched for one tap are still in L1 for the next.
+          int const tp = it % taps, c0 = (it / taps) * 32;
           int2 const te = tapLut[tp];
           uint32_t const e = (uint32_t)te.y;
           bool const on = ((hm >> (e & 31u)) & (wm >> (e >> 5)) & 1u) != 0;
@@ -1322,7 +1323,7 @@ __global__ void flip_filters_kernel(float* __restrict__ ft, float const* __restr
 // into hi / lo once and laid out as ready-made shared-memory tile images -- for n-tile t and k-block
 // kb: [hi tile BN x 32][lo tile BN x 32], K-major with the 128-byte swizzle -- so that a producer
 // fetches a whole stage of B with one bulk copy.
-// modes 3 / 4: as 0 / 1 with the reduction index ordered channel-fastest.
+// modes 3 / 4: as 0 / 1 with the reduction index in blocks of 32 channels, all filter taps of a block one after the other.
 // mode 0: B(n, r) = F[n*R + r].  mode 2: B(n, r) = dY[pixel, n, image] with r = pixel + P*image.  mode 1 (data gradient of a stride-1 convolution): n = channel c,
 // r = fh' + FH*(fw' + FW*k), B = F[FH-1-fh', FW-1-fw', c, k].
 template <bool kSplit>
@@ -1342,12 +1343,12 @@ __global__ void prep_b_tiles_kernel(float* __restrict__ out, float const* __rest
         int img = r / FH, pix = r - img * FH;
         val = f[((size_t)img * N + n) * FH + pix];
       } else if (mode == 3) {
-        // forward filters, channel-fastest reduction: r = c + C*tap
-        int c = r % C, tap = r / C;
-        val = f[(size_t)n * R + tap + (size_t)(FH * FW) * c];
+        // forward filters, reduction in blocks of 32 channels: r = c%32 + 32*(tap + taps*(c/32))
+        int taps = FH * FW, t = r >> 5, tap = t % taps, c = (t / taps) * 32 + (r & 31);
+        val = f[(size_t)n * R + tap + (size_t)taps * c];
       } else if (mode == 4) {
-        // data gradient, channel-fastest reduction: r = k + K*(fh' + FH*fw')
-        int k = r % K, tap = r / K, fh = tap % FH, fw = tap / FH;
+        // data gradient, reduction in blocks of 32 filters: r = k%32 + 32*(tap' + taps*(k/32)), tap' = fh' + FH*fw'
+        int taps = FH * FW, t = r >> 5, tap = t % taps, k = (t / taps) * 32 + (r & 31), fh = tap % FH, fw = tap / FH;
         val = f[(FH - 1 - fh) + (size_t)FH * ((FW - 1 - fw) + (size_t)FW * (n + (size_t)C * k))];
       } else {
         int fh = r % FH, t = r / FH, fw = t % FW, k = t / FW;
