@@ -79,6 +79,12 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------- CPU arm
+# dram__bytes_read.sum + dram__bytes_write.sum of the tensor-core contraction launches of one step of this workload
+# (batch 64, 3xTF32), from the ncu launch list summarised in profiles/bench_vgg16_batch64_launch_list.md: 20.2 GB over
+# 46 launches.  Per launch, like roofline.achieved.
+NCU_DRAM_BYTES_PER_CONTRACTION_LAUNCH = 20.24e9 / 46
+
+
 def cpu_vgg16(batch, steps, warmup, threads):
     """The reference's CPU backend (oracle/_ref when built, else the C restatement) on VGG-16."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
@@ -260,7 +266,8 @@ def main():
     achieved = tc_flops / (tc_ms * 1e-3) / 1e12 if tc_ms > 0 else 0.0
     passes = 3 if args.precision == "3xtf32" else 1
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "traffic": None, "kernel": "tc_gemm_kernel (conv fprop/dgrad/wgrad + fully connected)",
+                "traffic": NCU_DRAM_BYTES_PER_CONTRACTION_LAUNCH if (B == PER_GPU_BATCH and passes == 3) else None,
+                "kernel": "conv_ts_kernel (conv fprop/dgrad) + tc_gemm_kernel (conv wgrad, fully connected)",
                 "launches_per_step": tc_launches, "ms_per_step": tc_ms, "mma_passes": passes,
                 "tensor_work_frac": passes * achieved / peak, "peak_source": peak_src,
                 "note": "achieved counts each contraction's 2*M*N*K once; the 3xTF32 arithmetic issues 3 MMAs per product"}
