@@ -2,20 +2,24 @@
 // (reference bits/nnconv.cu:71-317, bits/nnfullyconnected.cu:30-185) on tcgen05 / TMEM.
 //
 // Every contraction on the path is D[m][n] = sum_r A(m,r) * B(n,r) with fp32 accumulation
-// in tensor memory.  One kernel template, 128 x BN output tile per CTA, reduction in blocks
-// of 32, warp-specialised:
-//   warps 0-3   epilogue: tcgen05.ld the accumulator (one TMEM lane = one output row per
-//               thread) and store to global memory, coalesced along m;
-//   warp  4     allocates TMEM and issues tcgen05.mma (kind::tf32, cta_group::1) from one
-//               lane; tcgen05.commit releases a stage / publishes the accumulator;
-//   warps 5-16  producers: gather the operand tiles from the MATLAB-order tensors
-//               (no patch matrix: the reference writes one per image, bits/nnconv.cu:109-117),
-//               split every value into a TF32 "hi" part and an exactly representable
-//               remainder "lo", and write both as 128-byte-swizzled UMMA tiles.
+// in tensor memory, 128 x BN output tile, reduction in blocks of 32.  Two kernels:
+//
+//   conv_ts_kernel   convolution forward and stride-1 data gradient: the gathered operand goes to
+//                    tensor memory, only the filter tiles to shared memory (further down).
+//   tc_gemm_kernel   filter gradient, fully connected layers, and convolutions whose filter support
+//                    exceeds the tap table: both operands in shared memory, warp-specialised:
+//     warps 0-3   fp32 drain of the accumulation chains, then epilogue: tcgen05.ld the accumulator
+//                 (one TMEM lane = one output row per thread), store to global memory, coalesced along m;
+//     warp  4     allocates TMEM and issues tcgen05.mma (kind::tf32, cta_group::1) from one
+//                 lane; tcgen05.commit releases a stage / hands a chain to the drain warps;
+//     warps 5-16  producers: gather the operand tiles from the MATLAB-order tensors
+//                 (no patch matrix: the reference writes one per image, bits/nnconv.cu:109-117),
+//                 split every value into a TF32 "hi" part and an exactly representable
+//                 remainder "lo", and write both as 128-byte-swizzled UMMA tiles.
 // The split is what makes the result fp32-faithful: x*y ~ hi*hi + hi*lo + lo*hi, three
 // MMAs per product ("3xTF32"); the dropped lo*lo term is below 2^-22 relative.  The
 // single-pass TF32 mode issues only hi*hi.
-// Stages are handed over with mbarriers; every wait is bounded (about a second) and on
+// Stages are handed over with mbarriers; every wait is bounded (about a tenth of a second) and on
 // expiry records a status word and unwinds, releasing TMEM, instead of spinning forever.
 //
 // Operand layouts in shared memory (canonical UMMA layouts, 128-byte swizzle):
