@@ -171,10 +171,13 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path in this engine)"
     torch.cuda.set_device(local)
+    stdout_fd = None
     if world > 1:
-        # NCCL_DEBUG=VERSION makes NCCL print a banner on stdout, where only the JSON line belongs
-        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"
+        # NCCL prints its version banner on stdout when its first communicator comes up; only the JSON line
+        # belongs there, so stdout points at stderr until the line is printed.
+        sys.stdout.flush()
+        stdout_fd = os.dup(1)
+        os.dup2(2, 1)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     warmup = max(args.warmup, 3)
 
@@ -297,6 +300,9 @@ def main():
                 line["cpu_baseline"] = base
             except Exception as exc:      # the checker is not part of the product: report, do not fail the bench
                 line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": "failed: %r" % (exc,)}
+        if stdout_fd is not None:
+            sys.stdout.flush()
+            os.dup2(stdout_fd, 1)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
