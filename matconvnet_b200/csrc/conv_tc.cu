@@ -1255,9 +1255,16 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
           int2 const te = tapLut[tp];
           uint32_t const e = (uint32_t)te.y;
           bool const on = ((hm >> (e & 31u)) & (wm >> (e >> 5)) & 1u) != 0;
-          float const* const q = xq + ((long long)c0 * HW + te.x);
+          // unconditional loads (a pixel outside the image reads the start of the tensor instead and discards it):
+          // nothing for the compiler to predicate or branch around, all 32 in flight together
+          float const* const q = on ? xq + ((long long)c0 * HW + te.x) : p.a.ptr;
+          long long const step = on ? (long long)HW : 0;
 #pragma unroll
-          for (int k = 0; k < 32; ++k) { v[k] = 0.f; ldg32_if(v[k], q + (long long)k * HW, on); }
+          for (int k = 0; k < 32; ++k) v[k] = __ldg(q + k * step);
+          if (!on) {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) v[k] = 0.f;
+          }
         } else {
           int tap = r % taps, ch = r / taps;
 #pragma unroll
