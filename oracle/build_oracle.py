@@ -20,7 +20,8 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_ROOT = os.environ.get("MCN_REFERENCE_ROOT", "/root/reference")
+# the reference checkout: MCN_REFERENCE_ROOT, else a directory "reference" beside this repository
+REF_ROOT = os.environ.get("MCN_REFERENCE_ROOT", os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 REF_BITS = os.path.join(REF_ROOT, "matlab", "src", "bits")
 REF_OUT = os.path.join(HERE, "_ref")
 REF_SO = os.path.join(REF_OUT, "libmcn_ref.so")
