@@ -198,6 +198,52 @@ def test_c4_vgg16_topology_small(gpu, oracle):
     _replay(res, mat, oracle, layers)
 
 
+def test_c4_vgg16_full_size_vs_compiled_reference(gpu, oracle):
+    """The real VGG-16 (224x224 inputs, 4096-wide fully connected layers, 1000 classes) at batch 2 against the
+    reference's own compiled CPU backend in double precision, its GEMMs routed to a threaded BLAS so that the 62 GFLOP
+    finish in seconds: the loss, and every layer replayed from the GPU's own input and output derivative."""
+    import os
+    import torch
+    import cpu_net
+    import oracle as O
+    from matconvnet_b200 import models, simplenn
+    nn, mat, ctx = gpu
+    ref = O.reference()
+    if ref is None or not O.reference_use_openblas(os.cpu_count() or 1):
+        pytest.skip("the compiled reference backend or a threaded BLAS for it is not available")
+    try:
+        ctx.set_precision(0)
+        ctx.reserve_workspace(3 << 30)
+        rng = np.random.default_rng(106)
+        net = models.vgg16(seed=3)
+        labels = rng.integers(1, 1001, size=2).astype(np.float32)
+        net["layers"][-1]["class"] = torch.from_numpy(labels).cuda()
+        x = np.asfortranarray(rng.standard_normal((224, 224, 3, 2)).astype(np.float32))
+        res = simplenn.vl_simplenn(net, mat.from_numpy(x), 1.0, ctx=ctx)
+        assert ctx.device_status() == 0
+        host = _np_layers(net["layers"], mat)
+        f64 = lambda t: np.asfortranarray(mat.to_numpy(t), dtype=np.float64)
+        full = cpu_net.simplenn(ref, oracle, host, np.asfortranarray(x, dtype=np.float64), np.float64(1.0), conserve_memory=True)
+        loss, loss_ref = float(res[-1]["x"].cpu()[0]), float(full[-1]["x"])
+        assert abs(loss - loss_ref) <= 5e-5 * abs(loss_ref), (loss, loss_ref)
+        del full
+        for i, l in enumerate(host):
+            xi = f64(res[i]["x"])
+            y = cpu_net.layer_forward(ref, oracle, l, xi)
+            got = res[i + 1]["x"].cpu().numpy() if l["type"] == "softmaxloss" else mat.to_numpy(res[i + 1]["x"])
+            assert rel_l2(got, y) < TOL, ("layer %d (%s) forward" % (i, l["type"]), rel_l2(got, y))
+            d = res[i + 1]["dzdx"]
+            d = np.float64(d) if np.isscalar(d) else f64(d)
+            dx, dw = cpu_net.layer_backward(ref, oracle, l, xi, d)
+            assert rel_l2(mat.to_numpy(res[i]["dzdx"]), dx) < TOL, ("layer %d (%s) dzdx" % (i, l["type"]),)
+            for j, w in enumerate(dw or []):
+                if w is not None and res[i]["dzdw"][j] is not None:
+                    err = rel_l2(mat.to_numpy(res[i]["dzdw"][j]).ravel(), np.asarray(w).ravel())
+                    assert err < TOL, ("layer %d (%s) dzdw[%d]" % (i, l["type"], j), err)
+    finally:
+        O.reference_use_plain_blas()
+
+
 def test_c5_fast_rcnn_head_and_sampler(gpu, oracle):
     """ROI max-pool 7x7 on a 38x50x512x2 map with ROIs in feature-map coordinates, two conv-as-FC layers
     (widths reduced for the CPU checker), backward; and the bilinear sampler backward with an affine grid of
