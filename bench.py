@@ -199,7 +199,7 @@ def main():
 
     def step():
         res = simplenn.vl_simplenn(net, x, one, on_dzdw=lambda i, j, w: exchange.push("l%d_%d" % (i, j), w), ctx=ctx,
-                                   conserve_memory=True)
+                                   conserve_memory=True, fuse_relu=True)
         exchange.pull_all()
         return res
 

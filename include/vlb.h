@@ -86,6 +86,14 @@ int vlb_conv_output_shape(vlb_conv_desc const* d, int* Ho, int* Wo);
 int vlb_conv_forward(vlb_ctx* ctx, float* Y, double outMult, float const* X, double inMult,
                      float const* F, float const* b, vlb_conv_desc const* d);
 
+/* Forward convolution followed by ReLU in one call: Y = max(conv(X,F) + b, 0).  No counterpart among the reference's
+ * operator classes: vl_simplenn runs vl_nnrelu as a layer of its own (matlab/simplenn/vl_simplenn.m:334-336), and when it
+ * has dropped the ReLU's input to save memory (:386) it takes the mask from the ReLU's output (:448-455) -- which is what a
+ * caller of this entry point does in the backward pass, vlb_relu_backward(dX, Y, dY).  The result is bit-identical to
+ * vlb_conv_forward followed by vlb_relu_forward. */
+int vlb_conv_relu_forward(vlb_ctx* ctx, float* Y, float const* X, float const* F, float const* b,
+                          vlb_conv_desc const* d);
+
 /* Convolution::backward (bits/nnconv.cu:163-317).  dX, dF, db are overwritten; any may be NULL. */
 int vlb_conv_backward(vlb_ctx* ctx, float* dX, float* dF, float* db, float const* X,
                       float const* F, float const* dY, vlb_conv_desc const* d);

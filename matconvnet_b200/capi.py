@@ -58,6 +58,7 @@ SIGNATURES = {
     "vlb_ctx_profile_end": (_I, [_P, C.POINTER(_D), C.POINTER(_D), C.POINTER(C.c_longlong)]),
     "vlb_conv_output_shape": (_I, [C.POINTER(ConvDesc), C.POINTER(_I), C.POINTER(_I)]),
     "vlb_conv_forward": (_I, [_P, _P, _D, _P, _D, _P, _P, C.POINTER(ConvDesc)]),
+    "vlb_conv_relu_forward": (_I, [_P, _P, _P, _P, _P, C.POINTER(ConvDesc)]),
     "vlb_conv_backward": (_I, [_P, _P, _P, _P, _P, _P, _P, C.POINTER(ConvDesc)]),
     "vlb_fc_forward": (_I, [_P, _P, _P, _P, _P, C.POINTER(ConvDesc)]),
     "vlb_fc_backward": (_I, [_P, _P, _P, _P, _P, _P, _P, C.POINTER(ConvDesc)]),

@@ -24,6 +24,9 @@ struct vlb_ctx {
                                  // 4096 zeroed ticket counters for last-block-finishes reductions, left at zero by their users
   // optional timing of the tensor-core launches with events on the launching stream
   struct ProfRec { cudaEvent_t start, stop; double flops; };
+  // set by vlb_conv_relu_forward around its call of the forward convolution: the path that ran applies max(., 0) in its
+  // epilogue and says so, otherwise the caller runs the ReLU kernel on the result
+  bool fuseRelu = false, reluDone = false;
   bool profiling = false;
   std::vector<ProfRec> prof;
 };

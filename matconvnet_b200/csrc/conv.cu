@@ -153,9 +153,23 @@ int vlb_conv_forward(vlb_ctx* ctx, float* Y, double outMult, float const* X, dou
   if (ctx->precision != VLB_PRECISION_FP32) {
     rc = vlb::conv_fprop_tc(ctx, g, Y, (float)outMult, X, (float)inMult, F, b);
     if (rc != VLB_Unsupported) return rc ? vlb::pass_error(ctx, rc, "vlb_conv_forward") : rc;
+    ctx->reluDone = false;      // the CUDA-core kernel below has no fused ReLU
   }
   rc = vlb::conv_fprop_simt(ctx, g, Y, (float)outMult, X, (float)inMult, F, b);
   return rc ? vlb::pass_error(ctx, rc, "vlb_conv_forward") : rc;
+}
+
+int vlb_conv_relu_forward(vlb_ctx* ctx, float* Y, float const* X, float const* F, float const* b, vlb_conv_desc const* d)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  ctx->fuseRelu = true; ctx->reluDone = false;
+  int rc = vlb_conv_forward(ctx, Y, 0.0, X, 1.0, F, b, d);
+  bool const done = ctx->reluDone;
+  ctx->fuseRelu = false; ctx->reluDone = false;
+  if (rc || done) return rc;
+  int Ho = 0, Wo = 0;
+  vlb_conv_output_shape(d, &Ho, &Wo);
+  return vlb_relu_forward(ctx, Y, Y, (size_t)Ho * Wo * d->K * d->N);
 }
 
 int vlb_conv_backward(vlb_ctx* ctx, float* dX, float* dF, float* db, float const* X, float const* F,

@@ -24,6 +24,7 @@ struct SmallParams {
   float inMult, outMult;
   int H, W, Cin, N, Ho, Wo, Kout;
   int FH, FW, sy, sx, pt, pl, dy, dx;
+  int relu;             // apply max(., 0) to the stored value
   int flip;             // 0: forward filters F[fh,fw,c,k]; 1: data gradient, F[FH-1-fh, FW-1-fw, k(out), c(in)]
   int Cf;               // the filter bank's third extent (channels of the forward input)
 };
@@ -102,6 +103,7 @@ __global__ void __launch_bounds__(kThreads) conv_small_r_kernel(SmallParams p)
       float o = p.inMult * acc[k];
       if (p.bias) o += p.bias[k0 + k];
       if (p.outMult != 0.f) o += p.outMult * *dst;
+      if (p.relu) o = o > 0.f ? o : 0.f;
       *dst = o;
     }
   }
@@ -158,6 +160,7 @@ __global__ void __launch_bounds__(kThreads) conv_small_n_kernel(SmallParams p)
       float o = p.inMult * acc[k];
       if (p.bias) o += p.bias[k];
       if (p.outMult != 0.f) o += p.outMult * *dst;
+      if (p.relu) o = o > 0.f ? o : 0.f;
       *dst = o;
     }
   }
@@ -184,6 +187,7 @@ int conv_fprop_small(vlb_ctx* ctx, ConvGeom const& g, float* Y, float outMult, f
   p.H = g.H; p.W = g.W; p.Cin = g.C; p.N = g.N; p.Ho = g.Ho; p.Wo = g.Wo; p.Kout = g.K;
   p.FH = g.FH; p.FW = g.FW; p.sy = g.sy; p.sx = g.sx; p.pt = g.pt; p.pl = g.pl; p.dy = g.dy; p.dx = g.dx;
   p.flip = 0; p.Cf = g.FC;
+  p.relu = ctx->fuseRelu; ctx->reluDone = ctx->fuseRelu;
   long long const M = (long long)g.Ho * g.Wo * g.N;
   int const KC = g.K > 32 ? 64 : (g.K > 16 ? 32 : 16);
   dim3 grid((unsigned)ceil_div(M, kThreads), (unsigned)ceil_div(g.K, KC));

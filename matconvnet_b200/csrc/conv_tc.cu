@@ -84,6 +84,7 @@ struct Epilogue {
   long long splitStride;
   float inMult, outMult;
   int P, Ktot;
+  int relu;            // apply max(., 0) to the stored value (forward convolution followed by a ReLU layer)
 };
 
 struct Params {
@@ -908,10 +909,12 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(Params p)
                 float o = p.e.inMult * acc;
                 if (p.e.bias) o += p.e.bias[n];
                 if (p.e.outMult != 0.f) o += p.e.outMult * *dst;
+                if (p.e.relu) o = o > 0.f ? o : 0.f;
                 *dst = o;
               } else {
                 float o = acc;
                 if (p.e.bias) o += p.e.bias[m];
+                if (p.e.relu) o = o > 0.f ? o : 0.f;
                 p.e.out[rowBase + (long long)n * p.e.ldd] = o;
               }
             }
@@ -1005,6 +1008,7 @@ __device__ __forceinline__ void ts_store_tile(Params const& p, float const* P, i
     float o = p.e.inMult * P[c * BM + row];
     if (p.e.bias) o += p.e.bias[n0 + c];
     if (p.e.outMult != 0.f) o += p.e.outMult * *dst;
+    if (p.e.relu) o = o > 0.f ? o : 0.f;
     *dst = o;
   }
 }
@@ -1654,6 +1658,7 @@ int conv_fprop_tc(vlb_ctx* ctx, ConvGeom const& g, float* Y, float outMult, floa
     p.e = Epilogue{}; p.e.ldd = g.K;
     if (splits == 1) {
       p.e.out = Y; p.e.bias = b;
+      p.e.relu = ctx->fuseRelu; ctx->reluDone = ctx->fuseRelu;
       return launch<OP_DENSE_K, OP_DENSE_K, EPI_PLAIN>(ctx, p, 1, "fc_fprop_tc");
     }
     size_t nOut = (size_t)g.K * g.N;
@@ -1675,6 +1680,7 @@ int conv_fprop_tc(vlb_ctx* ctx, ConvGeom const& g, float* Y, float outMult, floa
   p.BN = pick_bn(p.N);
   p.numKb = ceil_div(p.R, BK); p.kbPerSplit = p.numKb;
   p.e = Epilogue{}; p.e.out = Y; p.e.bias = b; p.e.inMult = inMult; p.e.outMult = outMult; p.e.P = g.Ho * g.Wo; p.e.Ktot = g.K;
+  p.e.relu = ctx->fuseRelu; ctx->reluDone = ctx->fuseRelu;
   if (p.a.fast) {
     p.chanFast = g.C % 32 == 0;
     p.bTiles = prep_b_tiles(ctx, F, g.K, V, p.BN, p.numKb, p.chanFast ? 3 : 0, g);

@@ -12,7 +12,8 @@ inline bool aligned16(void const* p) { return (((uintptr_t)p) & 15) == 0; }
 
 // ---------------------------------------------------------------- ReLU / sum / scale
 // y = max(x, 0) (reference matlab/vl_nnrelu.m:45)
-__global__ void relu_fwd_kernel(float* __restrict__ y, float const* __restrict__ x, size_t n, bool vec)
+// y and x may be the same array (element i is read before it is written)
+__global__ void relu_fwd_kernel(float* y, float const* x, size_t n, bool vec)
 {
   size_t stride = (size_t)gridDim.x * blockDim.x, i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (vec) {

@@ -76,10 +76,11 @@ def _is_fc(d, Ho, Wo):
 
 
 def vl_nnconv(x, f, b, dzdy=None, stride=1, pad=0, dilate=1, no_der_data=False, no_der_filters=False,
-              no_der_biases=False, ctx=None):
+              no_der_biases=False, relu=False, ctx=None):
     """Y = VL_NNCONV(X, F, B) / [DX, DF, DB] = VL_NNCONV(X, F, B, DZDY) (matlab/vl_nnconv.m;
     gateway matlab/src/vl_nnconv.cu:87-503).  B may be None.  Empty F (the subsampling mode of
-    the reference) is not part of this engine."""
+    the reference) is not part of this engine.  relu=True (forward only) returns max(Y, 0) from the same kernels,
+    bit-identical to vl_nnrelu(vl_nnconv(...))."""
     ctx = _ctx(ctx)
     x, f, b, dzdy = _need(x, "x"), _need(f, "f"), _need(b, "b"), _need(dzdy, "dzdy")
     if f is None or f.numel() == 0:
@@ -94,7 +95,9 @@ def vl_nnconv(x, f, b, dzdy=None, stride=1, pad=0, dilate=1, no_der_data=False, 
     fc = _is_fc(d, Ho, Wo)
     if dzdy is None:
         y = mat.empty((Ho, Wo, d.K, d.N), x.device)
-        if fc:
+        if relu:
+            ctx.check(lib.vlb_conv_relu_forward(ctx.handle, mat.ptr(y), mat.ptr(x), mat.ptr(f), mat.ptr(b), C.byref(d)))
+        elif fc:
             ctx.check(lib.vlb_fc_forward(ctx.handle, mat.ptr(y), mat.ptr(x), mat.ptr(f), mat.ptr(b), C.byref(d)))
         else:
             ctx.check(lib.vlb_conv_forward(ctx.handle, mat.ptr(y), 0.0, mat.ptr(x), 1.0, mat.ptr(f), mat.ptr(b),

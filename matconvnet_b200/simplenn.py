@@ -20,21 +20,32 @@ def _get(l, key, default):
 
 
 def vl_simplenn(net, x, dzdy=None, res=None, on_dzdw=None, ctx=None, skip_forward=False,
-                back_prop_depth=None, conserve_memory=False):
+                back_prop_depth=None, conserve_memory=False, fuse_relu=False):
     layers = net["layers"]
     n = len(layers)
     if res is None:
         res = [dict(x=None, dzdx=None, dzdw=None, aux=None) for _ in range(n + 1)]
     if not skip_forward:
         res[0]["x"] = x
+        fused = False
         for i, l in enumerate(layers):
             t = l["type"]
             xi = res[i]["x"]
             if t == "conv":
-                res[i + 1]["x"] = nn.vl_nnconv(xi, l["weights"][0], l["weights"][1], stride=_get(l, "stride", 1),
-                                               pad=_get(l, "pad", 0), dilate=_get(l, "dilate", 1), ctx=ctx)
+                # fuse_relu: a ReLU that follows is applied by the convolution's own kernels; the ReLU's input is never
+                # stored, as when the reference drops it to conserve memory (vl_simplenn.m:386)
+                fused = fuse_relu and i + 1 < n and layers[i + 1]["type"] == "relu"
+                y = nn.vl_nnconv(xi, l["weights"][0], l["weights"][1], stride=_get(l, "stride", 1),
+                                 pad=_get(l, "pad", 0), dilate=_get(l, "dilate", 1), relu=fused, ctx=ctx)
+                if fused:
+                    res[i + 1]["x"], res[i + 2]["x"] = None, y
+                else:
+                    res[i + 1]["x"] = y
             elif t == "relu":
-                res[i + 1]["x"] = nn.vl_nnrelu(xi, ctx=ctx)
+                if fused:
+                    fused = False          # done by the convolution before
+                else:
+                    res[i + 1]["x"] = nn.vl_nnrelu(xi, ctx=ctx)
             elif t == "pool":
                 res[i + 1]["x"] = nn.vl_nnpool(xi, l["pool"], stride=_get(l, "stride", 1), pad=_get(l, "pad", 0),
                                                method=_get(l, "method", "max"), ctx=ctx)
@@ -59,7 +70,9 @@ def vl_simplenn(net, x, dzdy=None, res=None, on_dzdw=None, ctx=None, skip_forwar
                                       pad=_get(l, "pad", 0), dilate=_get(l, "dilate", 1), ctx=ctx)
             res[i]["dzdx"], res[i]["dzdw"] = dx, [df, db]
         elif t == "relu":
-            res[i]["dzdx"] = nn.vl_nnrelu(xi, d, ctx=ctx)
+            # an input that was not kept: the mask comes from the output, which is positive exactly where the input is
+            # (vl_simplenn.m:448-455)
+            res[i]["dzdx"] = nn.vl_nnrelu(xi if xi is not None else res[i + 1]["x"], d, ctx=ctx)
         elif t == "pool":
             res[i]["dzdx"] = nn.vl_nnpool(xi, l["pool"], d, stride=_get(l, "stride", 1), pad=_get(l, "pad", 0),
                                           method=_get(l, "method", "max"), ctx=ctx)

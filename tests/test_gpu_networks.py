@@ -297,3 +297,39 @@ def test_c5_fast_rcnn_head_and_sampler(gpu, oracle):
     dxr, dgr = oracle.sampler_backward(xs, grid, dys)
     assert rel_l2(mat.to_numpy(dxs), dxr) < 1e-6
     assert np.array_equal(mat.to_numpy(dgs), dgr)
+
+
+def test_fused_relu_is_bit_identical(gpu):
+    """vl_nnconv(..., relu=True) against vl_nnrelu(vl_nnconv(...)) for every forward path (tensor-memory kernel, fully
+    connected with and without split reduction, image-end kernel, CUDA-core fallback), and a whole network run with
+    fuse_relu against the plain schedule: same loss and same gradients, bit for bit."""
+    import torch
+    from matconvnet_b200 import models, simplenn
+    nn, mat, ctx = gpu
+    ctx.set_precision(0)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    cases = [((20, 24, 32, 3), (3, 3, 32, 48), dict(pad=1)),                 # tensor-memory kernel
+             ((64, 48, 3, 2), (3, 3, 3, 64), dict(pad=1)),                   # image-end kernel
+             ((7, 7, 64, 5), (7, 7, 64, 40), dict()),                        # fully connected, split reduction
+             ((1, 1, 96, 6), (1, 1, 96, 20), dict()),                        # fully connected, one pass
+             ((10, 10, 8, 2), (3, 3, 2, 12), dict(pad=1)),                   # filter groups: CUDA-core fallback
+             ((17, 15, 6, 3), (3, 3, 6, 10), dict(stride=2, pad=(1, 0, 1, 1)))]
+    for xs, fs, kw in cases:
+        x = mat.as_mat(torch.randn(*xs, device="cuda", generator=g))
+        f = mat.as_mat(torch.randn(*fs, device="cuda", generator=g) * 0.1)
+        b = mat.as_mat(torch.randn(1, fs[3], device="cuda", generator=g))
+        want = nn.vl_nnrelu(nn.vl_nnconv(x, f, b, **kw))
+        got = nn.vl_nnconv(x, f, b, relu=True, **kw)
+        assert torch.equal(got, want), (xs, fs)
+    net = models.cifar(seed=4)
+    labels = torch.randint(1, 11, (8,), device="cuda", generator=g).float()
+    net["layers"][-1]["class"] = labels
+    x = mat.as_mat(torch.randn(32, 32, 3, 8, device="cuda", generator=g))
+    plain = simplenn.vl_simplenn(net, x, 1.0, ctx=ctx)
+    fused = simplenn.vl_simplenn(net, x, 1.0, ctx=ctx, fuse_relu=True)
+    assert torch.equal(plain[-1]["x"], fused[-1]["x"])
+    assert torch.equal(plain[0]["dzdx"], fused[0]["dzdx"])
+    for a, c in zip(plain, fused):
+        if a["dzdw"] is not None:
+            for u, v in zip(a["dzdw"], c["dzdw"]):
+                assert (u is None and v is None) or torch.equal(u, v)
