@@ -98,6 +98,14 @@ int vlb_conv_relu_forward(vlb_ctx* ctx, float* Y, float const* X, float const* F
 int vlb_conv_backward(vlb_ctx* ctx, float* dX, float* dF, float* db, float const* X,
                       float const* F, float const* dY, vlb_conv_desc const* d);
 
+/* Backward convolution and the ReLU before it in one call, for a convolution whose input X is the output of a ReLU:
+ * dF, db as vlb_conv_backward; dX is the derivative with respect to the ReLU's input, conv_backward's dX zeroed where X is
+ * not positive.  vl_simplenn runs the two as separate layers (matlab/simplenn/vl_simplenn.m:410-421 and :448-455, the
+ * mask taken from the ReLU's output when its input was dropped); here the data-gradient kernel applies the mask as it
+ * stores.  Bit-identical to vlb_conv_backward followed by vlb_relu_backward(dX, X, dX).  Accepts fully connected shapes. */
+int vlb_relu_conv_backward(vlb_ctx* ctx, float* dX, float* dF, float* db, float const* X,
+                           float const* F, float const* dY, vlb_conv_desc const* d);
+
 /* ---- fully connected: vl::nn::FullyConnected (bits/nnfullyconnected.hpp:20-37) ---------------
  * The gateway routes here when the output is 1x1, stride 1, no pad, no dilation, one group
  * (matlab/src/vl_nnconv.cu:351-361).  d->FH==d->H, d->FW==d->W, d->FC==d->C.  F == NULL copies. */
@@ -164,6 +172,11 @@ int vlb_pool_forward(vlb_ctx* ctx, float* Y, float const* X, vlb_pool_desc const
  * contributions added in the reference's window order, so the result is the same bit for bit and the
  * caller's zero fill is harmless but unnecessary. */
 int vlb_pool_backward(vlb_ctx* ctx, float* dX, float const* X, float const* dY, vlb_pool_desc const* d);
+/* Pooling backward and the ReLU before it in one call, for a pooling layer whose input X is the output of a ReLU: dX is
+ * the derivative with respect to the ReLU's input, pool_backward's dX zeroed where X is not positive (the sequence
+ * matlab/simplenn/vl_simplenn.m:423-428 then :448-455).  Bit-identical to vlb_pool_backward followed by
+ * vlb_relu_backward(dX, X, dX). */
+int vlb_relu_pool_backward(vlb_ctx* ctx, float* dX, float const* X, float const* dY, vlb_pool_desc const* d);
 
 /* ---- ROI pooling: vl::nn::ROIPooling (bits/nnroipooling.hpp:23-45) ----------------------------
  * rois: 5 x numROIs floats [image(1-based); u1; v1; u2; v2]; transform: 6 doubles, 2x3 column-major.

@@ -60,6 +60,7 @@ SIGNATURES = {
     "vlb_conv_forward": (_I, [_P, _P, _D, _P, _D, _P, _P, C.POINTER(ConvDesc)]),
     "vlb_conv_relu_forward": (_I, [_P, _P, _P, _P, _P, C.POINTER(ConvDesc)]),
     "vlb_conv_backward": (_I, [_P, _P, _P, _P, _P, _P, _P, C.POINTER(ConvDesc)]),
+    "vlb_relu_conv_backward": (_I, [_P, _P, _P, _P, _P, _P, _P, C.POINTER(ConvDesc)]),
     "vlb_fc_forward": (_I, [_P, _P, _P, _P, _P, C.POINTER(ConvDesc)]),
     "vlb_fc_backward": (_I, [_P, _P, _P, _P, _P, _P, _P, C.POINTER(ConvDesc)]),
     "vlb_bias_forward": (_I, [_P, _P, _D, _P, _D, _P, _D, _I, _I, _I, _I]),
@@ -72,6 +73,7 @@ SIGNATURES = {
     "vlb_pool_output_shape": (_I, [C.POINTER(PoolDesc), C.POINTER(_I), C.POINTER(_I)]),
     "vlb_pool_forward": (_I, [_P, _P, _P, C.POINTER(PoolDesc)]),
     "vlb_pool_backward": (_I, [_P, _P, _P, _P, C.POINTER(PoolDesc)]),
+    "vlb_relu_pool_backward": (_I, [_P, _P, _P, _P, C.POINTER(PoolDesc)]),
     "vlb_roipool_forward": (_I, [_P, _P, _P, _P] + [_I] * 7 + [C.POINTER(_D), _I]),
     "vlb_roipool_backward": (_I, [_P, _P, _P, _P, _P] + [_I] * 7 + [C.POINTER(_D), _I]),
     "vlb_roipool_bounds": (_I, [_P, _P, _P, _P] + [_I] * 6 + [C.POINTER(_D)]),

@@ -27,6 +27,10 @@ struct vlb_ctx {
   // set by vlb_conv_relu_forward around its call of the forward convolution: the path that ran applies max(., 0) in its
   // epilogue and says so, otherwise the caller runs the ReLU kernel on the result
   bool fuseRelu = false, reluDone = false;
+  // set by vlb_relu_conv_backward around its call of the backward convolution: the data-gradient path that ran zeroes dX
+  // where reluMask (the convolution's input, a ReLU's output) is not positive and says so, otherwise the caller masks dX
+  float const* reluMask = nullptr;
+  bool maskDone = false;
   bool profiling = false;
   std::vector<ProfRec> prof;
 };

@@ -202,6 +202,19 @@ int vlb_conv_backward(vlb_ctx* ctx, float* dX, float* dF, float* db, float const
   return VLB_Success;
 }
 
+int vlb_relu_conv_backward(vlb_ctx* ctx, float* dX, float* dF, float* db, float const* X, float const* F,
+                           float const* dY, vlb_conv_desc const* d)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  VLB_REQUIRE(ctx, !dX || X, "relu_conv_backward: the data derivative needs the data (the ReLU's output)");
+  ctx->reluMask = dX ? X : nullptr; ctx->maskDone = false;
+  int rc = vlb_conv_backward(ctx, dX, dF, db, X, F, dY, d);
+  bool const done = ctx->maskDone;
+  ctx->reluMask = nullptr; ctx->maskDone = false;
+  if (rc || done || !dX) return rc;
+  return vlb_relu_backward(ctx, dX, X, dX, (size_t)d->H * d->W * d->C * d->N);
+}
+
 int vlb_fc_forward(vlb_ctx* ctx, float* Y, float const* X, float const* F, float const* b, vlb_conv_desc const* d)
 {
   if (!ctx) return VLB_IllegalArgument;

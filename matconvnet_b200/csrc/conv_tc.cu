@@ -85,6 +85,7 @@ struct Epilogue {
   float inMult, outMult;
   int P, Ktot;
   int relu;            // apply max(., 0) to the stored value (forward convolution followed by a ReLU layer)
+  float const* mask;   // conv_ts_kernel, when non-null: laid out like out; the stored value is zeroed where mask is not positive
 };
 
 struct Params {
@@ -995,7 +996,8 @@ __device__ __forceinline__ int ts_chains(int numIter, int second)
 
 // Epilogue of conv_ts_kernel: the finished tile sits in shared memory, P[column][row]; this warp stores the rows of its
 // TMEM lane quarter for the columns rank, rank + nranks, ...: out[(image*Ktot + n)*P + pixel] = inMult*acc + bias[n] + outMult*old.
-__device__ __forceinline__ void ts_store_tile(Params const& p, float const* P, int quarter, int lane, int rank, int nranks, int m0, int n0)
+__device__ __forceinline__ void ts_store_tile(Params const& p, float const* P, int quarter, int lane, int rank, int nranks, int m0, int n0,
+                                              uint32_t const* maskBits = nullptr)
 {
   int const row = quarter * 32 + lane;
   int const m = m0 + row;
@@ -1003,6 +1005,46 @@ __device__ __forceinline__ void ts_store_tile(Params const& p, float const* P, i
   int const pix = m % p.e.P, img = m / p.e.P;
   float* const dst0 = p.e.out + ((long long)img * p.e.Ktot * p.e.P + pix);
   int const nEnd = min(p.BN, p.N - n0);
+  if (maskBits) {
+    // the mask of this row was fetched while the tile was being computed: bit c = the mask is positive in column c
+    uint32_t const b0 = maskBits[0], b1 = maskBits[1], b2 = maskBits[2], b3 = maskBits[3];
+    for (int c = rank; c < nEnd; c += nranks) {
+      float* dst = dst0 + (long long)(n0 + c) * p.e.P;
+      float o = p.e.inMult * P[c * BM + row];
+      if (p.e.bias) o += p.e.bias[n0 + c];
+      if (p.e.outMult != 0.f) o += p.e.outMult * *dst;
+      if (p.e.relu) o = o > 0.f ? o : 0.f;
+      uint32_t const w = c < 64 ? (c < 32 ? b0 : b1) : (c < 96 ? b2 : b3);
+      *dst = ((w >> (c & 31)) & 1u) ? o : 0.f;
+    }
+    return;
+  }
+  if (p.e.mask) {
+    // sixteen columns at a time, so that the mask loads of a batch are in flight together (one load per store in a plain
+    // loop leaves the warp waiting for memory once per column)
+    float const* const mk0 = p.e.mask + (dst0 - p.e.out);
+    for (int c0 = rank; c0 < nEnd; c0 += 16 * nranks) {
+      float mk[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        int const c = c0 + j * nranks;
+        mk[j] = c < nEnd ? __ldg(mk0 + (long long)(n0 + c) * p.e.P) : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        int const c = c0 + j * nranks;
+        if (c < nEnd) {
+          float* dst = dst0 + (long long)(n0 + c) * p.e.P;
+          float o = p.e.inMult * P[c * BM + row];
+          if (p.e.bias) o += p.e.bias[n0 + c];
+          if (p.e.outMult != 0.f) o += p.e.outMult * *dst;
+          if (p.e.relu) o = o > 0.f ? o : 0.f;
+          *dst = mk[j] > 0.f ? o : 0.f;
+        }
+      }
+    }
+    return;
+  }
   for (int c = rank; c < nEnd; c += nranks) {
     float* dst = dst0 + (long long)(n0 + c) * p.e.P;
     float o = p.e.inMult * P[c * BM + row];
@@ -1067,6 +1109,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
     float* const Prow = Psm + warp * 32 + lane;       // this thread's row of P: Prow[column * BM]
     int g = 0;                                        // chains in the order they are drained, over the CTA's life: chain g sits in T[g % 3]
     bool ok = true;
+    bool const preMask = p.e.mask != nullptr && !singleTile;
     for (int ts = 0; ts < myTiles && ok; ++ts) {
       int const tile = (int)blockIdx.x + ts * (int)gridDim.x;
       int const m0 = (tile / p.tilesN) * BM, n0 = (tile % p.tilesN) * BN;
@@ -1074,10 +1117,26 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
       int const chainsF = ts_chains<kSplit>(numIter, 0), chainsS = ts_chains<kSplit>(numIter, 1);   // of that issuer, of the other
       bool fresh = true;                              // P holds nothing of this tile yet
       (void)qFirst;
+      // ReLU mask of this thread's output row (persistent mode): sixteen columns are fetched before each of the tile's
+      // first chain waits, so that their latency passes while the chain is being computed, and kept as one bit each
+      uint32_t mbits[4] = {0u, 0u, 0u, 0u};
+      int const nEndT = min(BN, p.N - n0);
+      float const* mkRow = p.e.mask;
+      if (preMask) {
+        int const m = min(m0 + warp * 32 + lane, p.M - 1);
+        mkRow += ((long long)(m / p.e.P) * p.e.Ktot + n0) * p.e.P + m % p.e.P;
+      }
+      int lc = 0;                                     // batches of sixteen mask columns fetched so far
       for (int c = 0; c < chainsF && ok; ++c) {
         for (int h = 0; h < 2 && ok; ++h) {
           if (h == 1 && c >= chainsS) continue;
           int const t = g % 3;
+          float mk[16];
+          bool const fetch = preMask && 16 * lc < nEndT;
+          if (fetch) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) mk[j] = __ldg(mkRow + (long long)min(16 * lc + j, nEndT - 1) * p.e.P);
+          }
           ok = mbar_wait(smem_u32(&tFull[t]), (uint32_t)((g / 3) & 1));
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) { if (lane == 0) atomicExch(p.status, 5); break; }
@@ -1103,9 +1162,24 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&tFree[t]));     // T[t] may be overwritten
+          if (fetch) {
+            uint32_t b = 0;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) b |= (mk[j] > 0.f ? 1u : 0u) << j;
+            b <<= 16 * (lc & 1);
+            if (lc < 2) mbits[0] |= b; else if (lc < 4) mbits[1] |= b; else if (lc < 6) mbits[2] |= b; else mbits[3] |= b;
+            ++lc;
+          }
         }
       }
       if (!ok) break;
+      for (; preMask && 16 * lc < nEndT; ++lc) {        // a tile of fewer chains than batches: the rest of the mask
+        uint32_t b = 0;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) b |= (__ldg(mkRow + (long long)min(16 * lc + j, nEndT - 1) * p.e.P) > 0.f ? 1u : 0u) << j;
+        b <<= 16 * (lc & 1);
+        if (lc < 2) mbits[0] |= b; else if (lc < 4) mbits[1] |= b; else if (lc < 6) mbits[2] |= b; else mbits[3] |= b;
+      }
       if (singleTile) {
         // one tile per CTA: the producers have nothing left to do and share the stores
         __syncwarp();
@@ -1114,7 +1188,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
       } else {
         // the tile is complete in P: store it while the tensor core works on the next tile (its chains wait in
         // their T buffers until this is through)
-        ts_store_tile(p, Psm, warp, lane, 0, 1, m0, n0);
+        ts_store_tile(p, Psm, warp, lane, 0, 1, m0, n0, preMask ? mbits : nullptr);
       }
     }
   } else if (warp == kEpilogueWarps || warp == kEpilogueWarps + 1) {
@@ -1734,7 +1808,10 @@ int conv_dgrad_tc(vlb_ctx* ctx, ConvGeom const& g, float* dX, float const* F, fl
     p.b.ptr = ft; p.b.vec = (V % 4 == 0);
   }
   p.e = Epilogue{}; p.e.out = dX; p.e.inMult = 1.f; p.e.P = g.H * g.W; p.e.Ktot = g.C;
-  if (p.pipelined) return launch_ts(ctx, p, "conv_dgrad_ts");
+  if (p.pipelined) {
+    p.e.mask = ctx->reluMask; ctx->maskDone = ctx->reluMask != nullptr;
+    return launch_ts(ctx, p, "conv_dgrad_ts");
+  }
   return launch<OP_IM2COL, OP_DENSE_K, EPI_CONV>(ctx, p, 1, "conv_dgrad_tc");
 }
 

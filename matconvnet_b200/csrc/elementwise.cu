@@ -31,8 +31,8 @@ __global__ void relu_fwd_kernel(float* y, float const* x, size_t n, bool vec)
 }
 
 // dx = dy .* (x > 0) (reference matlab/vl_nnrelu.m:47)
-__global__ void relu_bwd_kernel(float* __restrict__ dx, float const* __restrict__ x,
-                                float const* __restrict__ dy, size_t n, bool vec)
+// dx may be dy (every element is read before it is written, by the same thread)
+__global__ void relu_bwd_kernel(float* dx, float const* __restrict__ x, float const* dy, size_t n, bool vec)
 {
   size_t stride = (size_t)gridDim.x * blockDim.x, i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (vec) {

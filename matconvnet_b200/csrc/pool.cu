@@ -59,9 +59,10 @@ __global__ void pool_fwd_generic(float* __restrict__ y, float const* __restrict_
 __device__ __forceinline__ int floor_div(int a, int b) { int q = a / b; return (a % b != 0 && ((a < 0) != (b < 0))) ? q - 1 : q; }
 __device__ __forceinline__ int ceil_div_i(int a, int b) { return -floor_div(-a, b); }
 
+// relu: x is the output of a ReLU and dx the derivative with respect to that ReLU's input: zero where x is not positive.
 template <bool kMax>
 __global__ void pool_bwd_generic(float* __restrict__ dx, float const* __restrict__ x,
-                                 float const* __restrict__ dy, PoolParams p)
+                                 float const* __restrict__ dy, PoolParams p, bool relu)
 {
   size_t total = p.planes * (size_t)p.H * p.W;
   size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -98,6 +99,7 @@ __global__ void pool_bwd_generic(float* __restrict__ dx, float const* __restrict
           acc = __fadd_rn(acc, __fmul_rn(d, scale));
         }
       }
+    if (relu) acc = xz[(size_t)u * p.H + v] > 0.f ? acc : 0.f;
     dx[i] = acc;
   }
 }
@@ -152,7 +154,7 @@ __global__ void pool2x2_fwd(float* __restrict__ y, float const* __restrict__ x, 
   }
 }
 
-template <int kV, bool kMax>
+template <int kV, bool kMax, bool kRelu>
 __global__ void pool2x2_bwd(float* __restrict__ dx, float const* __restrict__ x, float const* __restrict__ dy,
                             int H, int W, size_t planes)
 {
@@ -169,10 +171,12 @@ __global__ void pool2x2_bwd(float* __restrict__ dx, float const* __restrict__ x,
     size_t off = (z * W + 2 * (size_t)wo) * H + 2 * kV * (size_t)hv;
     float d[kV], ra[2 * kV], rb[2 * kV];
     unpack(*reinterpret_cast<out_t const*>(dy + col * Ho + kV * (size_t)hv), d);
-    if (kMax) {
-      float a[2 * kV], b[2 * kV];
+    float a[2 * kV], b[2 * kV];
+    if (kMax || kRelu) {
       unpack(*reinterpret_cast<in_t const*>(x + off), a);
       unpack(*reinterpret_cast<in_t const*>(x + off + H), b);
+    }
+    if (kMax) {
 #pragma unroll
       for (int j = 0; j < kV; ++j) {
         // scan order of the reference: column 0 rows 0,1 then column 1 rows 0,1; strict '>'
@@ -194,6 +198,10 @@ __global__ void pool2x2_bwd(float* __restrict__ dx, float const* __restrict__ x,
         float g = __fadd_rn(0.f, __fmul_rn(d[j], 0.25f));
         ra[2 * j] = g; ra[2 * j + 1] = g; rb[2 * j] = g; rb[2 * j + 1] = g;
       }
+    }
+    if (kRelu) {
+#pragma unroll
+      for (int j = 0; j < 2 * kV; ++j) { ra[j] = a[j] > 0.f ? ra[j] : 0.f; rb[j] = b[j] > 0.f ? rb[j] : 0.f; }
     }
     in_t va, vb;
     pack(va, ra);
@@ -226,6 +234,44 @@ int validate(vlb_ctx* ctx, vlb_pool_desc const* d, int* Ho, int* Wo)
   VLB_REQUIRE(ctx, d->method == VLB_POOL_MAX || d->method == VLB_POOL_AVG, "pooling: unknown method");
   vlb_pool_output_shape(d, Ho, Wo);
   return VLB_Success;
+}
+
+}  // namespace
+
+namespace {
+
+template <int kV, bool kMax>
+void launch2x2_bwd(vlb_ctx* ctx, unsigned grid, float* dX, float const* X, float const* dY, int H, int W, size_t planes, bool relu)
+{
+  if (relu) pool2x2_bwd<kV, kMax, true><<<grid, kThreads, 0, ctx->stream>>>(dX, X, dY, H, W, planes);
+  else      pool2x2_bwd<kV, kMax, false><<<grid, kThreads, 0, ctx->stream>>>(dX, X, dY, H, W, planes);
+}
+
+int pool_backward(vlb_ctx* ctx, float* dX, float const* X, float const* dY, vlb_pool_desc const* d, bool relu, char const* where)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  int Ho, Wo;
+  int rc = validate(ctx, d, &Ho, &Wo);
+  if (rc) return vlb::pass_error(ctx, rc, where);
+  VLB_REQUIRE(ctx, dX && X && dY, "pool_backward: null tensor");
+  size_t planes = (size_t)d->C * d->N;
+  bool isMax = d->method == VLB_POOL_MAX;
+  if (fast2x2(d, dX, X, dY)) {
+    bool v2 = (d->H % 4 == 0);
+    size_t total = planes * (size_t)Wo * (v2 ? Ho / 2 : Ho);
+    unsigned grid = vlb::grid_for(total, kThreads, ctx->smCount * 16);
+    if (v2) { if (isMax) launch2x2_bwd<2, true>(ctx, grid, dX, X, dY, d->H, d->W, planes, relu);
+              else       launch2x2_bwd<2, false>(ctx, grid, dX, X, dY, d->H, d->W, planes, relu); }
+    else    { if (isMax) launch2x2_bwd<1, true>(ctx, grid, dX, X, dY, d->H, d->W, planes, relu);
+              else       launch2x2_bwd<1, false>(ctx, grid, dX, X, dY, d->H, d->W, planes, relu); }
+  } else {
+    PoolParams p = {d->H, d->W, Ho, Wo, d->poolH, d->poolW, d->strideY, d->strideX, d->padTop, d->padLeft, planes};
+    unsigned grid = vlb::grid_for(planes * (size_t)d->H * d->W, kThreads, ctx->smCount * 16);
+    if (isMax) pool_bwd_generic<true><<<grid, kThreads, 0, ctx->stream>>>(dX, X, dY, p, relu);
+    else       pool_bwd_generic<false><<<grid, kThreads, 0, ctx->stream>>>(dX, X, dY, p, relu);
+  }
+  VLB_LAUNCHED(ctx, 1);
+  return vlb::check_launch(ctx, where);
 }
 
 }  // namespace
@@ -269,29 +315,12 @@ int vlb_pool_forward(vlb_ctx* ctx, float* Y, float const* X, vlb_pool_desc const
 
 int vlb_pool_backward(vlb_ctx* ctx, float* dX, float const* X, float const* dY, vlb_pool_desc const* d)
 {
-  if (!ctx) return VLB_IllegalArgument;
-  int Ho, Wo;
-  int rc = validate(ctx, d, &Ho, &Wo);
-  if (rc) return vlb::pass_error(ctx, rc, "vlb_pool_backward");
-  VLB_REQUIRE(ctx, dX && X && dY, "pool_backward: null tensor");
-  size_t planes = (size_t)d->C * d->N;
-  bool isMax = d->method == VLB_POOL_MAX;
-  if (fast2x2(d, dX, X, dY)) {
-    bool v2 = (d->H % 4 == 0);
-    size_t total = planes * (size_t)Wo * (v2 ? Ho / 2 : Ho);
-    unsigned grid = vlb::grid_for(total, kThreads, ctx->smCount * 16);
-    if (v2) { if (isMax) pool2x2_bwd<2, true><<<grid, kThreads, 0, ctx->stream>>>(dX, X, dY, d->H, d->W, planes);
-              else       pool2x2_bwd<2, false><<<grid, kThreads, 0, ctx->stream>>>(dX, X, dY, d->H, d->W, planes); }
-    else    { if (isMax) pool2x2_bwd<1, true><<<grid, kThreads, 0, ctx->stream>>>(dX, X, dY, d->H, d->W, planes);
-              else       pool2x2_bwd<1, false><<<grid, kThreads, 0, ctx->stream>>>(dX, X, dY, d->H, d->W, planes); }
-  } else {
-    PoolParams p = {d->H, d->W, Ho, Wo, d->poolH, d->poolW, d->strideY, d->strideX, d->padTop, d->padLeft, planes};
-    unsigned grid = vlb::grid_for(planes * (size_t)d->H * d->W, kThreads, ctx->smCount * 16);
-    if (isMax) pool_bwd_generic<true><<<grid, kThreads, 0, ctx->stream>>>(dX, X, dY, p);
-    else       pool_bwd_generic<false><<<grid, kThreads, 0, ctx->stream>>>(dX, X, dY, p);
-  }
-  VLB_LAUNCHED(ctx, 1);
-  return vlb::check_launch(ctx, "vlb_pool_backward");
+  return pool_backward(ctx, dX, X, dY, d, false, "vlb_pool_backward");
+}
+
+int vlb_relu_pool_backward(vlb_ctx* ctx, float* dX, float const* X, float const* dY, vlb_pool_desc const* d)
+{
+  return pool_backward(ctx, dX, X, dY, d, true, "vlb_relu_pool_backward");
 }
 
 }  // extern "C"

@@ -76,11 +76,12 @@ def _is_fc(d, Ho, Wo):
 
 
 def vl_nnconv(x, f, b, dzdy=None, stride=1, pad=0, dilate=1, no_der_data=False, no_der_filters=False,
-              no_der_biases=False, relu=False, ctx=None):
+              no_der_biases=False, relu=False, through_relu=False, ctx=None):
     """Y = VL_NNCONV(X, F, B) / [DX, DF, DB] = VL_NNCONV(X, F, B, DZDY) (matlab/vl_nnconv.m;
     gateway matlab/src/vl_nnconv.cu:87-503).  B may be None.  Empty F (the subsampling mode of
     the reference) is not part of this engine.  relu=True (forward only) returns max(Y, 0) from the same kernels,
-    bit-identical to vl_nnrelu(vl_nnconv(...))."""
+    bit-identical to vl_nnrelu(vl_nnconv(...)).  through_relu=True (backward only) is for an X that is the output of a
+    ReLU: DX is then the derivative with respect to that ReLU's input, bit-identical to vl_nnrelu(X, DX)."""
     ctx = _ctx(ctx)
     x, f, b, dzdy = _need(x, "x"), _need(f, "f"), _need(b, "b"), _need(dzdy, "dzdy")
     if f is None or f.numel() == 0:
@@ -108,7 +109,7 @@ def vl_nnconv(x, f, b, dzdy=None, stride=1, pad=0, dilate=1, no_der_data=False, 
     dx = None if no_der_data else mat.empty(mat.shape4(x), x.device)
     df = None if no_der_filters else mat.empty(mat.shape4(f), x.device)
     db = None if (no_der_biases or b is None) else mat.empty((1, d.K), x.device)
-    fn = lib.vlb_fc_backward if fc else lib.vlb_conv_backward
+    fn = lib.vlb_relu_conv_backward if through_relu else (lib.vlb_fc_backward if fc else lib.vlb_conv_backward)
     ctx.check(fn(ctx.handle, mat.ptr(dx), mat.ptr(df), mat.ptr(db), mat.ptr(x), mat.ptr(f), mat.ptr(dzdy),
                  C.byref(d)))
     return dx, df, db
@@ -150,9 +151,10 @@ def vl_nnbnorm(x, g, b, dzdy=None, epsilon=1e-4, moments=None, ctx=None):
 
 
 # --------------------------------------------------------------------- vl_nnpool
-def vl_nnpool(x, pool, dzdy=None, stride=1, pad=0, method="max", ctx=None):
+def vl_nnpool(x, pool, dzdy=None, stride=1, pad=0, method="max", through_relu=False, ctx=None):
     """Y = VL_NNPOOL(X, POOL) / DX = VL_NNPOOL(X, POOL, DZDY) (matlab/vl_nnpool.m; gateway
-    matlab/src/vl_nnpool.cu:72-315)."""
+    matlab/src/vl_nnpool.cu:72-315).  through_relu=True (backward only) is for an X that is the output of a ReLU: DX is
+    then the derivative with respect to that ReLU's input, bit-identical to vl_nnrelu(X, DX)."""
     ctx = _ctx(ctx)
     x, dzdy = _need(x, "x"), _need(dzdy, "dzdy")
     H, W, Cc, N = mat.shape4(x)
@@ -173,7 +175,8 @@ def vl_nnpool(x, pool, dzdy=None, stride=1, pad=0, method="max", ctx=None):
     if mat.shape4(dzdy) != (Ho, Wo, Cc, N):
         raise ValueError("DZDY dimensions are incompatible with X and POOL.")
     dx = mat.empty((H, W, Cc, N), x.device)
-    ctx.check(lib.vlb_pool_backward(ctx.handle, mat.ptr(dx), mat.ptr(x), mat.ptr(dzdy), C.byref(d)))
+    fn = lib.vlb_relu_pool_backward if through_relu else lib.vlb_pool_backward
+    ctx.check(fn(ctx.handle, mat.ptr(dx), mat.ptr(x), mat.ptr(dzdy), C.byref(d)))
     return dx
 
 

@@ -61,21 +61,31 @@ def vl_simplenn(net, x, dzdy=None, res=None, on_dzdw=None, ctx=None, skip_forwar
         return res
     res[n]["dzdx"] = dzdy
     first = 0 if back_prop_depth is None else max(0, n - back_prop_depth)
+    masked = False
     for i in range(n - 1, first - 1, -1):
         l = layers[i]
         t = l["type"]
         xi, d = res[i]["x"], res[i + 1]["dzdx"]
+        # fuse_relu: the backward pass of a ReLU directly before a convolution or pooling layer is done by that layer's
+        # own data-gradient kernel, which zeroes the derivative where its input (the ReLU's output) is not positive; the
+        # derivative between the two layers is never stored, as when the reference conserves memory (vl_simplenn.m:512-514)
+        through = fuse_relu and t in ("conv", "pool") and i - 1 >= first and layers[i - 1]["type"] == "relu"
         if t == "conv":
             dx, df, db = nn.vl_nnconv(xi, l["weights"][0], l["weights"][1], d, stride=_get(l, "stride", 1),
-                                      pad=_get(l, "pad", 0), dilate=_get(l, "dilate", 1), ctx=ctx)
-            res[i]["dzdx"], res[i]["dzdw"] = dx, [df, db]
+                                      pad=_get(l, "pad", 0), dilate=_get(l, "dilate", 1), through_relu=through, ctx=ctx)
+            res[i]["dzdw"] = [df, db]
+            res[i]["dzdx"], res[i - 1 if through else i]["dzdx"] = None, dx
         elif t == "relu":
-            # an input that was not kept: the mask comes from the output, which is positive exactly where the input is
-            # (vl_simplenn.m:448-455)
-            res[i]["dzdx"] = nn.vl_nnrelu(xi if xi is not None else res[i + 1]["x"], d, ctx=ctx)
+            if masked:
+                pass                       # done by the layer after
+            else:
+                # an input that was not kept: the mask comes from the output, which is positive exactly where the input
+                # is (vl_simplenn.m:448-455)
+                res[i]["dzdx"] = nn.vl_nnrelu(xi if xi is not None else res[i + 1]["x"], d, ctx=ctx)
         elif t == "pool":
-            res[i]["dzdx"] = nn.vl_nnpool(xi, l["pool"], d, stride=_get(l, "stride", 1), pad=_get(l, "pad", 0),
-                                          method=_get(l, "method", "max"), ctx=ctx)
+            dx = nn.vl_nnpool(xi, l["pool"], d, stride=_get(l, "stride", 1), pad=_get(l, "pad", 0),
+                              method=_get(l, "method", "max"), through_relu=through, ctx=ctx)
+            res[i]["dzdx"], res[i - 1 if through else i]["dzdx"] = None, dx
         elif t == "bnorm":
             dx, dg, db, mom = nn.vl_nnbnorm(xi, l["weights"][0], l["weights"][1], d,
                                             epsilon=_get(l, "epsilon", 1e-4), ctx=ctx)
@@ -88,6 +98,7 @@ def vl_simplenn(net, x, dzdy=None, res=None, on_dzdw=None, ctx=None, skip_forwar
             for j, w in enumerate(res[i]["dzdw"]):
                 if w is not None:
                     on_dzdw(i, j, w)
+        masked = through
         if conserve_memory and i + 1 < n:
             res[i + 1]["dzdx"] = None      # opts.conserveMemory (vl_simplenn.m:512-514)
     return res

@@ -301,8 +301,9 @@ def test_c5_fast_rcnn_head_and_sampler(gpu, oracle):
 
 def test_fused_relu_is_bit_identical(gpu):
     """vl_nnconv(..., relu=True) against vl_nnrelu(vl_nnconv(...)) for every forward path (tensor-memory kernel, fully
-    connected with and without split reduction, image-end kernel, CUDA-core fallback), and a whole network run with
-    fuse_relu against the plain schedule: same loss and same gradients, bit for bit."""
+    connected with and without split reduction, image-end kernel, CUDA-core fallback); the backward pass through a ReLU
+    before a convolution or pooling layer (through_relu=True) against the two separate calls; and whole networks run
+    with fuse_relu against the plain schedule: same loss and same gradients, bit for bit."""
     import torch
     from matconvnet_b200 import models, simplenn
     nn, mat, ctx = gpu
@@ -321,15 +322,44 @@ def test_fused_relu_is_bit_identical(gpu):
         want = nn.vl_nnrelu(nn.vl_nnconv(x, f, b, **kw))
         got = nn.vl_nnconv(x, f, b, relu=True, **kw)
         assert torch.equal(got, want), (xs, fs)
-    net = models.cifar(seed=4)
+        # backward through the ReLU before the convolution: x is that ReLU's output
+        xr = nn.vl_nnrelu(x)
+        dzdy = mat.as_mat(torch.randn(*mat.shape4(want), device="cuda", generator=g))
+        dx, df, db = nn.vl_nnconv(xr, f, b, dzdy, **kw)
+        dx2, df2, db2 = nn.vl_nnconv(xr, f, b, dzdy, through_relu=True, **kw)
+        assert torch.equal(dx2, nn.vl_nnrelu(xr, dx)), (xs, fs)
+        assert torch.equal(df2, df) and torch.equal(db2, db), (xs, fs)
+    pools = [((24, 20, 5, 3), (2, 2), dict(stride=2)),                        # 2x2 kernel, two outputs per thread
+             ((10, 6, 4, 2), (2, 2), dict(stride=2)),                         # 2x2 kernel, one output per thread
+             ((13, 11, 3, 2), (3, 3), dict(stride=2, pad=(0, 1, 0, 1))),      # generic kernel
+             ((9, 9, 2, 2), (3, 2), dict(stride=1, pad=1))]
+    for xs, pool, kw in pools:
+        for method in ("max", "avg"):
+            xr = nn.vl_nnrelu(mat.as_mat(torch.randn(*xs, device="cuda", generator=g)))
+            y = nn.vl_nnpool(xr, pool, method=method, **kw)
+            dzdy = mat.as_mat(torch.randn(*mat.shape4(y), device="cuda", generator=g))
+            want = nn.vl_nnrelu(xr, nn.vl_nnpool(xr, pool, dzdy, method=method, **kw))
+            got = nn.vl_nnpool(xr, pool, dzdy, method=method, through_relu=True, **kw)
+            assert torch.equal(got, want), (xs, pool, method)
     labels = torch.randint(1, 11, (8,), device="cuda", generator=g).float()
-    net["layers"][-1]["class"] = labels
-    x = mat.as_mat(torch.randn(32, 32, 3, 8, device="cuda", generator=g))
-    plain = simplenn.vl_simplenn(net, x, 1.0, ctx=ctx)
-    fused = simplenn.vl_simplenn(net, x, 1.0, ctx=ctx, fuse_relu=True)
-    assert torch.equal(plain[-1]["x"], fused[-1]["x"])
-    assert torch.equal(plain[0]["dzdx"], fused[0]["dzdx"])
-    for a, c in zip(plain, fused):
-        if a["dzdw"] is not None:
-            for u, v in zip(a["dzdw"], c["dzdw"]):
-                assert (u is None and v is None) or torch.equal(u, v)
+    # a VGG-like chain (conv 3x3 + relu pairs, 2x2 max-pools, conv-as-FC + relu): every ReLU sits before a convolution,
+    # a pooling or a fully connected layer
+    rng = np.random.default_rng(9)
+    cv = lambda fh, cin, cout, pad: models._conv(rng, fh, fh, cin, cout, 1, pad)
+    vgg = [cv(3, 3, 32, 1), models._relu(), cv(3, 32, 32, 1), models._relu(), models._pool("max", 2, 2),
+           cv(3, 32, 64, 1), models._relu(), cv(3, 64, 64, 1), models._relu(), models._pool("max", 2, 2),
+           cv(8, 64, 64, 0), models._relu(), cv(1, 64, 10, 0), {"type": "softmaxloss", "class": None}]
+    nets = [(models.cifar(seed=4), (32, 32, 3, 8)), ({"layers": vgg}, (32, 32, 3, 8))]
+    for net, xs in nets:
+        net["layers"][-1]["class"] = labels
+        x = mat.as_mat(torch.randn(*xs, device="cuda", generator=g))
+        plain = simplenn.vl_simplenn(net, x, 1.0, ctx=ctx)
+        fused = simplenn.vl_simplenn(net, x, 1.0, ctx=ctx, fuse_relu=True)
+        assert torch.equal(plain[-1]["x"], fused[-1]["x"])
+        assert torch.equal(plain[0]["dzdx"], fused[0]["dzdx"])
+        for a, c in zip(plain, fused):
+            if torch.is_tensor(c["dzdx"]):      # the fused schedule keeps no derivative between a ReLU and the layer after
+                assert torch.equal(a["dzdx"], c["dzdx"])
+            if a["dzdw"] is not None:
+                for u, v in zip(a["dzdw"], c["dzdw"]):
+                    assert (u is None and v is None) or torch.equal(u, v)
