@@ -94,6 +94,8 @@ LAYERS = {
     "small_r_stride": ((41, 37, 2, 5), (3, 5, 2, 20), (2, 1), (1, 0, 2, 1), 1),
     "small_r_dilate_c1": ((50, 47, 1, 3), (3, 3, 1, 70), 1, (2, 1, 0, 2), 2),
     "small_n_4ch_5x5": ((36, 40, 4, 4), (5, 5, 4, 24), 1, 2, 1),
+    "small_n_rgb_3x3": ((40, 36, 3, 3), (3, 3, 3, 20), 1, 1, 1),
+    "small_n_3x3_pad_dilate_y": ((33, 38, 2, 4), (3, 3, 2, 9), 1, (2, 2, 0, 2), (2, 1)),
 }
 
 
