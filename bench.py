@@ -80,9 +80,9 @@ class ClockSampler:
 
 # ----------------------------------------------------------------------------- CPU arm
 # dram__bytes_read.sum + dram__bytes_write.sum of the tensor-core contraction launches of one step of this workload
-# (batch 64, 3xTF32), from the ncu launch list summarised in profiles/bench_vgg16_batch64_launch_list.md: 20.2 GB over
+# (batch 64, 3xTF32), from the ncu launch list summarised in profiles/bench_vgg16_batch64_launch_list.md: 22.2 GB over
 # 46 launches.  Per launch, like roofline.achieved.
-NCU_DRAM_BYTES_PER_CONTRACTION_LAUNCH = 20.24e9 / 46
+NCU_DRAM_BYTES_PER_CONTRACTION_LAUNCH = 22.20e9 / 46
 
 
 def cpu_vgg16(batch, steps, warmup, threads):
