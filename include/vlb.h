@@ -106,6 +106,27 @@ int vlb_conv_backward(vlb_ctx* ctx, float* dX, float* dF, float* db, float const
 int vlb_relu_conv_backward(vlb_ctx* ctx, float* dX, float* dF, float* db, float const* X,
                            float const* F, float const* dY, vlb_conv_desc const* d);
 
+/* ---- convolution transpose: vl::nn::ConvolutionTranspose (bits/nnconv.hpp:54-80) -----------------
+ * Y (Ho x Wo x FD*numGroups x N) from X (H x W x C x N) and F (FH x FW x FD x FN), FN == C
+ * (matlab/src/vl_nnconvt.cu:262-301). */
+typedef struct {
+  int H, W, C, N;            /* input */
+  int FH, FW, FD, FN;        /* filter bank: FD output channels per group, FN == C */
+  int upsampleY, upsampleX;
+  int cropTop, cropBottom, cropLeft, cropRight;
+  int numGroups;
+} vlb_convt_desc;
+/* Ho = (H-1)*upsampleY - (cropTop+cropBottom) + FH, likewise Wo (matlab/src/vl_nnconvt.cu:293-296). */
+int vlb_convt_output_shape(vlb_convt_desc const* d, int* Ho, int* Wo);
+/* ConvolutionTranspose::forward (bits/nnconv.cu:323-374): the data gradient of the convolution with stride = upsample,
+ * pad = crop, then the bias.  b may be NULL. */
+int vlb_convt_forward(vlb_ctx* ctx, float* Y, float const* X, float const* F, float const* b,
+                      vlb_convt_desc const* d);
+/* ConvolutionTranspose::backward (bits/nnconv.cu:380-421): dX = that convolution's forward pass of dY, dF = its filter
+ * gradient with data and output derivative exchanged, db = sum of dY.  Any of dX, dF, db may be NULL. */
+int vlb_convt_backward(vlb_ctx* ctx, float* dX, float* dF, float* db, float const* X, float const* F,
+                       float const* dY, vlb_convt_desc const* d);
+
 /* ---- fully connected: vl::nn::FullyConnected (bits/nnfullyconnected.hpp:20-37) ---------------
  * The gateway routes here when the output is 1x1, stride 1, no pad, no dilation, one group
  * (matlab/src/vl_nnconv.cu:351-361).  d->FH==d->H, d->FW==d->W, d->FC==d->C.  F == NULL copies. */

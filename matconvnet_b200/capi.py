@@ -27,6 +27,11 @@ class ConvDesc(C.Structure):
                                        "padTop", "padBottom", "padLeft", "padRight", "dilateY", "dilateX")]
 
 
+class ConvtDesc(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("H", "W", "C", "N", "FH", "FW", "FD", "FN", "upsampleY", "upsampleX",
+                                       "cropTop", "cropBottom", "cropLeft", "cropRight", "numGroups")]
+
+
 class PoolDesc(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("H", "W", "C", "N", "poolH", "poolW", "strideY", "strideX",
                                        "padTop", "padBottom", "padLeft", "padRight", "method")]
@@ -61,6 +66,9 @@ SIGNATURES = {
     "vlb_conv_relu_forward": (_I, [_P, _P, _P, _P, _P, C.POINTER(ConvDesc)]),
     "vlb_conv_backward": (_I, [_P, _P, _P, _P, _P, _P, _P, C.POINTER(ConvDesc)]),
     "vlb_relu_conv_backward": (_I, [_P, _P, _P, _P, _P, _P, _P, C.POINTER(ConvDesc)]),
+    "vlb_convt_output_shape": (_I, [C.POINTER(ConvtDesc), C.POINTER(_I), C.POINTER(_I)]),
+    "vlb_convt_forward": (_I, [_P, _P, _P, _P, _P, C.POINTER(ConvtDesc)]),
+    "vlb_convt_backward": (_I, [_P, _P, _P, _P, _P, _P, _P, C.POINTER(ConvtDesc)]),
     "vlb_fc_forward": (_I, [_P, _P, _P, _P, _P, C.POINTER(ConvDesc)]),
     "vlb_fc_backward": (_I, [_P, _P, _P, _P, _P, _P, _P, C.POINTER(ConvDesc)]),
     "vlb_bias_forward": (_I, [_P, _P, _D, _P, _D, _P, _D, _I, _I, _I, _I]),

@@ -215,6 +215,77 @@ int vlb_relu_conv_backward(vlb_ctx* ctx, float* dX, float* dF, float* db, float 
   return vlb_relu_backward(ctx, dX, X, dX, (size_t)d->H * d->W * d->C * d->N);
 }
 
+// ---- convolution transpose: the convolution whose data gradient / forward pass it re-uses ------------------
+// The transposed convolution of X (H x W x C x N) with F (FH x FW x FD x C) is the data gradient of a convolution
+// with stride = upsample and pad = crop whose input is the transposed convolution's output (reference
+// bits/nnconv.cu:323-374); c receives that convolution's descriptor.
+static int convt_geom(vlb_ctx* ctx, vlb_convt_desc const* d, vlb_conv_desc* c)
+{
+  VLB_REQUIRE(ctx, d, "convt: null descriptor");
+  VLB_REQUIRE(ctx, d->H > 0 && d->W > 0 && d->C > 0 && d->N > 0, "convt: empty input");
+  // matlab/src/vl_nnconvt.cu:262-290
+  VLB_REQUIRE(ctx, d->upsampleY >= 1 && d->upsampleX >= 1, "convt: at least one element of UPSAMPLE is smaller than one");
+  VLB_REQUIRE(ctx, d->cropTop >= 0 && d->cropBottom >= 0 && d->cropLeft >= 0 && d->cropRight >= 0,
+              "convt: an element of CROP is negative");
+  VLB_REQUIRE(ctx, d->FH > 0 && d->FW > 0 && d->FD > 0, "convt: a dimension of FILTERS is void");
+  VLB_REQUIRE(ctx, d->numGroups >= 1, "convt: NUMGROUPS is less than 1");
+  VLB_REQUIRE(ctx, d->FN % d->numGroups == 0, "convt: the number of filter groups does not divide the filter bank depth");
+  VLB_REQUIRE(ctx, d->FN == d->C, "convt: the filter bank depth is not the same as the data depth");
+  int Ho = 0, Wo = 0;
+  vlb_convt_output_shape(d, &Ho, &Wo);
+  VLB_REQUIRE(ctx, Ho >= 1 && Wo >= 1, "convt: the output array is empty due to CROP being too large");   // :299-301
+  c->H = Ho; c->W = Wo; c->C = d->FD * d->numGroups; c->N = d->N;
+  c->FH = d->FH; c->FW = d->FW; c->FC = d->FD; c->K = d->C;
+  c->strideY = d->upsampleY; c->strideX = d->upsampleX;
+  c->padTop = d->cropTop; c->padBottom = d->cropBottom; c->padLeft = d->cropLeft; c->padRight = d->cropRight;
+  c->dilateY = 1; c->dilateX = 1;
+  return VLB_Success;
+}
+
+int vlb_convt_output_shape(vlb_convt_desc const* d, int* Ho, int* Wo)
+{
+  if (!d) return VLB_IllegalArgument;
+  if (Ho) *Ho = (d->H - 1) * d->upsampleY - (d->cropTop + d->cropBottom) + d->FH;
+  if (Wo) *Wo = (d->W - 1) * d->upsampleX - (d->cropLeft + d->cropRight) + d->FW;
+  return VLB_Success;
+}
+
+int vlb_convt_forward(vlb_ctx* ctx, float* Y, float const* X, float const* F, float const* b, vlb_convt_desc const* d)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  vlb_conv_desc c;
+  int rc = convt_geom(ctx, d, &c);
+  if (rc) return vlb::pass_error(ctx, rc, "vlb_convt_forward");
+  VLB_REQUIRE(ctx, Y && X && F, "convt_forward: null tensor");
+  // the whole batch in one call: this engine's data gradient writes every image's own slice (the reference loops over
+  // the images because its row2im accumulates, bits/nnconv.cu:338-367)
+  rc = vlb_conv_backward(ctx, Y, nullptr, nullptr, nullptr, F, X, &c);
+  if (rc || !b) return rc;
+  return vlb_bias_forward(ctx, Y, 1.0, nullptr, 0.0, b, 1.0, c.H, c.W, c.C, c.N);       // bits/nnconv.cu:368-370
+}
+
+int vlb_convt_backward(vlb_ctx* ctx, float* dX, float* dF, float* db, float const* X, float const* F,
+                       float const* dY, vlb_convt_desc const* d)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  vlb_conv_desc c;
+  int rc = convt_geom(ctx, d, &c);
+  if (rc) return vlb::pass_error(ctx, rc, "vlb_convt_backward");
+  VLB_REQUIRE(ctx, dY, "convt_backward: null derOutput");
+  VLB_REQUIRE(ctx, !dX || F, "convt_backward: the data derivative needs the filters");
+  VLB_REQUIRE(ctx, !dF || X, "convt_backward: the filter derivative needs the data");
+  if (dX) {                                             // bits/nnconv.cu:398-403
+    rc = vlb_conv_forward(ctx, dX, 0.0, dY, 1.0, F, nullptr, &c);
+    if (rc) return rc;
+  }
+  if (dF) {                                             // :405-409: the roles of data and output derivative exchanged
+    rc = vlb_conv_backward(ctx, nullptr, dF, nullptr, dY, nullptr, X, &c);
+    if (rc) return rc;
+  }
+  if (db) return vlb_bias_backward(ctx, nullptr, 0.0, db, 0.0, 0.0, 1.0, dY, c.H, c.W, c.C, c.N);      // :411-414
+  return VLB_Success;
+}
+
 int vlb_fc_forward(vlb_ctx* ctx, float* Y, float const* X, float const* F, float const* b, vlb_conv_desc const* d)
 {
   if (!ctx) return VLB_IllegalArgument;

@@ -115,6 +115,40 @@ def vl_nnconv(x, f, b, dzdy=None, stride=1, pad=0, dilate=1, no_der_data=False, 
     return dx, df, db
 
 
+# --------------------------------------------------------------------- vl_nnconvt
+def vl_nnconvt(x, f, b, dzdy=None, upsample=1, crop=0, num_groups=1, no_der_data=False, no_der_filters=False,
+               no_der_biases=False, ctx=None):
+    """Y = VL_NNCONVT(X, F, B) / [DX, DF, DB] = VL_NNCONVT(X, F, B, DZDY) (matlab/vl_nnconvt.m; gateway
+    matlab/src/vl_nnconvt.cu:87-417).  F is FH x FW x FD x C: FD output channels per filter group, its fourth dimension
+    the depth of X.  B may be None."""
+    ctx = _ctx(ctx)
+    x, f, b, dzdy = _need(x, "x"), _need(f, "f"), _need(b, "b"), _need(dzdy, "dzdy")
+    H, W, Cc, N = mat.shape4(x)
+    FH, FW, FD, FN = mat.shape4(f)
+    uy, ux = _pair(upsample, "UPSAMPLE")
+    ct, cb, cl, cr = _quad(crop, "CROP")
+    d = capi.ConvtDesc(H, W, Cc, N, FH, FW, FD, FN, uy, ux, ct, cb, cl, cr, int(num_groups))
+    K = FD * int(num_groups)
+    if b is not None and b.numel() != K:
+        raise ValueError("The number of elements of BIASES is not the same as the dimenison of the filters.")
+    lib = ctx.lib
+    Ho, Wo = C.c_int(), C.c_int()
+    lib.vlb_convt_output_shape(C.byref(d), C.byref(Ho), C.byref(Wo))
+    Ho, Wo = Ho.value, Wo.value
+    if dzdy is None:
+        y = mat.empty((max(Ho, 0), max(Wo, 0), K, N), x.device)
+        ctx.check(lib.vlb_convt_forward(ctx.handle, mat.ptr(y), mat.ptr(x), mat.ptr(f), mat.ptr(b), C.byref(d)))
+        return y
+    if mat.shape4(dzdy) != (Ho, Wo, K, N):
+        raise ValueError("DEROUTPUT dimensions are incompatible with X and FILTERS.")
+    dx = None if no_der_data else mat.empty(mat.shape4(x), x.device)
+    df = None if no_der_filters else mat.empty(mat.shape4(f), x.device)
+    db = None if (no_der_biases or b is None) else mat.empty((1, K), x.device)
+    ctx.check(lib.vlb_convt_backward(ctx.handle, mat.ptr(dx), mat.ptr(df), mat.ptr(db), mat.ptr(x), mat.ptr(f),
+                                     mat.ptr(dzdy), C.byref(d)))
+    return dx, df, db
+
+
 # --------------------------------------------------------------------- vl_nnbnorm
 def vl_nnbnorm(x, g, b, dzdy=None, epsilon=1e-4, moments=None, ctx=None):
     """[Y, MOMENTS] = VL_NNBNORM(X, G, B) / [DX, DG, DB, MOMENTS] = VL_NNBNORM(X, G, B, DZDY)

@@ -53,6 +53,14 @@ int mcno_fc_backward(int dt, void* dx, void* df, void* db, void const* x, void c
 { return dt ? fc_backward_f64(D(dx), D(df), D(db), CD(x), CD(f), CD(dy), shape)
             : fc_backward_f32(F(dx), F(df), F(db), CF(x), CF(f), CF(dy), shape); }
 
+int mcno_convt_forward(int dt, void* y, void const* x, void const* f, void const* b, int const* shape, int const* prm)
+{ return dt ? convt_forward_f64(D(y), CD(x), CD(f), CD(b), shape, prm) : convt_forward_f32(F(y), CF(x), CF(f), CF(b), shape, prm); }
+
+int mcno_convt_backward(int dt, void* dx, void* df, void* db, void const* x, void const* f, void const* dy,
+                        int const* shape, int const* prm)
+{ return dt ? convt_backward_f64(D(dx), D(df), D(db), CD(x), CD(f), CD(dy), shape, prm)
+            : convt_backward_f32(F(dx), F(df), F(db), CF(x), CF(f), CF(dy), shape, prm); }
+
 int mcno_bias_forward(int dt, void* y, double ymult, void const* x, double xmult, void const* b, double bmult,
                       int H, int W, int K, int N)
 { return dt ? bias_forward_f64(D(y), ymult, CD(x), xmult, CD(b), bmult, H, W, K, N)

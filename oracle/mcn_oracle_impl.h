@@ -254,6 +254,47 @@ static int FN(bias_backward)(T* dx, double dxmult, T* db, double dbmult, double 
   return 0;
 }
 
+/* Convolution transpose (nnconv.cu:323-421).  shape = {H,W,C,N,FH,FW,FD,FN} (FN == C); prm = {upY,upX,cropT,cropB,
+ * cropL,cropR,numGroups}.  The convolution it re-uses has the transposed convolution's output as its input, stride =
+ * upsample and pad = crop.  Forward: that convolution's data gradient, image by image (:338-367), then the bias
+ * (:368-370).  Backward: dx = its forward pass of dy (:398-403), df = its filter gradient with data and output
+ * derivative exchanged (:405-409), db = sum of dy (:411-414). */
+static void FN(convt_geom)(int const* shape, int const* prm, int* cshape, int* cprm)
+{
+  int H = shape[0], W = shape[1], FH = shape[4], FW = shape[5], FD = shape[6], G = prm[6];
+  cshape[0] = (H - 1) * prm[0] - (prm[2] + prm[3]) + FH;
+  cshape[1] = (W - 1) * prm[1] - (prm[4] + prm[5]) + FW;
+  cshape[2] = FD * G; cshape[3] = shape[3];
+  cshape[4] = FH; cshape[5] = FW; cshape[6] = FD; cshape[7] = shape[2];
+  cprm[0] = prm[0]; cprm[1] = prm[1]; cprm[2] = prm[2]; cprm[3] = prm[3]; cprm[4] = prm[4]; cprm[5] = prm[5];
+  cprm[6] = 1; cprm[7] = 1;
+}
+
+static int FN(convt_forward)(T* y, T const* x, T const* f, T const* b, int const* shape, int const* prm)
+{
+  int cs[8], cp[8];
+  FN(convt_geom)(shape, prm, cs, cp);
+  int N = shape[3];
+  size_t inStep = (size_t)shape[0] * shape[1] * shape[2], outStep = (size_t)cs[0] * cs[1] * cs[2];
+  cs[3] = 1;
+  for (int n = 0; n < N; ++n) {
+    int rc = FN(conv_backward)(y + outStep * n, NULL, NULL, NULL, f, x + inStep * n, cs, cp);
+    if (rc) return rc;
+  }
+  if (b) return FN(bias_forward)(y, 1.0, NULL, 0.0, b, 1.0, cs[0], cs[1], cs[2], N);
+  return 0;
+}
+
+static int FN(convt_backward)(T* dx, T* df, T* db, T const* x, T const* f, T const* dy, int const* shape, int const* prm)
+{
+  int cs[8], cp[8], rc = 0;
+  FN(convt_geom)(shape, prm, cs, cp);
+  if (dx) { rc = FN(conv_forward)(dx, dy, f, NULL, cs, cp); if (rc) return rc; }
+  if (df) { rc = FN(conv_backward)(NULL, df, NULL, dy, NULL, x, cs, cp); if (rc) return rc; }
+  if (db) rc = FN(bias_backward)(NULL, 0.0, db, 0.0, 0.0, 1.0, dy, cs[0], cs[1], cs[2], cs[3]);
+  return rc;
+}
+
 /* ------------------------------------------------------------------ */
 /* Batch normalisation (nnbnorm.cu:46-164 helpers, :170-365 functors)  */
 /* ------------------------------------------------------------------ */

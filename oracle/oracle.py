@@ -49,6 +49,14 @@ def conv_out_shape(x_shape, f_shape, stride=(1, 1), pad=(0, 0, 0, 0), dilate=(1,
     return (Ho, Wo, K, N)
 
 
+def convt_out_shape(x_shape, f_shape, upsample=(1, 1), crop=(0, 0, 0, 0), num_groups=1):
+    # matlab/src/vl_nnconvt.cu:293-296
+    H, W, _, N = x_shape
+    FH, FW, FD, _ = f_shape
+    return ((H - 1) * upsample[0] - (crop[0] + crop[1]) + FH, (W - 1) * upsample[1] - (crop[2] + crop[3]) + FW,
+            FD * num_groups, N)
+
+
 def pool_out_shape(x_shape, pool, stride=(1, 1), pad=(0, 0, 0, 0)):
     """Output shape of vl_nnpool (reference matlab/src/vl_nnpool.cu:240-247)."""
     H, W, Cc, N = x_shape
@@ -107,6 +115,29 @@ class CpuBackend:
         fn = self._fn("conv_backward", [C.c_int] + [C.c_void_p] * 6 + [c_int_p, c_int_p])
         self._check(fn(self._dt(x), _ptr(dx), _ptr(df), _ptr(db), _ptr(x), _ptr(f), _ptr(dy), shape, prm),
                     "conv_backward")
+        return dx, df, db
+
+    # --- convolution transpose ---------------------------------------
+    def convt_forward(self, x, f, b=None, upsample=(1, 1), crop=(0, 0, 0, 0), num_groups=1):
+        x, f = fa(x), fa(f)
+        b = None if b is None else fa(b, x.dtype)
+        y = np.zeros(convt_out_shape(x.shape, f.shape, upsample, crop, num_groups), dtype=x.dtype, order="F")
+        shape = _ints(list(x.shape) + list(f.shape))
+        prm = _ints(list(upsample) + list(crop) + [num_groups])
+        fn = self._fn("convt_forward", [C.c_int] + [C.c_void_p] * 4 + [c_int_p, c_int_p])
+        self._check(fn(self._dt(x), _ptr(y), _ptr(x), _ptr(f), _ptr(b), shape, prm), "convt_forward")
+        return y
+
+    def convt_backward(self, x, f, dy, upsample=(1, 1), crop=(0, 0, 0, 0), num_groups=1, want=(True, True, True)):
+        x, f, dy = fa(x), fa(f), fa(dy)
+        dx = np.zeros(x.shape, x.dtype, order="F") if want[0] else None
+        df = np.zeros(f.shape, x.dtype, order="F") if want[1] else None
+        db = np.zeros((f.shape[2] * num_groups,), x.dtype) if want[2] else None
+        shape = _ints(list(x.shape) + list(f.shape))
+        prm = _ints(list(upsample) + list(crop) + [num_groups])
+        fn = self._fn("convt_backward", [C.c_int] + [C.c_void_p] * 6 + [c_int_p, c_int_p])
+        self._check(fn(self._dt(x), _ptr(dx), _ptr(df), _ptr(db), _ptr(x), _ptr(f), _ptr(dy), shape, prm),
+                    "convt_backward")
         return dx, df, db
 
     def fc_forward(self, x, f, b=None):

@@ -73,6 +73,29 @@ int mcnref_conv_backward(int dtype, void* dx, void* df, void* db, void const* x,
   return op.backward(DX, DF, DB, X, F, DY);
 }
 
+// Convolution transpose (bits/nnconv.hpp:54-80): shape = {H,W,C,N, FH,FW,FD,FN}; prm = {upsampleY,upsampleX,cropT,cropB,
+// cropL,cropR,numGroups}; output extent as in the gateway (matlab/src/vl_nnconvt.cu:293-296).
+int mcnref_convt_forward(int dtype, void* y, void const* x, void const* f, void const* b, int const* shape, int const* prm)
+{
+  int H = shape[0], W = shape[1], C = shape[2], N = shape[3], FH = shape[4], FW = shape[5], FD = shape[6], FN = shape[7];
+  int Ho = (H - 1) * prm[0] - (prm[2] + prm[3]) + FH, Wo = (W - 1) * prm[1] - (prm[4] + prm[5]) + FW, K = FD * prm[6];
+  vl::Tensor X = view(x, dtype, H, W, C, N), F = view(f, dtype, FH, FW, FD, FN);
+  vl::Tensor B = view(b, dtype, 1, 1, 1, K), Y = view(y, dtype, Ho, Wo, K, N);
+  vl::nn::ConvolutionTranspose op(ctx(), prm[0], prm[1], prm[2], prm[3], prm[4], prm[5]);
+  return op.forward(Y, X, F, B);
+}
+
+int mcnref_convt_backward(int dtype, void* dx, void* df, void* db, void const* x, void const* f, void const* dy,
+                          int const* shape, int const* prm)
+{
+  int H = shape[0], W = shape[1], C = shape[2], N = shape[3], FH = shape[4], FW = shape[5], FD = shape[6], FN = shape[7];
+  int Ho = (H - 1) * prm[0] - (prm[2] + prm[3]) + FH, Wo = (W - 1) * prm[1] - (prm[4] + prm[5]) + FW, K = FD * prm[6];
+  vl::Tensor X = view(x, dtype, H, W, C, N), F = view(f, dtype, FH, FW, FD, FN), DY = view(dy, dtype, Ho, Wo, K, N);
+  vl::Tensor DX = view(dx, dtype, H, W, C, N), DF = view(df, dtype, FH, FW, FD, FN), DB = view(db, dtype, 1, 1, 1, K);
+  vl::nn::ConvolutionTranspose op(ctx(), prm[0], prm[1], prm[2], prm[3], prm[4], prm[5]);
+  return op.backward(DX, DF, DB, X, F, DY);
+}
+
 // Fully-connected mode (output 1x1): shape = {H,W,C,N, FH,FW,FC,K} with FH=H, FW=W, FC=C.
 int mcnref_fc_forward(int dtype, void* y, void const* x, void const* f, void const* b, int const* shape)
 {

@@ -62,11 +62,42 @@ POOL_CASES = {
 }
 
 
+# name: x shape, filter shape (FH, FW, FD, FN = C), upsample, crop, groups  (the shapes of xtest/suite/nnconvt.m:
+# upsampling 1-3 by 1-3, crops, two filter groups)
+CONVT_CASES = {
+    "up2_crop": ((5, 6, 4, 2), (3, 3, 5, 4), (2, 2), (1, 0, 1, 1), 1),
+    "groups2_up12": ((4, 4, 6, 2), (4, 3, 2, 6), (1, 2), (0, 1, 2, 0), 2),
+    "up31_nocrop": ((7, 5, 3, 1), (2, 2, 4, 3), (3, 1), (0, 0, 0, 0), 1),
+    "up1_is_full_correlation": ((6, 6, 2, 2), (3, 3, 3, 2), (1, 1), (0, 0, 0, 0), 1),
+    "fcn_upsample_4x": ((4, 5, 3, 1), (8, 8, 1, 3), (4, 4), (2, 2, 2, 2), 3),
+}
+
+
+def gen_convt(ref):
+    rng = np.random.default_rng(20240608)
+    out = {}
+    for name, (xs, fs, up, crop, groups) in CONVT_CASES.items():
+        x, f, b = randn(rng, *xs), randn(rng, *fs), randn(rng, fs[2] * groups)
+        y = ref.convt_forward(x, f, b, up, crop, groups)
+        dy = randn(rng, *y.shape)
+        dx, df, db = ref.convt_backward(x, f, dy, up, crop, groups)
+        x64, f64, b64, dy64 = (a.astype(np.float64) for a in (x, f, b, dy))
+        y64 = ref.convt_forward(x64, f64, b64, up, crop, groups)
+        dx64, df64, db64 = ref.convt_backward(x64, f64, dy64, up, crop, groups)
+        for k, v in dict(x=x, f=f, b=b, y=y, dy=dy, dx=dx, df=df, db=db, y64=y64, dx64=dx64, df64=df64,
+                         db64=db64, prm=np.array(list(up) + list(crop) + [groups])).items():
+            out[name + "." + k] = v
+    np.savez_compressed(os.path.join(OUT, "convt.npz"), **out)
+
+
 def main():
     build_oracle.build_reference()
     ref = O.reference()
     assert ref is not None, "reference checkout not found: cannot make golden vectors"
     O.reference_use_plain_blas()
+    gen_convt(ref)
+    if "--only-convt" in sys.argv:          # the other files are left as they are
+        return
     rng = np.random.default_rng(20240607)
 
     out = {}

@@ -28,6 +28,24 @@ def test_conv_golden(oracle):
             assert rel_l2(got, g[c + "." + name + "64"]) < 1e-5, (c, name)
 
 
+def test_convt_golden(oracle):
+    g = load_golden("convt")
+    for c in cases_of(g):
+        prm = [int(v) for v in g[c + ".prm"]]
+        kw = dict(upsample=tuple(prm[0:2]), crop=tuple(prm[2:6]), num_groups=prm[6])
+        y = oracle.convt_forward(g[c + ".x"], g[c + ".f"], g[c + ".b"], **kw)
+        dx, df, db = oracle.convt_backward(g[c + ".x"], g[c + ".f"], g[c + ".dy"], **kw)
+        for got, name in ((y, "y"), (dx, "dx"), (df, "df"), (db, "db")):
+            assert rel_l2(got, g[c + "." + name]) < 1e-6, (c, name)
+            assert rel_l2(got, g[c + "." + name + "64"]) < 1e-5, (c, name)
+    # upsample 1, no crop: the transposed convolution is the convolution of the zero-padded input with the flipped filters
+    # whose last two dimensions are exchanged (matlab/vl_nnconvt.m)
+    c = "up1_is_full_correlation"
+    x, f, b = g[c + ".x"], g[c + ".f"], g[c + ".b"]
+    ft = np.asfortranarray(np.transpose(f[::-1, ::-1], (0, 1, 3, 2)))
+    assert rel_l2(oracle.conv_forward(x, ft, b, pad=(2, 2, 2, 2)), g[c + ".y"]) < 1e-6
+
+
 def test_fc_golden(oracle):
     g = load_golden("fc")
     for c in cases_of(g):
