@@ -235,6 +235,15 @@ int vlb_softmaxloss_backward(vlb_ctx* ctx, float* dX, float const* X, float cons
 int vlb_sum(vlb_ctx* ctx, float* Y, float const* A, float const* B, size_t n);
 /* x *= alpha: the 1/numWorkers scaling of an all-reduced gradient (examples/cnn_train.m:482-483). */
 int vlb_scale(vlb_ctx* ctx, float* x, double alpha, size_t n);
+/* vl_taccum (matlab/vl_taccum.m, matlab/src/vl_taccummex.cu:50-76): Y = alpha*A + beta*B, computed as the reference does
+ * (A scaled, then an axpy of B).  Y may alias A. */
+int vlb_taccum(vlb_ctx* ctx, float* Y, double alpha, float const* A, double beta, float const* B, size_t n);
+/* The trainer's SGD step on one parameter tensor after the gradient exchange (examples/cnn_train.m:478-499), its four
+ * vl_taccum passes fused into one: g = gradMult*G + decay*W (gradMult = 1/numWorkers); M = momentum*M - g;
+ * delta = nesterov ? momentum*M - g : M; W += lr*delta.  W (parameters) and M (momentum state) are updated in place, G
+ * is only read.  Bit-identical to the four vlb_taccum calls. */
+int vlb_sgd_update(vlb_ctx* ctx, float* W, float* M, float const* G, size_t n, double gradMult, double decay,
+                   double momentum, double lr, int nesterov);
 
 #ifdef __cplusplus
 }

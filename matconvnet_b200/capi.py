@@ -93,6 +93,8 @@ SIGNATURES = {
     "vlb_softmaxloss_backward": (_I, [_P, _P, _P, _P, _D, _I, _I, _I, _I]),
     "vlb_sum": (_I, [_P, _P, _P, _P, _Z]),
     "vlb_scale": (_I, [_P, _P, _D, _Z]),
+    "vlb_taccum": (_I, [_P, _P, _D, _P, _D, _P, _Z]),
+    "vlb_sgd_update": (_I, [_P, _P, _P, _P, _Z, _D, _D, _D, _D, _I]),
 }
 
 _lib = None

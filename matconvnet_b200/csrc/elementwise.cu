@@ -50,6 +50,58 @@ __global__ void relu_bwd_kernel(float* dx, float const* __restrict__ x, float co
   }
 }
 
+// y = alpha*a + beta*b as the reference computes it: a scaled by alpha, then an axpy of b (matlab/src/vl_taccummex.cu:50-76);
+// y may be a.
+__device__ __forceinline__ float taccum1(float alpha, float a, float beta, float b) { return __fmaf_rn(beta, b, __fmul_rn(alpha, a)); }
+
+__global__ void taccum_kernel(float* y, float alpha, float const* a, float beta, float const* b, size_t n, bool vec)
+{
+  size_t stride = (size_t)gridDim.x * blockDim.x, i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (vec) {
+    size_t n4 = n >> 2;
+    for (size_t i = i0; i < n4; i += stride) {
+      float4 u = reinterpret_cast<float4 const*>(a)[i], v = reinterpret_cast<float4 const*>(b)[i];
+      u.x = taccum1(alpha, u.x, beta, v.x); u.y = taccum1(alpha, u.y, beta, v.y);
+      u.z = taccum1(alpha, u.z, beta, v.z); u.w = taccum1(alpha, u.w, beta, v.w);
+      reinterpret_cast<float4*>(y)[i] = u;
+    }
+    for (size_t i = (n4 << 2) + i0; i < n; i += stride) y[i] = taccum1(alpha, a[i], beta, b[i]);
+  } else {
+    for (size_t i = i0; i < n; i += stride) y[i] = taccum1(alpha, a[i], beta, b[i]);
+  }
+}
+
+// The trainer's update of one parameter tensor (reference examples/cnn_train.m:478-499), its four vl_taccum passes in one:
+//   g = gradMult*G + decay*W;  M = momentum*M - g;  delta = nesterov ? momentum*M - g : M;  W = W + lr*delta
+// with every intermediate rounded as in the separate passes.
+struct SgdParams { float gradMult, decay, momentum, lr; int nesterov; };
+
+__device__ __forceinline__ void sgd1(float& w, float& m, float g0, SgdParams const& p)
+{
+  float const g = taccum1(p.gradMult, g0, p.decay, w);
+  m = taccum1(p.momentum, m, -1.f, g);
+  float const delta = p.nesterov ? __fsub_rn(__fmul_rn(p.momentum, m), g) : m;
+  w = taccum1(1.f, w, p.lr, delta);
+}
+
+__global__ void sgd_update_kernel(float* w, float* m, float const* __restrict__ g, size_t n, SgdParams p, bool vec)
+{
+  size_t stride = (size_t)gridDim.x * blockDim.x, i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (vec) {
+    size_t n4 = n >> 2;
+    for (size_t i = i0; i < n4; i += stride) {
+      float4 W = reinterpret_cast<float4*>(w)[i], M = reinterpret_cast<float4*>(m)[i];
+      float4 const G = reinterpret_cast<float4 const*>(g)[i];
+      sgd1(W.x, M.x, G.x, p); sgd1(W.y, M.y, G.y, p); sgd1(W.z, M.z, G.z, p); sgd1(W.w, M.w, G.w, p);
+      reinterpret_cast<float4*>(w)[i] = W;
+      reinterpret_cast<float4*>(m)[i] = M;
+    }
+    for (size_t i = (n4 << 2) + i0; i < n; i += stride) sgd1(w[i], m[i], g[i], p);
+  } else {
+    for (size_t i = i0; i < n; i += stride) sgd1(w[i], m[i], g[i], p);
+  }
+}
+
 __global__ void sum_kernel(float* y, float const* a, float const* b, size_t n, bool vec)
 {
   size_t stride = (size_t)gridDim.x * blockDim.x, i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -257,6 +309,31 @@ int vlb_scale(vlb_ctx* ctx, float* x, double alpha, size_t n)
   scale_kernel<<<vlb::grid_for(vec ? n / 4 + 1 : n, kThreads, ctx->smCount * 8), kThreads, 0, ctx->stream>>>(x, (float)alpha, n, vec);
   VLB_LAUNCHED(ctx, 1);
   return vlb::check_launch(ctx, "vlb_scale");
+}
+
+int vlb_taccum(vlb_ctx* ctx, float* Y, double alpha, float const* A, double beta, float const* B, size_t n)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  VLB_REQUIRE(ctx, Y && A && B, "taccum: null tensor");
+  if (n == 0) return VLB_Success;
+  bool vec = aligned16(Y) && aligned16(A) && aligned16(B);
+  taccum_kernel<<<vlb::grid_for(vec ? n / 4 + 1 : n, kThreads, ctx->smCount * 8), kThreads, 0, ctx->stream>>>(
+      Y, (float)alpha, A, (float)beta, B, n, vec);
+  VLB_LAUNCHED(ctx, 1);
+  return vlb::check_launch(ctx, "vlb_taccum");
+}
+
+int vlb_sgd_update(vlb_ctx* ctx, float* W, float* M, float const* G, size_t n, double gradMult, double decay,
+                   double momentum, double lr, int nesterov)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  VLB_REQUIRE(ctx, W && M && G, "sgd_update: null tensor");
+  if (n == 0) return VLB_Success;
+  SgdParams p = {(float)gradMult, (float)decay, (float)momentum, (float)lr, nesterov ? 1 : 0};
+  bool vec = aligned16(W) && aligned16(M) && aligned16(G);
+  sgd_update_kernel<<<vlb::grid_for(vec ? n / 4 + 1 : n, kThreads, ctx->smCount * 8), kThreads, 0, ctx->stream>>>(W, M, G, n, p, vec);
+  VLB_LAUNCHED(ctx, 1);
+  return vlb::check_launch(ctx, "vlb_sgd_update");
 }
 
 int vlb_bias_forward(vlb_ctx* ctx, float* Y, double yMult, float const* X, double xMult, float const* b,

@@ -301,6 +301,35 @@ def scale_(t, alpha, ctx=None):
     return t
 
 
+def _flat32(t, name):
+    if not (isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == torch.float32):
+        raise TypeError("%s must be a CUDA float32 tensor" % name)
+    return t
+
+
+def vl_taccum(alpha, a, beta, b, out=None, ctx=None):
+    """Y = VL_TACCUM(ALPHA, A, BETA, B) = ALPHA*A + BETA*B (matlab/vl_taccum.m); out=a updates A in place."""
+    ctx = _ctx(ctx)
+    a, b = _flat32(a, "a"), _flat32(b, "b")
+    if a.numel() != b.numel():
+        raise ValueError("A and B do not have the same number of elements.")
+    y = torch.empty_like(a) if out is None else out
+    ctx.check(ctx.lib.vlb_taccum(ctx.handle, y.data_ptr(), float(alpha), a.data_ptr(), float(beta), b.data_ptr(), a.numel()))
+    return y
+
+
+def sgd_update_(w, momentum_state, grad, grad_mult, decay, momentum, lr, nesterov=False, ctx=None):
+    """The trainer's momentum-SGD step on one parameter tensor, in place on w and momentum_state
+    (examples/cnn_train.m:478-499: four vl_taccum passes, here one kernel)."""
+    ctx = _ctx(ctx)
+    w, m, g = _flat32(w, "w"), _flat32(momentum_state, "momentum_state"), _flat32(grad, "grad")
+    if not (w.numel() == m.numel() == g.numel()):
+        raise ValueError("parameter, momentum and gradient do not have the same number of elements.")
+    ctx.check(ctx.lib.vlb_sgd_update(ctx.handle, w.data_ptr(), m.data_ptr(), g.data_ptr(), w.numel(), float(grad_mult),
+                                     float(decay), float(momentum), float(lr), 1 if nesterov else 0))
+    return w
+
+
 # --------------------------------------------------------------------- MATLAB-only blocks
 def vl_nnrelu(x, dzdy=None, ctx=None):
     """matlab/vl_nnrelu.m:43-48 with LEAK = 0."""

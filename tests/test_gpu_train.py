@@ -1,0 +1,109 @@
+"""vl_taccum and the fused SGD step against the reference trainer's arithmetic (examples/cnn_train.m:451-500)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _taccum_np(alpha, a, beta, b):
+    # a scaled in single precision, then an axpy with one rounding (matlab/src/vl_taccummex.cu:50-76)
+    t = (np.float32(alpha) * a).astype(np.float32)
+    return (np.float64(np.float32(beta)) * b.astype(np.float64) + t.astype(np.float64)).astype(np.float32)
+
+
+@pytest.mark.parametrize("n", [1, 7, 4096, 100003])
+def test_taccum_matches_the_two_blas_calls(gpu, n):
+    import torch
+    nn, mat, ctx = gpu
+    g = torch.Generator(device="cuda").manual_seed(n)
+    a = torch.randn(n, device="cuda", generator=g)
+    b = torch.randn(n, device="cuda", generator=g)
+    want = _taccum_np(0.9, a.cpu().numpy(), -0.37, b.cpu().numpy())
+    got = nn.vl_taccum(0.9, a, -0.37, b).cpu().numpy()
+    # the double rounding of the emulation can differ from the fused multiply-add in the last place
+    assert np.max(np.abs(got - want) / np.maximum(np.abs(want), 1e-30)) <= 2.5e-7
+    a2 = a.clone()
+    nn.vl_taccum(0.9, a2, -0.37, b, out=a2)
+    assert torch.equal(a2.cpu(), torch.from_numpy(got))
+    # unaligned views take the scalar path and agree bit for bit
+    if n > 8:
+        assert torch.equal(nn.vl_taccum(0.9, a[1:], -0.37, b[1:]), torch.from_numpy(got).cuda()[1:])
+
+
+@pytest.mark.parametrize("nesterov", [False, True])
+def test_sgd_update_is_the_four_taccum_passes(gpu, nesterov):
+    import torch
+    nn, mat, ctx = gpu
+    g = torch.Generator(device="cuda").manual_seed(11)
+    n = 70001
+    w = torch.randn(n, device="cuda", generator=g)
+    m = torch.randn(n, device="cuda", generator=g) * 0.01
+    der = torch.randn(n, device="cuda", generator=g)
+    workers, decay, momentum, lr = 4, 0.0005, 0.9, 0.01
+    # the reference's sequence (cnn_train.m:478-499)
+    par = nn.vl_taccum(1.0 / workers, der, decay, w)
+    m_ref = nn.vl_taccum(momentum, m, -1.0, par)
+    delta = (momentum * m_ref - par) if nesterov else m_ref
+    w_ref = nn.vl_taccum(1.0, w, lr, delta)
+    w2, m2, der0 = w.clone(), m.clone(), der.clone()
+    nn.sgd_update_(w2, m2, der, 1.0 / workers, decay, momentum, lr, nesterov)
+    assert torch.equal(m2, m_ref) and torch.equal(w2, w_ref) and torch.equal(der, der0)
+    # and the closed form in double precision
+    wd, md, gd = w.double(), m.double(), der.double()
+    pd = gd / workers + decay * wd
+    md2 = momentum * md - pd
+    dd = momentum * md2 - pd if nesterov else md2
+    assert float((w2.double() - (wd + lr * dd)).abs().max()) < 1e-6
+    assert float((m2.double() - md2).abs().max()) < 1e-6
+
+
+def test_accumulate_gradients_follows_the_trainer(gpu):
+    """One training step of a small network with a bnorm layer: forward/backward, then the update; the parameters move as
+    the trainer's formulas say, the bnorm moments by the moving average, a layer with learning rate 0 and no decay stays."""
+    import torch
+    from matconvnet_b200 import models, simplenn, train
+    nn, mat, ctx = gpu
+    ctx.set_precision(0)
+    rng = np.random.default_rng(2)
+    g = torch.Generator(device="cuda").manual_seed(2)
+    C = 8
+    layers = [models._conv(rng, 3, 3, 3, C, 1, 1),
+              {"type": "bnorm", "weights": [mat.from_numpy(np.ones((C, 1), np.float32)), mat.from_numpy(np.zeros((C, 1), np.float32)),
+                                            mat.from_numpy(np.zeros((C, 2), np.float32))], "epsilon": 1e-4,
+               "learningRate": [2.0, 1.0, 0.1], "weightDecay": [0.0, 0.0, 0.0]},
+              models._relu(), models._pool("max", 2, 2),
+              models._conv(rng, 4, 4, C, 5, 1, 0),
+              {"type": "softmaxloss", "class": torch.randint(1, 6, (6,), device="cuda", generator=g).float()}]
+    layers[4]["learningRate"] = [0.0, 1.0]
+    layers[4]["weightDecay"] = [0.0, 1.0]
+    net = {"layers": layers}
+    x = mat.as_mat(torch.randn(8, 8, 3, 6, device="cuda", generator=g))
+    res = simplenn.vl_simplenn(net, x, 1.0, ctx=ctx)
+    before = {(l, j): w.clone() for l, lay in enumerate(layers) if "weights" in lay for j, w in enumerate(lay["weights"])}
+    params = dict(learning_rate=0.05, weight_decay=0.001, momentum=0.9, nesterov_update=False)
+    state = {}
+    workers = 2
+    train.accumulate_gradients(net, res, state, params, num_workers=workers, ctx=ctx)
+    for (l, j), w0 in before.items():
+        lay = layers[l]
+        w1, der = lay["weights"][j], res[l]["dzdw"][j]
+        lrm = lay.get("learningRate", [1.0] * 3)[j]
+        wdm = lay.get("weightDecay", [1.0] * 3)[j]
+        if lay["type"] == "bnorm" and j == 2:
+            want = (1 - lrm) * w0.double() + lrm / workers * der.double()
+        elif lrm == 0 and wdm == 0:
+            assert torch.equal(w1, w0) and (l, j) not in state
+            continue
+        else:
+            par = der.double() / workers + params["weight_decay"] * wdm * w0.double()
+            want = w0.double() + params["learning_rate"] * lrm * (-par)           # the momentum starts at zero
+            assert float((state[(l, j)].double() + par).abs().max()) < 1e-6
+        assert float((w1.double() - want).abs().max()) < 1e-6, (l, j)
+    # a second step uses the stored momentum
+    res = simplenn.vl_simplenn(net, x, 1.0, ctx=ctx)
+    m0 = state[(0, 0)].clone()
+    w0 = layers[0]["weights"][0].clone()
+    train.accumulate_gradients(net, res, state, params, num_workers=workers, ctx=ctx)
+    par = res[0]["dzdw"][0].double() / workers + params["weight_decay"] * w0.double()
+    m1 = params["momentum"] * m0.double() - par
+    assert float((layers[0]["weights"][0].double() - (w0.double() + params["learning_rate"] * m1)).abs().max()) < 1e-6
