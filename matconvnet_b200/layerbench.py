@@ -123,13 +123,26 @@ def bandwidth_rows(kind, iters, flush):
         t_b = timed(lambda: nn.vl_nnbilinearsampler(x, grid, dy), iters, flush)
         nbytes = 4.0 * (3 * x.numel() + 2 * grid.numel())
         rows.append({"block": "sampler 64x64x32x256", "fwd_ms": t_f, "bwd_ms": t_b, "bwd_GBs": nbytes / t_b / 1e6})
+    elif kind == "update":
+        # the trainer's SGD step on VGG-16's largest parameter tensors (fc6 filters 102.8M, fc7 16.8M, conv5 2.4M floats):
+        # the fused kernel (reads W, M, G; writes W, M) against the reference's four vl_taccum passes
+        for name, n in (("fc6 filters", 7 * 7 * 512 * 4096), ("fc7 filters", 4096 * 4096), ("conv5 filters", 3 * 3 * 512 * 512)):
+            w, m, g = (torch.randn(n, device="cuda") for _ in range(3))
+
+            def four():
+                par = nn.vl_taccum(0.5, g, 0.0005, w)
+                nn.vl_taccum(0.9, m, -1.0, par, out=m)
+                nn.vl_taccum(1.0, w, 0.01, m, out=w)
+            t_f = timed(lambda: nn.sgd_update_(w, m, g, 0.5, 0.0005, 0.9, 0.01), iters, flush)
+            t_4 = timed(four, iters, flush)
+            rows.append({"block": "sgd update, " + name, "fused_ms": t_f, "fused_GBs": 20.0 * n / t_f / 1e6, "taccum_x3_ms": t_4})
     return rows
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--net", default="vgg16", choices=["vgg16", "resnet"])
-    ap.add_argument("--kind", default="conv", choices=["conv", "bnorm", "pool", "roipool", "sampler"])
+    ap.add_argument("--kind", default="conv", choices=["conv", "bnorm", "pool", "roipool", "sampler", "update"])
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--precision", default="3xtf32", choices=["3xtf32", "tf32", "fp32"])
