@@ -314,21 +314,29 @@ def test_fused_relu_is_bit_identical(gpu):
              ((7, 7, 64, 5), (7, 7, 64, 40), dict()),                        # fully connected, split reduction
              ((1, 1, 96, 6), (1, 1, 96, 20), dict()),                        # fully connected, one pass
              ((10, 10, 8, 2), (3, 3, 2, 12), dict(pad=1)),                   # filter groups: CUDA-core fallback
-             ((17, 15, 6, 3), (3, 3, 6, 10), dict(stride=2, pad=(1, 0, 1, 1)))]
+             ((17, 15, 6, 3), (3, 3, 6, 10), dict(stride=2, pad=(1, 0, 1, 1))),
+             # more tiles than SMs, so that each CTA walks several tiles and the data gradient fetches its ReLU mask as
+             # bits while a tile is computed: 32 columns and few chains per tile; 128 columns and 18 chains per tile
+             ((48, 48, 32, 16), (3, 3, 32, 48), dict(pad=1)),
+             ((56, 56, 128, 8), (3, 3, 128, 256), dict(pad=1)),
+             ((52, 50, 72, 9), (3, 3, 72, 40), dict(pad=1))]          # ragged: 72 of 128 columns, last row tile partial
     for xs, fs, kw in cases:
-        x = mat.as_mat(torch.randn(*xs, device="cuda", generator=g))
-        f = mat.as_mat(torch.randn(*fs, device="cuda", generator=g) * 0.1)
-        b = mat.as_mat(torch.randn(1, fs[3], device="cuda", generator=g))
-        want = nn.vl_nnrelu(nn.vl_nnconv(x, f, b, **kw))
-        got = nn.vl_nnconv(x, f, b, relu=True, **kw)
-        assert torch.equal(got, want), (xs, fs)
-        # backward through the ReLU before the convolution: x is that ReLU's output
-        xr = nn.vl_nnrelu(x)
-        dzdy = mat.as_mat(torch.randn(*mat.shape4(want), device="cuda", generator=g))
-        dx, df, db = nn.vl_nnconv(xr, f, b, dzdy, **kw)
-        dx2, df2, db2 = nn.vl_nnconv(xr, f, b, dzdy, through_relu=True, **kw)
-        assert torch.equal(dx2, nn.vl_nnrelu(xr, dx)), (xs, fs)
-        assert torch.equal(df2, df) and torch.equal(db2, db), (xs, fs)
+        for prec in (0, 1):                  # 3xTF32 and plain TF32 (one chain per issuer and tile)
+            ctx.set_precision(prec)
+            x = mat.as_mat(torch.randn(*xs, device="cuda", generator=g))
+            f = mat.as_mat(torch.randn(*fs, device="cuda", generator=g) * 0.1)
+            b = mat.as_mat(torch.randn(1, fs[3], device="cuda", generator=g))
+            want = nn.vl_nnrelu(nn.vl_nnconv(x, f, b, **kw))
+            got = nn.vl_nnconv(x, f, b, relu=True, **kw)
+            assert torch.equal(got, want), (xs, fs)
+            # backward through the ReLU before the convolution: x is that ReLU's output
+            xr = nn.vl_nnrelu(x)
+            dzdy = mat.as_mat(torch.randn(*mat.shape4(want), device="cuda", generator=g))
+            dx, df, db = nn.vl_nnconv(xr, f, b, dzdy, **kw)
+            dx2, df2, db2 = nn.vl_nnconv(xr, f, b, dzdy, through_relu=True, **kw)
+            assert torch.equal(dx2, nn.vl_nnrelu(xr, dx)), (xs, fs)
+            assert torch.equal(df2, df) and torch.equal(db2, db), (xs, fs)
+    ctx.set_precision(0)
     pools = [((24, 20, 5, 3), (2, 2), dict(stride=2)),                        # 2x2 kernel, two outputs per thread
              ((10, 6, 4, 2), (2, 2), dict(stride=2)),                         # 2x2 kernel, one output per thread
              ((13, 11, 3, 2), (3, 3), dict(stride=2, pad=(0, 1, 0, 1))),      # generic kernel
