@@ -58,8 +58,16 @@ int vlb_ctx_clear_workspace(vlb_ctx* ctx);       /* Context::clearWorkspace, bit
 long long vlb_ctx_launch_count(vlb_ctx* ctx);    /* kernels enqueued through this context so far */
 /* Synchronises the stream and reads the status word that the tensor-core kernels set when one of
  * their bounded pipeline waits expires (0 = none did).  Returns VLE_Timeout, as the reference's own
- * waits do (matlab/src/vl_tmove.cu:1344-1359), when the word is non-zero, and clears it. */
+ * waits do (matlab/src/vl_tmove.cu:1344-1359), when the word is non-zero, and clears it; VLE_IllegalArgument when the word
+ * says that vlb_softmaxloss_* met a class label above the number of classes. */
 int vlb_ctx_device_status(vlb_ctx* ctx, int* status);
+/* The bound on a single pipeline wait of the tensor-core kernels, in SM clock cycles; 0 restores the default (2e8, about a
+ * tenth of a second).  Applies to the current device.  Exists so that a test can make a wait run out quickly. */
+int vlb_ctx_set_wait_limit(vlb_ctx* ctx, long long cycles);
+/* Test switches (0 = none).  Bit 0: the filter-tile loader of the tensor-memory convolution kernel stays idle, so every
+ * wait behind it runs out: the kernel records its status word, releases its tensor memory and returns
+ * (vlb_ctx_device_status then gives VLE_Timeout; the output of that call is undefined).  Nothing traps or spins. */
+int vlb_ctx_set_test_switch(vlb_ctx* ctx, int switches);
 /* Measurement aid: between begin and end every tensor-core contraction launch is bracketed by CUDA
  * events on the context's stream.  end synchronises and returns the summed kernel time, the summed
  * algorithmic flops (2*M*N*K of each contraction, counted once whatever the arithmetic mode) and the
@@ -168,7 +176,7 @@ int vlb_bnorm_backward_moment(vlb_ctx* ctx, float* dX, float* dG, float* dB, flo
  * library image, which every GPU that loads the library holds until the process exits.
  *   - C may be at most 4096 channels; more is refused with VLE_IllegalArgument and a message.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress); make
- *     that first call before any stream capture begins.
+ *     that first call before any stream capture begins, and from one host thread per device.
  *   - All calls on a device share the one array, so two calls whose kernels overlap on the GPU (different
  *     streams, no dependency) race on it; serialise them.  Nothing in it needs clearing between calls:
  *     each call rewrites the entries of channels [0, C) before reading them.
@@ -201,8 +209,10 @@ int vlb_relu_pool_backward(vlb_ctx* ctx, float* dX, float const* X, float const*
 
 /* ---- ROI pooling: vl::nn::ROIPooling (bits/nnroipooling.hpp:23-45) ----------------------------
  * rois: 5 x numROIs floats [image(1-based); u1; v1; u2; v2]; transform: 6 doubles, 2x3 column-major.
- * Y / dY: S0 x S1 x C x numROIs.  dX is overwritten (zeroed, then accumulated with atomics because
- * ROIs overlap), matching the reference CPU's memset (bits/nnroipooling.cu:237). */
+ * Y / dY: S0 x S1 x C x numROIs.  dX is overwritten, as after the reference CPU's memset (bits/nnroipooling.cu:237).
+ * Backward gathers: every element of dX adds the derivatives of the bins routed to it in the CPU loop's order (ROI, bin
+ * column, bin row), so the result is the CPU's bit for bit and the same from run to run; no atomics.  (Maps of 65535
+ * pixels or more, or too large for a shared-memory slab, fall back to a zero fill and an atomic scatter.) */
 int vlb_roipool_forward(vlb_ctx* ctx, float* Y, float const* X, float const* rois, int H, int W, int C,
                         int N, int numROIs, int S0, int S1, double const* transform, int method);
 int vlb_roipool_backward(vlb_ctx* ctx, float* dX, float const* X, float const* rois, float const* dY,
@@ -215,7 +225,10 @@ int vlb_roipool_bounds(vlb_ctx* ctx, int* bounds, int* images, float const* rois
 
 /* ---- bilinear sampler: vl::nn::BilinearSampler (bits/nnbilinearsampler.hpp:21-36) -------------
  * X: H x W x C x N; grid: 2 x Ho x Wo x Ng (y first), Ng a multiple of N; Y, dY: Ho x Wo x C x Ng.
- * dX and dGrid are overwritten (either may be NULL). */
+ * dX and dGrid are overwritten (either may be NULL).  dGrid is the CPU's bit for bit.  dX is a gather when the planes fit
+ * the shared memory (H*W and Ho*Wo up to a few thousand each): every input pixel adds its contributions in the CPU
+ * loop's order, bit for bit the CPU's result and run-to-run identical; only when one input pixel receives more than 48
+ * contributions from one grid, or for larger planes, dX is accumulated with float atomics instead. */
 int vlb_sampler_forward(vlb_ctx* ctx, float* Y, float const* X, float const* grid, int H, int W, int C,
                         int N, int Ho, int Wo, int Ng);
 int vlb_sampler_backward(vlb_ctx* ctx, float* dX, float* dGrid, float const* X, float const* grid,
@@ -225,8 +238,9 @@ int vlb_sampler_backward(vlb_ctx* ctx, float* dX, float* dGrid, float const* X, 
 /* matlab/vl_nnrelu.m:43-48 (leak 0). */
 int vlb_relu_forward(vlb_ctx* ctx, float* Y, float const* X, size_t n);
 int vlb_relu_backward(vlb_ctx* ctx, float* dX, float const* X, float const* dY, size_t n);
-/* matlab/vl_nnsoftmaxloss.m:56-84, one 1-based class label (as float) per image.
- * loss: one float on the device. */
+/* matlab/vl_nnsoftmaxloss.m:56-84, one 1-based class label (as float) per image; label 0 skips the image (its loss term
+ * and derivative are zero, :55-67).  A label above C (an indexing error in the reference) is skipped likewise and
+ * reported by vlb_ctx_device_status.  loss: one float on the device. */
 int vlb_softmaxloss_forward(vlb_ctx* ctx, float* loss, float const* X, float const* labels,
                             int H, int W, int C, int N);
 int vlb_softmaxloss_backward(vlb_ctx* ctx, float* dX, float const* X, float const* labels, double dzdy,

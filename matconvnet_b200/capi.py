@@ -59,6 +59,8 @@ SIGNATURES = {
     "vlb_ctx_clear_workspace": (_I, [_P]),
     "vlb_ctx_launch_count": (C.c_longlong, [_P]),
     "vlb_ctx_device_status": (_I, [_P, C.POINTER(_I)]),
+    "vlb_ctx_set_wait_limit": (_I, [_P, C.c_longlong]),
+    "vlb_ctx_set_test_switch": (_I, [_P, _I]),
     "vlb_ctx_profile_begin": (_I, [_P]),
     "vlb_ctx_profile_end": (_I, [_P, C.POINTER(_D), C.POINTER(_D), C.POINTER(C.c_longlong)]),
     "vlb_conv_output_shape": (_I, [C.POINTER(ConvDesc), C.POINTER(_I), C.POINTER(_I)]),

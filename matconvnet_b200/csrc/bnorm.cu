@@ -510,7 +510,14 @@ extern "C" int vlb_bnorm_backward_noalloc(void* cudaStream, float* dX, float* dG
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) { report(errbuf, errlen, "bnorm_backward_noalloc: no usable current device"); return VLB_Cuda; }
   if (!g_noAllocPtr[dev]) {
-    // first call on this device: resolve the array's device address (no allocation takes place)
+    // first call on this device: the kernels are built for sm_100a only, so refuse anything else before a launch
+    // could fail and leave its error pending for the host process; then resolve the array's device address (no
+    // allocation takes place).  Two host threads making their first call on one device at the same time would both
+    // do this and store the same address: harmless, but the entry point is meant for one calling thread per device.
+    int major = 0;
+    e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess) { cudaGetLastError(); report(errbuf, errlen, cudaGetErrorString(e)); return VLB_Cuda; }
+    if (major != 10) { report(errbuf, errlen, "bnorm_backward_noalloc: the kernels are built for sm_100a only"); return VLB_Unsupported; }
     float* p = nullptr;
     e = cudaGetSymbolAddress((void**)&p, g_bnormNoAllocScratch);
     if (e != cudaSuccess || !p) {
@@ -539,6 +546,10 @@ extern "C" int vlb_bnorm_backward_noalloc(void* cudaStream, float* dX, float* dG
   if (vec) bnorm_bwd_apply_kernel<true><<<blocks, kThreads, 0, stream>>>(dX, X, dY, cf, WH, C, total);
   else     bnorm_bwd_apply_kernel<false><<<blocks, kThreads, 0, stream>>>(dX, X, dY, cf, WH, C, total);
   e = cudaPeekAtLastError();
-  if (e != cudaSuccess) { report(errbuf, errlen, cudaGetErrorString(e)); return VLB_Cuda; }
+  if (e != cudaSuccess) {
+    report(errbuf, errlen, cudaGetErrorString(e));
+    cudaGetLastError();      // reported once: cleared so that later calls are not blamed for it
+    return VLB_Cuda;
+  }
   return VLB_Success;
 }

@@ -33,7 +33,14 @@ struct vlb_ctx {
   bool maskDone = false;
   bool profiling = false;
   std::vector<ProfRec> prof;
+  // vlb_ctx_set_test_switch: bit 0 makes the filter-tile loader of the tensor-memory convolution kernel stay idle, so that
+  // the bounded waits behind it run out (a test of the time-out path: nothing faults or spins, the kernel gives up and returns)
+  int testSwitch = 0;
 };
+
+// Values of the device status word (vlb_ctx::deviceStatus[0]).  1..63: a bounded pipeline wait of a tensor-core kernel
+// ran out (the number says which); kStatusBadLabel: the softmax loss met a class label above the number of classes.
+constexpr int kStatusBadLabel = 64;
 
 namespace vlb {
 

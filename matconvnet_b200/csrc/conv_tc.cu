@@ -51,7 +51,8 @@ constexpr int KSTEP = 32 / CH;                    // MN-major tiles: k rows betw
 constexpr int RSTEP = BM / CH;                    // K-major tiles: rows between a thread's consecutive chunks
 constexpr int kMaxStages = 8;
 constexpr int kDrainEvery = 8;                    // 3xTF32: k-blocks (of 32) accumulated by the tensor core before the fp32 drain
-constexpr long long kWaitCycles = 200000000LL;    // bound on any single barrier wait (about 0.1 s)
+constexpr long long kWaitCycles = 200000000LL;    // default bound on any single barrier wait (about 0.1 s)
+__constant__ long long gWaitCycles = kWaitCycles; // the bound in force on this device (vlb_ctx_set_wait_limit)
 
 enum OperandMode {
   OP_DENSE_K = 0,    // addr(i, r) = (r / P) * bs + i * ld + (r % P)      (reduction contiguous)
@@ -101,6 +102,7 @@ struct Params {
   int pipelined;          // 1: producers prefetch one stage ahead in registers (aligned gathers only)
   float const* bTiles;    // when non-null: B pre-split into shared-memory tile images, fetched with bulk copies
   int* status;
+  int testSwitch;         // vlb_ctx_set_test_switch: bit 0 = conv_ts_kernel's filter-tile loader stays idle
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -112,7 +114,7 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
 __device__ __forceinline__ void mbar_arrive(uint32_t bar)
 { asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.shared::cta.b64 st, [%0];\n}" ::"r"(bar) : "memory"); }
 
-// Bounded wait: false when the phase did not complete within kWaitCycles.
+// Bounded wait: false when the phase did not complete within gWaitCycles.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
 {
   long long t0 = 0;
@@ -125,7 +127,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
     if ((it & 15u) == 15u) {
       long long now = clock64();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitCycles) return false;
+      else if (now - t0 > gWaitCycles) return false;
     }
   }
 }
@@ -1271,7 +1273,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
     tc_fence_before();
   } else if (warp == kTsLoaderWarp) {
     // ============================== filter tiles: bulk copies ==============================
-    if (lane == 0) {
+    if (lane == 0 && !(p.testSwitch & 1)) {
       int sb = 0; uint32_t ph = 1;                       // first use of a stage: nothing to wait for
       bool ok = true;
       for (int ts = 0; ts < myTiles && ok; ++ts) {
@@ -1598,6 +1600,17 @@ int pick_bn(int N) { return N > 64 ? 128 : (N > 32 ? 64 : (N > 16 ? 32 : 16)); }
 
 bool aligned16(void const* p) { return (((uintptr_t)p) & 15) == 0; }
 
+// The opt-in to more than 48 KB of dynamic shared memory, once per kernel and device instead of before every launch.
+template <auto kKernel>
+cudaError_t allow_large_smem(int device)
+{
+  static bool done[64] = {};
+  if (device >= 0 && device < 64 && done[device]) return cudaSuccess;
+  cudaError_t e = cudaFuncSetAttribute(kKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  if (e == cudaSuccess && device >= 0 && device < 64) done[device] = true;
+  return e;
+}
+
 template <int kAMode, int kBMode, int kEpi>
 int launch(vlb_ctx* ctx, Params& p, int splits, char const* where)
 {
@@ -1620,13 +1633,11 @@ int launch(vlb_ctx* ctx, Params& p, int splits, char const* where)
     cudaEventRecord(rec.start, ctx->stream);
   }
   if (split3) {
-    auto k = tc_gemm_kernel<kAMode, kBMode, kEpi, true>;
-    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smemBytes);
-    if (e == cudaSuccess) k<<<grid, kThreads, smemBytes, ctx->stream>>>(p);
+    e = allow_large_smem<tc_gemm_kernel<kAMode, kBMode, kEpi, true>>(ctx->device);
+    if (e == cudaSuccess) tc_gemm_kernel<kAMode, kBMode, kEpi, true><<<grid, kThreads, smemBytes, ctx->stream>>>(p);
   } else {
-    auto k = tc_gemm_kernel<kAMode, kBMode, kEpi, false>;
-    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smemBytes);
-    if (e == cudaSuccess) k<<<grid, kThreads, smemBytes, ctx->stream>>>(p);
+    e = allow_large_smem<tc_gemm_kernel<kAMode, kBMode, kEpi, false>>(ctx->device);
+    if (e == cudaSuccess) tc_gemm_kernel<kAMode, kBMode, kEpi, false><<<grid, kThreads, smemBytes, ctx->stream>>>(p);
   }
   if (ctx->profiling) { cudaEventRecord(rec.stop, ctx->stream); ctx->prof.push_back(rec); }
   if (e != cudaSuccess) { cudaGetLastError(); return vlb::set_error(ctx, VLB_Cuda, cudaGetErrorString(e)); }
@@ -1639,6 +1650,7 @@ int launch_ts(vlb_ctx* ctx, Params& p, char const* where)
 {
   bool split3 = ctx->precision == VLB_PRECISION_3XTF32;
   p.status = ctx->deviceStatus;
+  p.testSwitch = ctx->testSwitch;
   // at least 120 KB, so that two CTAs (each allocating all 512 TMEM columns) never share an SM
   size_t smemBytes = (size_t)kTsBStages * (split3 ? 2u : 1u) * (size_t)p.BN * BK * 4 + sizeof(float) * (size_t)p.BN * BM + 1024;
   if (smemBytes < 120u * 1024u) smemBytes = 120u * 1024u;
@@ -1657,13 +1669,11 @@ int launch_ts(vlb_ctx* ctx, Params& p, char const* where)
     cudaEventRecord(rec.start, ctx->stream);
   }
   if (split3) {
-    auto k = conv_ts_kernel<true>;
-    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smemBytes);
-    if (e == cudaSuccess) k<<<grid, kTsThreads, smemBytes, ctx->stream>>>(p);
+    e = allow_large_smem<conv_ts_kernel<true>>(ctx->device);
+    if (e == cudaSuccess) conv_ts_kernel<true><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p);
   } else {
-    auto k = conv_ts_kernel<false>;
-    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smemBytes);
-    if (e == cudaSuccess) k<<<grid, kTsThreads, smemBytes, ctx->stream>>>(p);
+    e = allow_large_smem<conv_ts_kernel<false>>(ctx->device);
+    if (e == cudaSuccess) conv_ts_kernel<false><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p);
   }
   if (ctx->profiling) { cudaEventRecord(rec.stop, ctx->stream); ctx->prof.push_back(rec); }
   if (e != cudaSuccess) { cudaGetLastError(); return vlb::set_error(ctx, VLB_Cuda, cudaGetErrorString(e)); }
@@ -1877,3 +1887,14 @@ int conv_wgrad_tc(vlb_ctx* ctx, ConvGeom const& g, float* dF, float* db, float c
 }
 
 }  // namespace vlb
+
+extern "C" int vlb_ctx_set_wait_limit(vlb_ctx* ctx, long long cycles)
+{
+  if (!ctx || cycles < 0) return VLB_IllegalArgument;
+  long long const v = cycles == 0 ? kWaitCycles : cycles;
+  // ordered behind the kernels already enqueued on the context's stream, which keep the limit they were launched under
+  cudaError_t e = cudaMemcpyToSymbolAsync(gWaitCycles, &v, sizeof(v), 0, cudaMemcpyHostToDevice, ctx->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+  if (e != cudaSuccess) { cudaGetLastError(); return vlb::set_error(ctx, VLB_Cuda, cudaGetErrorString(e)); }
+  return VLB_Success;
+}

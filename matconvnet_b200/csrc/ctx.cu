@@ -54,6 +54,7 @@ int check_launch(vlb_ctx* ctx, char const* where)
 {
   cudaError_t e = cudaPeekAtLastError();
   if (e == cudaSuccess) return VLB_Success;
+  cudaGetLastError();      // reported once: a launch error that stayed pending would be blamed on every later call
   set_error(ctx, VLB_Cuda, cudaGetErrorString(e));
   return pass_error(ctx, VLB_Cuda, where);
 }
@@ -171,8 +172,17 @@ int vlb_ctx_device_status(vlb_ctx* ctx, int* status)
   if (e != cudaSuccess) return vlb::set_error(ctx, VLB_Cuda, cudaGetErrorString(e));
   if (*status != 0) {
     cudaMemset(ctx->deviceStatus, 0, sizeof(int));
+    if (*status == kStatusBadLabel)
+      return vlb::set_error(ctx, VLB_IllegalArgument, "softmaxloss: a class label is larger than the number of classes");
     return vlb::set_error(ctx, VLB_Timeout, "a tensor-core kernel gave up waiting on a pipeline barrier");
   }
+  return VLB_Success;
+}
+
+int vlb_ctx_set_test_switch(vlb_ctx* ctx, int switches)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  ctx->testSwitch = switches;
   return VLB_Success;
 }
 

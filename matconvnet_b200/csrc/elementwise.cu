@@ -229,7 +229,7 @@ __device__ float block_reduce(float v, bool isMax, float* red)
 }
 
 __global__ void softmaxloss_kernel(float* __restrict__ terms, float* __restrict__ dx, float const* __restrict__ x,
-                                   float const* __restrict__ labels, float scale, int P, int C)
+                                   float const* __restrict__ labels, float scale, int P, int C, int* __restrict__ status)
 {
   __shared__ float red[32];
   int p = blockIdx.x, n = blockIdx.y;
@@ -240,16 +240,23 @@ __global__ void softmaxloss_kernel(float* __restrict__ terms, float* __restrict_
   float s = 0.f;
   for (int c = threadIdx.x; c < C; c += blockDim.x) s += expf(xp[(size_t)P * c] - m);
   s = block_reduce(s, false, red);
-  int lab = (int)labels[n] - 1;
+  // class 0 skips the location: mass = (c > 0), index max(c - 1, 0) (matlab/vl_nnsoftmaxloss.m:55-67).  A class above C
+  // is an indexing error in the reference; here it is reported through the context's status word and skipped likewise.
+  float const labf = labels[n];
+  bool const tooBig = labf > (float)C;
+  if (tooBig && threadIdx.x == 0) atomicExch(status, kStatusBadLabel);
+  float const mass = (labf > 0.f && !tooBig) ? 1.f : 0.f;
+  int const lab = min(max((int)labf - 1, 0), C - 1);
   if (dx) {
     float* dp = dx + p + (size_t)P * C * n;
+    float const ms = mass * scale;
     for (int c = threadIdx.x; c < C; c += blockDim.x) {
       float v = expf(xp[(size_t)P * c] - m) / s;
       if (c == lab) v -= 1.f;
-      dp[(size_t)P * c] = v * scale;
+      dp[(size_t)P * c] = v * ms;
     }
   } else if (threadIdx.x == 0) {
-    terms[p + (size_t)P * n] = m + logf(s) - xp[(size_t)P * lab];
+    terms[p + (size_t)P * n] = mass * (m + logf(s) - xp[(size_t)P * lab]);
   }
 }
 
@@ -387,7 +394,7 @@ int vlb_softmaxloss_forward(vlb_ctx* ctx, float* loss, float const* X, float con
   float* terms = (float*)vlb::workspace(ctx, sizeof(float) * (size_t)P * N);
   if (!terms) return vlb::pass_error(ctx, ctx->lastError, "vlb_softmaxloss_forward");
   int threads = C >= 256 ? 256 : (C >= 64 ? 64 : 32);
-  softmaxloss_kernel<<<dim3(P, N), threads, 0, ctx->stream>>>(terms, nullptr, X, labels, 0.f, P, C);
+  softmaxloss_kernel<<<dim3(P, N), threads, 0, ctx->stream>>>(terms, nullptr, X, labels, 0.f, P, C, ctx->deviceStatus);
   loss_finish_kernel<<<1, 256, 0, ctx->stream>>>(loss, terms, P * N, 1.f / (float)N);
   VLB_LAUNCHED(ctx, 2);
   return vlb::check_launch(ctx, "vlb_softmaxloss_forward");
@@ -401,7 +408,7 @@ int vlb_softmaxloss_backward(vlb_ctx* ctx, float* dX, float const* X, float cons
   VLB_REQUIRE(ctx, H > 0 && W > 0 && C > 0 && N > 0 && N <= 65535, "softmaxloss_backward: bad shape");
   int P = H * W;
   int threads = C >= 256 ? 256 : (C >= 64 ? 64 : 32);
-  softmaxloss_kernel<<<dim3(P, N), threads, 0, ctx->stream>>>(nullptr, dX, X, labels, (float)dzdy / (float)N, P, C);
+  softmaxloss_kernel<<<dim3(P, N), threads, 0, ctx->stream>>>(nullptr, dX, X, labels, (float)dzdy / (float)N, P, C, ctx->deviceStatus);
   VLB_LAUNCHED(ctx, 1);
   return vlb::check_launch(ctx, "vlb_softmaxloss_backward");
 }

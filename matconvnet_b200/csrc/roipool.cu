@@ -6,9 +6,20 @@
 // float, float products with floor/ceil (bits/nnroipooling.cu:129-165) -- using the
 // _rn intrinsics so that no multiply-add is contracted; the reference's own GPU code
 // does the same maths in float throughout and can differ in the last place.
-// One thread per output bin; adjacent threads take adjacent ph, so reads of a bin
-// column are contiguous.  Backward scatters with atomics because ROIs overlap; the
-// scan order for the arg-max is the CPU's (w outer, h inner, first strictly greater).
+// Forward: one thread per output bin; adjacent threads take adjacent ph, so reads of a bin
+// column are contiguous.  The scan order for the arg-max is the CPU's (w outer, h inner,
+// first strictly greater).
+//
+// Backward is a gather, not the reference GPU code's thread-per-bin atomicAdd scatter
+// (bits/impl/nnroipooling_gpu.cu:114-246): one CTA owns a slab of channels of one image and keeps
+// it in shared memory.  It (1) finds the arg-max of every bin of every ROI of its image from the
+// slab, as 16-bit pixel indices in shared memory, (2) tabulates for every ROI which bin rows cover
+// each map row and which bin columns cover each map column, and (3) lets every (pixel, channel)
+// of the slab walk the ROIs in ascending order and add the derivatives of the bins that routed
+// to it, bin columns outer and bin rows inner -- the order in which the CPU loop reaches that
+// element (bits/nnroipooling.cu:239-300), so the sums are the CPU's bit for bit, run-to-run
+// identical, and dX is written exactly once: no atomics, no zero fill, no scratch in global
+// memory; x, dY and dX cross HBM once.  Maps too large for the slab take the scatter kernel.
 #include "common.cuh"
 #include <math.h>
 
@@ -126,6 +137,164 @@ __global__ void roipool_kernel(float* __restrict__ out, float const* __restrict_
   }
 }
 
+// ---- backward as a gather (see the header comment) ----
+constexpr int kGatherThreads = 1024;
+constexpr uint32_t kNoBin = 0xFFFFu;
+
+struct GatherPlan {
+  int CH;            // channels per slab
+  int RB;            // ROIs per batch (tables and arg-max indices of one batch are in shared memory at a time)
+  int chunks;        // slabs per image
+  size_t smem;
+};
+
+// Shared-memory layout (bytes): slab float[CH*HW] | argmax uint16[RB*CH*S0*S1] | rowTab uint16[RB*H] | colTab uint16[RB*W] |
+// roiIdx int[RB].  A table entry is lo | hi << 8 (bin range covering that row / column) or kNoBin.
+__host__ __device__ inline size_t gather_smem(int CH, int RB, int H, int W, int S0, int S1, bool isMax)
+{
+  size_t b = isMax ? sizeof(float) * (size_t)CH * H * W : 0;
+  b += isMax ? ((sizeof(uint16_t) * (size_t)RB * CH * S0 * S1 + 15) & ~(size_t)15) : 0;
+  b += (sizeof(uint16_t) * (size_t)RB * (H + W) + 15) & ~(size_t)15;
+  b += sizeof(int) * (size_t)RB;
+  return b + 64;
+}
+
+template <bool kMax>
+__global__ void __launch_bounds__(kGatherThreads, 1)
+roipool_bwd_gather_kernel(float* __restrict__ dx, float const* __restrict__ x, float const* __restrict__ rois,
+                          float const* __restrict__ dy, RoiParams p, int CH, int RB, int chunks)
+{
+  extern __shared__ __align__(16) uint8_t sm[];
+  __shared__ int sCount, sNext;
+  int const HW = p.H * p.W, bins = p.S0 * p.S1;
+  int const img = blockIdx.x / chunks, c0 = (blockIdx.x % chunks) * CH;
+  int const nch = min(CH, p.C - c0);
+  int const tid = threadIdx.x, lane = tid & 31;
+  uint8_t* q = sm;
+  float* slab = reinterpret_cast<float*>(q);
+  if (kMax) q += sizeof(float) * (size_t)CH * HW;
+  uint16_t* am = reinterpret_cast<uint16_t*>(q);
+  if (kMax) q += (sizeof(uint16_t) * (size_t)RB * CH * bins + 15) & ~(size_t)15;
+  uint16_t* rowTab = reinterpret_cast<uint16_t*>(q);
+  uint16_t* colTab = rowTab + (size_t)RB * p.H;
+  q += (sizeof(uint16_t) * (size_t)RB * (p.H + p.W) + 15) & ~(size_t)15;
+  int* roiIdx = reinterpret_cast<int*>(q);
+
+  size_t const slabOff = (size_t)HW * ((size_t)c0 + (size_t)p.C * img);
+  if (kMax) {
+    for (int i = tid; i < nch * HW; i += kGatherThreads) slab[i] = x[slabOff + i];
+  }
+  bool first = true;
+  int base = 0;
+  while (true) {
+    __syncthreads();                                  // the previous batch's tables are no longer read
+    if (tid < 32) {
+      // the next RB ROIs of this image, in ascending order
+      int cnt = 0, r = base;
+      while (r < p.numROIs && cnt < RB) {
+        int const rr = r + lane;
+        bool mine = false;
+        if (rr < p.numROIs) {
+          int image = (int)rois[5 * (size_t)rr];
+          mine = min(max(image - 1, 0), p.N - 1) == img;
+        }
+        unsigned const m = __ballot_sync(0xffffffffu, mine);
+        int const pos = cnt + __popc(m & ((1u << lane) - 1u));
+        if (mine && pos < RB) roiIdx[pos] = rr;
+        int const tot = __popc(m);
+        if (cnt + tot > RB) {                           // the batch is full inside this group of 32: resume behind its last member
+          r += (int)__fns(m, 0, RB - cnt) + 1;
+          cnt = RB;
+          break;
+        }
+        cnt += tot; r += 32;
+      }
+      if (lane == 0) { sCount = cnt; sNext = min(r, p.numROIs); }
+    }
+    __syncthreads();
+    int const nb = sCount;
+    base = sNext;
+    if (nb == 0) break;
+    // which bin rows cover map row h, which bin columns cover map column w
+    for (int i = tid; i < nb * (p.H + p.W); i += kGatherThreads) {
+      bool const isRow = i < nb * p.H;
+      int const k = isRow ? i : i - nb * p.H;
+      int const ext = isRow ? p.H : p.W, S = isRow ? p.S0 : p.S1;
+      int const j = k / ext, pos = k - j * ext;
+      RoiGeom g = roi_geom(rois + 5 * (size_t)roiIdx[j], p);
+      uint32_t lo = kNoBin, hi = 0;
+      for (int b = 0; b < S; ++b) {
+        int s, e;
+        roi_bin(b, isRow ? g.bin_h : g.bin_w, isRow ? g.start_h : g.start_w, ext, s, e);
+        if (s <= pos && pos < e) { if (lo == kNoBin) lo = (uint32_t)b; hi = (uint32_t)b; }
+      }
+      (isRow ? rowTab : colTab)[k] = (uint16_t)(lo == kNoBin ? kNoBin : (lo | (hi << 8)));
+    }
+    if (kMax) {
+      // arg-max of every bin: CPU scan order, first strictly greater, none for an empty or all -inf / NaN bin
+      for (int b = tid; b < nb * nch * bins; b += kGatherThreads) {
+        int const ph = b % p.S0;
+        int t = b / p.S0;
+        int const pw = t % p.S1; t /= p.S1;
+        int const cc = t % nch, j = t / nch;
+        RoiGeom g = roi_geom(rois + 5 * (size_t)roiIdx[j], p);
+        int hs, he, ws, we;
+        roi_bin(ph, g.bin_h, g.start_h, p.H, hs, he);
+        roi_bin(pw, g.bin_w, g.start_w, p.W, ws, we);
+        float const* xz = slab + (size_t)cc * HW;
+        float best = -INFINITY;
+        uint32_t where = kNoBin;
+        for (int w = ws; w < we; ++w)
+          for (int h = hs; h < he; ++h) {
+            float a = xz[w * p.H + h];
+            if (a > best) { best = a; where = (uint32_t)(w * p.H + h); }
+          }
+        am[b] = (uint16_t)where;
+      }
+    }
+    __syncthreads();
+    for (int item = tid; item < nch * HW; item += kGatherThreads) {
+      int const cc = item / HW, pix = item - cc * HW;
+      int const w = pix / p.H, h = pix - w * p.H;
+      float* const dst = dx + slabOff + item;
+      float acc = first ? 0.f : *dst;
+      for (int j = 0; j < nb; ++j) {
+        uint32_t const rt = rowTab[j * p.H + h], ct = colTab[j * p.W + w];
+        if (rt == kNoBin || ct == kNoBin) continue;
+        float const* dyr = dy + (size_t)bins * ((size_t)(c0 + cc) + (size_t)p.C * roiIdx[j]);
+        if (kMax) {
+          uint16_t const* amr = am + (size_t)bins * (cc + (size_t)nch * j);
+          for (uint32_t pw = ct & 255u; pw <= (ct >> 8); ++pw)
+            for (uint32_t ph = rt & 255u; ph <= (rt >> 8); ++ph) {
+              int const b = (int)(ph + p.S0 * pw);
+              if (amr[b] == (uint32_t)pix) acc = __fadd_rn(acc, dyr[b]);
+            }
+        } else {
+          // every bin that covers the pixel contributes dy / area (bits/nnroipooling.cu:74-90, acc_sum)
+          RoiGeom g = roi_geom(rois + 5 * (size_t)roiIdx[j], p);
+          for (uint32_t pw = ct & 255u; pw <= (ct >> 8); ++pw) {
+            int ws, we;
+            roi_bin((int)pw, g.bin_w, g.start_w, p.W, ws, we);
+            for (uint32_t ph = rt & 255u; ph <= (rt >> 8); ++ph) {
+              int hs, he;
+              roi_bin((int)ph, g.bin_h, g.start_h, p.H, hs, he);
+              float const scale = __fdiv_rn(1.f, (float)((he - hs) * (we - ws)));
+              acc = __fadd_rn(acc, __fmul_rn(dyr[ph + p.S0 * pw], scale));
+            }
+          }
+        }
+      }
+      *dst = acc;
+    }
+    first = false;
+    if (base >= p.numROIs) break;
+  }
+  if (first) {
+    // no ROI of this image: the slab of dX is zero
+    for (int i = tid; i < nch * HW; i += kGatherThreads) dx[slabOff + i] = 0.f;
+  }
+}
+
 int make_params(vlb_ctx* ctx, RoiParams* p, int H, int W, int C, int N, int numROIs, int S0, int S1,
                 double const* tf, int method)
 {
@@ -182,6 +351,41 @@ int vlb_roipool_backward(vlb_ctx* ctx, float* dX, float const* X, float const* r
   int rc = make_params(ctx, &p, H, W, C, N, numROIs, S0, S1, transform, method);
   if (rc) return rc;
   VLB_REQUIRE(ctx, dX && X && rois && dY, "roipool_backward: null tensor");
+  {
+    // the gather: slabs of about 64 KB per CTA, at least as many CTAs as SMs where the channels allow, and as many ROIs
+    // per batch as the rest of the shared memory holds
+    bool const isMax = method == VLB_POOL_MAX;
+    long long const HW = (long long)H * W;
+    size_t const budget = 200 * 1024;
+    if (HW < 65535 && S0 <= 255 && S1 <= 255 && numROIs > 0) {
+      int CH = (int)((64 * 1024) / (4 * HW));
+      if (CH > C) CH = C;
+      while (CH > 1 && (long long)N * vlb::ceil_div(C, CH) < ctx->smCount) --CH;
+      if (CH >= 1) {
+        size_t const fixed = gather_smem(CH, 0, H, W, S0, S1, isMax);
+        size_t const perRoi = gather_smem(CH, 1, H, W, S0, S1, isMax) - fixed + 32;
+        long long RB = fixed < budget ? (long long)((budget - fixed) / perRoi) : 0;
+        if (RB > numROIs) RB = numROIs;
+        if (RB >= 8 || RB == numROIs) {
+          int const chunks = vlb::ceil_div(C, CH);
+          size_t const smem = gather_smem(CH, (int)RB, H, W, S0, S1, isMax) + 64;
+          static bool attrDone[2][64] = {};
+          if (!(ctx->device < 64 && attrDone[isMax][ctx->device])) {
+            cudaError_t ea = isMax ? cudaFuncSetAttribute(roipool_bwd_gather_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)
+                                   : cudaFuncSetAttribute(roipool_bwd_gather_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            if (ea != cudaSuccess) { cudaGetLastError(); return vlb::set_error(ctx, VLB_Cuda, cudaGetErrorString(ea)); }
+            if (ctx->device < 64) attrDone[isMax][ctx->device] = true;
+          }
+          unsigned const grid = (unsigned)(N * chunks);
+          if (isMax) roipool_bwd_gather_kernel<true><<<grid, kGatherThreads, smem, ctx->stream>>>(dX, X, rois, dY, p, CH, (int)RB, chunks);
+          else       roipool_bwd_gather_kernel<false><<<grid, kGatherThreads, smem, ctx->stream>>>(dX, X, rois, dY, p, CH, (int)RB, chunks);
+          VLB_LAUNCHED(ctx, 1);
+          return vlb::check_launch(ctx, "vlb_roipool_backward");
+        }
+      }
+    }
+  }
+  // maps too large for a shared-memory slab: zero fill and scatter with atomics
   cudaError_t e = cudaMemsetAsync(dX, 0, sizeof(float) * (size_t)H * W * C * N, ctx->stream);
   if (e != cudaSuccess) return vlb::set_error(ctx, VLB_Cuda, cudaGetErrorString(e));
   if (numROIs == 0) return VLB_Success;

@@ -1,14 +1,24 @@
 // Bilinear sampler (vl::nn::BilinearSampler, reference bits/nnbilinearsampler.hpp:21-36;
 // CPU definition bits/nnbilinearsampler.cu:32-149).
 //
-// One thread per output pixel (q = ho + Ho*wo, grid n) walks the C channels: the grid
-// entry and the four tap weights are computed once and reused for every channel; reads
-// of dy and writes of y are contiguous across the warp; x taps of neighbouring output
-// pixels fall in the same or adjacent 32-byte sectors.  Backward-to-data scatters with
-// atomicAdd (footprints of different outputs overlap); backward-to-grid accumulates
-// the channels in ascending order in a register, the order of the CPU loop, and writes
-// each grid entry once.  dx and dgrid are overwritten: dx is cleared first, dgrid is
-// written whole.
+// Forward and backward-to-grid: one thread per output pixel (q = ho + Ho*wo, grid n) walks the C
+// channels: the grid entry and the four tap weights are computed once and reused for every
+// channel; reads of dy and writes of y are contiguous across the warp; x taps of neighbouring
+// output pixels fall in the same or adjacent 32-byte sectors.  Backward-to-grid accumulates the
+// channels in ascending order in a register, the order of the CPU loop, and writes each grid
+// entry once.
+//
+// Backward-to-data is a gather, not the reference GPU code's four atomicAdds per output element
+// (bits/impl/nnbilinearsampler_gpu.cu:38-118).  Which output pixels touch an input pixel depends
+// on the grid alone, not on the channel, so one CTA per image first inverts the grid in shared
+// memory: it counts the taps that land on every input pixel, prefix-sums the counts, fills one
+// list (output pixel, tap weight) per input pixel and sorts each list by output pixel.  Then every
+// input pixel adds up its list, for eight channels at a time, in ascending output-pixel order --
+// the order in which the CPU loop reaches that element (bits/nnbilinearsampler.cu:72-131) -- and
+// writes dX once: no atomics, no zero fill, the CPU's result bit for bit, identical from run to
+// run.  dy is read once from HBM (the grid derivative, computed by the same CTA afterwards, finds
+// it in L2).  A grid that sends more than kMaxList taps to one input pixel, and planes too large
+// for the lists, take the atomic scatter instead.
 //
 // Boundary rule of the CPU reference, kept as it is: the taps are guarded by
 // `-1 <= sy && sy < inHeight` with inHeight a size_t (bits/nnbilinearsampler.cu:92), so
@@ -113,6 +123,199 @@ __global__ void sampler_kernel(float* __restrict__ y, float* __restrict__ dx, fl
   }
 }
 
+// ---- backward-to-data as a gather (see the header comment) ----
+constexpr int kGatherThreads = 1024;
+constexpr int kMaxList = 48;          // taps of one grid on one input pixel beyond which the scatter path is used
+constexpr int kChan = 8;              // channels accumulated together per input pixel
+
+__host__ __device__ inline size_t gather_smem(int HW, int Q)
+{
+  return sizeof(int) * (size_t)HW + (sizeof(float) + sizeof(uint16_t)) * 4 * (size_t)Q + 64;
+}
+
+// Exclusive prefix sum of v[0..n) in place by the whole block; returns nothing, total not needed.
+__device__ void block_exclusive_scan(int* v, int n, int* warpSums)
+{
+  int const tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int const per = (n + kGatherThreads - 1) / kGatherThreads;
+  int const beg = min(tid * per, n), end = min(beg + per, n);
+  int sum = 0;
+  for (int i = beg; i < end; ++i) sum += v[i];
+  int incl = sum;
+  for (int o = 1; o < 32; o <<= 1) { int t = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += t; }
+  if (lane == 31) warpSums[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int w = warpSums[lane];
+    int wi = w;
+    for (int o = 1; o < 32; o <<= 1) { int t = __shfl_up_sync(0xffffffffu, wi, o); if (lane >= o) wi += t; }
+    warpSums[lane] = wi - w;      // exclusive over the warps
+  }
+  __syncthreads();
+  int run = warpSums[warp] + incl - sum;
+  for (int i = beg; i < end; ++i) { int c = v[i]; v[i] = run; run += c; }
+  __syncthreads();
+}
+
+template <bool kWantGrid>
+__global__ void __launch_bounds__(kGatherThreads, 1)
+sampler_bwd_gather_kernel(float* __restrict__ dx, float* __restrict__ dgrid, float const* __restrict__ x,
+                          float const* __restrict__ grid, float const* __restrict__ dy, int H, int W, int C, int N, int Q, int Ng,
+                          int chunks, int CH)
+{
+  extern __shared__ __align__(16) uint8_t sm[];
+  __shared__ int warpSums[32];
+  int const HW = H * W, tid = threadIdx.x;
+  int* cur = reinterpret_cast<int*>(sm);                                   // [HW]  list ends (starts before the fill)
+  float* entW = reinterpret_cast<float*>(sm + sizeof(int) * (size_t)HW);   // [4Q]  tap weight wwx*wwy
+  uint16_t* entQ = reinterpret_cast<uint16_t*>(entW + 4 * (size_t)Q);     // [4Q]  output pixel
+  int const group = Ng / N;
+  int const img = blockIdx.x / chunks, c0 = (blockIdx.x % chunks) * CH, nch = min(CH, C - c0);
+  size_t const imgOff = (size_t)HW * C * (size_t)img;
+
+  for (int gi = 0; gi < group; ++gi) {
+    int const n = img * group + gi;
+    float2 const* gr = reinterpret_cast<float2 const*>(grid) + (size_t)Q * n;
+    // ---- invert the grid: count, scan, fill, sort
+    for (int i = tid; i < HW; i += kGatherThreads) cur[i] = 0;
+    __syncthreads();
+    for (int q = tid; q < Q; q += kGatherThreads) {
+      float2 const gv = gr[q];
+      Taps t = make_taps(gv.x, gv.y, H, W);
+      if (t.inside) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int ii = 0; ii < 2; ++ii) {
+            int const ssy = t.sy + ii, ssx = t.sx + j;
+            if (ssy < H && ssx < W) atomicAdd(&cur[ssy + ssx * H], 1);
+          }
+      }
+    }
+    __syncthreads();
+    bool tooLong = false;
+    for (int i = tid; i < HW; i += kGatherThreads) tooLong |= cur[i] > kMaxList;
+    bool const scatter = __syncthreads_or(tooLong) != 0;
+    if (!scatter) {
+      block_exclusive_scan(cur, HW, warpSums);
+      for (int q = tid; q < Q; q += kGatherThreads) {
+        float2 const gv = gr[q];
+        Taps t = make_taps(gv.x, gv.y, H, W);
+        if (t.inside) {
+          float const wwx[2] = {__fadd_rn(1.f, -t.wx), t.wx};
+          float const wwy[2] = {__fadd_rn(1.f, -t.wy), t.wy};
+#pragma unroll
+          for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int ii = 0; ii < 2; ++ii) {
+              int const ssy = t.sy + ii, ssx = t.sx + j;
+              if (ssy < H && ssx < W) {
+                int const pos = atomicAdd(&cur[ssy + ssx * H], 1);
+                entQ[pos] = (uint16_t)q;
+                entW[pos] = __fmul_rn(wwx[j], wwy[ii]);
+              }
+            }
+        }
+      }
+      __syncthreads();
+      // every input pixel: sort its list by output pixel, then add it up for kChan channels at a time
+      for (int pix = tid; pix < HW; pix += kGatherThreads) {
+        int const beg = pix == 0 ? 0 : cur[pix - 1], end = cur[pix];
+        for (int a = beg + 1; a < end; ++a) {
+          uint16_t const kq = entQ[a];
+          float const kw = entW[a];
+          int b = a - 1;
+          while (b >= beg && entQ[b] > kq) { entQ[b + 1] = entQ[b]; entW[b + 1] = entW[b]; --b; }
+          entQ[b + 1] = kq; entW[b + 1] = kw;
+        }
+        for (int cb = 0; cb < nch; cb += kChan) {
+          float acc[kChan];
+          float* const dst = dx + imgOff + (size_t)HW * (c0 + cb) + pix;
+          float const* const src = dy + (size_t)Q * ((size_t)(c0 + cb) + (size_t)C * n);
+#pragma unroll
+          for (int k = 0; k < kChan; ++k) acc[k] = (gi > 0 && cb + k < nch) ? dst[(size_t)HW * k] : 0.f;
+          for (int e = beg; e < end; ++e) {
+            float const w = entW[e];
+            float const* const s = src + entQ[e];
+#pragma unroll
+            for (int k = 0; k < kChan; ++k)
+              if (cb + k < nch) acc[k] = __fadd_rn(acc[k], __fmul_rn(w, __ldg(s + (size_t)Q * k)));
+          }
+#pragma unroll
+          for (int k = 0; k < kChan; ++k)
+            if (cb + k < nch) dst[(size_t)HW * k] = acc[k];
+        }
+      }
+    } else {
+      // a grid that piles its taps on a few input pixels: zero (first grid of the image) and scatter with atomics
+      if (gi == 0) {
+        for (size_t i = tid; i < (size_t)HW * nch; i += kGatherThreads) dx[imgOff + (size_t)HW * c0 + i] = 0.f;
+      }
+      __syncthreads();
+      for (int q = tid; q < Q; q += kGatherThreads) {
+        float2 const gv = gr[q];
+        Taps t = make_taps(gv.x, gv.y, H, W);
+        if (!t.inside) continue;
+        float const wwx[2] = {__fadd_rn(1.f, -t.wx), t.wx};
+        float const wwy[2] = {__fadd_rn(1.f, -t.wy), t.wy};
+        for (int c = 0; c < nch; ++c) {
+          float const d = dy[q + (size_t)Q * ((size_t)(c0 + c) + (size_t)C * n)];
+          float* const dxz = dx + imgOff + (size_t)HW * (c0 + c);
+#pragma unroll
+          for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int ii = 0; ii < 2; ++ii) {
+              int const ssy = t.sy + ii, ssx = t.sx + j;
+              if (ssy < H && ssx < W) atomicAdd(dxz + ssy + ssx * H, __fmul_rn(__fmul_rn(wwx[j], wwy[ii]), d));
+            }
+        }
+      }
+    }
+    __syncthreads();       // this grid's additions to dX are visible to the block before the next grid reads them
+    if (kWantGrid) {
+      // ---- the grid derivative, channels in ascending order (the sequence of sampler_kernel<1>)
+      for (int q = tid; q < Q; q += kGatherThreads) {
+        float2 const gv = gr[q];
+        Taps t = make_taps(gv.x, gv.y, H, W);
+        float const wwx[2] = {__fadd_rn(1.f, -t.wx), t.wx};
+        float const wwy[2] = {__fadd_rn(1.f, -t.wy), t.wy};
+        bool ok[2][2];
+        int idx[2][2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int ii = 0; ii < 2; ++ii) {
+            int const ssy = t.sy + ii, ssx = t.sx + j;
+            ok[j][ii] = t.inside && ssy < H && ssx < W;
+            idx[j][ii] = ok[j][ii] ? ssy + ssx * H : 0;
+          }
+        float const* xz = x + imgOff;
+        float const* dz = dy + q + (size_t)Q * C * (size_t)n;
+        float accGy = 0.f, accGx = 0.f;
+        for (int c = 0; c < C; ++c) {
+          float const d = dz[0];
+          float dgx = 0.f, dgy = 0.f;
+#pragma unroll
+          for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int ii = 0; ii < 2; ++ii)
+              if (ok[j][ii]) {
+                float const xv = __ldg(xz + idx[j][ii]);
+                float const sj = j ? 1.f : -1.f, si = ii ? 1.f : -1.f;
+                dgx = __fadd_rn(dgx, __fmul_rn(__fmul_rn(__fmul_rn(sj, wwy[ii]), d), xv));
+                dgy = __fadd_rn(dgy, __fmul_rn(__fmul_rn(__fmul_rn(si, wwx[j]), d), xv));
+              }
+          accGy = __fadd_rn(accGy, __fmul_rn(__fmul_rn(0.5f, (float)(H - 1)), dgy));
+          accGx = __fadd_rn(accGx, __fmul_rn(__fmul_rn(0.5f, (float)(W - 1)), dgx));
+          xz += HW; dz += Q;
+        }
+        reinterpret_cast<float2*>(dgrid)[(size_t)Q * n + q] = make_float2(accGy, accGx);
+      }
+    }
+    __syncthreads();       // the lists are rebuilt for the next grid
+  }
+}
+
 int validate(vlb_ctx* ctx, int H, int W, int C, int N, int Ho, int Wo, int Ng)
 {
   VLB_REQUIRE(ctx, H > 0 && W > 0 && C > 0 && N > 0 && Ho > 0 && Wo > 0 && Ng > 0, "bilinearsampler: empty tensor");
@@ -151,6 +354,36 @@ int vlb_sampler_backward(vlb_ctx* ctx, float* dX, float* dGrid, float const* X, 
   VLB_REQUIRE(ctx, !dGrid || X, "sampler_backward: the grid derivative needs the input");
   VLB_REQUIRE(ctx, ((((uintptr_t)grid) | ((uintptr_t)dGrid)) & 7) == 0, "sampler_backward: grid must be 8-byte aligned");
   if (!dX && !dGrid) return VLB_Success;
+  int const Qo = Ho * Wo, HWi = H * W;
+  if (dX && Qo <= 65535 && gather_smem(HWi, Qo) <= 200 * 1024) {
+    // gather: one CTA per image; with fewer images than SMs the channels are shared out among several CTAs per image,
+    // and the grid derivative (which runs over all channels of an output pixel in order) is left to the other kernel
+    int chunks = 1;
+    if (N < ctx->smCount) chunks = vlb::ceil_div(ctx->smCount, N);
+    int CH = vlb::ceil_div(C, chunks);
+    CH = vlb::ceil_div(CH, kChan) * kChan;
+    chunks = vlb::ceil_div(C, CH);
+    bool const fusedGrid = dGrid != nullptr && chunks == 1;
+    static bool attrDone[64] = {};
+    if (!(ctx->device < 64 && attrDone[ctx->device])) {
+      cudaError_t ea = cudaFuncSetAttribute(sampler_bwd_gather_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+      if (ea == cudaSuccess) ea = cudaFuncSetAttribute(sampler_bwd_gather_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+      if (ea != cudaSuccess) { cudaGetLastError(); return vlb::set_error(ctx, VLB_Cuda, cudaGetErrorString(ea)); }
+      if (ctx->device < 64) attrDone[ctx->device] = true;
+    }
+    size_t const smem = gather_smem(HWi, Qo);
+    unsigned const blocks = (unsigned)(N * chunks);
+    if (fusedGrid) sampler_bwd_gather_kernel<true><<<blocks, kGatherThreads, smem, ctx->stream>>>(dX, dGrid, X, grid, dY, H, W, C, N, Qo, Ng, chunks, CH);
+    else           sampler_bwd_gather_kernel<false><<<blocks, kGatherThreads, smem, ctx->stream>>>(dX, nullptr, X, grid, dY, H, W, C, N, Qo, Ng, chunks, CH);
+    VLB_LAUNCHED(ctx, 1);
+    if (dGrid && !fusedGrid) {
+      size_t total = (size_t)Qo * Ng;
+      sampler_kernel<1><<<vlb::grid_for(total, kThreads, ctx->smCount * 32), kThreads, 0, ctx->stream>>>(
+          nullptr, nullptr, dGrid, X, grid, dY, H, W, C, N, Qo, Ng);
+      VLB_LAUNCHED(ctx, 1);
+    }
+    return vlb::check_launch(ctx, "vlb_sampler_backward");
+  }
   if (dX) {
     cudaError_t e = cudaMemsetAsync(dX, 0, sizeof(float) * (size_t)H * W * C * N, ctx->stream);
     if (e != cudaSuccess) return vlb::set_error(ctx, VLB_Cuda, cudaGetErrorString(e));

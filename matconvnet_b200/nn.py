@@ -75,13 +75,26 @@ def _is_fc(d, Ho, Wo):
             and d.FH == d.H and d.FW == d.W)
 
 
+def _der_out(given, shape, device, name):
+    """A caller-supplied output for a parameter derivative (e.g. a view into a gradient bucket), checked, else a new one."""
+    if given is None:
+        return mat.empty(shape, device)
+    if not (isinstance(given, torch.Tensor) and given.is_cuda and given.dtype == torch.float32 and mat.is_mat(given)
+            and given.numel() == int(np.prod(shape)) and given.data_ptr() % 16 == 0):
+        raise ValueError("%s: the supplied output must be a dense 16-byte aligned CUDA float32 tensor of %d elements"
+                         % (name, int(np.prod(shape))))
+    return given
+
+
 def vl_nnconv(x, f, b, dzdy=None, stride=1, pad=0, dilate=1, no_der_data=False, no_der_filters=False,
-              no_der_biases=False, relu=False, through_relu=False, ctx=None):
+              no_der_biases=False, relu=False, through_relu=False, der_out=None, ctx=None):
     """Y = VL_NNCONV(X, F, B) / [DX, DF, DB] = VL_NNCONV(X, F, B, DZDY) (matlab/vl_nnconv.m;
     gateway matlab/src/vl_nnconv.cu:87-503).  B may be None.  Empty F (the subsampling mode of
     the reference) is not part of this engine.  relu=True (forward only) returns max(Y, 0) from the same kernels,
     bit-identical to vl_nnrelu(vl_nnconv(...)).  through_relu=True (backward only) is for an X that is the output of a
-    ReLU: DX is then the derivative with respect to that ReLU's input, bit-identical to vl_nnrelu(X, DX)."""
+    ReLU: DX is then the derivative with respect to that ReLU's input, bit-identical to vl_nnrelu(X, DX).
+    der_out=(DF, DB) (backward only; either may be None) makes the kernels write the parameter derivatives into tensors the
+    caller owns -- views into a gradient-exchange bucket -- instead of new ones; they are returned as DF, DB."""
     ctx = _ctx(ctx)
     x, f, b, dzdy = _need(x, "x"), _need(f, "f"), _need(b, "b"), _need(dzdy, "dzdy")
     if f is None or f.numel() == 0:
@@ -107,8 +120,9 @@ def vl_nnconv(x, f, b, dzdy=None, stride=1, pad=0, dilate=1, no_der_data=False, 
     if mat.shape4(dzdy) != (Ho, Wo, d.K, d.N):
         raise ValueError("DEROUTPUT dimensions are incompatible with X and FILTERS.")
     dx = None if no_der_data else mat.empty(mat.shape4(x), x.device)
-    df = None if no_der_filters else mat.empty(mat.shape4(f), x.device)
-    db = None if (no_der_biases or b is None) else mat.empty((1, d.K), x.device)
+    gdf, gdb = der_out if der_out is not None else (None, None)
+    df = None if no_der_filters else _der_out(gdf, mat.shape4(f), x.device, "DF")
+    db = None if (no_der_biases or b is None) else _der_out(gdb, (1, d.K), x.device, "DB")
     fn = lib.vlb_relu_conv_backward if through_relu else (lib.vlb_fc_backward if fc else lib.vlb_conv_backward)
     ctx.check(fn(ctx.handle, mat.ptr(dx), mat.ptr(df), mat.ptr(db), mat.ptr(x), mat.ptr(f), mat.ptr(dzdy),
                  C.byref(d)))
@@ -150,7 +164,7 @@ def vl_nnconvt(x, f, b, dzdy=None, upsample=1, crop=0, num_groups=1, no_der_data
 
 
 # --------------------------------------------------------------------- vl_nnbnorm
-def vl_nnbnorm(x, g, b, dzdy=None, epsilon=1e-4, moments=None, ctx=None):
+def vl_nnbnorm(x, g, b, dzdy=None, epsilon=1e-4, moments=None, der_out=None, ctx=None):
     """[Y, MOMENTS] = VL_NNBNORM(X, G, B) / [DX, DG, DB, MOMENTS] = VL_NNBNORM(X, G, B, DZDY)
     (matlab/vl_nnbnorm.m; gateway matlab/src/vl_nnbnorm.cu:73-302).  MOMENTS is C x 2:
     [mean, sigma] with sigma = sqrt(var + epsilon)."""
@@ -176,8 +190,9 @@ def vl_nnbnorm(x, g, b, dzdy=None, epsilon=1e-4, moments=None, ctx=None):
     if mat.shape4(dzdy) != (H, W, Cc, N):
         raise ValueError("DZDY dimensions are incompatible with X.")
     dx = mat.empty((H, W, Cc, N), x.device)
-    dg = mat.empty((Cc, 1), x.device)
-    db = mat.empty((Cc, 1), x.device)
+    gdg, gdb = der_out if der_out is not None else (None, None)     # caller-owned outputs, as in vl_nnconv
+    dg = _der_out(gdg, (Cc, 1), x.device, "DG")
+    db = _der_out(gdb, (Cc, 1), x.device, "DB")
     fn = lib.vlb_bnorm_backward_moment if given else lib.vlb_bnorm_backward
     ctx.check(fn(ctx.handle, mat.ptr(dx), mat.ptr(dg), mat.ptr(db), mat.ptr(mom), mat.ptr(x), mat.ptr(g),
                  mat.ptr(b), mat.ptr(dzdy), H, W, Cc, N, float(epsilon)))

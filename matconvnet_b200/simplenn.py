@@ -10,9 +10,29 @@ vl_simplenn.m:294-398) and, when dzdy is given, the backward pass in reverse ord
 As in the reference, each layer's parameter derivatives are handed to the gradient exchange
 as soon as they exist (vl_simplenn.m:504-509): ``on_dzdw(i, j, tensor)`` is called right
 after layer i's backward, which is what lets the all-reduce overlap the remaining layers.
+``grad_out`` maps (i, j) to a tensor the derivative of parameter j of layer i is written into (views
+into the gradient exchange's buckets, ``dataparallel.GradientExchange.plan``) instead of a new one.
 Every block is a call into the C ABI; nothing is computed on the host.
 """
 from . import nn
+
+
+def grad_name(i, j):
+    """The name under which the derivative of parameter j of layer i is handed to the gradient exchange."""
+    return "l%d_%d" % (i, j)
+
+
+def gradient_specs(net):
+    """[(name, MATLAB shape)] of the parameter derivatives of conv and bnorm layers in the order the backward pass
+    produces them (last layer first, filters before biases): the input of GradientExchange.plan."""
+    specs = []
+    for i in range(len(net["layers"]) - 1, -1, -1):
+        l = net["layers"][i]
+        if l["type"] in ("conv", "bnorm"):
+            for j, w in enumerate(l["weights"][:2]):
+                if w is not None:
+                    specs.append((grad_name(i, j), tuple(int(v) for v in w.shape)))
+    return specs
 
 
 def _get(l, key, default):
@@ -20,7 +40,7 @@ def _get(l, key, default):
 
 
 def vl_simplenn(net, x, dzdy=None, res=None, on_dzdw=None, ctx=None, skip_forward=False,
-                back_prop_depth=None, conserve_memory=False, fuse_relu=False):
+                back_prop_depth=None, conserve_memory=False, fuse_relu=False, grad_out=None):
     layers = net["layers"]
     n = len(layers)
     if res is None:
@@ -60,6 +80,7 @@ def vl_simplenn(net, x, dzdy=None, res=None, on_dzdw=None, ctx=None, skip_forwar
     if dzdy is None:
         return res
     res[n]["dzdx"] = dzdy
+    grad_out = grad_out or {}
     first = 0 if back_prop_depth is None else max(0, n - back_prop_depth)
     masked = False
     for i in range(n - 1, first - 1, -1):
@@ -72,7 +93,8 @@ def vl_simplenn(net, x, dzdy=None, res=None, on_dzdw=None, ctx=None, skip_forwar
         through = fuse_relu and t in ("conv", "pool") and i - 1 >= first and layers[i - 1]["type"] == "relu"
         if t == "conv":
             dx, df, db = nn.vl_nnconv(xi, l["weights"][0], l["weights"][1], d, stride=_get(l, "stride", 1),
-                                      pad=_get(l, "pad", 0), dilate=_get(l, "dilate", 1), through_relu=through, ctx=ctx)
+                                      pad=_get(l, "pad", 0), dilate=_get(l, "dilate", 1), through_relu=through,
+                                      der_out=(grad_out.get((i, 0)), grad_out.get((i, 1))), ctx=ctx)
             res[i]["dzdw"] = [df, db]
             res[i]["dzdx"], res[i - 1 if through else i]["dzdx"] = None, dx
         elif t == "relu":
@@ -87,8 +109,8 @@ def vl_simplenn(net, x, dzdy=None, res=None, on_dzdw=None, ctx=None, skip_forwar
                               method=_get(l, "method", "max"), through_relu=through, ctx=ctx)
             res[i]["dzdx"], res[i - 1 if through else i]["dzdx"] = None, dx
         elif t == "bnorm":
-            dx, dg, db, mom = nn.vl_nnbnorm(xi, l["weights"][0], l["weights"][1], d,
-                                            epsilon=_get(l, "epsilon", 1e-4), ctx=ctx)
+            dx, dg, db, mom = nn.vl_nnbnorm(xi, l["weights"][0], l["weights"][1], d, epsilon=_get(l, "epsilon", 1e-4),
+                                            der_out=(grad_out.get((i, 0)), grad_out.get((i, 1))), ctx=ctx)
             res[i]["dzdx"], res[i]["dzdw"] = dx, [dg, db, mom]
         elif t == "softmaxloss":
             res[i]["dzdx"] = nn.vl_nnsoftmaxloss(xi, l["class"], d, ctx=ctx)

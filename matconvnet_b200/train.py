@@ -18,8 +18,10 @@ def default_params():
 
 
 def accumulate_gradients(net, res, state, params, num_workers=1, pulled=None, ctx=None):
-    """net, res as in vl_simplenn; pulled: {(l, j): tensor} of derivatives already summed over the workers (the result of
-    the gradient exchange), else res[l]['dzdw'][j] is used as it is (cnn_train.m:459-464)."""
+    """net, res as in vl_simplenn; pulled: {(l, j): tensor} of derivatives SUMMED over the workers -- what
+    GradientExchange.pull_all() returns by default and ParameterServer.pull returns in the reference -- else
+    res[l]['dzdw'][j] is used as it is (cnn_train.m:459-464).  This function is the one place that divides by
+    num_workers (cnn_train.m:455,482), so an exchange built with average=True must not be combined with num_workers > 1."""
     layers = net["layers"]
     for l in range(len(layers) - 1, -1, -1):
         dzdw = res[l]["dzdw"]

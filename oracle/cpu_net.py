@@ -19,11 +19,21 @@ def _quad(v):
     return (int(v[0]),) * 4 if v.size == 1 else tuple(int(i) for i in v)
 
 
+def _is_fc(l, xi):
+    """The gateway's test for the fully connected shortcut (matlab/src/vl_nnconv.cu:351-361): the filters cover the
+    whole input, no padding, unit stride and dilation, one filter group."""
+    f = l["weights"][0]
+    return (tuple(f.shape[:3]) == tuple(xi.shape[:3]) and _pair(l.get("stride", 1)) == (1, 1)
+            and _quad(l.get("pad", 0)) == (0, 0, 0, 0) and _pair(l.get("dilate", 1)) == (1, 1))
+
+
 def layer_forward(backend, glue, l, xi):
     """Output of one layer on input xi."""
     t = l["type"]
     if t == "conv":
         bias = None if l["weights"][1] is None else np.asarray(l["weights"][1]).ravel()
+        if _is_fc(l, xi):
+            return backend.fc_forward(xi, l["weights"][0], bias)
         return backend.conv_forward(xi, l["weights"][0], bias, _pair(l.get("stride", 1)), _quad(l.get("pad", 0)),
                                     _pair(l.get("dilate", 1)))
     if t == "relu":
@@ -41,6 +51,9 @@ def layer_forward(backend, glue, l, xi):
 def layer_backward(backend, glue, l, xi, d):
     """(dzdx, dzdw or None) of one layer from its input xi and the derivative d of its output."""
     t = l["type"]
+    if t == "conv" and _is_fc(l, xi):
+        dx, df, db = backend.fc_backward(xi, l["weights"][0], d)
+        return dx, [df, db if l["weights"][1] is not None else None]
     if t == "conv":
         dx, df, db = backend.conv_backward(xi, l["weights"][0], d, _pair(l.get("stride", 1)), _quad(l.get("pad", 0)),
                                            _pair(l.get("dilate", 1)))

@@ -738,7 +738,8 @@ static int FN(relu_backward)(T* dx, T const* x, T const* dy, size_t n)
 { for (size_t i = 0; i < n; ++i) dx[i] = x[i] > (T)0 ? dy[i] : (T)0; return 0; }
 
 /* matlab/vl_nnsoftmaxloss.m:56-84.  x is H x W x C x N, labels c is one class
- * (1-based) per image, broadcast over pixels (:45-52).  Forward returns the
+ * (1-based) per image, broadcast over pixels (:45-52); class 0 skips the image:
+ * mass = (c > 0), index max(c - 1, 0) (:55-67).  Forward returns the
  * scalar sum over pixels and images of (xmax + log sum exp(x - xmax) - x_c),
  * divided by N (:72-77,:84).  Backward: dx = dzdy/N * (softmax - onehot). */
 static int FN(softmaxloss_forward)(T* loss, T const* x, T const* labels, int H, int W, int C, int N)
@@ -752,8 +753,11 @@ static int FN(softmaxloss_forward)(T* loss, T const* x, T const* labels, int H, 
       for (int c = 1; c < C; ++c) if (xp[P * c] > xmax) xmax = xp[P * c];
       T se = 0;
       for (int c = 0; c < C; ++c) se += (T)exp(xp[P * c] - xmax);
+      T mass = labels[n] > (T)0 ? (T)1 : (T)0;
       int lab = (int)labels[n] - 1;
-      total += xmax + (T)log(se) - xp[P * lab];
+      if (lab < 0) lab = 0;
+      if (lab >= C) return 1;      /* an indexing error in the reference */
+      total += mass * (xmax + (T)log(se) - xp[P * lab]);
     }
   *loss = total / (T)N;
   return 0;
@@ -771,11 +775,14 @@ static int FN(softmaxloss_backward)(T* dx, T const* x, T const* labels, T dzdy, 
       for (int c = 1; c < C; ++c) if (xp[P * c] > xmax) xmax = xp[P * c];
       T se = 0;
       for (int c = 0; c < C; ++c) se += (T)exp(xp[P * c] - xmax);
+      T mass = labels[n] > (T)0 ? (T)1 : (T)0;
       int lab = (int)labels[n] - 1;
+      if (lab < 0) lab = 0;
+      if (lab >= C) return 1;      /* an indexing error in the reference */
       for (int c = 0; c < C; ++c) {
         T v = (T)exp(xp[P * c] - xmax) / se;
         if (c == lab) v -= (T)1;
-        dp[P * c] = v * scale;
+        dp[P * c] = v * (mass * scale);
       }
     }
   return 0;

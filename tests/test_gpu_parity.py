@@ -160,6 +160,30 @@ def test_relu_and_loss(gpu, oracle):
         assert abs(loss - ref) <= 1e-5 * abs(ref)
         dx = nn.vl_nnsoftmaxloss(xd, labd, 1.0)
         assert rel_l2(mat.to_numpy(dx), oracle.softmaxloss_backward(x.astype(np.float64), lab.astype(np.float64), 1.0)) < TOL_FAITHFUL
+    # class 0 skips an image, first image included (matlab/vl_nnsoftmaxloss.m:55-67)
+    x = np.asfortranarray((rng.standard_normal((2, 2, 7, 5)) * 3).astype(np.float32))
+    lab = np.array([0, 3, 7, 0, 1], np.float32)
+    xd, labd = _up(mat, x, lab)
+    loss = float(nn.vl_nnsoftmaxloss(xd, labd).cpu()[0])
+    ref = float(oracle.softmaxloss_forward(x.astype(np.float64), lab.astype(np.float64)))
+    assert abs(loss - ref) <= 1e-5 * abs(ref)
+    dx = mat.to_numpy(nn.vl_nnsoftmaxloss(xd, labd, 0.5))
+    assert rel_l2(dx, oracle.softmaxloss_backward(x.astype(np.float64), lab.astype(np.float64), 0.5)) < TOL_FAITHFUL
+    assert np.all(dx[:, :, :, 0] == 0) and np.all(dx[:, :, :, 3] == 0)
+
+
+def test_softmaxloss_label_above_the_class_count_is_reported(gpu):
+    """An indexing error in the reference (x(c_) out of range); here the image is skipped, nothing is read out of range,
+    and the context's status word makes the next vlb_ctx_device_status return VLE_IllegalArgument."""
+    from matconvnet_b200 import capi
+    nn, mat, ctx = gpu
+    x = mat.from_numpy(np.zeros((1, 1, 4, 3), np.float32))
+    lab = mat.from_numpy(np.array([1, 9, 2], np.float32))
+    nn.vl_nnsoftmaxloss(x, lab)
+    with pytest.raises(capi.VlbError) as err:
+        ctx.device_status()
+    assert err.value.code == capi.ERROR_NAMES.index("VLE_IllegalArgument")
+    assert ctx.device_status() == 0          # the word was cleared
 
 
 # ------------------------------------------------------------------ ROI pooling
@@ -177,14 +201,11 @@ def test_roipool_golden(gpu):
         assert bit_equal(mat.to_numpy(y), g[key + ".y"]), key
         (dyi,) = _up(mat, g[key + ".dyi"])
         dxi = nn.vl_nnroipool(x, rois, dyi, subdivisions=sub, transform=tf, method=method)
-        if method == "max":
-            # integer gradients: sums are exact whatever the order of the atomics => routing is bit-exact
-            assert bit_equal(mat.to_numpy(dxi), g[key + ".dxi"]), key
-        else:
-            assert rel_l2(mat.to_numpy(dxi), g[key + ".dxi"]) < 1e-6, key
+        # the backward pass gathers in the CPU loop's order (ROI, bin column, bin row): bit for bit, integer-valued or not
+        assert bit_equal(mat.to_numpy(dxi), g[key + ".dxi"]), key
         (dy,) = _up(mat, g[key + ".dy"])
         dx = nn.vl_nnroipool(x, rois, dy, subdivisions=sub, transform=tf, method=method)
-        assert rel_l2(mat.to_numpy(dx), g[key + ".dx"]) < 1e-6, key
+        assert bit_equal(mat.to_numpy(dx), g[key + ".dx"]), key
 
 
 def test_roipool_bins_bit_exact(gpu, oracle):
@@ -253,3 +274,66 @@ def test_sampler_affine_vs_oracle(gpu, oracle):
     dxr, dgr = oracle.sampler_backward(x, grid, dy)
     assert bit_equal(mat.to_numpy(dgrid), dgr)
     assert rel_l2(mat.to_numpy(dx), dxr) < 1e-6
+
+
+def test_sampler_backward_gather_paths(gpu, oracle):
+    """The data gradient's three routes against the checker: the shared-memory gather with the channels of an image
+    shared out among several CTAs (few images; channel count not a multiple of the inner block; two grids per image) --
+    bit for bit, real-valued derivatives; a grid that piles every tap on a few input pixels (lists too long: atomic
+    scatter inside the gather kernel); planes too large for the lists (the scatter kernel).  The last two with
+    integer-valued derivatives, whose sums are exact in any order."""
+    import torch
+    nn, mat, _ = gpu
+    rng = np.random.default_rng(17)
+    # 1: gather, chunked channels, grouped grids
+    H, W, C, N, Ng, Ho, Wo = 12, 20, 13, 3, 6, 16, 8
+    x = np.asfortranarray(rng.standard_normal((H, W, C, N)).astype(np.float32))
+    grid = np.asfortranarray(rng.uniform(-1.1, 1.1, (2, Ho, Wo, Ng)).astype(np.float32))
+    dy = np.asfortranarray(rng.standard_normal((Ho, Wo, C, Ng)).astype(np.float32))
+    xd, gd, dyd = _up(mat, x, grid, dy)
+    dx, dgrid = nn.vl_nnbilinearsampler(xd, gd, dyd)
+    dxr, dgr = oracle.sampler_backward(x, grid, dy)
+    assert bit_equal(mat.to_numpy(dx), dxr) and bit_equal(mat.to_numpy(dgrid), dgr)
+    dx2, _ = nn.vl_nnbilinearsampler(xd, gd, dyd)
+    assert torch.equal(dx, dx2)
+    # 2: every output pixel samples around one point
+    grid2 = np.asfortranarray((0.013 * rng.standard_normal((2, Ho, Wo, Ng)) + 0.2).astype(np.float32))
+    dyi = np.asfortranarray(rng.integers(-3, 4, (Ho, Wo, C, Ng)).astype(np.float32))
+    x1 = np.ones_like(x)
+    dx, dgrid = nn.vl_nnbilinearsampler(*_up(mat, x1, grid2, dyi))
+    dxr, dgr = oracle.sampler_backward(x1, grid2, dyi)
+    assert rel_l2(mat.to_numpy(dx), dxr) < 1e-6 and bit_equal(mat.to_numpy(dgrid), dgr)
+    # 3: planes of 150 x 150
+    x3 = np.asfortranarray(rng.standard_normal((150, 150, 2, 1)).astype(np.float32))
+    grid3 = np.asfortranarray(rng.uniform(-1, 1, (2, 150, 150, 1)).astype(np.float32))
+    dy3 = np.asfortranarray(rng.integers(-3, 4, (150, 150, 2, 1)).astype(np.float32))
+    dx, dgrid = nn.vl_nnbilinearsampler(*_up(mat, x3, grid3, dy3))
+    dxr, dgr = oracle.sampler_backward(x3, grid3, dy3)
+    assert rel_l2(mat.to_numpy(dx), dxr) < 1e-6 and bit_equal(mat.to_numpy(dgrid), dgr)
+
+
+def test_roipool_backward_batches_and_fallback(gpu, oracle):
+    """ROI pooling backward beyond one shared-memory batch (many ROIs on one image, processed in several batches with the
+    partial sums carried in dX), with an image that no ROI names (its slab is zero), and on a map too large for a slab
+    (atomic scatter, integer-valued derivatives)."""
+    nn, mat, _ = gpu
+    rng = np.random.default_rng(18)
+    H, W, C, N, K = 20, 30, 24, 3, 3000
+    x = np.asfortranarray(rng.standard_normal((H, W, C, N)).astype(np.float32))
+    u1, v1 = rng.uniform(1, W - 2, K), rng.uniform(1, H - 2, K)
+    u2, v2 = np.minimum(u1 + rng.uniform(0, W, K), W), np.minimum(v1 + rng.uniform(0, H, K), H)
+    image = np.where(rng.uniform(size=K) < 0.9, 1, 3)            # image 2 has no ROI
+    rois = np.asfortranarray(np.stack([image, u1, v1, u2, v2]).astype(np.float32))
+    for method in ("max", "avg"):
+        y = oracle.roipool_forward(x, rois, (7, 7), 1.0, method)
+        dy = np.asfortranarray(rng.standard_normal(y.shape).astype(np.float32))
+        dx = nn.vl_nnroipool(*_up(mat, x, rois, dy), subdivisions=(7, 7), method=method)
+        want = oracle.roipool_backward(x, rois, dy, (7, 7), 1.0, method)
+        assert bit_equal(mat.to_numpy(dx), want), method
+        assert np.all(mat.to_numpy(dx)[:, :, :, 1] == 0)
+    xb = np.asfortranarray(rng.standard_normal((300, 260, 2, 1)).astype(np.float32))
+    rb = np.asfortranarray(np.array([[1, 5, 9, 200, 250], [1, 100, 50, 260, 300], [1, 1, 1, 20, 20]], np.float32).T)
+    yb = oracle.roipool_forward(xb, rb, (6, 5), 1.0, "max")
+    dyb = np.asfortranarray(rng.integers(-3, 4, yb.shape).astype(np.float32))
+    dxb = nn.vl_nnroipool(*_up(mat, xb, rb, dyb), subdivisions=(6, 5), method="max")
+    assert bit_equal(mat.to_numpy(dxb), oracle.roipool_backward(xb, rb, dyb, (6, 5), 1.0, "max"))

@@ -107,3 +107,59 @@ def test_accumulate_gradients_follows_the_trainer(gpu):
     par = res[0]["dzdw"][0].double() / workers + params["weight_decay"] * w0.double()
     m1 = params["momentum"] * m0.double() - par
     assert float((layers[0]["weights"][0].double() - (w0.double() + params["learning_rate"] * m1)).abs().max()) < 1e-6
+
+
+def test_exchanged_sums_are_normalised_exactly_once(gpu, monkeypatch):
+    """pull_all returns sums (ParameterServer.pull); accumulate_gradients divides by the number of workers
+    (cnn_train.m:455,482).  Four workers with identical shards -- the collective is faked as "multiply by four" -- must
+    therefore move the parameters exactly as one worker alone does.  The derivatives are written straight into the
+    exchange's buckets."""
+    import copy
+    import torch
+    import torch.distributed as dist
+    from matconvnet_b200 import dataparallel, models, simplenn, train
+    nn, mat, ctx = gpu
+    ctx.set_precision(0)
+    world = 4
+
+    class _Done:
+        def wait(self, *a):
+            return True
+
+    def fake_all_reduce(t, op=None, async_op=False):
+        assert op == dist.ReduceOp.SUM
+        t.mul_(world)
+        return _Done()
+
+    monkeypatch.setattr(dist, "all_reduce", fake_all_reduce)
+    g = torch.Generator(device="cuda").manual_seed(5)
+
+    def make():
+        rng = np.random.default_rng(9)
+        layers = [models._conv(rng, 3, 3, 3, 8, 1, 1), models._relu(), models._pool("max", 2, 2),
+                  models._conv(rng, 4, 4, 8, 5, 1, 0),
+                  {"type": "softmaxloss", "class": torch.tensor([1, 5, 2, 3, 4, 1], device="cuda").float()}]
+        return {"layers": layers}
+
+    x = mat.as_mat(torch.randn(8, 8, 3, 6, device="cuda", generator=g))
+    params = dict(learning_rate=0.05, weight_decay=0.001, momentum=0.9, nesterov_update=False)
+
+    alone = make()
+    res = simplenn.vl_simplenn(alone, x, 1.0, ctx=ctx)
+    train.accumulate_gradients(alone, res, {}, params, num_workers=1, ctx=ctx)
+
+    net = make()
+    ex = dataparallel.GradientExchange(world, bucket_bytes=1 << 12)
+    views = ex.plan(simplenn.gradient_specs(net), "cuda")
+    key = {simplenn.grad_name(i, j): (i, j) for i in range(len(net["layers"])) for j in range(2)}
+    grad_out = {key[n]: v for n, v in views.items()}
+    res = simplenn.vl_simplenn(net, x, 1.0, ctx=ctx, grad_out=grad_out,
+                               on_dzdw=lambda i, j, w: ex.push(simplenn.grad_name(i, j), w))
+    assert res[0]["dzdw"][0].data_ptr() == views[simplenn.grad_name(0, 0)].data_ptr()
+    torch.cuda.synchronize()
+    pulled = {key[n]: t for n, t in ex.pull_all().items()}
+    assert ex.collectives < len(pulled)                      # bucketed: fewer collectives than tensors
+    train.accumulate_gradients(net, res, {}, params, num_workers=world, pulled=pulled, ctx=ctx)
+    for la, lb in zip(alone["layers"], net["layers"]):
+        for wa, wb in zip(la.get("weights", []), lb.get("weights", [])):
+            assert float((wa.double() - wb.double()).abs().max()) < 1e-6

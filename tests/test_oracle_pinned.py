@@ -245,3 +245,24 @@ def test_numeric_derivatives(oracle):
     dl = oracle.softmaxloss_backward(xl, lab, 1.0)
     nd = _numder(lambda v: np.array(oracle.softmaxloss_forward(v, lab)), xl, np.array(1.0))
     assert np.allclose(dl, nd, atol=1e-4)
+
+
+def test_softmaxloss_class_zero_skips_the_image(oracle):
+    # matlab/vl_nnsoftmaxloss.m:55-67: mass = (c > 0), index max(c - 1, 0); a float64 closed form of those lines
+    rng = np.random.default_rng(16)
+    x = np.asfortranarray(rng.standard_normal((2, 3, 5, 4)) * 2)
+    lab = np.array([2.0, 0.0, 5.0, 0.0])
+    mass = (lab > 0).astype(np.float64)
+    idx = np.maximum(lab.astype(int) - 1, 0)
+    xmax = x.max(axis=2, keepdims=True)
+    ex = np.exp(x - xmax)
+    picked = np.stack([x[:, :, idx[n], n] for n in range(4)], axis=-1)
+    t = xmax[:, :, 0, :] + np.log(ex.sum(axis=2)) - picked
+    want = (t * mass).sum() / 4
+    assert abs(float(oracle.softmaxloss_forward(x, lab)) - want) < 1e-12
+    y = ex / ex.sum(axis=2, keepdims=True)
+    for n in range(4):
+        y[:, :, idx[n], n] -= 1
+    want_dx = y * mass[None, None, None, :] * 0.7 / 4
+    assert np.allclose(oracle.softmaxloss_backward(x, lab, 0.7), want_dx, atol=1e-13)
+    assert np.all(oracle.softmaxloss_backward(x, lab, 0.7)[:, :, :, 1] == 0)
