@@ -68,12 +68,16 @@ int vlb_ctx_set_wait_limit(vlb_ctx* ctx, long long cycles);
  * wait behind it runs out: the kernel records its status word, releases its tensor memory and returns
  * (vlb_ctx_device_status then gives VLE_Timeout; the output of that call is undefined).  Nothing traps or spins. */
 int vlb_ctx_set_test_switch(vlb_ctx* ctx, int switches);
-/* Measurement aid: between begin and end every tensor-core contraction launch is bracketed by CUDA
- * events on the context's stream.  end synchronises and returns the summed kernel time, the summed
+/* Measurement aid: between begin and end every tensor-core contraction (with the launches that prepare its operands
+ * and finish its result) is bracketed by CUDA events on the context's stream.  end synchronises and returns the summed kernel time, the summed
  * algorithmic flops (2*M*N*K of each contraction, counted once whatever the arithmetic mode) and the
  * number of launches.  (The reference times whole layers with tic/toc, matlab/simplenn/vl_simplenn.m:297,397.) */
 int vlb_ctx_profile_begin(vlb_ctx* ctx);
 int vlb_ctx_profile_end(vlb_ctx* ctx, double* ms, double* flops, long long* launches);
+/* After vlb_ctx_profile_end: the same three sums for one kind of contraction -- 0 convolution forward, 1 convolution data
+ * gradient, 2 convolution filter gradient (its operand tile images, bias gradient and split-reduction pass included),
+ * 3 fully connected (all three passes). */
+int vlb_ctx_profile_kind(vlb_ctx* ctx, int kind, double* ms, double* flops, long long* count);
 char const* vlb_error_message(int code);         /* vl::getErrorMessage, bits/data.cu:83-100 (all 13 codes named) */
 int vlb_version(void);
 
@@ -258,6 +262,20 @@ int vlb_taccum(vlb_ctx* ctx, float* Y, double alpha, float const* A, double beta
  * is only read.  Bit-identical to the four vlb_taccum calls. */
 int vlb_sgd_update(vlb_ctx* ctx, float* W, float* M, float const* G, size_t n, double gradMult, double decay,
                    double momentum, double lr, int nesterov);
+
+/* The trainer's other solvers after the gradient exchange (examples/+solver/adagrad.m, adadelta.m, adam.m, rmsprop.m, called
+ * at examples/cnn_train.m:503-507), each fused with the pass before it: g = gradMult*G + decay*W (cnn_train.m:481-483), then
+ * the solver's element-wise update of W and of its state, every MATLAB operation rounded to single as MATLAB does.
+ *   adagrad:  S1 = S1*rho + g^2;                 W -= lr*g / (sqrt(S1) + epsilon)
+ *   rmsprop:  S1 = S1*rho + g^2*(1-rho);         W -= lr*g / (sqrt(S1) + epsilon)
+ *   adadelta: S1 = S1*rho + g^2*(1-rho);  d = -sqrt((S2+epsilon)/(S1+epsilon))*g;  S2 = S2*rho + d^2*(1-rho);  W += d
+ *   adam:     S1 = beta1*S1 + (1-beta1)*g;  S2 = beta2*S2 + (1-beta2)*g^2;  W -= lr*sqrt(1-beta2^t)/(1-beta1^t) * S1/(sqrt(S2)+epsilon)
+ * S1, S2: state tensors of n floats, zero before the first step (S2 only for adadelta and adam); t: adam's step count
+ * after this step (1 on the first).  W, S1, S2 are updated in place, G is only read. */
+enum { VLB_SOLVER_ADAGRAD = 0, VLB_SOLVER_ADADELTA = 1, VLB_SOLVER_ADAM = 2, VLB_SOLVER_RMSPROP = 3 };
+typedef struct { double rho, epsilon, beta1, beta2; } vlb_solver_opts;
+int vlb_solver_update(vlb_ctx* ctx, int solver, float* W, float* S1, float* S2, float const* G, size_t n, double gradMult,
+                      double decay, double lr, vlb_solver_opts const* opts, long long t);
 
 #ifdef __cplusplus
 }

@@ -1,7 +1,10 @@
 """Per-layer timing of the hot-path kernels through the C ABI.
 
-    python -m matconvnet_b200.layerbench [--net vgg16] [--batch 64] [--precision 3xtf32] [--layers conv3_1,fc6]
-    python -m matconvnet_b200.layerbench --kind bnorm|pool|roipool|sampler
+    python layerbench.py [--net vgg16] [--batch 64] [--precision 3xtf32] [--layers conv3_1,fc6]
+    python layerbench.py --kind bnorm|pool|roipool|sampler|update
+
+A measuring tool beside bench.py (which imports its bandwidth rows for the bench line's `kernels` list); not part of
+the library.
 
 Each row is one block of the network at the given batch: forward, data-gradient and
 filter-gradient times from CUDA events on the launching stream (median of --iters after warm-up, the
@@ -10,11 +13,14 @@ L2 flushed between iterations by writing a 256 MB buffer), and the algorithmic r
 """
 import argparse
 import json
+import os
+import sys
 
 import numpy as np
 import torch
 
-from . import mat, nn
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from matconvnet_b200 import mat, nn  # noqa: E402
 
 VGG = [("conv1_1", 224, 3, 64, 3, 1), ("conv1_2", 224, 64, 64, 3, 1), ("conv2_1", 112, 64, 128, 3, 1),
        ("conv2_2", 112, 128, 128, 3, 1), ("conv3_1", 56, 128, 256, 3, 1), ("conv3_2", 56, 256, 256, 3, 1),
@@ -114,15 +120,27 @@ def bandwidth_rows(kind, iters, flush):
         t_f = timed(lambda: nn.vl_nnroipool(x, rois, subdivisions=(7, 7)), iters, flush)
         t_b = timed(lambda: nn.vl_nnroipool(x, rois, dy, subdivisions=(7, 7)), iters, flush)
         nbytes = 4.0 * (2 * x.numel() + y.numel())
-        rows.append({"block": "roipool 38x50x512x2, 256 rois, 7x7", "fwd_ms": t_f, "bwd_ms": t_b, "bwd_GBs": nbytes / t_b / 1e6})
+        rows.append({"block": "roipool 38x50x512x2, 256 rois, 7x7", "fwd_ms": t_f, "bwd_ms": t_b, "bwd_bytes": nbytes,
+                     "bwd_GBs": nbytes / t_b / 1e6})
     elif kind == "sampler":
-        x = mat.as_mat(torch.randn(64, 64, 32, 256, device="cuda"))
-        grid = mat.as_mat(torch.rand(2, 64, 64, 256, device="cuda") * 2 - 1)
-        dy = mat.as_mat(torch.randn(64, 64, 32, 256, device="cuda"))
+        # 256 affine grids of small rotations and scales (matlab/+dagnn/AffineGridGenerator.m:36-57): grid = [yy xx] * A + t
+        g = torch.Generator(device="cuda").manual_seed(0)
+        x = mat.as_mat(torch.randn(64, 64, 32, 256, device="cuda", generator=g))
+        lin = torch.linspace(-1, 1, 64, device="cuda")
+        yy = lin.view(64, 1, 1).expand(64, 64, 256)           # (ho, wo, n): row coordinate
+        xx = lin.view(1, 64, 1).expand(64, 64, 256)
+        th = (torch.rand(256, device="cuda", generator=g) - 0.5) * 0.4
+        sc = 0.8 + 0.4 * torch.rand(256, device="cuda", generator=g)
+        t = (torch.rand(2, 256, device="cuda", generator=g) - 0.5) * 0.2
+        gy = sc * (torch.cos(th) * yy + torch.sin(th) * xx) + t[0]
+        gx = sc * (-torch.sin(th) * yy + torch.cos(th) * xx) + t[1]
+        grid = mat.as_mat(torch.stack([gy, gx]))
+        dy = mat.as_mat(torch.randn(64, 64, 32, 256, device="cuda", generator=g))
         t_f = timed(lambda: nn.vl_nnbilinearsampler(x, grid), iters, flush)
         t_b = timed(lambda: nn.vl_nnbilinearsampler(x, grid, dy), iters, flush)
         nbytes = 4.0 * (3 * x.numel() + 2 * grid.numel())
-        rows.append({"block": "sampler 64x64x32x256", "fwd_ms": t_f, "bwd_ms": t_b, "bwd_GBs": nbytes / t_b / 1e6})
+        rows.append({"block": "sampler 64x64x32x256, 256 affine grids", "fwd_ms": t_f, "bwd_ms": t_b, "bwd_bytes": nbytes,
+                     "bwd_GBs": nbytes / t_b / 1e6})
     elif kind == "update":
         # the trainer's SGD step on VGG-16's largest parameter tensors (fc6 filters 102.8M, fc7 16.8M, conv5 2.4M floats):
         # the fused kernel (reads W, M, G; writes W, M) against the reference's four vl_taccum passes

@@ -37,6 +37,15 @@ class PoolDesc(C.Structure):
                                        "padTop", "padBottom", "padLeft", "padRight", "method")]
 
 
+class SolverOpts(C.Structure):
+    _fields_ = [(n, C.c_double) for n in ("rho", "epsilon", "beta1", "beta2")]
+
+
+SOLVERS = {"adagrad": 0, "adadelta": 1, "adam": 2, "rmsprop": 3}
+# the defaults each solver returns when called without arguments (examples/+solver/*.m)
+SOLVER_DEFAULTS = {"adagrad": dict(epsilon=1e-10, rho=1.0), "adadelta": dict(epsilon=1e-6, rho=0.9),
+                   "adam": dict(beta1=0.9, beta2=0.999, epsilon=1e-8), "rmsprop": dict(epsilon=1e-8, rho=0.99)}
+
 _P = C.c_void_p
 _I = C.c_int
 _D = C.c_double
@@ -63,6 +72,7 @@ SIGNATURES = {
     "vlb_ctx_set_test_switch": (_I, [_P, _I]),
     "vlb_ctx_profile_begin": (_I, [_P]),
     "vlb_ctx_profile_end": (_I, [_P, C.POINTER(_D), C.POINTER(_D), C.POINTER(C.c_longlong)]),
+    "vlb_ctx_profile_kind": (_I, [_P, _I, C.POINTER(_D), C.POINTER(_D), C.POINTER(C.c_longlong)]),
     "vlb_conv_output_shape": (_I, [C.POINTER(ConvDesc), C.POINTER(_I), C.POINTER(_I)]),
     "vlb_conv_forward": (_I, [_P, _P, _D, _P, _D, _P, _P, C.POINTER(ConvDesc)]),
     "vlb_conv_relu_forward": (_I, [_P, _P, _P, _P, _P, C.POINTER(ConvDesc)]),
@@ -97,6 +107,7 @@ SIGNATURES = {
     "vlb_scale": (_I, [_P, _P, _D, _Z]),
     "vlb_taccum": (_I, [_P, _P, _D, _P, _D, _P, _Z]),
     "vlb_sgd_update": (_I, [_P, _P, _P, _P, _Z, _D, _D, _D, _D, _I]),
+    "vlb_solver_update": (_I, [_P, _I, _P, _P, _P, _P, _Z, _D, _D, _D, C.POINTER(SolverOpts), C.c_longlong]),
 }
 
 _lib = None
@@ -179,6 +190,12 @@ class Context:
         """(milliseconds, algorithmic flops, launches) of the tensor-core kernels since profile_begin."""
         ms, fl, n = C.c_double(), C.c_double(), C.c_longlong()
         self.check(self.lib.vlb_ctx_profile_end(self.handle, C.byref(ms), C.byref(fl), C.byref(n)))
+        return ms.value, fl.value, n.value
+
+    def profile_kind(self, kind):
+        """(milliseconds, flops, count) of one kind of contraction in the last profile: 0 fprop, 1 dgrad, 2 wgrad, 3 fc."""
+        ms, fl, n = C.c_double(), C.c_double(), C.c_longlong()
+        self.check(self.lib.vlb_ctx_profile_kind(self.handle, int(kind), C.byref(ms), C.byref(fl), C.byref(n)))
         return ms.value, fl.value, n.value
 
     def last_error(self):

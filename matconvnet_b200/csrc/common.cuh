@@ -23,7 +23,10 @@ struct vlb_ctx {
   int* deviceStatus = nullptr;   // one word the tensor-core kernels set when a bounded wait expires; behind it (byte 256)
                                  // 4096 zeroed ticket counters for last-block-finishes reductions, left at zero by their users
   // optional timing of the tensor-core launches with events on the launching stream
-  struct ProfRec { cudaEvent_t start, stop; double flops; };
+  struct ProfRec { cudaEvent_t start, stop; double flops; int kind; };
+  int profDepth = 0;             // > 0: inside a bracket that spans several launches (vlb::ProfScope); the launches inside record nothing
+  double profKindMs[4] = {0, 0, 0, 0}, profKindFlops[4] = {0, 0, 0, 0};     // per kind, filled by vlb_ctx_profile_end
+  long long profKindCount[4] = {0, 0, 0, 0};
   // set by vlb_conv_relu_forward around its call of the forward convolution: the path that ran applies max(., 0) in its
   // epilogue and says so, otherwise the caller runs the ReLU kernel on the result
   bool fuseRelu = false, reluDone = false;
@@ -51,6 +54,30 @@ int pass_error(vlb_ctx* ctx, int code, char const* where);
 void* workspace(vlb_ctx* ctx, size_t bytes);
 // cudaPeekAtLastError after a launch, as the reference does (bits/datacu.cu:356-371).
 int check_launch(vlb_ctx* ctx, char const* where);
+
+// Kinds of tensor-core contraction the profile tells apart (vlb_ctx_profile_kind).
+enum { kProfFprop = 0, kProfDgrad = 1, kProfWgrad = 2, kProfFc = 3 };
+
+// While profiling, brackets everything a contraction enqueues -- operand tile images, the contraction, the reduction of
+// split partial results -- with one pair of events on the context's stream.  Records only when `flops` was set.
+struct ProfScope {
+  vlb_ctx* ctx;
+  vlb_ctx::ProfRec rec;
+  bool on;
+  ProfScope(vlb_ctx* c, int kind) : ctx(c), on(c->profiling && c->profDepth == 0)
+  {
+    rec.flops = 0; rec.kind = kind;
+    ++ctx->profDepth;
+    if (on) { cudaEventCreate(&rec.start); cudaEventCreate(&rec.stop); cudaEventRecord(rec.start, ctx->stream); }
+  }
+  ~ProfScope()
+  {
+    --ctx->profDepth;
+    if (!on) return;
+    if (rec.flops > 0) { cudaEventRecord(rec.stop, ctx->stream); ctx->prof.push_back(rec); }
+    else { cudaEventDestroy(rec.start); cudaEventDestroy(rec.stop); }
+  }
+};
 
 inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
 inline unsigned grid_for(size_t n, int threads, int maxBlocks = 148 * 16)

@@ -37,6 +37,8 @@
 namespace {
 
 using vlb::ConvGeom;
+using vlb::ProfScope;
+using vlb::kProfFprop; using vlb::kProfDgrad; using vlb::kProfWgrad; using vlb::kProfFc;
 
 constexpr int BM = 128;          // output rows per CTA (TMEM lanes)
 constexpr int BK = 32;           // reduction elements per stage (one 128-byte swizzle row)
@@ -1627,9 +1629,10 @@ int launch(vlb_ctx* ctx, Params& p, int splits, char const* where)
   if (grid.y > 65535u || grid.z > 65535u) return VLB_Unsupported;
   cudaError_t e;
   vlb_ctx::ProfRec rec;
-  if (ctx->profiling) {
+  bool const record = ctx->profiling && ctx->profDepth == 0;
+  if (record) {
     cudaEventCreate(&rec.start); cudaEventCreate(&rec.stop);
-    rec.flops = 2.0 * (double)p.M * (double)p.N * (double)p.R;
+    rec.flops = 2.0 * (double)p.M * (double)p.N * (double)p.R; rec.kind = -1;
     cudaEventRecord(rec.start, ctx->stream);
   }
   if (split3) {
@@ -1639,7 +1642,7 @@ int launch(vlb_ctx* ctx, Params& p, int splits, char const* where)
     e = allow_large_smem<tc_gemm_kernel<kAMode, kBMode, kEpi, false>>(ctx->device);
     if (e == cudaSuccess) tc_gemm_kernel<kAMode, kBMode, kEpi, false><<<grid, kThreads, smemBytes, ctx->stream>>>(p);
   }
-  if (ctx->profiling) { cudaEventRecord(rec.stop, ctx->stream); ctx->prof.push_back(rec); }
+  if (record) { cudaEventRecord(rec.stop, ctx->stream); ctx->prof.push_back(rec); }
   if (e != cudaSuccess) { cudaGetLastError(); return vlb::set_error(ctx, VLB_Cuda, cudaGetErrorString(e)); }
   VLB_LAUNCHED(ctx, 1);
   return vlb::check_launch(ctx, where);
@@ -1663,9 +1666,10 @@ int launch_ts(vlb_ctx* ctx, Params& p, char const* where)
   dim3 grid((unsigned)(persistent && numTiles > ctx->smCount ? ctx->smCount : numTiles), 1, 1);
   cudaError_t e;
   vlb_ctx::ProfRec rec;
-  if (ctx->profiling) {
+  bool const record = ctx->profiling && ctx->profDepth == 0;
+  if (record) {
     cudaEventCreate(&rec.start); cudaEventCreate(&rec.stop);
-    rec.flops = 2.0 * (double)p.M * (double)p.N * (double)p.R;
+    rec.flops = 2.0 * (double)p.M * (double)p.N * (double)p.R; rec.kind = -1;
     cudaEventRecord(rec.start, ctx->stream);
   }
   if (split3) {
@@ -1675,7 +1679,7 @@ int launch_ts(vlb_ctx* ctx, Params& p, char const* where)
     e = allow_large_smem<conv_ts_kernel<false>>(ctx->device);
     if (e == cudaSuccess) conv_ts_kernel<false><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p);
   }
-  if (ctx->profiling) { cudaEventRecord(rec.stop, ctx->stream); ctx->prof.push_back(rec); }
+  if (record) { cudaEventRecord(rec.stop, ctx->stream); ctx->prof.push_back(rec); }
   if (e != cudaSuccess) { cudaGetLastError(); return vlb::set_error(ctx, VLB_Cuda, cudaGetErrorString(e)); }
   VLB_LAUNCHED(ctx, 1);
   return vlb::check_launch(ctx, where);
@@ -1730,6 +1734,8 @@ int conv_fprop_tc(vlb_ctx* ctx, ConvGeom const& g, float* Y, float outMult, floa
   if (is_fc(g)) {
     // Y(K x N) = F'(K x V) X(V x N) + b 1'  (reference bits/nnfullyconnected.cu:45-70): rows = filters
     if (outMult != 0.f || inMult != 1.f) return VLB_Unsupported;
+    ProfScope prof(ctx, kProfFc);
+    prof.rec.flops = 2.0 * (double)g.K * (double)g.N * (double)V;
     p.M = g.K; p.N = g.N; p.R = V;
     p.a = Operand{}; p.a.ptr = F; p.a.ld = V; p.a.rows = g.K; p.a.vec = (V % 4 == 0) && aligned16(F);
     p.b = Operand{}; p.b.ptr = X; p.b.ld = V; p.b.rows = g.N; p.b.vec = (V % 4 == 0) && aligned16(X);
@@ -1757,6 +1763,8 @@ int conv_fprop_tc(vlb_ctx* ctx, ConvGeom const& g, float* Y, float outMult, floa
     return check_launch(ctx, "fc_fprop_tc");
   }
   long long M = (long long)g.Ho * g.Wo * g.N;
+  ProfScope prof(ctx, kProfFprop);
+  prof.rec.flops = 2.0 * (double)M * (double)g.K * (double)V;
   p.M = (int)M; p.N = g.K; p.R = V;
   conv_operand(p.a, g, X, g.C);
   p.a.rows = p.M;
@@ -1782,6 +1790,8 @@ int conv_dgrad_tc(vlb_ctx* ctx, ConvGeom const& g, float* dX, float const* F, fl
   if (is_fc(g)) {
     // dX(V x N) = F(V x K) dY(K x N)  (reference bits/nnfullyconnected.cu:139-151): rows = input elements
     int const V = g.FH * g.FW * g.FC;
+    ProfScope prof(ctx, kProfFc);
+    prof.rec.flops = 2.0 * (double)V * (double)g.N * (double)g.K;
     p.M = V; p.N = g.N; p.R = g.K;
     p.a = Operand{}; p.a.ptr = F; p.a.ld = V; p.a.rows = V; p.a.vec = (V % 4 == 0) && aligned16(F);
     p.b = Operand{}; p.b.ptr = dY; p.b.ld = g.K; p.b.rows = g.N; p.b.vec = (g.K % 4 == 0) && aligned16(dY);
@@ -1797,6 +1807,8 @@ int conv_dgrad_tc(vlb_ctx* ctx, ConvGeom const& g, float* dX, float const* F, fl
   t.pt = (g.FH - 1) * g.dy - g.pt; t.pl = (g.FW - 1) * g.dx - g.pl;
   long long M = (long long)g.H * g.W * g.N;
   int const V = g.FH * g.FW * g.K;
+  ProfScope prof(ctx, kProfDgrad);
+  prof.rec.flops = 2.0 * (double)M * (double)g.C * (double)V;
   p.M = (int)M; p.N = g.C; p.R = V;
   conv_operand(p.a, t, dY, g.K);
   p.a.rows = p.M;
@@ -1833,6 +1845,8 @@ int conv_wgrad_tc(vlb_ctx* ctx, ConvGeom const& g, float* dF, float* db, float c
   Params p = {};
   if (is_fc(g)) {
     // dF(V x K) = X(V x N) dY'(N x K)  (reference bits/nnfullyconnected.cu:126-137): reduction over the batch
+    ProfScope prof(ctx, kProfFc);
+    prof.rec.flops = 2.0 * (double)V * (double)g.K * (double)g.N;
     p.M = V; p.N = g.K; p.R = g.N;
     p.a = Operand{}; p.a.ptr = X; p.a.ld = V; p.a.rows = V; p.a.vec = (V % 4 == 0) && aligned16(X);
     p.b = Operand{}; p.b.ptr = dY; p.b.ld = g.K; p.b.rows = g.K; p.b.vec = (g.K % 4 == 0) && aligned16(dY);
@@ -1842,6 +1856,8 @@ int conv_wgrad_tc(vlb_ctx* ctx, ConvGeom const& g, float* dF, float* db, float c
     return launch<OP_DENSE_MN, OP_DENSE_MN, EPI_PLAIN>(ctx, p, 1, "fc_wgrad_tc");
   }
   long long R = (long long)g.Ho * g.Wo * g.N;
+  ProfScope prof(ctx, kProfWgrad);      // includes the dY tile images (with the bias gradient) and the sum of the split partial results
+  prof.rec.flops = 2.0 * (double)V * (double)g.K * (double)R;
   p.M = V; p.N = g.K; p.R = (int)R;
   conv_operand(p.a, g, X, g.C);
   p.a.rows = V;

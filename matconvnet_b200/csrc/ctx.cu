@@ -150,10 +150,12 @@ int vlb_ctx_profile_end(vlb_ctx* ctx, double* ms, double* flops, long long* laun
   ctx->profiling = false;
   cudaError_t e = cudaStreamSynchronize(ctx->stream);
   double tms = 0, tf = 0;
+  for (int k = 0; k < 4; ++k) { ctx->profKindMs[k] = 0; ctx->profKindFlops[k] = 0; ctx->profKindCount[k] = 0; }
   for (auto& r : ctx->prof) {
     float t = 0.f;
     if (e == cudaSuccess) e = cudaEventElapsedTime(&t, r.start, r.stop);
     tms += t; tf += r.flops;
+    if (r.kind >= 0 && r.kind < 4) { ctx->profKindMs[r.kind] += t; ctx->profKindFlops[r.kind] += r.flops; ++ctx->profKindCount[r.kind]; }
     cudaEventDestroy(r.start); cudaEventDestroy(r.stop);
   }
   if (ms) *ms = tms;
@@ -161,6 +163,15 @@ int vlb_ctx_profile_end(vlb_ctx* ctx, double* ms, double* flops, long long* laun
   if (launches) *launches = (long long)ctx->prof.size();
   ctx->prof.clear();
   if (e != cudaSuccess) return vlb::set_error(ctx, VLB_Cuda, cudaGetErrorString(e));
+  return VLB_Success;
+}
+
+int vlb_ctx_profile_kind(vlb_ctx* ctx, int kind, double* ms, double* flops, long long* count)
+{
+  if (!ctx || kind < 0 || kind > 3) return VLB_IllegalArgument;
+  if (ms) *ms = ctx->profKindMs[kind];
+  if (flops) *flops = ctx->profKindFlops[kind];
+  if (count) *count = ctx->profKindCount[kind];
   return VLB_Success;
 }
 

@@ -102,6 +102,69 @@ __global__ void sgd_update_kernel(float* w, float* m, float const* __restrict__ 
   }
 }
 
+// The trainer's other solvers (reference examples/+solver/adagrad.m, adadelta.m, adam.m, rmsprop.m; call site
+// examples/cnn_train.m:478-507): the normalisation + weight decay pass (vl_taccum) and the solver's element-wise MATLAB
+// expression in one kernel.  Every MATLAB operation on single arrays rounds to single, so each is one _rn operation here
+// and nothing is contracted into a fused multiply-add.
+struct SolverParams { int solver; float gradMult, decay, lr, rho, eps, beta1, beta2, omb2; };
+
+__device__ __forceinline__ void solver1(float& w, float& s1, float& s2, float g0, SolverParams const& p)
+{
+  float const g = taccum1(p.gradMult, g0, p.decay, w);
+  float const gg = __fmul_rn(g, g);
+  if (p.solver == VLB_SOLVER_ADAGRAD) {
+    // g_sqr = g_sqr * rho + grad.^2 ;  w = w - lr * grad ./ (sqrt(g_sqr) + epsilon)
+    s1 = __fadd_rn(__fmul_rn(s1, p.rho), gg);
+    w = __fsub_rn(w, __fdiv_rn(__fmul_rn(p.lr, g), __fadd_rn(__fsqrt_rn(s1), p.eps)));
+  } else if (p.solver == VLB_SOLVER_RMSPROP) {
+    // g_sqr = g_sqr * rho + grad.^2 * (1 - rho) ;  w = w - lr * grad ./ (sqrt(g_sqr) + epsilon)
+    s1 = __fadd_rn(__fmul_rn(s1, p.rho), __fmul_rn(gg, p.beta1));          // beta1 carries single(1 - rho)
+    w = __fsub_rn(w, __fdiv_rn(__fmul_rn(p.lr, g), __fadd_rn(__fsqrt_rn(s1), p.eps)));
+  } else if (p.solver == VLB_SOLVER_ADADELTA) {
+    // g_sqr = g_sqr * rho + grad.^2 * (1 - rho) ;  new_delta = -sqrt((delta_sqr + eps) ./ (g_sqr + eps)) .* grad ;
+    // delta_sqr = delta_sqr * rho + new_delta.^2 * (1 - rho) ;  w = w + new_delta
+    s1 = __fadd_rn(__fmul_rn(s1, p.rho), __fmul_rn(gg, p.beta1));
+    float const nd = __fmul_rn(-__fsqrt_rn(__fdiv_rn(__fadd_rn(s2, p.eps), __fadd_rn(s1, p.eps))), g);
+    s2 = __fadd_rn(__fmul_rn(s2, p.rho), __fmul_rn(__fmul_rn(nd, nd), p.beta1));
+    w = __fadd_rn(w, nd);
+  } else {
+    // m = beta1 * m + (1 - beta1) * grad ;  v = beta2 * v + (1 - beta2) * grad.^2 ;  w = w - lr_t * m ./ (v.^0.5 + eps)
+    // (lr carries lr_t, rho carries single(1 - beta1), omb2 single(1 - beta2): see vlb_solver_update)
+    s1 = __fadd_rn(__fmul_rn(p.beta1, s1), __fmul_rn(p.rho, g));
+    s2 = __fadd_rn(__fmul_rn(p.beta2, s2), __fmul_rn(p.omb2, gg));
+    w = __fsub_rn(w, __fdiv_rn(__fmul_rn(p.lr, s1), __fadd_rn(__fsqrt_rn(s2), p.eps)));
+  }
+}
+
+__global__ void solver_update_kernel(float* w, float* s1, float* s2, float const* __restrict__ g, size_t n, SolverParams p, bool vec)
+{
+  size_t stride = (size_t)gridDim.x * blockDim.x, i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  bool const two = s2 != nullptr;
+  if (vec) {
+    size_t n4 = n >> 2;
+    for (size_t i = i0; i < n4; i += stride) {
+      float4 W = reinterpret_cast<float4*>(w)[i], A = reinterpret_cast<float4*>(s1)[i];
+      float4 B = two ? reinterpret_cast<float4*>(s2)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      float4 const G = reinterpret_cast<float4 const*>(g)[i];
+      solver1(W.x, A.x, B.x, G.x, p); solver1(W.y, A.y, B.y, G.y, p); solver1(W.z, A.z, B.z, G.z, p); solver1(W.w, A.w, B.w, G.w, p);
+      reinterpret_cast<float4*>(w)[i] = W;
+      reinterpret_cast<float4*>(s1)[i] = A;
+      if (two) reinterpret_cast<float4*>(s2)[i] = B;
+    }
+    for (size_t i = (n4 << 2) + i0; i < n; i += stride) {
+      float b = two ? s2[i] : 0.f;
+      solver1(w[i], s1[i], b, g[i], p);
+      if (two) s2[i] = b;
+    }
+  } else {
+    for (size_t i = i0; i < n; i += stride) {
+      float b = two ? s2[i] : 0.f;
+      solver1(w[i], s1[i], b, g[i], p);
+      if (two) s2[i] = b;
+    }
+  }
+}
+
 __global__ void sum_kernel(float* y, float const* a, float const* b, size_t n, bool vec)
 {
   size_t stride = (size_t)gridDim.x * blockDim.x, i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -341,6 +404,33 @@ int vlb_sgd_update(vlb_ctx* ctx, float* W, float* M, float const* G, size_t n, d
   sgd_update_kernel<<<vlb::grid_for(vec ? n / 4 + 1 : n, kThreads, ctx->smCount * 8), kThreads, 0, ctx->stream>>>(W, M, G, n, p, vec);
   VLB_LAUNCHED(ctx, 1);
   return vlb::check_launch(ctx, "vlb_sgd_update");
+}
+
+int vlb_solver_update(vlb_ctx* ctx, int solver, float* W, float* S1, float* S2, float const* G, size_t n, double gradMult,
+                      double decay, double lr, vlb_solver_opts const* opts, long long t)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  VLB_REQUIRE(ctx, solver >= VLB_SOLVER_ADAGRAD && solver <= VLB_SOLVER_RMSPROP, "solver_update: unknown solver");
+  bool const two = solver == VLB_SOLVER_ADADELTA || solver == VLB_SOLVER_ADAM;
+  VLB_REQUIRE(ctx, W && S1 && G && opts && (!two || S2), "solver_update: null tensor");
+  VLB_REQUIRE(ctx, solver != VLB_SOLVER_ADAM || t >= 1, "solver_update: adam needs the step count t >= 1");
+  if (n == 0) return VLB_Success;
+  SolverParams p = {};
+  p.solver = solver; p.gradMult = (float)gradMult; p.decay = (float)decay; p.lr = (float)lr;
+  p.rho = (float)opts->rho; p.eps = (float)opts->epsilon;
+  // MATLAB evaluates scalar expressions such as (1 - rho) in double and converts the result to single when it meets the array
+  p.beta1 = (float)(1.0 - opts->rho);
+  if (solver == VLB_SOLVER_ADAM) {
+    p.beta1 = (float)opts->beta1; p.beta2 = (float)opts->beta2;
+    p.rho = (float)(1.0 - opts->beta1); p.omb2 = (float)(1.0 - opts->beta2);
+    // lr_t = lr * (((1 - beta2^t)^0.5) / (1 - beta1^t))   (examples/+solver/adam.m)
+    p.lr = (float)(lr * (sqrt(1.0 - pow(opts->beta2, (double)t)) / (1.0 - pow(opts->beta1, (double)t))));
+  }
+  bool vec = aligned16(W) && aligned16(S1) && aligned16(G) && (!two || aligned16(S2));
+  solver_update_kernel<<<vlb::grid_for(vec ? n / 4 + 1 : n, kThreads, ctx->smCount * 8), kThreads, 0, ctx->stream>>>(
+      W, S1, two ? S2 : nullptr, G, n, p, vec);
+  VLB_LAUNCHED(ctx, 1);
+  return vlb::check_launch(ctx, "vlb_solver_update");
 }
 
 int vlb_bias_forward(vlb_ctx* ctx, float* Y, double yMult, float const* X, double xMult, float const* b,

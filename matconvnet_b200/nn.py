@@ -345,6 +345,32 @@ def sgd_update_(w, momentum_state, grad, grad_mult, decay, momentum, lr, nestero
     return w
 
 
+def solver_update_(solver, w, state, grad, grad_mult, decay, lr, opts=None, ctx=None):
+    """One step of examples/+solver/<solver>.m on one parameter tensor, fused with the trainer's normalisation and weight
+    decay pass (examples/cnn_train.m:481-507), in place on w and on the solver state.  state: {} before the first step;
+    afterwards it holds the solver's tensors (g_sqr; g_sqr and delta_sqr; m, v and the step count t)."""
+    ctx = _ctx(ctx)
+    if solver not in capi.SOLVERS:
+        raise ValueError("unknown solver '%s'" % solver)
+    w, g = _flat32(w, "w"), _flat32(grad, "grad")
+    if w.numel() != g.numel():
+        raise ValueError("parameter and gradient do not have the same number of elements.")
+    o = dict(capi.SOLVER_DEFAULTS[solver])
+    o.update(opts or {})
+    two = solver in ("adadelta", "adam")
+    if "s1" not in state:
+        state["s1"] = torch.zeros_like(w)
+        if two:
+            state["s2"] = torch.zeros_like(w)
+        state["t"] = 0
+    state["t"] += 1
+    so = capi.SolverOpts(float(o.get("rho", 0.0)), float(o["epsilon"]), float(o.get("beta1", 0.0)), float(o.get("beta2", 0.0)))
+    ctx.check(ctx.lib.vlb_solver_update(ctx.handle, capi.SOLVERS[solver], w.data_ptr(), state["s1"].data_ptr(),
+                                        state["s2"].data_ptr() if two else None, g.data_ptr(), w.numel(), float(grad_mult),
+                                        float(decay), float(lr), C.byref(so), state["t"]))
+    return w
+
+
 # --------------------------------------------------------------------- MATLAB-only blocks
 def vl_nnrelu(x, dzdy=None, ctx=None):
     """matlab/vl_nnrelu.m:43-48 with LEAK = 0."""

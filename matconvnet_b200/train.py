@@ -4,7 +4,8 @@ workers, add weight decay, update the momentum and the parameter -- or, for the 
 moments), move the stored moments towards the batch's (cnn_train.m:468-476).
 
 ``params``: dict with learning_rate, weight_decay, momentum, nesterov_update (cnn_train.m:17-45 defaults: 0.001, 0.0005,
-0.9, False).  A layer may carry 'learningRate' / 'weightDecay' lists (per parameter multipliers, default 1;
+0.9, False) and optionally solver ('adagrad', 'adadelta', 'adam' or 'rmsprop': examples/+solver/*.m, called at
+cnn_train.m:503-507 instead of the momentum step) with solver_opts (the solver's own defaults otherwise).  A layer may carry 'learningRate' / 'weightDecay' lists (per parameter multipliers, default 1;
 vl_simplenn_tidy).  ``state`` maps (layer index, parameter index) to the momentum tensor, created as zeros on first use
 (cnn_train.m:292-301).  Every tensor operation is a call into the C ABI.
 """
@@ -43,6 +44,10 @@ def accumulate_gradients(net, res, state, params, num_workers=1, pulled=None, ct
             lr = params["learning_rate"] * lr_mult
             if lr > 0 or decay > 0:
                 key = (l, j)
+                if params.get("solver"):
+                    nn.solver_update_(params["solver"], w, state.setdefault(key, {}), der, 1.0 / num_workers, decay, lr,
+                                      params.get("solver_opts"), ctx=ctx)
+                    continue
                 if key not in state:
                     state[key] = torch.zeros_like(w)
                 nn.sgd_update_(w, state[key], der, 1.0 / num_workers, decay, params["momentum"], lr,

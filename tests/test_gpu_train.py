@@ -163,3 +163,102 @@ def test_exchanged_sums_are_normalised_exactly_once(gpu, monkeypatch):
     for la, lb in zip(alone["layers"], net["layers"]):
         for wa, wb in zip(la.get("weights", []), lb.get("weights", [])):
             assert float((wa.double() - wb.double()).abs().max()) < 1e-6
+
+
+def _solver_np(solver, w, s1, s2, g0, grad_mult, decay, lr, o, t):
+    """examples/+solver/*.m on float32 arrays, one rounding per MATLAB operation, after the trainer's normalisation pass."""
+    f = np.float32
+    g = _taccum_np(grad_mult, g0, decay, w)
+    gg = g * g
+    if solver == "adagrad":
+        s1 = s1 * f(o["rho"]) + gg
+        w = w - (f(lr) * g) / (np.sqrt(s1) + f(o["epsilon"]))
+    elif solver == "rmsprop":
+        s1 = s1 * f(o["rho"]) + gg * f(1.0 - o["rho"])
+        w = w - (f(lr) * g) / (np.sqrt(s1) + f(o["epsilon"]))
+    elif solver == "adadelta":
+        s1 = s1 * f(o["rho"]) + gg * f(1.0 - o["rho"])
+        nd = -np.sqrt((s2 + f(o["epsilon"])) / (s1 + f(o["epsilon"]))) * g
+        s2 = s2 * f(o["rho"]) + (nd * nd) * f(1.0 - o["rho"])
+        w = w + nd
+    else:
+        s1 = f(o["beta1"]) * s1 + f(1.0 - o["beta1"]) * g
+        s2 = f(o["beta2"]) * s2 + f(1.0 - o["beta2"]) * gg
+        lr_t = f(lr * (np.sqrt(1.0 - o["beta2"] ** t) / (1.0 - o["beta1"] ** t)))
+        w = w - (lr_t * s1) / (np.sqrt(s2) + f(o["epsilon"]))
+    return w.astype(f), s1.astype(f), None if s2 is None else s2.astype(f)
+
+
+@pytest.mark.parametrize("solver", ["adagrad", "adadelta", "adam", "rmsprop"])
+def test_solver_update_follows_the_matlab_expressions(gpu, solver):
+    """Three steps of each solver of examples/+solver on one tensor: bit for bit a float32 evaluation of the MATLAB
+    expressions operation by operation (the taccum pass before it to its last-place tolerance), and within 1e-6 of the
+    same formulas in double precision."""
+    import torch
+    from matconvnet_b200 import capi
+    nn, mat, ctx = gpu
+    g = torch.Generator(device="cuda").manual_seed(31)
+    n = 50003
+    w = torch.randn(n, device="cuda", generator=g)
+    o = capi.SOLVER_DEFAULTS[solver]
+    two = solver in ("adadelta", "adam")
+    wn = w.cpu().numpy().copy()
+    s1n, s2n = np.zeros(n, np.float32), (np.zeros(n, np.float32) if two else None)
+    wd, s1d, s2d = wn.astype(np.float64), np.zeros(n), np.zeros(n)
+    state = {}
+    workers, decay, lr = 4, 0.0005, 0.01
+    for t in range(1, 4):
+        der = torch.randn(n, device="cuda", generator=g)
+        der0 = der.clone()
+        nn.solver_update_(solver, w, state, der, 1.0 / workers, decay, lr, ctx=ctx)
+        assert torch.equal(der, der0) and state["t"] == t
+        wn, s1n, s2n = _solver_np(solver, wn, s1n, s2n, der.cpu().numpy(), 1.0 / workers, decay, lr, o, t)
+        # double-precision closed form
+        gd = der.cpu().numpy().astype(np.float64) / workers + decay * wd
+        if solver == "adagrad":
+            s1d = s1d * o["rho"] + gd ** 2
+            wd = wd - lr * gd / (np.sqrt(s1d) + o["epsilon"])
+        elif solver == "rmsprop":
+            s1d = s1d * o["rho"] + gd ** 2 * (1 - o["rho"])
+            wd = wd - lr * gd / (np.sqrt(s1d) + o["epsilon"])
+        elif solver == "adadelta":
+            s1d = s1d * o["rho"] + gd ** 2 * (1 - o["rho"])
+            nd = -np.sqrt((s2d + o["epsilon"]) / (s1d + o["epsilon"])) * gd
+            s2d = s2d * o["rho"] + nd ** 2 * (1 - o["rho"])
+            wd = wd + nd
+        else:
+            s1d = o["beta1"] * s1d + (1 - o["beta1"]) * gd
+            s2d = o["beta2"] * s2d + (1 - o["beta2"]) * gd ** 2
+            wd = wd - lr * (np.sqrt(1 - o["beta2"] ** t) / (1 - o["beta1"] ** t)) * s1d / (np.sqrt(s2d) + o["epsilon"])
+    got = w.cpu().numpy()
+    assert np.max(np.abs(got - wd)) < 2e-6
+    # the emulated taccum pass rounds twice where the kernel's fused multiply-add rounds once: last-place differences
+    assert np.max(np.abs(got - wn) / np.maximum(np.abs(wn), 1e-3)) < 2e-6
+    assert np.max(np.abs(state["s1"].cpu().numpy() - s1n) / np.maximum(np.abs(s1n), 1e-6)) < 1e-5
+
+
+def test_accumulate_gradients_with_a_solver(gpu):
+    """train.accumulate_gradients(params['solver']='adam') moves a network's parameters as nn.solver_update_ does tensor
+    by tensor (the call site examples/cnn_train.m:503-507)."""
+    import torch
+    from matconvnet_b200 import models, simplenn, train
+    nn, mat, ctx = gpu
+    ctx.set_precision(0)
+    rng = np.random.default_rng(4)
+    g = torch.Generator(device="cuda").manual_seed(4)
+    layers = [models._conv(rng, 3, 3, 3, 8, 1, 1), models._relu(), models._conv(rng, 8, 8, 8, 5, 1, 0),
+              {"type": "softmaxloss", "class": torch.tensor([1, 2, 3, 4], device="cuda").float()}]
+    net = {"layers": layers}
+    x = mat.as_mat(torch.randn(8, 8, 3, 4, device="cuda", generator=g))
+    res = simplenn.vl_simplenn(net, x, 1.0, ctx=ctx)
+    want = {}
+    for l in (0, 2):
+        for j in (0, 1):
+            w = layers[l]["weights"][j].clone()
+            nn.solver_update_("adam", w, {}, res[l]["dzdw"][j], 0.5, 0.0005, 0.001, ctx=ctx)
+            want[(l, j)] = w
+    state = {}
+    train.accumulate_gradients(net, res, state, dict(learning_rate=0.001, weight_decay=0.0005, momentum=0.9, solver="adam"),
+                               num_workers=2, ctx=ctx)
+    for (l, j), w in want.items():
+        assert torch.equal(layers[l]["weights"][j], w) and state[(l, j)]["t"] == 1
