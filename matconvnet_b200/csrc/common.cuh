@@ -79,6 +79,17 @@ struct ProfScope {
   }
 };
 
+// The opt-in to more than 48 KB of dynamic shared memory: everything the SM offers one block (227 KB) minus what the
+// kernel declares statically.  Called once per kernel and device by the launch sites.
+template <class Kernel>
+inline cudaError_t allow_max_dynamic_smem(Kernel kernel)
+{
+  cudaFuncAttributes attr;
+  cudaError_t e = cudaFuncGetAttributes(&attr, kernel);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - (int)attr.sharedSizeBytes);
+}
+
 inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
 inline unsigned grid_for(size_t n, int threads, int maxBlocks = 148 * 16)
 {

@@ -1608,7 +1608,7 @@ cudaError_t allow_large_smem(int device)
 {
   static bool done[64] = {};
   if (device >= 0 && device < 64 && done[device]) return cudaSuccess;
-  cudaError_t e = cudaFuncSetAttribute(kKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  cudaError_t e = vlb::allow_max_dynamic_smem(kKernel);
   if (e == cudaSuccess && device >= 0 && device < 64) done[device] = true;
   return e;
 }

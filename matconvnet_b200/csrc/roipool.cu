@@ -141,19 +141,17 @@ __global__ void roipool_kernel(float* __restrict__ out, float const* __restrict_
 constexpr int kGatherThreads = 1024;
 constexpr uint32_t kNoBin = 0xFFFFu;
 
-struct GatherPlan {
-  int CH;            // channels per slab
-  int RB;            // ROIs per batch (tables and arg-max indices of one batch are in shared memory at a time)
-  int chunks;        // slabs per image
-  size_t smem;
-};
-
-// Shared-memory layout (bytes): slab float[CH*HW] | argmax uint16[RB*CH*S0*S1] | rowTab uint16[RB*H] | colTab uint16[RB*W] |
-// roiIdx int[RB].  A table entry is lo | hi << 8 (bin range covering that row / column) or kNoBin.
+// Shared-memory layout (bytes): slab float[CH*HW] (max only) | argmax uint16[RB*CH*S0*S1] (max only) |
+// binRow uint32[RB*S0], binCol uint32[RB*S1]: start | end << 16 of every bin row / column of every ROI of the batch |
+// rowMask uint32[H*words], colMask uint32[W*words]: bit j of word k set when ROI 32k+j of the batch covers that map row /
+// column | rowTab uint16[RB*H], colTab uint16[RB*W]: lo | hi << 8, the bin rows / columns covering it, or kNoBin | roiIdx int[RB].
 __host__ __device__ inline size_t gather_smem(int CH, int RB, int H, int W, int S0, int S1, bool isMax)
 {
+  int const words = (RB + 31) / 32;
   size_t b = isMax ? sizeof(float) * (size_t)CH * H * W : 0;
   b += isMax ? ((sizeof(uint16_t) * (size_t)RB * CH * S0 * S1 + 15) & ~(size_t)15) : 0;
+  b += sizeof(uint32_t) * (size_t)RB * (S0 + S1);
+  b += sizeof(uint32_t) * (size_t)words * (H + W);
   b += (sizeof(uint16_t) * (size_t)RB * (H + W) + 15) & ~(size_t)15;
   b += sizeof(int) * (size_t)RB;
   return b + 64;
@@ -166,7 +164,7 @@ roipool_bwd_gather_kernel(float* __restrict__ dx, float const* __restrict__ x, f
 {
   extern __shared__ __align__(16) uint8_t sm[];
   __shared__ int sCount, sNext;
-  int const HW = p.H * p.W, bins = p.S0 * p.S1;
+  int const HW = p.H * p.W, bins = p.S0 * p.S1, words = (RB + 31) / 32;
   int const img = blockIdx.x / chunks, c0 = (blockIdx.x % chunks) * CH;
   int const nch = min(CH, p.C - c0);
   int const tid = threadIdx.x, lane = tid & 31;
@@ -175,9 +173,13 @@ roipool_bwd_gather_kernel(float* __restrict__ dx, float const* __restrict__ x, f
   if (kMax) q += sizeof(float) * (size_t)CH * HW;
   uint16_t* am = reinterpret_cast<uint16_t*>(q);
   if (kMax) q += (sizeof(uint16_t) * (size_t)RB * CH * bins + 15) & ~(size_t)15;
-  uint16_t* rowTab = reinterpret_cast<uint16_t*>(q);
+  uint32_t* binRow = reinterpret_cast<uint32_t*>(q);
+  uint32_t* binCol = binRow + (size_t)RB * p.S0;
+  uint32_t* rowMask = binCol + (size_t)RB * p.S1;
+  uint32_t* colMask = rowMask + (size_t)words * p.H;
+  uint16_t* rowTab = reinterpret_cast<uint16_t*>(colMask + (size_t)words * p.W);
   uint16_t* colTab = rowTab + (size_t)RB * p.H;
-  q += (sizeof(uint16_t) * (size_t)RB * (p.H + p.W) + 15) & ~(size_t)15;
+  q = reinterpret_cast<uint8_t*>(rowTab) + ((sizeof(uint16_t) * (size_t)RB * (p.H + p.W) + 15) & ~(size_t)15);
   int* roiIdx = reinterpret_cast<int*>(q);
 
   size_t const slabOff = (size_t)HW * ((size_t)c0 + (size_t)p.C * img);
@@ -215,18 +217,29 @@ roipool_bwd_gather_kernel(float* __restrict__ dx, float const* __restrict__ x, f
     int const nb = sCount;
     base = sNext;
     if (nb == 0) break;
+    // bin geometry of every ROI of the batch, once (the double-precision part of the arithmetic)
+    for (int i = tid; i < nb * (p.S0 + p.S1); i += kGatherThreads) {
+      bool const isRow = i < nb * p.S0;
+      int const k = isRow ? i : i - nb * p.S0;
+      int const S = isRow ? p.S0 : p.S1;
+      int const j = k / S, b = k - j * S;
+      RoiGeom g = roi_geom(rois + 5 * (size_t)roiIdx[j], p);
+      int s, e;
+      roi_bin(b, isRow ? g.bin_h : g.bin_w, isRow ? g.start_h : g.start_w, isRow ? p.H : p.W, s, e);
+      (isRow ? binRow : binCol)[k] = (uint32_t)s | ((uint32_t)e << 16);
+    }
+    __syncthreads();
     // which bin rows cover map row h, which bin columns cover map column w
     for (int i = tid; i < nb * (p.H + p.W); i += kGatherThreads) {
       bool const isRow = i < nb * p.H;
       int const k = isRow ? i : i - nb * p.H;
       int const ext = isRow ? p.H : p.W, S = isRow ? p.S0 : p.S1;
       int const j = k / ext, pos = k - j * ext;
-      RoiGeom g = roi_geom(rois + 5 * (size_t)roiIdx[j], p);
+      uint32_t const* tab = (isRow ? binRow : binCol) + (size_t)j * S;
       uint32_t lo = kNoBin, hi = 0;
       for (int b = 0; b < S; ++b) {
-        int s, e;
-        roi_bin(b, isRow ? g.bin_h : g.bin_w, isRow ? g.start_h : g.start_w, ext, s, e);
-        if (s <= pos && pos < e) { if (lo == kNoBin) lo = (uint32_t)b; hi = (uint32_t)b; }
+        uint32_t const se = tab[b];
+        if ((int)(se & 0xFFFFu) <= pos && pos < (int)(se >> 16)) { if (lo == kNoBin) lo = (uint32_t)b; hi = (uint32_t)b; }
       }
       (isRow ? rowTab : colTab)[k] = (uint16_t)(lo == kNoBin ? kNoBin : (lo | (hi << 8)));
     }
@@ -237,10 +250,8 @@ roipool_bwd_gather_kernel(float* __restrict__ dx, float const* __restrict__ x, f
         int t = b / p.S0;
         int const pw = t % p.S1; t /= p.S1;
         int const cc = t % nch, j = t / nch;
-        RoiGeom g = roi_geom(rois + 5 * (size_t)roiIdx[j], p);
-        int hs, he, ws, we;
-        roi_bin(ph, g.bin_h, g.start_h, p.H, hs, he);
-        roi_bin(pw, g.bin_w, g.start_w, p.W, ws, we);
+        uint32_t const rs = binRow[j * p.S0 + ph], cs = binCol[j * p.S1 + pw];
+        int const hs = (int)(rs & 0xFFFFu), he = (int)(rs >> 16), ws = (int)(cs & 0xFFFFu), we = (int)(cs >> 16);
         float const* xz = slab + (size_t)cc * HW;
         float best = -INFINITY;
         uint32_t where = kNoBin;
@@ -253,33 +264,47 @@ roipool_bwd_gather_kernel(float* __restrict__ dx, float const* __restrict__ x, f
       }
     }
     __syncthreads();
+    // bit masks: the ROIs of the batch that cover a map row / column, so that a pixel visits only ROIs that contain it
+    for (int i = tid; i < words * (p.H + p.W); i += kGatherThreads) {
+      bool const isRow = i < words * p.H;
+      int const k = isRow ? i : i - words * p.H;
+      int const ext = isRow ? p.H : p.W;
+      int const pos = k / words, wd = k - pos * words;
+      uint16_t const* tab = isRow ? rowTab : colTab;
+      uint32_t m = 0;
+      for (int j = wd * 32; j < min(nb, wd * 32 + 32); ++j)
+        if (tab[j * ext + pos] != kNoBin) m |= 1u << (j & 31);
+      (isRow ? rowMask : colMask)[k] = m;
+    }
+    __syncthreads();
     for (int item = tid; item < nch * HW; item += kGatherThreads) {
       int const cc = item / HW, pix = item - cc * HW;
       int const w = pix / p.H, h = pix - w * p.H;
       float* const dst = dx + slabOff + item;
       float acc = first ? 0.f : *dst;
-      for (int j = 0; j < nb; ++j) {
-        uint32_t const rt = rowTab[j * p.H + h], ct = colTab[j * p.W + w];
-        if (rt == kNoBin || ct == kNoBin) continue;
-        float const* dyr = dy + (size_t)bins * ((size_t)(c0 + cc) + (size_t)p.C * roiIdx[j]);
-        if (kMax) {
-          uint16_t const* amr = am + (size_t)bins * (cc + (size_t)nch * j);
-          for (uint32_t pw = ct & 255u; pw <= (ct >> 8); ++pw)
-            for (uint32_t ph = rt & 255u; ph <= (rt >> 8); ++ph) {
-              int const b = (int)(ph + p.S0 * pw);
-              if (amr[b] == (uint32_t)pix) acc = __fadd_rn(acc, dyr[b]);
-            }
-        } else {
-          // every bin that covers the pixel contributes dy / area (bits/nnroipooling.cu:74-90, acc_sum)
-          RoiGeom g = roi_geom(rois + 5 * (size_t)roiIdx[j], p);
-          for (uint32_t pw = ct & 255u; pw <= (ct >> 8); ++pw) {
-            int ws, we;
-            roi_bin((int)pw, g.bin_w, g.start_w, p.W, ws, we);
-            for (uint32_t ph = rt & 255u; ph <= (rt >> 8); ++ph) {
-              int hs, he;
-              roi_bin((int)ph, g.bin_h, g.start_h, p.H, hs, he);
-              float const scale = __fdiv_rn(1.f, (float)((he - hs) * (we - ws)));
-              acc = __fadd_rn(acc, __fmul_rn(dyr[ph + p.S0 * pw], scale));
+      for (int wd = 0; wd < words; ++wd) {
+        uint32_t m = rowMask[h * words + wd] & colMask[w * words + wd];
+        while (m) {
+          int const j = wd * 32 + __ffs(m) - 1;          // ascending: the order of the CPU loop over the ROIs
+          m &= m - 1;
+          uint32_t const rt = rowTab[j * p.H + h], ct = colTab[j * p.W + w];
+          float const* dyr = dy + (size_t)bins * ((size_t)(c0 + cc) + (size_t)p.C * roiIdx[j]);
+          if (kMax) {
+            uint16_t const* amr = am + (size_t)bins * (cc + (size_t)nch * j);
+            for (uint32_t pw = ct & 255u; pw <= (ct >> 8); ++pw)
+              for (uint32_t ph = rt & 255u; ph <= (rt >> 8); ++ph) {
+                int const b = (int)(ph + p.S0 * pw);
+                if (amr[b] == (uint32_t)pix) acc = __fadd_rn(acc, dyr[b]);
+              }
+          } else {
+            // every bin that covers the pixel contributes dy / area (bits/nnroipooling.cu:74-90, acc_sum)
+            for (uint32_t pw = ct & 255u; pw <= (ct >> 8); ++pw) {
+              uint32_t const cs = binCol[j * p.S1 + pw];
+              for (uint32_t ph = rt & 255u; ph <= (rt >> 8); ++ph) {
+                uint32_t const rs = binRow[j * p.S0 + ph];
+                int const area = (int)((rs >> 16) - (rs & 0xFFFFu)) * (int)((cs >> 16) - (cs & 0xFFFFu));
+                acc = __fadd_rn(acc, __fmul_rn(dyr[ph + p.S0 * pw], __fdiv_rn(1.f, (float)area)));
+              }
             }
           }
         }
@@ -371,8 +396,8 @@ int vlb_roipool_backward(vlb_ctx* ctx, float* dX, float const* X, float const* r
           size_t const smem = gather_smem(CH, (int)RB, H, W, S0, S1, isMax) + 64;
           static bool attrDone[2][64] = {};
           if (!(ctx->device < 64 && attrDone[isMax][ctx->device])) {
-            cudaError_t ea = isMax ? cudaFuncSetAttribute(roipool_bwd_gather_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)
-                                   : cudaFuncSetAttribute(roipool_bwd_gather_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            cudaError_t ea = isMax ? vlb::allow_max_dynamic_smem(roipool_bwd_gather_kernel<true>)
+                                   : vlb::allow_max_dynamic_smem(roipool_bwd_gather_kernel<false>);
             if (ea != cudaSuccess) { cudaGetLastError(); return vlb::set_error(ctx, VLB_Cuda, cudaGetErrorString(ea)); }
             if (ctx->device < 64) attrDone[isMax][ctx->device] = true;
           }

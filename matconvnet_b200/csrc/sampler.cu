@@ -124,7 +124,7 @@ __global__ void sampler_kernel(float* __restrict__ y, float* __restrict__ dx, fl
 }
 
 // ---- backward-to-data as a gather (see the header comment) ----
-constexpr int kGatherThreads = 1024;
+constexpr int kGatherThreads = 512;    // two CTAs per SM: one inverts its grid while the other streams its channels
 constexpr int kMaxList = 48;          // taps of one grid on one input pixel beyond which the scatter path is used
 constexpr int kChan = 8;              // channels accumulated together per input pixel
 
@@ -146,7 +146,7 @@ __device__ void block_exclusive_scan(int* v, int n, int* warpSums)
   if (lane == 31) warpSums[warp] = incl;
   __syncthreads();
   if (warp == 0) {
-    int w = warpSums[lane];
+    int w = lane < kGatherThreads / 32 ? warpSums[lane] : 0;
     int wi = w;
     for (int o = 1; o < 32; o <<= 1) { int t = __shfl_up_sync(0xffffffffu, wi, o); if (lane >= o) wi += t; }
     warpSums[lane] = wi - w;      // exclusive over the warps
@@ -158,7 +158,7 @@ __device__ void block_exclusive_scan(int* v, int n, int* warpSums)
 }
 
 template <bool kWantGrid>
-__global__ void __launch_bounds__(kGatherThreads, 1)
+__global__ void __launch_bounds__(kGatherThreads, 2)
 sampler_bwd_gather_kernel(float* __restrict__ dx, float* __restrict__ dgrid, float const* __restrict__ x,
                           float const* __restrict__ grid, float const* __restrict__ dy, int H, int W, int C, int N, int Q, int Ng,
                           int chunks, int CH)
@@ -355,19 +355,19 @@ int vlb_sampler_backward(vlb_ctx* ctx, float* dX, float* dGrid, float const* X, 
   VLB_REQUIRE(ctx, ((((uintptr_t)grid) | ((uintptr_t)dGrid)) & 7) == 0, "sampler_backward: grid must be 8-byte aligned");
   if (!dX && !dGrid) return VLB_Success;
   int const Qo = Ho * Wo, HWi = H * W;
-  if (dX && Qo <= 65535 && gather_smem(HWi, Qo) <= 200 * 1024) {
+  if (dX && Qo <= 65535 && gather_smem(HWi, Qo) <= 200 * 1024) {      // at most half of that leaves room for two CTAs per SM
     // gather: one CTA per image; with fewer images than SMs the channels are shared out among several CTAs per image,
     // and the grid derivative (which runs over all channels of an output pixel in order) is left to the other kernel
     int chunks = 1;
-    if (N < ctx->smCount) chunks = vlb::ceil_div(ctx->smCount, N);
+    if (N < ctx->smCount) chunks = vlb::ceil_div(2 * ctx->smCount, N);
     int CH = vlb::ceil_div(C, chunks);
     CH = vlb::ceil_div(CH, kChan) * kChan;
     chunks = vlb::ceil_div(C, CH);
     bool const fusedGrid = dGrid != nullptr && chunks == 1;
     static bool attrDone[64] = {};
     if (!(ctx->device < 64 && attrDone[ctx->device])) {
-      cudaError_t ea = cudaFuncSetAttribute(sampler_bwd_gather_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-      if (ea == cudaSuccess) ea = cudaFuncSetAttribute(sampler_bwd_gather_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+      cudaError_t ea = vlb::allow_max_dynamic_smem(sampler_bwd_gather_kernel<true>);
+      if (ea == cudaSuccess) ea = vlb::allow_max_dynamic_smem(sampler_bwd_gather_kernel<false>);
       if (ea != cudaSuccess) { cudaGetLastError(); return vlb::set_error(ctx, VLB_Cuda, cudaGetErrorString(ea)); }
       if (ctx->device < 64) attrDone[ctx->device] = true;
     }
