@@ -33,6 +33,8 @@
 #include "conv_internal.cuh"
 #include <cuda.h>
 #include <stdlib.h>
+#include <string.h>
+#include <algorithm>
 
 namespace {
 
@@ -105,6 +107,11 @@ struct Params {
   float const* bTiles;    // when non-null: B pre-split into shared-memory tile images, fetched with bulk copies
   int* status;
   int testSwitch;         // vlb_ctx_set_test_switch: bit 0 = conv_ts_kernel's filter-tile loader stays idle
+  // conv_ts_kernel fed by tensor-map copies (tma != 0): an output tile is a box of bh x bw pixels of one image (tilesH x
+  // tilesW boxes per image); its input window -- boxH rows (rowOff spare rows in front, so that the copy starts on a
+  // 16-byte boundary) x boxW columns x 32 channels -- arrives in shared memory by one cp.async.bulk.tensor per channel block
+  int tma, bh, bw, tilesH, tilesW, boxH, boxW, rowOff;
+  int bStages;            // conv_ts_kernel: filter-tile stages in shared memory (4, or 3 where the input windows need the room)
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -963,8 +970,9 @@ constexpr int kTsGroups = 2;
 constexpr int kTsLoaderWarp = kEpilogueWarps + 2;
 constexpr int kTsForwardWarp = kEpilogueWarps + 3;
 constexpr int kTsFirstProducer = kEpilogueWarps + 4;
-constexpr int kTsThreads = (kTsFirstProducer + 4 * kTsGroups) * 32;      // 512
-constexpr int kTsBStages = 4;
+constexpr int kTsWindowWarp = kTsFirstProducer + 4 * kTsGroups;          // warp 16: input-window loader (tensor-map copies)
+constexpr int kTsThreads = (kTsWindowWarp + 1) * 32;                     // 544
+constexpr int kTsBStages = 4;           // at most; Params::bStages are in use
 constexpr int kTsDrainEvery = 4;        // own k-blocks per accumulation chain: 4 x 4 k-steps x 3 MMAs.  Measured relative error of one layer
                                         // at the full VGG sizes: 4 -> 9e-7, 8 -> 1.7e-6, 16 -> 3.3e-6 (8 is 5-8% faster, 16 another 0-7%), but with 8
                                         // the end-to-end gradients of the LeNet and ResNet configurations no longer stay within 1e-5
@@ -998,15 +1006,54 @@ __device__ __forceinline__ int ts_chains(int numIter, int second)
   return kSplit ? (nOwn + kTsDrainEvery - 1) / kTsDrainEvery : (nOwn > 0 ? 1 : 0);
 }
 
+// 4-D tensor-map copy global -> shared (tile mode, no multicast: the map covers this GPU's own memory only); completion
+// is signalled on the mbarrier as transaction bytes.  The innermost coordinate c0 must be a multiple of four elements.
+__device__ __forceinline__ void tma_load_4d(uint32_t dstSmem, void const* map, int c0, int c1, int c2, int c3, uint32_t bar)
+{
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+               ::"r"(dstSmem), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ float lds32(uint32_t addr)
+{
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
+}
+
+// Where row `row` (0..127, = TMEM lane) of row tile `tm` lies in the output: image, pixel ho + Ho*wo, and whether it exists.
+// Linear mode: the tile is 128 consecutive output pixels (ho fastest, images following one another).  Box mode (p.tma):
+// the tile is a box of bh x bw pixels of one image, row = dh + bh*dw.
+struct RowPos { int img, pix; bool valid; };
+
+__device__ __forceinline__ RowPos row_pos(Params const& p, int tm, int row)
+{
+  RowPos r;
+  if (!p.tma) {
+    int const m = tm * BM + row;
+    r.valid = m < p.M;
+    int const mm = min(m, p.M - 1);
+    r.img = mm / p.e.P; r.pix = mm - r.img * p.e.P;
+  } else {
+    int const per = p.tilesH * p.tilesW;
+    int const n = tm / per, t = tm - n * per, wb = t / p.tilesH, hb = t - wb * p.tilesH;
+    int const dw = row / p.bh, dh = row - dw * p.bh;
+    int const h = hb * p.bh + dh, w = wb * p.bw + dw;
+    r.valid = dw < p.bw && h < p.a.Ho && w < p.a.Wo;
+    r.img = n; r.pix = r.valid ? h + p.a.Ho * w : 0;
+  }
+  return r;
+}
+
 // Epilogue of conv_ts_kernel: the finished tile sits in shared memory, P[column][row]; this warp stores the rows of its
 // TMEM lane quarter for the columns rank, rank + nranks, ...: out[(image*Ktot + n)*P + pixel] = inMult*acc + bias[n] + outMult*old.
-__device__ __forceinline__ void ts_store_tile(Params const& p, float const* P, int quarter, int lane, int rank, int nranks, int m0, int n0,
+__device__ __forceinline__ void ts_store_tile(Params const& p, float const* P, int quarter, int lane, int rank, int nranks, int tm, int n0,
                                               uint32_t const* maskBits = nullptr)
 {
   int const row = quarter * 32 + lane;
-  int const m = m0 + row;
-  if (m >= p.M) return;
-  int const pix = m % p.e.P, img = m / p.e.P;
+  RowPos const rp = row_pos(p, tm, row);
+  if (!rp.valid) return;
+  int const pix = rp.pix, img = rp.img;
   float* const dst0 = p.e.out + ((long long)img * p.e.Ktot * p.e.P + pix);
   int const nEnd = min(p.BN, p.N - n0);
   if (maskBits) {
@@ -1059,22 +1106,30 @@ __device__ __forceinline__ void ts_store_tile(Params const& p, float const* P, i
   }
 }
 
-template <bool kSplit>
-__global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
+// kTma: the producers take the input windows from shared memory, where warp 16 has them delivered by tensor-map copies
+// (one box of boxH x boxW pixels x 32 channels per channel block and tile, zero-filled outside the image by the copy
+// engine, two buffers), instead of gathering them from global memory with per-thread loads.  xmap: the 4-D tensor map
+// (H, W, C, N) of the gathered tensor; unused otherwise.
+template <bool kSplit, bool kTma>
+__global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p, const __grid_constant__ CUtensorMap xmap)
 {
   extern __shared__ uint8_t smemRaw[];
   __shared__ __align__(8) uint64_t fullA[kTsGroups], emptyA[kTsGroups], fullB[kTsBStages], emptyB[kTsBStages];
-  __shared__ __align__(8) uint64_t tFull[3], tFree[3], tileDone, turn[2];
+  __shared__ __align__(8) uint64_t tFull[3], tFree[3], tileDone, turn[2], fullX[2], emptyX[2];
   __shared__ uint32_t tmemBase;
-  __shared__ int2 tapLut[64];       // per filter tap fh + FH*fw: {element offset of the tap, fh | fw << 5}
+  __shared__ int2 tapLut[64];       // per filter tap fh + FH*fw: {element offset of the tap (in the input window when kTma), fh | fw << 5}
 
   uint8_t* smem = smemRaw + ((1024u - (smem_u32(smemRaw) & 1023u)) & 1023u);
   int const BN = p.BN;
+  int const nB = p.bStages;
   uint32_t const bTileBytes = (uint32_t)BN * BK * 4;
   uint32_t const bBytes = (kSplit ? 2u : 1u) * bTileBytes;
   uint32_t const tmemCols = 512;
   uint32_t const colA = (uint32_t)(3 * BN);
-  float* const Psm = reinterpret_cast<float*>(smem + (size_t)kTsBStages * bBytes);      // [BN][BM]
+  float* const Psm = reinterpret_cast<float*>(smem + (size_t)nB * bBytes);      // [BN][BM]
+  // input windows (kTma): two buffers of boxH*boxW*32 floats behind P
+  uint32_t const xPlane = (uint32_t)(p.boxH * p.boxW), xTileBytes = xPlane * 32u * 4u;
+  uint32_t const xTile0 = smem_u32(Psm) + (uint32_t)BN * BM * 4u;
 
   int const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int const numIter = p.numKb;                     // k-blocks per tile
@@ -1091,12 +1146,15 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
     for (int b = 0; b < 3; ++b) { mbar_init(smem_u32(&tFull[b]), 1); mbar_init(smem_u32(&tFree[b]), kEpilogueWarps); }
     mbar_init(smem_u32(&tileDone), kEpilogueWarps);
     mbar_init(smem_u32(&turn[0]), 1); mbar_init(smem_u32(&turn[1]), 1);
+    // an input window is full when its copy has landed (one arrival with the byte count), empty when all eight producer warps are done with it
+    for (int b = 0; b < 2; ++b) { mbar_init(smem_u32(&fullX[b]), 1); mbar_init(smem_u32(&emptyX[b]), 4 * kTsGroups); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == kEpilogueWarps) tmem_alloc(smem_u32(&tmemBase), tmemCols);
   if ((int)threadIdx.x < p.a.FH * p.a.FW) {
     int const fh = (int)threadIdx.x % p.a.FH, fw = (int)threadIdx.x / p.a.FH;
-    tapLut[threadIdx.x] = make_int2((fw * p.a.dx - p.a.pl) * p.a.H + fh * p.a.dy - p.a.pt, fh | (fw << 5));
+    if (kTma) tapLut[threadIdx.x] = make_int2(fw * p.a.dx * p.boxH + fh * p.a.dy, fh | (fw << 5));
+    else      tapLut[threadIdx.x] = make_int2((fw * p.a.dx - p.a.pl) * p.a.H + fh * p.a.dy - p.a.pt, fh | (fw << 5));
   }
   tc_fence_before();
   __syncthreads();
@@ -1116,7 +1174,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
     bool const preMask = p.e.mask != nullptr && !singleTile;
     for (int ts = 0; ts < myTiles && ok; ++ts) {
       int const tile = (int)blockIdx.x + ts * (int)gridDim.x;
-      int const m0 = (tile / p.tilesN) * BM, n0 = (tile % p.tilesN) * BN;
+      int const tm = tile / p.tilesN, n0 = (tile % p.tilesN) * BN;
       int const qFirst = (int)(((long long)ts * numIter) & 1);          // the issuer that owns the tile's first k-block
       int const chainsF = ts_chains<kSplit>(numIter, 0), chainsS = ts_chains<kSplit>(numIter, 1);   // of that issuer, of the other
       bool fresh = true;                              // P holds nothing of this tile yet
@@ -1127,8 +1185,8 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
       int const nEndT = min(BN, p.N - n0);
       float const* mkRow = p.e.mask;
       if (preMask) {
-        int const m = min(m0 + warp * 32 + lane, p.M - 1);
-        mkRow += ((long long)(m / p.e.P) * p.e.Ktot + n0) * p.e.P + m % p.e.P;
+        RowPos const rp = row_pos(p, tm, warp * 32 + lane);     // a row that does not exist reads (and discards) the mask of a pixel that does
+        mkRow += ((long long)rp.img * p.e.Ktot + n0) * p.e.P + rp.pix;
       }
       int lc = 0;                                     // batches of sixteen mask columns fetched so far
       for (int c = 0; c < chainsF && ok; ++c) {
@@ -1188,11 +1246,11 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
         // one tile per CTA: the producers have nothing left to do and share the stores
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&tileDone));
-        ts_store_tile(p, Psm, warp, lane, 0, 1 + kTsGroups, m0, n0);
+        ts_store_tile(p, Psm, warp, lane, 0, 1 + kTsGroups, tm, n0);
       } else {
         // the tile is complete in P: store it while the tensor core works on the next tile (its chains wait in
         // their T buffers until this is through)
-        ts_store_tile(p, Psm, warp, lane, 0, 1, m0, n0, preMask ? mbits : nullptr);
+        ts_store_tile(p, Psm, warp, lane, 0, 1, tm, n0, preMask ? mbits : nullptr);
       }
     }
   } else if (warp == kEpilogueWarps || warp == kEpilogueWarps + 1) {
@@ -1265,7 +1323,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
           if (takeTurns) mbar_arrive(smem_u32(&turn[q ^ 1]));    // all twelve are queued: the other issuer may queue its k-block behind them
           umma_commit(smem_u32(&emptyA[q]));      // frees the A stage; its producers pass the news on for the B stage
           phA ^= 1u;
-          sb += 2; if (sb >= kTsBStages) sb -= kTsBStages;
+          sb += 2; if (sb >= nB) sb -= nB;
           if (chunkEnd) umma_commit(smem_u32(&tFull[g % 3]));   // chain complete: hand it to the drain warps
         }
         gBase += chainsF + chainsS;
@@ -1285,7 +1343,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
           if (!mbar_wait(smem_u32(&emptyB[sb]), ph)) { atomicExch(p.status, 8); ok = false; break; }
           mbar_arrive_expect_tx(smem_u32(&fullB[sb]), bBytes);
           bulk_copy_g2s(smem_u32(smem + (size_t)sb * bBytes), src + (size_t)it * (bBytes / 4), bBytes, smem_u32(&fullB[sb]));
-          if (++sb == kTsBStages) { sb = 0; ph ^= 1u; }
+          if (++sb == nB) { sb = 0; ph ^= 1u; }
         }
       }
     }
@@ -1303,7 +1361,29 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
         if (!mbar_wait(smem_u32(&fullB[sb]), phB)) { atomicExch(p.status, 7); break; }
         if (gi >= kTsGroups && !mbar_wait(smem_u32(&fullA[sa]), (uint32_t)(((gi >> 1) - 1) & 1))) { atomicExch(p.status, 9); break; }
         mbar_arrive(smem_u32(&fullA[sa]));
-        if (++sb == kTsBStages) { sb = 0; phB ^= 1u; }
+        if (++sb == nB) { sb = 0; phB ^= 1u; }
+      }
+    }
+    __syncwarp();
+  } else if (warp == kTsWindowWarp) {
+    // ============================== input windows: tensor-map copies ==============================
+    // Window xs (numbered over the CTA's life: one per tile and block of 32 channels) goes into buffer xs & 1 as soon as
+    // the producers have let go of window xs - 2, i.e. as far ahead of its use as two buffers allow.
+    if (kTma && lane == 0) {
+      int const numCb = numIter / (p.a.FH * p.a.FW);
+      int const per = p.tilesH * p.tilesW;
+      long long xs = 0;
+      bool ok = true;
+      for (int ts = 0; ts < myTiles && ok; ++ts) {
+        int const tm = ((int)blockIdx.x + ts * (int)gridDim.x) / p.tilesN;
+        int const n = tm / per, t = tm - n * per, wb = t / p.tilesH, hb = t - wb * p.tilesH;
+        int const c0 = hb * p.bh - p.a.pt - p.rowOff, c1 = wb * p.bw - p.a.pl;      // c0 is a multiple of four: bh and pt + rowOff are
+        for (int cb = 0; cb < numCb; ++cb, ++xs) {
+          int const buf = (int)(xs & 1);
+          if (xs >= 2 && !mbar_wait(smem_u32(&emptyX[buf]), (uint32_t)(((xs >> 1) - 1) & 1))) { atomicExch(p.status, 12); ok = false; break; }
+          mbar_arrive_expect_tx(smem_u32(&fullX[buf]), xTileBytes);
+          tma_load_4d(xTile0 + (uint32_t)buf * xTileBytes, &xmap, c0, c1, cb * 32, n, smem_u32(&fullX[buf]));
+        }
       }
     }
     __syncwarp();
@@ -1318,71 +1398,111 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
     int sbFree = grp;                                   // filter stage of the k-block whose MMAs this group sees complete next
     long long gi = 0;                                   // k-blocks numbered over the CTA's life; this group takes gi % 2 == grp
     bool ok = true;
-    for (int ts = 0; ts < myTiles && ok; ++ts) {
-      int const tile = (int)blockIdx.x + ts * (int)gridDim.x;
-      int const m = (tile / p.tilesN) * BM + quarter * 32 + lane;
-      uint32_t hm = 0, wm = 0;                          // tap rows / columns inside the image for this pixel
-      float const* xq = p.a.ptr;
-      if (m < p.M) {
-        int const ho = m % p.a.Ho, q = m / p.a.Ho, wo = q % p.a.Wo, n = q / p.a.Wo;
-        xq += (long long)n * p.a.imgStride + (long long)wo * p.a.sx * p.a.H + ho * p.a.sy;
-        for (int fh = 0; fh < p.a.FH; ++fh) { int h = ho * p.a.sy + fh * p.a.dy - p.a.pt; if (h >= 0 && h < p.a.H) hm |= 1u << fh; }
-        for (int fw = 0; fw < p.a.FW; ++fw) { int w = wo * p.a.sx + fw * p.a.dx - p.a.pl; if (w >= 0 && w < p.a.W) wm |= 1u << fw; }
+
+    // One k-block, from the 32 gathered values of this thread's pixel to the arrival on the A-stage barrier.
+    auto hand_over = [&](float const (&v)[32], int it) -> bool {
+      uint32_t hi[32];
+#pragma unroll
+      for (int k = 0; k < 32; ++k) hi[k] = __float_as_uint(tf32_hi(v[k]));
+      if (!mbar_wait(smem_u32(&emptyA[grp]), phE)) { atomicExch(p.status, 1); return false; }
+      phE ^= 1u;
+      if (herald && gi + it >= kTsGroups) {                      // the MMAs of the k-block two before this one are complete: its filter stage is free too
+        mbar_arrive(smem_u32(&emptyB[sbFree]));
+        sbFree += kTsGroups; if (sbFree >= nB) sbFree -= nB;
       }
-      for (int it = (int)((gi ^ grp) & 1); it < numIter; it += kTsGroups) {
-        int const r = it * BK;
-        float v[32];
-        if (p.chanFast) {
-          // the whole k-block is one filter tap and 32 consecutive channels: one validity test, constant stride.  The taps
-          // of a channel block follow one another, so that the lines fetched for one tap are still in L1 for the next.
-          int const tp = it % taps, c0 = (it / taps) * 32;
-          int2 const te = tapLut[tp];
-          uint32_t const e = (uint32_t)te.y;
-          bool const on = ((hm >> (e & 31u)) & (wm >> (e >> 5)) & 1u) != 0;
-          // unconditional loads (a pixel outside the image reads the start of the tensor instead and discards it):
-          // nothing for the compiler to predicate or branch around, all 32 in flight together
-          float const* const q = on ? xq + ((long long)c0 * HW + te.x) : p.a.ptr;
-          long long const step = on ? (long long)HW : 0;
+      tc_fence_after();
+      tmem_st32(aAddr, hi);
+      if (kSplit) {
 #pragma unroll
-          for (int k = 0; k < 32; ++k) v[k] = __ldg(q + k * step);
-          if (!on) {
+        for (int k = 0; k < 32; ++k) hi[k] = __float_as_uint(v[k] - __uint_as_float(hi[k]));
+        tmem_st32(aAddr + 32u, hi);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&fullA[grp]));
+      return true;
+    };
+
+    if (kTma) {
+      // This thread's pixel inside the input window: row dh + rowOff, column dw (a lane beyond the box reads the window's
+      // first element; its row is never stored).  A k-block is one filter tap and 32 channels: 32 loads from shared memory
+      // one channel plane apart.
+      int const row = quarter * 32 + lane;
+      int const dw = row / p.bh, dh = row - dw * p.bh;
+      uint32_t const laneOff = dw < p.bw ? (uint32_t)(dw * p.boxH + dh + p.rowOff) * 4u : 0u;
+      uint32_t const planeBytes = xPlane * 4u;
+      int const numCb = numIter / taps;
+      long long xs = 0;
+      for (int ts = 0; ts < myTiles && ok; ++ts) {
+        int const par = (int)((gi ^ grp) & 1);              // this group's k-blocks of the tile: it % 2 == par
+        for (int cb = 0; cb < numCb && ok; ++cb, ++xs) {
+          int const buf = (int)(xs & 1);
+          // every producer warp waits for and lets go of every window, whether or not one of its k-blocks falls into it:
+          // a warp can then never arrive twice in one phase of the window's barrier
+          if (!mbar_wait(smem_u32(&fullX[buf]), (uint32_t)((xs >> 1) & 1))) { atomicExch(p.status, 11); ok = false; break; }
+          uint32_t const base = xTile0 + (uint32_t)buf * xTileBytes + laneOff;
+          int const itBeg = cb * taps;
+          for (int it = itBeg + ((itBeg ^ par) & 1); it < itBeg + taps; it += kTsGroups) {
+            uint32_t const src = base + (uint32_t)tapLut[it - itBeg].x * 4u;
+            float v[32];
 #pragma unroll
-            for (int k = 0; k < 32; ++k) v[k] = 0.f;
+            for (int k = 0; k < 32; ++k) v[k] = lds32(src + (uint32_t)k * planeBytes);
+            if (!hand_over(v, it)) { ok = false; break; }
           }
-        } else {
-          int tap = r % taps, ch = r / taps;
-#pragma unroll
-          for (int k = 0; k < 32; ++k) {
-            int2 const te = tapLut[tap];
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&emptyX[buf]));     // this warp's loads from the window have completed (their values were used above)
+        }
+        gi += numIter;
+      }
+    } else {
+      for (int ts = 0; ts < myTiles && ok; ++ts) {
+        int const tile = (int)blockIdx.x + ts * (int)gridDim.x;
+        int const m = (tile / p.tilesN) * BM + quarter * 32 + lane;
+        uint32_t hm = 0, wm = 0;                          // tap rows / columns inside the image for this pixel
+        float const* xq = p.a.ptr;
+        if (m < p.M) {
+          int const ho = m % p.a.Ho, q = m / p.a.Ho, wo = q % p.a.Wo, n = q / p.a.Wo;
+          xq += (long long)n * p.a.imgStride + (long long)wo * p.a.sx * p.a.H + ho * p.a.sy;
+          for (int fh = 0; fh < p.a.FH; ++fh) { int h = ho * p.a.sy + fh * p.a.dy - p.a.pt; if (h >= 0 && h < p.a.H) hm |= 1u << fh; }
+          for (int fw = 0; fw < p.a.FW; ++fw) { int w = wo * p.a.sx + fw * p.a.dx - p.a.pl; if (w >= 0 && w < p.a.W) wm |= 1u << fw; }
+        }
+        for (int it = (int)((gi ^ grp) & 1); it < numIter; it += kTsGroups) {
+          int const r = it * BK;
+          float v[32];
+          if (p.chanFast) {
+            // the whole k-block is one filter tap and 32 consecutive channels: one validity test, constant stride.  The taps
+            // of a channel block follow one another, so that the lines fetched for one tap are still in L1 for the next.
+            int const tp = it % taps, c0 = (it / taps) * 32;
+            int2 const te = tapLut[tp];
             uint32_t const e = (uint32_t)te.y;
-            bool const on = ((r + k < p.R ? 1u : 0u) & (hm >> (e & 31u)) & (wm >> (e >> 5))) != 0;
-            v[k] = 0.f;
-            ldg32_if(v[k], xq + (ch * HW + te.x), on);
-            if (++tap == taps) { tap = 0; ++ch; }
+            bool const on = ((hm >> (e & 31u)) & (wm >> (e >> 5)) & 1u) != 0;
+            // unconditional loads (a pixel outside the image reads the start of the tensor instead and discards it):
+            // nothing for the compiler to predicate or branch around, all 32 in flight together
+            float const* const q = on ? xq + ((long long)c0 * HW + te.x) : p.a.ptr;
+            long long const step = on ? (long long)HW : 0;
+#pragma unroll
+            for (int k = 0; k < 32; ++k) v[k] = __ldg(q + k * step);
+            if (!on) {
+#pragma unroll
+              for (int k = 0; k < 32; ++k) v[k] = 0.f;
+            }
+          } else {
+            int tap = r % taps, ch = r / taps;
+#pragma unroll
+            for (int k = 0; k < 32; ++k) {
+              int2 const te = tapLut[tap];
+              uint32_t const e = (uint32_t)te.y;
+              bool const on = ((r + k < p.R ? 1u : 0u) & (hm >> (e & 31u)) & (wm >> (e >> 5))) != 0;
+              v[k] = 0.f;
+              ldg32_if(v[k], xq + (ch * HW + te.x), on);
+              if (++tap == taps) { tap = 0; ++ch; }
+            }
           }
+          if (!hand_over(v, it)) { ok = false; break; }
         }
-        uint32_t hi[32];
-#pragma unroll
-        for (int k = 0; k < 32; ++k) hi[k] = __float_as_uint(tf32_hi(v[k]));
-        if (!mbar_wait(smem_u32(&emptyA[grp]), phE)) { atomicExch(p.status, 1); ok = false; break; }
-        phE ^= 1u;
-        if (herald && gi + it >= kTsGroups) {                      // the MMAs of the k-block two before this one are complete: its filter stage is free too
-          mbar_arrive(smem_u32(&emptyB[sbFree]));
-          sbFree += kTsGroups; if (sbFree >= kTsBStages) sbFree -= kTsBStages;
-        }
-        tc_fence_after();
-        tmem_st32(aAddr, hi);
-        if (kSplit) {
-#pragma unroll
-          for (int k = 0; k < 32; ++k) hi[k] = __float_as_uint(v[k] - __uint_as_float(hi[k]));
-          tmem_st32(aAddr + 32u, hi);
-        }
-        tmem_st_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&fullA[grp]));
+        gi += numIter;
       }
-      gi += numIter;
     }
     if (singleTile && ok && myTiles > 0) {
       bool done = mbar_wait(smem_u32(&tileDone), 0);
@@ -1391,7 +1511,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p)
       if (!done) { if (lane == 0) atomicExch(p.status, 3); }
       else {
         int const tile = (int)blockIdx.x;
-        ts_store_tile(p, Psm, quarter, lane, 1 + grp, 1 + kTsGroups, (tile / p.tilesN) * BM, (tile % p.tilesN) * BN);
+        ts_store_tile(p, Psm, quarter, lane, 1 + grp, 1 + kTsGroups, tile / p.tilesN, (tile % p.tilesN) * BN);
       }
       tc_fence_before();
     }
@@ -1648,6 +1768,75 @@ int launch(vlb_ctx* ctx, Params& p, int splits, char const* where)
   return vlb::check_launch(ctx, where);
 }
 
+// cuTensorMapEncodeTiled through the runtime's driver entry point query (the library does not link libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, cuuint64_t const*, cuuint64_t const*,
+                                  cuuint32_t const*, cuuint32_t const*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled()
+{
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)f;
+    else
+      cudaGetLastError();
+  }
+  return fn;
+}
+
+// Decides whether conv_ts_kernel can take its input windows from tensor-map copies and, if so, fills the box geometry in p,
+// the tensor map and the shared-memory size.  Needs: reduction in blocks of 32 channels, unit stride, input rows a multiple
+// of four elements (every global stride of a tensor map is a multiple of 16 bytes) on a 16-byte aligned base, an output
+// map that boxes of bh x bw <= 128 pixels (bh a multiple of four, so that every box's window starts on a 16-byte boundary)
+// cover with at least 80% of the tile rows in use, and room in shared memory for two windows.
+bool plan_windows(vlb_ctx* ctx, Params& p, CUtensorMap* map, size_t* smemBytes, bool split3)
+{
+  Operand const& a = p.a;
+  if (ctx->testSwitch & 2) return false;
+  if (!p.chanFast || a.sy != 1 || a.sx != 1 || a.H % 4 != 0 || !aligned16(a.ptr)) return false;
+  EncodeTiledFn const encode = encode_tiled();
+  if (!encode) return false;
+  int const Ho = a.Ho, Wo = a.Wo;
+  int bestBh = 0, bestBw = 0;
+  double bestUtil = 0.0;
+  for (int bh = 4; bh <= 128 && bh < Ho + 4; bh += 4) {
+    int const bw = std::min(128 / bh, Wo);
+    // share of the 128 tile rows that are output pixels, over all boxes of an image
+    double const util = (double)Ho * Wo / ((double)vlb::ceil_div(Ho, bh) * (double)vlb::ceil_div(Wo, bw) * 128.0);
+    if (util >= bestUtil - 1e-9) { bestUtil = util; bestBh = bh; bestBw = bw; }      // on a tie the taller box: longer contiguous runs
+  }
+  if (bestBh == 0 || bestUtil < 0.8) return false;
+  int const rowOff = (4 - a.pt % 4) % 4;
+  int const boxH = (rowOff + bestBh + (a.FH - 1) * a.dy + 3) / 4 * 4, boxW = bestBw + (a.FW - 1) * a.dx;
+  if (boxH > 256 || boxW > 256) return false;
+  size_t const xTileBytes = (size_t)boxH * boxW * 32 * 4;
+  size_t const bBytes = (size_t)(split3 ? 2 : 1) * p.BN * BK * 4, pBytes = sizeof(float) * (size_t)p.BN * BM;
+  size_t const limit = 227 * 1024 - 1536;      // what one block may have, less the kernel's static shared memory
+  int nB = 0;
+  for (int n = kTsBStages; n >= 3 && !nB; --n)
+    if ((size_t)n * bBytes + pBytes + 2 * xTileBytes + 1024 <= limit) nB = n;
+  if (!nB) return false;
+  long long const images = (long long)p.M / ((long long)Ho * Wo);
+  cuuint64_t const dims[4] = {(cuuint64_t)a.H, (cuuint64_t)a.W, (cuuint64_t)a.C, (cuuint64_t)images};
+  cuuint64_t const strides[3] = {(cuuint64_t)a.H * 4, (cuuint64_t)a.H * a.W * 4, (cuuint64_t)a.imgStride * 4};
+  cuuint32_t const box[4] = {(cuuint32_t)boxH, (cuuint32_t)boxW, 32u, 1u};
+  cuuint32_t const estr[4] = {1u, 1u, 1u, 1u};
+  CUresult const r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(a.ptr), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  p.tma = 1; p.bh = bestBh; p.bw = bestBw; p.tilesH = vlb::ceil_div(Ho, bestBh); p.tilesW = vlb::ceil_div(Wo, bestBw);
+  p.boxH = boxH; p.boxW = boxW; p.rowOff = rowOff; p.bStages = nB;
+  p.tilesM = (int)(images * p.tilesH * p.tilesW);
+  *smemBytes = (size_t)nB * bBytes + pBytes + 2 * xTileBytes + 1024;
+  return true;
+}
+
 // fprop / stride-1 dgrad with the gathered operand in tensor memory (p.bTiles set, p.a a convolution operand).
 int launch_ts(vlb_ctx* ctx, Params& p, char const* where)
 {
@@ -1656,8 +1845,12 @@ int launch_ts(vlb_ctx* ctx, Params& p, char const* where)
   p.testSwitch = ctx->testSwitch;
   // at least 120 KB, so that two CTAs (each allocating all 512 TMEM columns) never share an SM
   size_t smemBytes = (size_t)kTsBStages * (split3 ? 2u : 1u) * (size_t)p.BN * BK * 4 + sizeof(float) * (size_t)p.BN * BM + 1024;
-  if (smemBytes < 120u * 1024u) smemBytes = 120u * 1024u;
+  p.bStages = kTsBStages;
   p.tilesM = vlb::ceil_div(p.M, BM); p.tilesN = vlb::ceil_div(p.N, p.BN);
+  CUtensorMap map;
+  memset(&map, 0, sizeof(map));
+  bool const windows = plan_windows(ctx, p, &map, &smemBytes, split3);
+  if (smemBytes < 120u * 1024u) smemBytes = 120u * 1024u;
   long long const numTiles = (long long)p.tilesM * p.tilesN;
   if (numTiles >= (1LL << 31)) return VLB_Unsupported;
   // Persistent: one CTA per SM walks the tiles, so that the pipeline never drains between tiles and a tile is stored
@@ -1673,11 +1866,21 @@ int launch_ts(vlb_ctx* ctx, Params& p, char const* where)
     cudaEventRecord(rec.start, ctx->stream);
   }
   if (split3) {
-    e = allow_large_smem<conv_ts_kernel<true>>(ctx->device);
-    if (e == cudaSuccess) conv_ts_kernel<true><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p);
+    if (windows) {
+      e = allow_large_smem<conv_ts_kernel<true, true>>(ctx->device);
+      if (e == cudaSuccess) conv_ts_kernel<true, true><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p, map);
+    } else {
+      e = allow_large_smem<conv_ts_kernel<true, false>>(ctx->device);
+      if (e == cudaSuccess) conv_ts_kernel<true, false><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p, map);
+    }
   } else {
-    e = allow_large_smem<conv_ts_kernel<false>>(ctx->device);
-    if (e == cudaSuccess) conv_ts_kernel<false><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p);
+    if (windows) {
+      e = allow_large_smem<conv_ts_kernel<false, true>>(ctx->device);
+      if (e == cudaSuccess) conv_ts_kernel<false, true><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p, map);
+    } else {
+      e = allow_large_smem<conv_ts_kernel<false, false>>(ctx->device);
+      if (e == cudaSuccess) conv_ts_kernel<false, false><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p, map);
+    }
   }
   if (record) { cudaEventRecord(rec.stop, ctx->stream); ctx->prof.push_back(rec); }
   if (e != cudaSuccess) { cudaGetLastError(); return vlb::set_error(ctx, VLB_Cuda, cudaGetErrorString(e)); }
