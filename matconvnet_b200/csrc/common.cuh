@@ -101,6 +101,36 @@ inline unsigned grid_for(size_t n, int threads, int maxBlocks = 148 * 16)
 
 }  // namespace vlb
 
+#ifdef __CUDACC__
+namespace vlb {
+// Exclusive prefix sum of v[0..n) in place by a whole block of kThreads threads (a multiple of 32, at most 1024);
+// warpSums: 32 ints of shared memory.  Ends with a block barrier.
+template <int kThreads>
+__device__ inline void block_exclusive_scan(int* v, int n, int* warpSums)
+{
+  int const tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int const per = (n + kThreads - 1) / kThreads;
+  int const beg = min(tid * per, n), end = min(beg + per, n);
+  int sum = 0;
+  for (int i = beg; i < end; ++i) sum += v[i];
+  int incl = sum;
+  for (int o = 1; o < 32; o <<= 1) { int t = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += t; }
+  if (lane == 31) warpSums[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int const w = lane < kThreads / 32 ? warpSums[lane] : 0;
+    int wi = w;
+    for (int o = 1; o < 32; o <<= 1) { int t = __shfl_up_sync(0xffffffffu, wi, o); if (lane >= o) wi += t; }
+    warpSums[lane] = wi - w;      // exclusive over the warps
+  }
+  __syncthreads();
+  int run = warpSums[warp] + incl - sum;
+  for (int i = beg; i < end; ++i) { int c = v[i]; v[i] = run; run += c; }
+  __syncthreads();
+}
+}  // namespace vlb
+#endif
+
 #define VLB_REQUIRE(ctx, cond, msg) \
   do { if (!(cond)) return vlb::set_error((ctx), VLB_IllegalArgument, (msg)); } while (0)
 

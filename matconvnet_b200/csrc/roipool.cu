@@ -10,16 +10,18 @@
 // column are contiguous.  The scan order for the arg-max is the CPU's (w outer, h inner,
 // first strictly greater).
 //
-// Backward is a gather, not the reference GPU code's thread-per-bin atomicAdd scatter
-// (bits/impl/nnroipooling_gpu.cu:114-246): one CTA owns a slab of channels of one image and keeps
-// it in shared memory.  It (1) finds the arg-max of every bin of every ROI of its image from the
-// slab, as 16-bit pixel indices in shared memory, (2) tabulates for every ROI which bin rows cover
-// each map row and which bin columns cover each map column, and (3) lets every (pixel, channel)
-// of the slab walk the ROIs in ascending order and add the derivatives of the bins that routed
-// to it, bin columns outer and bin rows inner -- the order in which the CPU loop reaches that
-// element (bits/nnroipooling.cu:239-300), so the sums are the CPU's bit for bit, run-to-run
-// identical, and dX is written exactly once: no atomics, no zero fill, no scratch in global
-// memory; x, dY and dX cross HBM once.  Maps too large for the slab take the scatter kernel.
+// Backward (max) does not scatter with atomics as the reference GPU code does
+// (bits/impl/nnroipooling_gpu.cu:114-246).  One CTA takes one image and a few channels.  All its
+// threads first find, from the input plane in shared memory, the arg-max pixel of every bin of every
+// ROI of the image; then one warp per channel walks the bins in the order of the CPU loop (ROI, bin
+// column, bin row; bits/nnroipooling.cu:239-300), 32 at a time, and adds their derivatives to a copy
+// of the channel's dX plane in shared memory -- lanes whose bins routed to the same pixel one after
+// the other in lane order (__match_any_sync), all others at once.  The work is proportional to the
+// number of bins, the sums are the CPU's bit for bit and identical from run to run, dX is written
+// exactly once (no zero fill), and nothing but x, dY and dX crosses HBM.  Backward (avg), where every
+// pixel of a bin receives a share, is a gather: every pixel of a channel slab walks the ROIs that
+// cover it, in the same order.  Maps too large for shared memory take a zero fill and an atomic
+// scatter.
 #include "common.cuh"
 #include <math.h>
 
@@ -320,6 +322,143 @@ roipool_bwd_gather_kernel(float* __restrict__ dx, float const* __restrict__ x, f
   }
 }
 
+// ---- backward (max): arg-max of every bin in parallel, then one warp per channel adds the bins' derivatives to their
+// pixels in bin order (see the header comment) ----
+constexpr int kOrdThreads = 256;
+
+// Shared memory (bytes): plane float[HW] | dxs float[G*HW] | binRow uint32[RB*S0] | binCol uint32[RB*S1] | roiIdx int[RB] |
+// am uint16[G*RB*bins]
+__host__ __device__ inline size_t ordered_smem(int G, int RB, int HW, int S0, int S1)
+{
+  return 4 * (size_t)HW * (1 + G) + 4 * (size_t)RB * (S0 + S1) + 4 * (size_t)RB + 2 * (size_t)G * RB * S0 * S1 + 64;
+}
+
+__global__ void __launch_bounds__(kOrdThreads)
+roipool_bwd_ordered_kernel(float* __restrict__ dx, float const* __restrict__ x, float const* __restrict__ rois,
+                           float const* __restrict__ dy, RoiParams p, int G, int RB, int groups)
+{
+  extern __shared__ __align__(16) uint8_t sm[];
+  __shared__ int sCount, sNext;
+  int const HW = p.H * p.W, bins = p.S0 * p.S1;
+  int const img = blockIdx.x / groups, c0 = (blockIdx.x % groups) * G;
+  int const nch = min(G, p.C - c0);
+  int const tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  float* plane = reinterpret_cast<float*>(sm);
+  float* dxs = plane + HW;
+  uint32_t* binRow = reinterpret_cast<uint32_t*>(dxs + (size_t)G * HW);
+  uint32_t* binCol = binRow + (size_t)RB * p.S0;
+  int* roiIdx = reinterpret_cast<int*>(binCol + (size_t)RB * p.S1);
+  uint16_t* am = reinterpret_cast<uint16_t*>(roiIdx + RB);
+  float const invBins = 1.f / (float)bins, invS0 = 1.f / (float)p.S0;
+
+  for (int i = tid; i < nch * HW; i += kOrdThreads) dxs[i] = 0.f;
+  int base = 0;
+  while (true) {
+    __syncthreads();
+    if (tid < 32) {
+      // the next RB ROIs of this image, in ascending order
+      int cnt = 0, r = base;
+      while (r < p.numROIs && cnt < RB) {
+        int const rr = r + lane;
+        bool mine = false;
+        if (rr < p.numROIs) {
+          int image = (int)rois[5 * (size_t)rr];
+          mine = min(max(image - 1, 0), p.N - 1) == img;
+        }
+        unsigned const m = __ballot_sync(0xffffffffu, mine);
+        int const pos = cnt + __popc(m & ((1u << lane) - 1u));
+        if (mine && pos < RB) roiIdx[pos] = rr;
+        int const tot = __popc(m);
+        if (cnt + tot > RB) {                           // the batch is full inside this group of 32: resume behind its last member
+          r += (int)__fns(m, 0, RB - cnt) + 1;
+          cnt = RB;
+          break;
+        }
+        cnt += tot; r += 32;
+      }
+      if (lane == 0) { sCount = cnt; sNext = min(r, p.numROIs); }
+    }
+    __syncthreads();
+    int const nb = sCount;
+    base = sNext;
+    if (nb == 0) break;
+    // bin geometry of every ROI of the batch, once (the double-precision part of the arithmetic)
+    for (int i = tid; i < nb * (p.S0 + p.S1); i += kOrdThreads) {
+      bool const isRow = i < nb * p.S0;
+      int const k = isRow ? i : i - nb * p.S0;
+      int const S = isRow ? p.S0 : p.S1;
+      int const j = k / S, b = k - j * S;
+      RoiGeom g = roi_geom(rois + 5 * (size_t)roiIdx[j], p);
+      int s, e;
+      roi_bin(b, isRow ? g.bin_h : g.bin_w, isRow ? g.start_h : g.start_w, isRow ? p.H : p.W, s, e);
+      (isRow ? binRow : binCol)[k] = (uint32_t)s | ((uint32_t)e << 16);
+    }
+    int const total = nb * bins;
+    // arg-max of every bin of every channel of the group, all threads: CPU scan order, first strictly greater, none for
+    // an empty or all -inf / NaN bin
+    for (int cc = 0; cc < nch; ++cc) {
+      __syncthreads();                                 // geometry written; the plane is no longer read
+      float const* const src = x + (size_t)HW * ((size_t)(c0 + cc) + (size_t)p.C * img);
+      for (int i = tid; i < HW; i += kOrdThreads) plane[i] = src[i];
+      __syncthreads();
+      uint16_t* const amc = am + (size_t)cc * RB * bins;
+      for (int b = tid; b < total; b += kOrdThreads) {
+        // quotients by way of a float reciprocal: exact for these small operands, a fraction of the cost of integer division
+        int const j = (int)(((float)b + 0.5f) * invBins), t = b - j * bins;
+        int const pw = (int)(((float)t + 0.5f) * invS0), ph = t - pw * p.S0;
+        uint32_t const rs = binRow[j * p.S0 + ph], cs = binCol[j * p.S1 + pw];
+        int const hs = (int)(rs & 0xFFFFu), he = (int)(rs >> 16), ws = (int)(cs & 0xFFFFu), we = (int)(cs >> 16);
+        float best = -INFINITY;
+        uint32_t where = kNoBin;
+        for (int w = ws; w < we; ++w)
+          for (int h = hs; h < he; ++h) {
+            float a = plane[w * p.H + h];
+            if (a > best) { best = a; where = (uint32_t)(w * p.H + h); }
+          }
+        amc[b] = (uint16_t)where;
+      }
+    }
+    __syncthreads();
+    // One warp per channel walks the bins in order -- ROI, bin column, bin row: the order of the CPU loop -- 32 at a time.
+    // Lanes whose bins routed to the same pixel add one after the other, in lane order; all others add at once.
+    for (int cc = warp; cc < nch; cc += kOrdThreads / 32) {
+      uint16_t const* const amc = am + (size_t)cc * RB * bins;
+      float* const acc = dxs + (size_t)cc * HW;
+      // eight steps' derivatives are fetched together, so that their latency passes once per eight steps
+      for (int b0 = 0; b0 < total; b0 += 32 * 8) {
+        uint32_t wh[8];
+        float vv[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          int const b = b0 + 32 * u + lane;
+          wh[u] = b < total ? amc[b] : kNoBin;
+          vv[u] = 0.f;
+          if (wh[u] != kNoBin) {
+            int const j = (int)(((float)b + 0.5f) * invBins);
+            vv[u] = __ldg(dy + (size_t)(b - j * bins) + (size_t)bins * ((size_t)(c0 + cc) + (size_t)p.C * roiIdx[j]));
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          if (b0 + 32 * u >= total) break;
+          uint32_t const where = wh[u];
+          unsigned const peers = __match_any_sync(0xffffffffu, where);
+          int const rank = where != kNoBin ? __popc(peers & ((1u << lane) - 1u)) : -1;
+          int const rounds = __reduce_max_sync(0xffffffffu, rank);
+          for (int r = 0; r <= rounds; ++r) {
+            if (rank == r) acc[where] = __fadd_rn(acc[where], vv[u]);
+            __syncwarp();
+          }
+        }
+      }
+    }
+    if (base >= p.numROIs) break;
+  }
+  __syncthreads();
+  // dX is written once: the sums, or zeros where no bin routed (and for an image that no ROI names)
+  for (int i = tid; i < nch * HW; i += kOrdThreads) dx[(size_t)HW * ((size_t)c0 + (size_t)p.C * img) + i] = dxs[i];
+}
+
 int make_params(vlb_ctx* ctx, RoiParams* p, int H, int W, int C, int N, int numROIs, int S0, int S1,
                 double const* tf, int method)
 {
@@ -382,6 +521,32 @@ int vlb_roipool_backward(vlb_ctx* ctx, float* dX, float const* X, float const* r
     bool const isMax = method == VLB_POOL_MAX;
     long long const HW = (long long)H * W;
     size_t const budget = 200 * 1024;
+    if (isMax && HW < 65535 && S0 <= 255 && S1 <= 255 && numROIs > 0) {
+      // channel groups so that about four CTAs come to every SM; as many ROIs per batch as the rest of 56 KB of shared
+      // memory per CTA holds (four CTAs resident per SM)
+      long long const planes = (long long)N * C;
+      int G = (int)((planes + 4LL * ctx->smCount - 1) / (4LL * ctx->smCount));
+      if (G < 1) G = 1;
+      if (G > kOrdThreads / 32) G = kOrdThreads / 32;
+      if (G > C) G = C;
+      size_t const budget = 56 * 1024;
+      size_t const fixed = ordered_smem(G, 0, (int)HW, S0, S1), perRoi = ordered_smem(G, 1, (int)HW, S0, S1) - fixed;
+      long long RB = fixed < budget ? (long long)((budget - fixed) / perRoi) : 0;
+      if (RB > numROIs) RB = numROIs;
+      if (RB >= 8 || RB == numROIs) {
+        int const groups = vlb::ceil_div(C, G);
+        size_t const smem = ordered_smem(G, (int)RB, (int)HW, S0, S1);
+        static bool attrDone[64] = {};
+        if (!(ctx->device < 64 && attrDone[ctx->device])) {
+          cudaError_t ea = vlb::allow_max_dynamic_smem(roipool_bwd_ordered_kernel);
+          if (ea != cudaSuccess) { cudaGetLastError(); return vlb::set_error(ctx, VLB_Cuda, cudaGetErrorString(ea)); }
+          if (ctx->device < 64) attrDone[ctx->device] = true;
+        }
+        roipool_bwd_ordered_kernel<<<(unsigned)(N * groups), kOrdThreads, smem, ctx->stream>>>(dX, X, rois, dY, p, G, (int)RB, groups);
+        VLB_LAUNCHED(ctx, 1);
+        return vlb::check_launch(ctx, "vlb_roipool_backward");
+      }
+    }
     if (HW < 65535 && S0 <= 255 && S1 <= 255 && numROIs > 0) {
       int CH = (int)((64 * 1024) / (4 * HW));
       if (CH > C) CH = C;

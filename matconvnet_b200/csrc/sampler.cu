@@ -124,41 +124,36 @@ __global__ void sampler_kernel(float* __restrict__ y, float* __restrict__ dx, fl
 }
 
 // ---- backward-to-data as a gather (see the header comment) ----
-constexpr int kGatherThreads = 512;    // two CTAs per SM: one inverts its grid while the other streams its channels
+constexpr int kGatherThreads = 1024;
 constexpr int kMaxList = 48;          // taps of one grid on one input pixel beyond which the scatter path is used
-constexpr int kChan = 8;              // channels accumulated together per input pixel
+constexpr int kMaxQPerThread = 4;     // output pixels per thread whose taps and grid derivative are kept in registers
 
+// Shared memory (bytes): cur int[HW] | entW float[4Q] | stage float[2][HW + Q] (x plane and dy plane of a channel, double
+// buffered) | entQ uint16[4Q]
 __host__ __device__ inline size_t gather_smem(int HW, int Q)
 {
-  return sizeof(int) * (size_t)HW + (sizeof(float) + sizeof(uint16_t)) * 4 * (size_t)Q + 64;
+  return sizeof(int) * (size_t)HW + (sizeof(float) + sizeof(uint16_t)) * 4 * (size_t)Q + sizeof(float) * 2 * ((size_t)HW + Q) + 64;
 }
 
-// Exclusive prefix sum of v[0..n) in place by the whole block; returns nothing, total not needed.
-__device__ void block_exclusive_scan(int* v, int n, int* warpSums)
+__device__ __forceinline__ void cp_async16(uint32_t dst, void const* src)
+{ asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory"); }
+__device__ __forceinline__ void cp_async4(uint32_t dst, void const* src)
+{ asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.commit_group;\n cp.async.wait_group 0;" ::: "memory"); }
+
+// n floats global -> shared by the whole block, asynchronously (16-byte pieces when both sides allow)
+__device__ __forceinline__ void stage_plane(float* dst, float const* src, int n)
 {
-  int const tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  int const per = (n + kGatherThreads - 1) / kGatherThreads;
-  int const beg = min(tid * per, n), end = min(beg + per, n);
-  int sum = 0;
-  for (int i = beg; i < end; ++i) sum += v[i];
-  int incl = sum;
-  for (int o = 1; o < 32; o <<= 1) { int t = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += t; }
-  if (lane == 31) warpSums[warp] = incl;
-  __syncthreads();
-  if (warp == 0) {
-    int w = lane < kGatherThreads / 32 ? warpSums[lane] : 0;
-    int wi = w;
-    for (int o = 1; o < 32; o <<= 1) { int t = __shfl_up_sync(0xffffffffu, wi, o); if (lane >= o) wi += t; }
-    warpSums[lane] = wi - w;      // exclusive over the warps
+  uint32_t const d = (uint32_t)__cvta_generic_to_shared(dst);
+  if ((n & 3) == 0 && ((((uintptr_t)src) | d) & 15) == 0) {
+    for (int i = threadIdx.x; i < n / 4; i += kGatherThreads) cp_async16(d + 16u * i, src + 4 * i);
+  } else {
+    for (int i = threadIdx.x; i < n; i += kGatherThreads) cp_async4(d + 4u * i, src + i);
   }
-  __syncthreads();
-  int run = warpSums[warp] + incl - sum;
-  for (int i = beg; i < end; ++i) { int c = v[i]; v[i] = run; run += c; }
-  __syncthreads();
 }
 
 template <bool kWantGrid>
-__global__ void __launch_bounds__(kGatherThreads, 2)
+__global__ void __launch_bounds__(kGatherThreads, 1)
 sampler_bwd_gather_kernel(float* __restrict__ dx, float* __restrict__ dgrid, float const* __restrict__ x,
                           float const* __restrict__ grid, float const* __restrict__ dy, int H, int W, int C, int N, int Q, int Ng,
                           int chunks, int CH)
@@ -167,8 +162,9 @@ sampler_bwd_gather_kernel(float* __restrict__ dx, float* __restrict__ dgrid, flo
   __shared__ int warpSums[32];
   int const HW = H * W, tid = threadIdx.x;
   int* cur = reinterpret_cast<int*>(sm);                                   // [HW]  list ends (starts before the fill)
-  float* entW = reinterpret_cast<float*>(sm + sizeof(int) * (size_t)HW);   // [4Q]  tap weight wwx*wwy
-  uint16_t* entQ = reinterpret_cast<uint16_t*>(entW + 4 * (size_t)Q);     // [4Q]  output pixel
+  float* entW = reinterpret_cast<float*>(cur + HW);                       // [4Q]  tap weight wwx*wwy
+  float* stage = entW + 4 * (size_t)Q;                                    // [2][HW + Q]
+  uint16_t* entQ = reinterpret_cast<uint16_t*>(stage + 2 * ((size_t)HW + Q));   // [4Q]  output pixel
   int const group = Ng / N;
   int const img = blockIdx.x / chunks, c0 = (blockIdx.x % chunks) * CH, nch = min(CH, C - c0);
   size_t const imgOff = (size_t)HW * C * (size_t)img;
@@ -176,6 +172,10 @@ sampler_bwd_gather_kernel(float* __restrict__ dx, float* __restrict__ dgrid, flo
   for (int gi = 0; gi < group; ++gi) {
     int const n = img * group + gi;
     float2 const* gr = reinterpret_cast<float2 const*>(grid) + (size_t)Q * n;
+    float const* const dyn = dy + (size_t)Q * C * (size_t)n;
+    // the first channel's planes start travelling while the grid is inverted
+    stage_plane(stage, x + imgOff + (size_t)HW * c0, HW);
+    stage_plane(stage + HW, dyn + (size_t)Q * c0, Q);
     // ---- invert the grid: count, scan, fill, sort
     for (int i = tid; i < HW; i += kGatherThreads) cur[i] = 0;
     __syncthreads();
@@ -197,7 +197,7 @@ sampler_bwd_gather_kernel(float* __restrict__ dx, float* __restrict__ dgrid, flo
     for (int i = tid; i < HW; i += kGatherThreads) tooLong |= cur[i] > kMaxList;
     bool const scatter = __syncthreads_or(tooLong) != 0;
     if (!scatter) {
-      block_exclusive_scan(cur, HW, warpSums);
+      vlb::block_exclusive_scan<kGatherThreads>(cur, HW, warpSums);
       for (int q = tid; q < Q; q += kGatherThreads) {
         float2 const gv = gr[q];
         Taps t = make_taps(gv.x, gv.y, H, W);
@@ -218,7 +218,7 @@ sampler_bwd_gather_kernel(float* __restrict__ dx, float* __restrict__ dgrid, flo
         }
       }
       __syncthreads();
-      // every input pixel: sort its list by output pixel, then add it up for kChan channels at a time
+      // every input pixel sorts its list by output pixel
       for (int pix = tid; pix < HW; pix += kGatherThreads) {
         int const beg = pix == 0 ? 0 : cur[pix - 1], end = cur[pix];
         for (int a = beg + 1; a < end; ++a) {
@@ -228,26 +228,93 @@ sampler_bwd_gather_kernel(float* __restrict__ dx, float* __restrict__ dgrid, flo
           while (b >= beg && entQ[b] > kq) { entQ[b + 1] = entQ[b]; entW[b + 1] = entW[b]; --b; }
           entQ[b + 1] = kq; entW[b + 1] = kw;
         }
-        for (int cb = 0; cb < nch; cb += kChan) {
-          float acc[kChan];
-          float* const dst = dx + imgOff + (size_t)HW * (c0 + cb) + pix;
-          float const* const src = dy + (size_t)Q * ((size_t)(c0 + cb) + (size_t)C * n);
+      }
+      // ---- channel by channel from shared memory: the planes of channel cc + 1 travel while channel cc is computed
+      float accGy[kMaxQPerThread], accGx[kMaxQPerThread];
+      // this thread's output pixels: first tap's offset in the plane, which of the four taps exist, the two fractions
+      int tapBase[kMaxQPerThread], tapOk[kMaxQPerThread];
+      float tapWx[kMaxQPerThread], tapWy[kMaxQPerThread];
 #pragma unroll
-          for (int k = 0; k < kChan; ++k) acc[k] = (gi > 0 && cb + k < nch) ? dst[(size_t)HW * k] : 0.f;
-          for (int e = beg; e < end; ++e) {
-            float const w = entW[e];
-            float const* const s = src + entQ[e];
-#pragma unroll
-            for (int k = 0; k < kChan; ++k)
-              if (cb + k < nch) acc[k] = __fadd_rn(acc[k], __fmul_rn(w, __ldg(s + (size_t)Q * k)));
+      for (int k = 0; k < kMaxQPerThread; ++k) {
+        accGy[k] = 0.f; accGx[k] = 0.f;
+        tapBase[k] = 0; tapOk[k] = 0; tapWx[k] = 0.f; tapWy[k] = 0.f;
+        int const q = tid + k * kGatherThreads;
+        if (kWantGrid && q < Q) {
+          float2 const gv = gr[q];
+          Taps t = make_taps(gv.x, gv.y, H, W);
+          tapWx[k] = t.wx; tapWy[k] = t.wy;
+          if (t.inside) {
+            tapBase[k] = t.sy + t.sx * H;
+            tapOk[k] = 1 | (t.sy + 1 < H ? 2 : 0) | (t.sx + 1 < W ? 4 : 0) | ((t.sy + 1 < H && t.sx + 1 < W) ? 8 : 0);   // bit ii + 2*j
           }
+        }
+      }
+      float const sclY = __fmul_rn(0.5f, (float)(H - 1)), sclX = __fmul_rn(0.5f, (float)(W - 1));
+      for (int cc = 0; cc < nch; ++cc) {
+        float const* const xs = stage + (size_t)(cc & 1) * (HW + Q);
+        float const* const ds = xs + HW;
+        cp_async_wait_all();
+        __syncthreads();                    // this channel's planes have landed; the other buffer is no longer read
+        if (cc + 1 < nch) {
+          float* const nx = stage + (size_t)((cc + 1) & 1) * (HW + Q);
+          stage_plane(nx, x + imgOff + (size_t)HW * (c0 + cc + 1), HW);
+          stage_plane(nx + HW, dyn + (size_t)Q * (c0 + cc + 1), Q);
+        }
+        // data gradient: every input pixel adds up its list in output-pixel order
+        float* const dxc = dx + imgOff + (size_t)HW * (c0 + cc);
+        for (int pix = tid; pix < HW; pix += kGatherThreads) {
+          int const beg = pix == 0 ? 0 : cur[pix - 1], end = cur[pix];
+          float acc = gi > 0 ? dxc[pix] : 0.f;
+          for (int e = beg; e < end; ++e) acc = __fadd_rn(acc, __fmul_rn(entW[e], ds[entQ[e]]));
+          dxc[pix] = acc;
+        }
+        // grid derivative: this channel's term of every output pixel, the taps in the CPU loop's order (column offset j
+        // outer, row offset i inner; bits/nnbilinearsampler.cu:98-128).  (2j-1)*wwy*dy*x is evaluated left to right there;
+        // a negation is exact, so the two magnitudes wwy0*dy and wwy1*dy serve all four taps.
+        if (kWantGrid) {
 #pragma unroll
-          for (int k = 0; k < kChan; ++k)
-            if (cb + k < nch) dst[(size_t)HW * k] = acc[k];
+          for (int k = 0; k < kMaxQPerThread; ++k) {
+            int const q = tid + k * kGatherThreads;
+            if (q < Q && tapOk[k]) {
+              float const d = ds[q];
+              float const wx1 = tapWx[k], wy1 = tapWy[k], wx0 = __fadd_rn(1.f, -wx1), wy0 = __fadd_rn(1.f, -wy1);
+              float const ty0 = __fmul_rn(wy0, d), ty1 = __fmul_rn(wy1, d), tx0 = __fmul_rn(wx0, d), tx1 = __fmul_rn(wx1, d);
+              float const* const xp = xs + tapBase[k];
+              int const ok = tapOk[k];
+              float dgx = 0.f, dgy = 0.f;
+              {                                         // j = 0, i = 0: dgx -= wwy0*d*x, dgy -= wwx0*d*x
+                float const xv = xp[0];
+                dgx = __fsub_rn(dgx, __fmul_rn(ty0, xv)); dgy = __fsub_rn(dgy, __fmul_rn(tx0, xv));
+              }
+              if (ok & 2) {                             // j = 0, i = 1: dgx -= wwy1*d*x, dgy += wwx0*d*x
+                float const xv = xp[1];
+                dgx = __fsub_rn(dgx, __fmul_rn(ty1, xv)); dgy = __fadd_rn(dgy, __fmul_rn(tx0, xv));
+              }
+              if (ok & 4) {                             // j = 1, i = 0: dgx += wwy0*d*x, dgy -= wwx1*d*x
+                float const xv = xp[H];
+                dgx = __fadd_rn(dgx, __fmul_rn(ty0, xv)); dgy = __fsub_rn(dgy, __fmul_rn(tx1, xv));
+              }
+              if (ok & 8) {                             // j = 1, i = 1: dgx += wwy1*d*x, dgy += wwx1*d*x
+                float const xv = xp[H + 1];
+                dgx = __fadd_rn(dgx, __fmul_rn(ty1, xv)); dgy = __fadd_rn(dgy, __fmul_rn(tx1, xv));
+              }
+              accGy[k] = __fadd_rn(accGy[k], __fmul_rn(sclY, dgy));
+              accGx[k] = __fadd_rn(accGx[k], __fmul_rn(sclX, dgx));
+            }
+          }
+        }
+      }
+      if (kWantGrid) {
+#pragma unroll
+        for (int k = 0; k < kMaxQPerThread; ++k) {
+          int const q = tid + k * kGatherThreads;
+          if (q < Q) reinterpret_cast<float2*>(dgrid)[(size_t)Q * n + q] = make_float2(accGy[k], accGx[k]);
         }
       }
     } else {
-      // a grid that piles its taps on a few input pixels: zero (first grid of the image) and scatter with atomics
+      // a grid that piles its taps on a few input pixels: zero (first grid of the image) and scatter with atomics, from
+      // global memory
+      cp_async_wait_all();
       if (gi == 0) {
         for (size_t i = tid; i < (size_t)HW * nch; i += kGatherThreads) dx[imgOff + (size_t)HW * c0 + i] = 0.f;
       }
@@ -255,64 +322,40 @@ sampler_bwd_gather_kernel(float* __restrict__ dx, float* __restrict__ dgrid, flo
       for (int q = tid; q < Q; q += kGatherThreads) {
         float2 const gv = gr[q];
         Taps t = make_taps(gv.x, gv.y, H, W);
-        if (!t.inside) continue;
         float const wwx[2] = {__fadd_rn(1.f, -t.wx), t.wx};
         float const wwy[2] = {__fadd_rn(1.f, -t.wy), t.wy};
-        for (int c = 0; c < nch; ++c) {
-          float const d = dy[q + (size_t)Q * ((size_t)(c0 + c) + (size_t)C * n)];
-          float* const dxz = dx + imgOff + (size_t)HW * (c0 + c);
+        float accGy = 0.f, accGx = 0.f;
+        for (int c = 0; c < (kWantGrid ? C : nch); ++c) {
+          int const ch = kWantGrid ? c : c0 + c;
+          float const d = dyn[q + (size_t)Q * ch];
+          float* const dxz = dx + imgOff + (size_t)HW * ch;
+          float const* const xz = x + imgOff + (size_t)HW * ch;
+          bool const mine = ch >= c0 && ch < c0 + nch;
+          float dgx = 0.f, dgy = 0.f;
 #pragma unroll
           for (int j = 0; j < 2; ++j)
 #pragma unroll
             for (int ii = 0; ii < 2; ++ii) {
               int const ssy = t.sy + ii, ssx = t.sx + j;
-              if (ssy < H && ssx < W) atomicAdd(dxz + ssy + ssx * H, __fmul_rn(__fmul_rn(wwx[j], wwy[ii]), d));
-            }
-        }
-      }
-    }
-    __syncthreads();       // this grid's additions to dX are visible to the block before the next grid reads them
-    if (kWantGrid) {
-      // ---- the grid derivative, channels in ascending order (the sequence of sampler_kernel<1>)
-      for (int q = tid; q < Q; q += kGatherThreads) {
-        float2 const gv = gr[q];
-        Taps t = make_taps(gv.x, gv.y, H, W);
-        float const wwx[2] = {__fadd_rn(1.f, -t.wx), t.wx};
-        float const wwy[2] = {__fadd_rn(1.f, -t.wy), t.wy};
-        bool ok[2][2];
-        int idx[2][2];
-#pragma unroll
-        for (int j = 0; j < 2; ++j)
-#pragma unroll
-          for (int ii = 0; ii < 2; ++ii) {
-            int const ssy = t.sy + ii, ssx = t.sx + j;
-            ok[j][ii] = t.inside && ssy < H && ssx < W;
-            idx[j][ii] = ok[j][ii] ? ssy + ssx * H : 0;
-          }
-        float const* xz = x + imgOff;
-        float const* dz = dy + q + (size_t)Q * C * (size_t)n;
-        float accGy = 0.f, accGx = 0.f;
-        for (int c = 0; c < C; ++c) {
-          float const d = dz[0];
-          float dgx = 0.f, dgy = 0.f;
-#pragma unroll
-          for (int j = 0; j < 2; ++j)
-#pragma unroll
-            for (int ii = 0; ii < 2; ++ii)
-              if (ok[j][ii]) {
-                float const xv = __ldg(xz + idx[j][ii]);
-                float const sj = j ? 1.f : -1.f, si = ii ? 1.f : -1.f;
-                dgx = __fadd_rn(dgx, __fmul_rn(__fmul_rn(__fmul_rn(sj, wwy[ii]), d), xv));
-                dgy = __fadd_rn(dgy, __fmul_rn(__fmul_rn(__fmul_rn(si, wwx[j]), d), xv));
+              if (t.inside && ssy < H && ssx < W) {
+                if (mine) atomicAdd(dxz + ssy + ssx * H, __fmul_rn(__fmul_rn(wwx[j], wwy[ii]), d));
+                if (kWantGrid) {
+                  float const xv = __ldg(xz + ssy + ssx * H);
+                  float const sj = j ? 1.f : -1.f, si = ii ? 1.f : -1.f;
+                  dgx = __fadd_rn(dgx, __fmul_rn(__fmul_rn(__fmul_rn(sj, wwy[ii]), d), xv));
+                  dgy = __fadd_rn(dgy, __fmul_rn(__fmul_rn(__fmul_rn(si, wwx[j]), d), xv));
+                }
               }
-          accGy = __fadd_rn(accGy, __fmul_rn(__fmul_rn(0.5f, (float)(H - 1)), dgy));
-          accGx = __fadd_rn(accGx, __fmul_rn(__fmul_rn(0.5f, (float)(W - 1)), dgx));
-          xz += HW; dz += Q;
+            }
+          if (kWantGrid) {
+            accGy = __fadd_rn(accGy, __fmul_rn(__fmul_rn(0.5f, (float)(H - 1)), dgy));
+            accGx = __fadd_rn(accGx, __fmul_rn(__fmul_rn(0.5f, (float)(W - 1)), dgx));
+          }
         }
-        reinterpret_cast<float2*>(dgrid)[(size_t)Q * n + q] = make_float2(accGy, accGx);
+        if (kWantGrid) reinterpret_cast<float2*>(dgrid)[(size_t)Q * n + q] = make_float2(accGy, accGx);
       }
     }
-    __syncthreads();       // the lists are rebuilt for the next grid
+    __syncthreads();       // this grid's additions to dX are visible to the block, and the lists free, before the next grid
   }
 }
 
@@ -355,13 +398,12 @@ int vlb_sampler_backward(vlb_ctx* ctx, float* dX, float* dGrid, float const* X, 
   VLB_REQUIRE(ctx, ((((uintptr_t)grid) | ((uintptr_t)dGrid)) & 7) == 0, "sampler_backward: grid must be 8-byte aligned");
   if (!dX && !dGrid) return VLB_Success;
   int const Qo = Ho * Wo, HWi = H * W;
-  if (dX && Qo <= 65535 && gather_smem(HWi, Qo) <= 200 * 1024) {      // at most half of that leaves room for two CTAs per SM
+  if (dX && Qo <= 65535 && Qo <= kMaxQPerThread * kGatherThreads && gather_smem(HWi, Qo) <= 200 * 1024) {
     // gather: one CTA per image; with fewer images than SMs the channels are shared out among several CTAs per image,
     // and the grid derivative (which runs over all channels of an output pixel in order) is left to the other kernel
     int chunks = 1;
-    if (N < ctx->smCount) chunks = vlb::ceil_div(2 * ctx->smCount, N);
+    if (N < ctx->smCount) chunks = vlb::ceil_div(ctx->smCount, N);
     int CH = vlb::ceil_div(C, chunks);
-    CH = vlb::ceil_div(CH, kChan) * kChan;
     chunks = vlb::ceil_div(C, CH);
     bool const fusedGrid = dGrid != nullptr && chunks == 1;
     static bool attrDone[64] = {};
