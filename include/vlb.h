@@ -265,6 +265,23 @@ int vlb_taccum(vlb_ctx* ctx, float* Y, double alpha, float const* A, double beta
 int vlb_sgd_update(vlb_ctx* ctx, float* W, float* M, float const* G, size_t n, double gradMult, double decay,
                    double momentum, double lr, int nesterov);
 
+/* ---- blocks of the reference's other ImageNet models (AlexNet, VGG-F/M/S; examples/imagenet/cnn_imagenet_init.m) ---- */
+/* Cross-channel local response normalisation, vl::nn::LRN (bits/nnnormalize.hpp:20-44; matlab/vl_nnnormalize.m, PARAM =
+ * [normDepth kappa alpha beta]): y_t = x_t * (kappa + alpha * sum of x_q^2 over q in [t - m1, t + m2])^-beta with
+ * m1 = (normDepth - 1) / 2, m2 = normDepth - m1 - 1 (bits/nnnormalize.cu:143-226).  The power is powf, as in the reference's
+ * GPU kernels; the reference's CPU code approximates it.  dX is overwritten; backward uses the context's scratch. */
+int vlb_lrn_forward(vlb_ctx* ctx, float* Y, float const* X, int H, int W, int C, int N, int normDepth, double kappa,
+                    double alpha, double beta);
+int vlb_lrn_backward(vlb_ctx* ctx, float* dX, float const* X, float const* dY, int H, int W, int C, int N, int normDepth,
+                     double kappa, double alpha, double beta);
+/* matlab/vl_nnsoftmax.m: softmax over the channels; backward takes X (not Y), as the MATLAB function does. */
+int vlb_softmax_forward(vlb_ctx* ctx, float* Y, float const* X, int H, int W, int C, int N);
+int vlb_softmax_backward(vlb_ctx* ctx, float* dX, float const* X, float const* dY, int H, int W, int C, int N);
+/* matlab/vl_nndropout.m: mask = 1/(1-rate) * (u >= rate) with u uniform in [0, 1) from a counter-based generator (element i
+ * of a call with the same seed always gets the same number); the forward and backward passes are Y = mask .* X (vlb_mul). */
+int vlb_dropout_mask(vlb_ctx* ctx, float* mask, size_t n, double rate, unsigned long long seed);
+int vlb_mul(vlb_ctx* ctx, float* Y, float const* A, float const* B, size_t n);
+
 /* The trainer's other solvers after the gradient exchange (examples/+solver/adagrad.m, adadelta.m, adam.m, rmsprop.m, called
  * at examples/cnn_train.m:503-507), each fused with the pass before it: g = gradMult*G + decay*W (cnn_train.m:481-483), then
  * the solver's element-wise update of W and of its state, every MATLAB operation rounded to single as MATLAB does.

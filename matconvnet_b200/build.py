@@ -14,7 +14,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libvlb.so")
 
-SOURCES = ["ctx.cu", "elementwise.cu", "pool.cu", "bnorm.cu", "roipool.cu", "sampler.cu",
+SOURCES = ["ctx.cu", "elementwise.cu", "normalize.cu", "pool.cu", "bnorm.cu", "roipool.cu", "sampler.cu",
            "conv.cu", "conv_simt.cu", "conv_small.cu", "conv_tc.cu"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -107,6 +107,12 @@ SIGNATURES = {
     "vlb_scale": (_I, [_P, _P, _D, _Z]),
     "vlb_taccum": (_I, [_P, _P, _D, _P, _D, _P, _Z]),
     "vlb_sgd_update": (_I, [_P, _P, _P, _P, _Z, _D, _D, _D, _D, _I]),
+    "vlb_lrn_forward": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _D, _D, _D]),
+    "vlb_lrn_backward": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _D, _D, _D]),
+    "vlb_softmax_forward": (_I, [_P, _P, _P, _I, _I, _I, _I]),
+    "vlb_softmax_backward": (_I, [_P, _P, _P, _P, _I, _I, _I, _I]),
+    "vlb_dropout_mask": (_I, [_P, _P, _Z, _D, C.c_ulonglong]),
+    "vlb_mul": (_I, [_P, _P, _P, _P, _Z]),
     "vlb_solver_update": (_I, [_P, _I, _P, _P, _P, _P, _Z, _D, _D, _D, C.POINTER(SolverOpts), C.c_longlong]),
 }
 

@@ -1006,7 +1006,7 @@ __device__ __forceinline__ int ts_chains(int numIter, int second)
   return kSplit ? (nOwn + kTsDrainEvery - 1) / kTsDrainEvery : (nOwn > 0 ? 1 : 0);
 }
 
-// 4-D tensor-map copy global -> shared (tile mode, no multicast: the map covers this GPU's own memory only); completion
+// 4-D tensor-map copy global -> shared (tile mode, one destination CTA; the map covers this GPU's own memory only); completion
 // is signalled on the mbarrier as transaction bytes.  The innermost coordinate c0 must be a multiple of four elements.
 __device__ __forceinline__ void tma_load_4d(uint32_t dstSmem, void const* map, int c0, int c1, int c2, int c3, uint32_t bar)
 {

@@ -384,6 +384,59 @@ def vl_nnrelu(x, dzdy=None, ctx=None):
     return out
 
 
+def vl_nnnormalize(x, param, dzdy=None, ctx=None):
+    """Y = VL_NNNORMALIZE(X, PARAM) / DZDX = VL_NNNORMALIZE(X, PARAM, DZDY), PARAM = [N KAPPA ALPHA BETA]
+    (matlab/vl_nnnormalize.m; gateway matlab/src/vl_nnnormalize.cu:117-162)."""
+    ctx = _ctx(ctx)
+    x, dzdy = _need(x, "x"), _need(dzdy, "dzdy")
+    param = [float(v) for v in np.asarray(param, dtype=np.float64).ravel()]
+    if len(param) != 4:
+        raise ValueError("PARAM is not a plain 4 vector.")
+    depth = int(param[0])
+    if depth < 1:
+        raise ValueError("The normalization depth is smaller than 1.")
+    H, W, Cc, N = mat.shape4(x)
+    out = mat.empty((H, W, Cc, N), x.device)
+    if dzdy is None:
+        ctx.check(ctx.lib.vlb_lrn_forward(ctx.handle, mat.ptr(out), mat.ptr(x), H, W, Cc, N, depth, param[1], param[2], param[3]))
+    else:
+        if mat.shape4(dzdy) != (H, W, Cc, N):
+            raise ValueError("DZDY dimensions are incompatible with X.")
+        ctx.check(ctx.lib.vlb_lrn_backward(ctx.handle, mat.ptr(out), mat.ptr(x), mat.ptr(dzdy), H, W, Cc, N, depth, param[1],
+                                           param[2], param[3]))
+    return out
+
+
+def vl_nnsoftmax(x, dzdy=None, ctx=None):
+    """Y = VL_NNSOFTMAX(X) / DZDX = VL_NNSOFTMAX(X, DZDY): softmax over the channels (matlab/vl_nnsoftmax.m)."""
+    ctx = _ctx(ctx)
+    x, dzdy = _need(x, "x"), _need(dzdy, "dzdy")
+    H, W, Cc, N = mat.shape4(x)
+    out = mat.empty((H, W, Cc, N), x.device)
+    if dzdy is None:
+        ctx.check(ctx.lib.vlb_softmax_forward(ctx.handle, mat.ptr(out), mat.ptr(x), H, W, Cc, N))
+    else:
+        ctx.check(ctx.lib.vlb_softmax_backward(ctx.handle, mat.ptr(out), mat.ptr(x), mat.ptr(dzdy), H, W, Cc, N))
+    return out
+
+
+def vl_nndropout(x, dzdy=None, rate=0.5, mask=None, seed=0, ctx=None):
+    """[Y, MASK] = VL_NNDROPOUT(X, 'rate', R) / [DZDX, MASK] = VL_NNDROPOUT(X, DZDY, 'mask', MASK) (matlab/vl_nndropout.m).
+    MASK is drawn when it is not given: 1/(1-rate) where a uniform number is at least the rate, else 0; `seed` selects the
+    stream of the counter-based generator (the reference draws from MATLAB's global stream)."""
+    ctx = _ctx(ctx)
+    x, dzdy, mask = _need(x, "x"), _need(dzdy, "dzdy"), _need(mask, "mask")
+    if mask is None:
+        mask = mat.empty(x.shape, x.device)
+        ctx.check(ctx.lib.vlb_dropout_mask(ctx.handle, mat.ptr(mask), x.numel(), float(rate), int(seed)))
+    elif mask.numel() != x.numel():
+        raise ValueError("MASK and X do not have the same number of elements.")
+    src = x if dzdy is None else dzdy
+    out = mat.empty(x.shape, x.device)
+    ctx.check(ctx.lib.vlb_mul(ctx.handle, mat.ptr(out), mat.ptr(mask), mat.ptr(src), x.numel()))
+    return out, mask
+
+
 def vl_nnsoftmaxloss(x, c, dzdy=None, ctx=None):
     """matlab/vl_nnsoftmaxloss.m:56-84 with one class label (1-based) per image."""
     ctx = _ctx(ctx)

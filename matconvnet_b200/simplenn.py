@@ -4,6 +4,8 @@ A network is ``{'layers': [layer, ...]}`` with layers shaped like the reference'
   {'type': 'conv', 'weights': [f, b], 'stride': s, 'pad': p, 'dilate': d}
   {'type': 'relu'}   {'type': 'pool', 'method': 'max'|'avg', 'pool': [ph pw], 'stride': s, 'pad': p}
   {'type': 'bnorm', 'weights': [g, b, moments], 'epsilon': e}   {'type': 'softmaxloss', 'class': c}
+  {'type': 'normalize', 'param': [N kappa alpha beta]}   {'type': 'softmax'}
+  {'type': 'dropout', 'rate': r}  (training mode: a new mask per forward pass, kept in res[i]['aux'] for the backward pass)
 ``vl_simplenn(net, x, dzdy)`` runs the forward pass storing every intermediate (res[i]['x'],
 vl_simplenn.m:294-398) and, when dzdy is given, the backward pass in reverse order
 (vl_simplenn.m:404-524), leaving res[i]['dzdx'] and, for parametrised layers, res[i]['dzdw'].
@@ -75,6 +77,14 @@ def vl_simplenn(net, x, dzdy=None, res=None, on_dzdw=None, ctx=None, skip_forwar
                                                                epsilon=_get(l, "epsilon", 1e-4), ctx=ctx)
             elif t == "softmaxloss":
                 res[i + 1]["x"] = nn.vl_nnsoftmaxloss(xi, l["class"], ctx=ctx)
+            elif t == "normalize":
+                res[i + 1]["x"] = nn.vl_nnnormalize(xi, l["param"], ctx=ctx)
+            elif t == "softmax":
+                res[i + 1]["x"] = nn.vl_nnsoftmax(xi, ctx=ctx)
+            elif t == "dropout":
+                # vl_simplenn.m:352-360 (training mode); 'seed' makes the mask reproducible, the layer index separates layers
+                res[i + 1]["x"], res[i]["aux"] = nn.vl_nndropout(xi, rate=_get(l, "rate", 0.5),
+                                                                 seed=(int(_get(l, "seed", 0)) << 16) + i, ctx=ctx)
             else:
                 raise ValueError("Unknown layer type '%s'." % t)
     if dzdy is None:
@@ -114,6 +124,12 @@ def vl_simplenn(net, x, dzdy=None, res=None, on_dzdw=None, ctx=None, skip_forwar
             res[i]["dzdx"], res[i]["dzdw"] = dx, [dg, db, mom]
         elif t == "softmaxloss":
             res[i]["dzdx"] = nn.vl_nnsoftmaxloss(xi, l["class"], d, ctx=ctx)
+        elif t == "normalize":
+            res[i]["dzdx"] = nn.vl_nnnormalize(xi, l["param"], d, ctx=ctx)
+        elif t == "softmax":
+            res[i]["dzdx"] = nn.vl_nnsoftmax(xi, d, ctx=ctx)
+        elif t == "dropout":
+            res[i]["dzdx"], _ = nn.vl_nndropout(xi, d, mask=res[i]["aux"], ctx=ctx)      # vl_simplenn.m:466-473
         else:
             raise ValueError("Unknown layer type '%s'." % t)
         if on_dzdw is not None and res[i]["dzdw"] is not None:

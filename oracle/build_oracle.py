@@ -29,7 +29,7 @@ ORACLE_SO = os.path.join(HERE, "libmcn_oracle.so")
 
 REF_SOURCES = [
     "data.cpp", "nnconv.cpp", "nnbias.cpp", "nnfullyconnected.cpp", "nnsubsample.cpp",
-    "nnpooling.cpp", "nnbnorm.cpp", "nnbilinearsampler.cpp", "nnroipooling.cpp",
+    "nnpooling.cpp", "nnbnorm.cpp", "nnbilinearsampler.cpp", "nnroipooling.cpp", "nnnormalize.cpp",
     "impl/im2row_cpu.cpp", "impl/copy_cpu.cpp",
 ]
 CXXFLAGS = ["-std=c++11", "-O2", "-fPIC", "-DENABLE_DOUBLE", "-DNDEBUG", "-ffp-contract=off", "-w"]
@@ -62,7 +62,7 @@ def build_reference(force=False):
         return REF_SO if os.path.exists(REF_SO) else None
     own = [os.path.join(HERE, "ref_capi.cpp"), os.path.join(HERE, "ref_blas.cpp"),
            os.path.join(HERE, "ref_shim", "blas.h")]
-    if not force and _newer(REF_SO, own):
+    if not force and _newer(REF_SO, own + [os.path.abspath(__file__)]):
         return REF_SO
     os.makedirs(REF_OUT, exist_ok=True)
     inc = ["-I", os.path.join(HERE, "ref_shim"), "-I", REF_BITS]

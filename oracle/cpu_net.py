@@ -45,6 +45,10 @@ def layer_forward(backend, glue, l, xi):
         return backend.bnorm_forward(xi, l["weights"][0], l["weights"][1], l.get("epsilon", 1e-4))[0]
     if t == "softmaxloss":
         return glue.softmaxloss_forward(xi, l["class"])
+    if t == "normalize":
+        return glue.lrn_forward(xi, l["param"])
+    if t == "softmax":
+        return glue.softmax(xi)
     raise ValueError(t)
 
 
@@ -68,6 +72,10 @@ def layer_backward(backend, glue, l, xi, d):
         return dx, [dg, db, mom]
     if t == "softmaxloss":
         return glue.softmaxloss_backward(xi, l["class"], float(d)), None
+    if t == "normalize":
+        return glue.lrn_backward(xi, l["param"], d), None
+    if t == "softmax":
+        return glue.softmax(xi, d), None
     raise ValueError(t)
 
 

@@ -136,3 +136,14 @@ int mcno_softmaxloss_forward(int dt, void* loss, void const* x, void const* labe
 int mcno_softmaxloss_backward(int dt, void* dx, void const* x, void const* labels, double dzdy, int H, int W, int C, int N)
 { return dt ? softmaxloss_backward_f64(D(dx), CD(x), CD(labels), dzdy, H, W, C, N)
             : softmaxloss_backward_f32(F(dx), CF(x), CF(labels), (float)dzdy, H, W, C, N); }
+
+int mcno_lrn_forward(int dt, void* y, void const* x, int H, int W, int C, int N, double const* prm)
+{ return dt ? lrn_forward_f64(D(y), CD(x), H, W, C, N, (int)prm[0], prm[1], prm[2], prm[3])
+            : lrn_forward_f32(F(y), CF(x), H, W, C, N, (int)prm[0], prm[1], prm[2], prm[3]); }
+
+int mcno_lrn_backward(int dt, void* dx, void const* x, void const* dy, int H, int W, int C, int N, double const* prm)
+{ return dt ? lrn_backward_f64(D(dx), CD(x), CD(dy), H, W, C, N, (int)prm[0], prm[1], prm[2], prm[3])
+            : lrn_backward_f32(F(dx), CF(x), CF(dy), H, W, C, N, (int)prm[0], prm[1], prm[2], prm[3]); }
+
+int mcno_softmax(int dt, void* out, void const* x, void const* dz, int H, int W, int C, int N)
+{ return dt ? softmax_f64(D(out), CD(x), dz ? CD(dz) : 0, H, W, C, N) : softmax_f32(F(out), CF(x), dz ? CF(dz) : 0, H, W, C, N); }

@@ -788,4 +788,81 @@ static int FN(softmaxloss_backward)(T* dx, T const* x, T const* labels, T dzdy, 
   return 0;
 }
 
+/* vl::nn::LRN (bits/nnnormalize.cu:143-226 forward, :232-400 backward): y_t = x_t * L_t^-beta,
+ * L_t = kappa + alpha * sum of x_q^2 over q in [t - m1, t + m2] clipped to the channels, m1 = (N - 1) / 2,
+ * m2 = N - m1 - 1; the window sum slides (acc += ap^2 - am^2, :169-176).  Backward as the plain loop nest of the
+ * reference (:257-288): dx_t += dz_t * L_t^-beta and dx_q -= dz_t * x_t * x_q * 2*alpha*beta * L_t^(-beta-1) for the q in
+ * t's window.  The reference's compiled CPU code replaces pow by a cubic approximation of log2 and exp2 (:49-125); this
+ * restatement uses the C library's pow, so it agrees with the compiled code only to that approximation's error. */
+static int FN(lrn_forward)(T* y, T const* x, int H, int W, int C, int N, int depth, double kappa, double alpha, double beta)
+{
+  size_t P = (size_t)H * W;
+  int m1 = (depth - 1) / 2, m2 = depth - m1 - 1;
+  for (int n = 0; n < N; ++n)
+    for (size_t p = 0; p < P; ++p) {
+      T const* xp = x + p + P * (size_t)C * n;
+      T* yp = y + p + P * (size_t)C * n;
+      T acc = 0;
+      for (int t = -m2; t < C; ++t) {
+        T ap = 0, am = 0;
+        if (t - m1 - 1 >= 0) am = xp[P * (t - m1 - 1)];
+        if (t + m2 < C) ap = xp[P * (t + m2)];
+        acc += ap * ap - am * am;
+        if (t >= 0) yp[P * t] = xp[P * t] * (T)pow((double)((T)kappa + (T)alpha * acc), -beta);
+      }
+    }
+  return 0;
+}
+
+static int FN(lrn_backward)(T* dx, T const* x, T const* dz, int H, int W, int C, int N, int depth, double kappa,
+                            double alpha, double beta)
+{
+  size_t P = (size_t)H * W;
+  int m1 = (depth - 1) / 2, m2 = depth - m1 - 1;
+  T ab2 = (T)(2 * alpha * beta);
+  for (int n = 0; n < N; ++n)
+    for (size_t p = 0; p < P; ++p) {
+      T const* xp = x + p + P * (size_t)C * n;
+      T const* zp = dz + p + P * (size_t)C * n;
+      T* yp = dx + p + P * (size_t)C * n;
+      T acc = 0;
+      for (int t = 0; t < C; ++t) yp[P * t] = 0;
+      for (int t = -m2; t < C; ++t) {
+        int q1 = t - m1, q2 = t + m2;
+        T ap = 0, am = 0;
+        if (t - m1 - 1 >= 0) am = xp[P * (t - m1 - 1)]; else q1 = 0;
+        if (t + m2 < C) ap = xp[P * (t + m2)]; else q2 = C - 1;
+        acc += ap * ap - am * am;
+        T L = (T)kappa + (T)alpha * acc;
+        T Lbeta = (T)pow((double)L, -beta);
+        T Lbeta1 = Lbeta / L;
+        if (t >= 0) {
+          yp[P * t] += zp[P * t] * Lbeta;
+          for (int q = q1; q <= q2; ++q) yp[P * q] -= zp[P * t] * xp[P * t] * xp[P * q] * ab2 * Lbeta1;
+        }
+      }
+    }
+  return 0;
+}
+
+/* matlab/vl_nnsoftmax.m: E = exp(x - max over channels); Y = E / sum(E); backward Y .* (dzdY - sum(dzdY .* Y)). */
+static int FN(softmax)(T* out, T const* x, T const* dz, int H, int W, int C, int N)
+{
+  size_t P = (size_t)H * W;
+  for (int n = 0; n < N; ++n)
+    for (size_t p = 0; p < P; ++p) {
+      T const* xp = x + p + P * (size_t)C * n;
+      T* op = out + p + P * (size_t)C * n;
+      T xmax = xp[0], se = 0, dot = 0;
+      for (int c = 1; c < C; ++c) if (xp[P * c] > xmax) xmax = xp[P * c];
+      for (int c = 0; c < C; ++c) se += (T)exp(xp[P * c] - xmax);
+      if (dz) for (int c = 0; c < C; ++c) dot += dz[p + P * (size_t)C * n + P * c] * ((T)exp(xp[P * c] - xmax) / se);
+      for (int c = 0; c < C; ++c) {
+        T yv = (T)exp(xp[P * c] - xmax) / se;
+        op[P * c] = dz ? yv * (dz[p + P * (size_t)C * n + P * c] - dot) : yv;
+      }
+    }
+  return 0;
+}
+
 #undef IDX4

@@ -297,6 +297,33 @@ class CpuBackend:
                     "sampler_backward")
         return dx, dgrid
 
+    # --- local response normalisation ---------------------------------
+    def lrn_forward(self, x, param):
+        x = fa(x)
+        y = np.zeros(x.shape, x.dtype, order="F")
+        prm = (C.c_double * 4)(*[float(v) for v in param])
+        fn = self._fn("lrn_forward", [C.c_int, C.c_void_p, C.c_void_p] + [C.c_int] * 4 + [c_double_p])
+        self._check(fn(self._dt(x), _ptr(y), _ptr(x), *x.shape, prm), "lrn_forward")
+        return y
+
+    def lrn_backward(self, x, param, dy):
+        x = fa(x)
+        dy = fa(dy, x.dtype)
+        dx = np.zeros(x.shape, x.dtype, order="F")
+        prm = (C.c_double * 4)(*[float(v) for v in param])
+        fn = self._fn("lrn_backward", [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p] + [C.c_int] * 4 + [c_double_p])
+        self._check(fn(self._dt(x), _ptr(dx), _ptr(x), _ptr(dy), *x.shape, prm), "lrn_backward")
+        return dx
+
+    def softmax(self, x, dzdy=None):
+        """Restatement only (matlab/vl_nnsoftmax.m)."""
+        x = fa(x)
+        dz = None if dzdy is None else fa(dzdy, x.dtype)
+        out = np.zeros(x.shape, x.dtype, order="F")
+        fn = self._fn("softmax", [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p] + [C.c_int] * 4)
+        self._check(fn(self._dt(x), _ptr(out), _ptr(x), _ptr(dz), *x.shape), "softmax")
+        return out
+
     # --- glue (restatement only: the reference has these in MATLAB) ----
     def relu_forward(self, x):
         x = fa(x)

@@ -22,6 +22,7 @@
 #include "nnpooling.hpp"
 #include "nnroipooling.hpp"
 #include "nnbilinearsampler.hpp"
+#include "nnnormalize.hpp"
 #include <array>
 #include <cstring>
 
@@ -252,6 +253,21 @@ int mcnref_sampler_backward(int dtype, void* dx, void* dgrid, void const* x, voi
   if (dgrid) memset(dgrid, 0, gs.getNumElements() * es);
   vl::nn::BilinearSampler op(ctx());
   return op.backward(DX, DG, X, G, DY);
+}
+
+// vl::nn::LRN (bits/nnnormalize.hpp:20-44); prm = {normDepth, kappa, alpha, beta}
+int mcnref_lrn_forward(int dtype, void* y, void const* x, int H, int W, int C, int N, double const* prm)
+{
+  vl::Tensor Y = view(y, dtype, H, W, C, N), X = view(x, dtype, H, W, C, N);
+  vl::nn::LRN op(ctx(), (int)prm[0], prm[1], prm[2], prm[3]);
+  return op.forward(Y, X);
+}
+
+int mcnref_lrn_backward(int dtype, void* dx, void const* x, void const* dy, int H, int W, int C, int N, double const* prm)
+{
+  vl::Tensor DX = view(dx, dtype, H, W, C, N), X = view(x, dtype, H, W, C, N), DY = view(dy, dtype, H, W, C, N);
+  vl::nn::LRN op(ctx(), (int)prm[0], prm[1], prm[2], prm[3]);
+  return op.backward(DX, X, DY);
 }
 
 }  // extern "C"

@@ -337,3 +337,95 @@ def test_roipool_backward_batches_and_fallback(gpu, oracle):
     dyb = np.asfortranarray(rng.integers(-3, 4, yb.shape).astype(np.float32))
     dxb = nn.vl_nnroipool(*_up(mat, xb, rb, dyb), subdivisions=(6, 5), method="max")
     assert bit_equal(mat.to_numpy(dxb), oracle.roipool_backward(xb, rb, dyb, (6, 5), 1.0, "max"))
+
+
+# ------------------------------------------------------------------ LRN, softmax, dropout
+@pytest.mark.parametrize("prm", [[5, 2.0, 1e-4, 0.75], [4, 1.0, 0.1, 0.5], [1, 1.5, 0.5, 1.0], [9, 2.0, 1e-2, 0.6]])
+def test_lrn_vs_oracle(gpu, oracle, reference_backend, prm):
+    """vl_nnnormalize forward and backward on AlexNet's first LRN shape (55x55x96, reduced batch) and a ragged one: within
+    1e-5 of the double-precision checker; within the error of the reference CPU code's approximate power (5e-3) of the
+    compiled reference."""
+    nn, mat, _ = gpu
+    rng = np.random.default_rng(40)
+    for shape in [(55, 55, 96, 2), (7, 5, 13, 3)]:
+        x = np.asfortranarray(rng.standard_normal(shape).astype(np.float32) * 3)
+        dy = np.asfortranarray(rng.standard_normal(shape).astype(np.float32))
+        xd, dyd = _up(mat, x, dy)
+        y = mat.to_numpy(nn.vl_nnnormalize(xd, prm))
+        dx = mat.to_numpy(nn.vl_nnnormalize(xd, prm, dyd))
+        assert rel_l2(y, oracle.lrn_forward(x.astype(np.float64), prm)) < TOL_FAITHFUL
+        assert rel_l2(dx, oracle.lrn_backward(x.astype(np.float64), prm, dy.astype(np.float64))) < TOL_FAITHFUL
+        if reference_backend is not None:
+            assert rel_l2(y, reference_backend.lrn_forward(x, prm)) < 5e-3
+            assert rel_l2(dx, reference_backend.lrn_backward(x, prm, dy)) < 5e-3
+
+
+def test_softmax_and_dropout(gpu, oracle):
+    import torch
+    nn, mat, _ = gpu
+    rng = np.random.default_rng(41)
+    for shape in [(1, 1, 1000, 16), (6, 5, 21, 3)]:
+        x = np.asfortranarray((rng.standard_normal(shape) * 4).astype(np.float32))
+        dy = np.asfortranarray(rng.standard_normal(shape).astype(np.float32))
+        xd, dyd = _up(mat, x, dy)
+        assert rel_l2(mat.to_numpy(nn.vl_nnsoftmax(xd)), oracle.softmax(x.astype(np.float64))) < 1e-6
+        assert rel_l2(mat.to_numpy(nn.vl_nnsoftmax(xd, dyd)), oracle.softmax(x.astype(np.float64), dy.astype(np.float64))) < TOL_FAITHFUL
+    # dropout (matlab/vl_nndropout.m): mask = 1/(1-rate) * (rand >= rate); y = mask .* x; backward = mask .* dzdy
+    x = mat.as_mat(torch.randn(64, 64, 32, 8, device="cuda"))
+    for rate in (0.5, 0.2, 0.0):
+        y, mask = nn.vl_nndropout(x, rate=rate, seed=3)
+        scale = np.float32(1.0 / (1.0 - rate))
+        assert bool(((mask == 0) | (mask == float(scale))).all())
+        kept = float((mask != 0).float().mean())
+        assert abs(kept - (1.0 - rate)) < 4e-3                      # 1M draws: 4e-3 is eight standard deviations
+        assert torch.equal(y, mask * x)
+        y2, mask2 = nn.vl_nndropout(x, rate=rate, seed=3)
+        assert torch.equal(mask, mask2)                             # the same seed gives the same mask
+        if rate > 0:
+            _, mask3 = nn.vl_nndropout(x, rate=rate, seed=4)
+            assert not torch.equal(mask, mask3)
+            agree = float(((mask != 0) == (mask3 != 0)).float().mean())
+            assert abs(agree - (rate ** 2 + (1 - rate) ** 2)) < 6e-3    # independent streams
+        dz = mat.as_mat(torch.randn(64, 64, 32, 8, device="cuda"))
+        dx, _ = nn.vl_nndropout(x, dz, mask=mask)
+        assert torch.equal(dx, mask * dz)
+
+
+def test_alexnet_style_chain_with_lrn_and_dropout(gpu, oracle):
+    """conv -> relu -> LRN -> max-pool -> conv-as-FC -> dropout -> conv-as-FC -> softmax loss through vl_simplenn; every
+    layer replayed from the GPU's own tensors (the dropout layer with the mask the forward pass drew)."""
+    import torch
+    import cpu_net
+    from matconvnet_b200 import models, simplenn
+    nn, mat, ctx = gpu
+    ctx.set_precision(0)
+    rng = np.random.default_rng(42)
+    layers = [models._conv(rng, 3, 3, 3, 16, 1, 1), models._relu(), {"type": "normalize", "param": [5, 2.0, 1e-4, 0.75]},
+              models._pool("max", 2, 2), models._conv(rng, 8, 8, 16, 24, 1, 0), models._relu(),
+              {"type": "dropout", "rate": 0.5, "seed": 7}, models._conv(rng, 1, 1, 24, 5, 1, 0),
+              {"type": "softmaxloss", "class": torch.tensor([1, 5, 2, 3], device="cuda").float()}]
+    net = {"layers": layers}
+    x = mat.from_numpy(np.asfortranarray(rng.standard_normal((16, 16, 3, 4)).astype(np.float32)))
+    res = simplenn.vl_simplenn(net, x, 1.0, ctx=ctx)
+    host = []
+    for l in layers:
+        m = dict(l)
+        if "weights" in l:
+            m["weights"] = [mat.to_numpy(w).astype(np.float64) for w in l["weights"]]
+        if l.get("class") is not None:
+            m["class"] = l["class"].cpu().numpy().astype(np.float64)
+        host.append(m)
+    f64 = lambda t: np.asfortranarray(mat.to_numpy(t), dtype=np.float64)
+    for i, l in enumerate(host):
+        d = res[i + 1]["dzdx"]
+        d = np.float64(d) if np.isscalar(d) else f64(d)
+        if l["type"] == "dropout":
+            mask = f64(res[i]["aux"])
+            assert bit_equal(mat.to_numpy(res[i + 1]["x"]), (mask * f64(res[i]["x"])).astype(np.float32))
+            assert bit_equal(mat.to_numpy(res[i]["dzdx"]), (mask * d).astype(np.float32))
+            continue
+        y = cpu_net.layer_forward(oracle, oracle, l, f64(res[i]["x"]))
+        got = res[i + 1]["x"].cpu().numpy() if l["type"] == "softmaxloss" else mat.to_numpy(res[i + 1]["x"])
+        assert rel_l2(got, y) < TOL_FAITHFUL, (i, l["type"])
+        dx, _ = cpu_net.layer_backward(oracle, oracle, l, f64(res[i]["x"]), d)
+        assert rel_l2(mat.to_numpy(res[i]["dzdx"]), dx) < TOL_FAITHFUL, (i, l["type"])

@@ -266,3 +266,44 @@ def test_softmaxloss_class_zero_skips_the_image(oracle):
     want_dx = y * mass[None, None, None, :] * 0.7 / 4
     assert np.allclose(oracle.softmaxloss_backward(x, lab, 0.7), want_dx, atol=1e-13)
     assert np.all(oracle.softmaxloss_backward(x, lab, 0.7)[:, :, :, 1] == 0)
+
+
+def _lrn_closed_form(x, prm):
+    n, kappa, alpha, beta = int(prm[0]), prm[1], prm[2], prm[3]
+    m1 = (n - 1) // 2
+    m2 = n - m1 - 1
+    L = np.zeros_like(x)
+    for t in range(x.shape[2]):
+        L[:, :, t, :] = kappa + alpha * (x[:, :, max(t - m1, 0):min(t + m2, x.shape[2] - 1) + 1, :] ** 2).sum(axis=2)
+    return x * L ** (-beta)
+
+
+@pytest.mark.parametrize("prm", [[5, 2.0, 1e-3, 0.75], [4, 1.0, 0.1, 0.5], [1, 1.5, 0.5, 1.0], [9, 2.0, 1e-2, 0.6]])
+def test_lrn_restatement_closed_form_and_compiled_reference(oracle, reference_backend, prm):
+    """vl::nn::LRN: the restatement against the definition in double precision (forward) and a numeric derivative
+    (backward); and against the reference's compiled CPU code, which evaluates the power with a cubic approximation of
+    log2 and exp2 (bits/nnnormalize.cu:49-125) and therefore agrees to a few parts in a thousand only (measured: 4e-4 to
+    2e-3, depending on the parameters)."""
+    rng = np.random.default_rng(31)
+    x = np.asfortranarray(rng.standard_normal((4, 3, 7, 2)))
+    dy = np.asfortranarray(rng.standard_normal(x.shape))
+    y = oracle.lrn_forward(x, prm)
+    assert rel_l2(y, _lrn_closed_form(x, prm)) < 1e-14
+    dx = oracle.lrn_backward(x, prm, dy)
+    assert np.allclose(dx, _numder(lambda v: oracle.lrn_forward(v, prm), x, dy), atol=1e-5)
+    if reference_backend is not None:
+        for dt in (np.float32, np.float64):
+            assert rel_l2(reference_backend.lrn_forward(x.astype(dt), prm), y) < 5e-3
+            assert rel_l2(reference_backend.lrn_backward(x.astype(dt), prm, dy.astype(dt)), dx) < 5e-3
+
+
+def test_softmax_restatement(oracle):
+    """matlab/vl_nnsoftmax.m:24-29 in numpy, and its derivative numerically."""
+    rng = np.random.default_rng(32)
+    x = np.asfortranarray(rng.standard_normal((3, 2, 6, 2)) * 3)
+    dy = np.asfortranarray(rng.standard_normal(x.shape))
+    e = np.exp(x - x.max(axis=2, keepdims=True))
+    y = e / e.sum(axis=2, keepdims=True)
+    assert np.allclose(oracle.softmax(x), y, atol=1e-15)
+    assert np.allclose(oracle.softmax(x, dy), y * (dy - (dy * y).sum(axis=2, keepdims=True)), atol=1e-14)
+    assert np.allclose(oracle.softmax(x, dy), _numder(lambda v: oracle.softmax(v), x, dy), atol=1e-5)
