@@ -165,6 +165,12 @@ int vlb_bias_backward(vlb_ctx* ctx, float* dX, double dXMult, float* db, double 
  * (matlab/src/vl_nnbnorm.cu:210-213, bits/nnbnorm.cu:65-70). */
 int vlb_bnorm_forward(vlb_ctx* ctx, float* Y, float* moments /* may be NULL */, float const* X,
                       float const* g, float const* b, int H, int W, int C, int N, double eps);
+/* Training-mode batch normalisation followed by ReLU in one call: Y = max(bnorm(X), 0), moments as vlb_bnorm_forward.  No
+ * counterpart among the reference's operator classes; the wrappers short-circuit a ReLU after another layer in the same way
+ * (matlab/+dagnn/ReLU.m:21-63).  Bit-identical to vlb_bnorm_forward followed by vlb_relu_forward; in the backward pass the
+ * ReLU takes its mask from Y (vlb_relu_backward(dX, Y, dY)), the batch normalisation needs only X. */
+int vlb_bnorm_relu_forward(vlb_ctx* ctx, float* Y, float* moments /* may be NULL */, float const* X, float const* g,
+                           float const* b, int H, int W, int C, int N, double eps);
 int vlb_bnorm_forward_moment(vlb_ctx* ctx, float* Y, float const* moments, float const* X,
                              float const* g, float const* b, int H, int W, int C, int N, double eps);
 int vlb_bnorm_backward(vlb_ctx* ctx, float* dX, float* dG, float* dB, float* moments /* may be NULL */,

@@ -86,6 +86,7 @@ SIGNATURES = {
     "vlb_bias_forward": (_I, [_P, _P, _D, _P, _D, _P, _D, _I, _I, _I, _I]),
     "vlb_bias_backward": (_I, [_P, _P, _D, _P, _D, _D, _D, _P, _I, _I, _I, _I]),
     "vlb_bnorm_forward": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _D]),
+    "vlb_bnorm_relu_forward": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _D]),
     "vlb_bnorm_forward_moment": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _D]),
     "vlb_bnorm_backward": (_I, [_P] * 9 + [_I, _I, _I, _I, _D]),
     "vlb_bnorm_backward_moment": (_I, [_P] * 9 + [_I, _I, _I, _I, _D]),

@@ -138,7 +138,7 @@ bnorm_fused_kernel(float* __restrict__ out,            // y or dx
                    float const* __restrict__ momentsIn,  // mode 2
                    float const* __restrict__ x, float const* __restrict__ dy,
                    float const* __restrict__ g, float const* __restrict__ b,
-                   int WH, int C, int N, float eps)
+                   int WH, int C, int N, float eps, int relu)      // relu (forward): the stored value is max(y, 0)
 {
   cg::cluster_group cluster = cg::this_cluster();
   __shared__ float part[4];
@@ -245,6 +245,7 @@ bnorm_fused_kernel(float* __restrict__ out,            // y or dx
         o.y = __fadd_rn(__fmul_rn(k1, __fadd_rn(xv.y, -k0)), k2);
         o.z = __fadd_rn(__fmul_rn(k1, __fadd_rn(xv.z, -k0)), k2);
         o.w = __fadd_rn(__fmul_rn(k1, __fadd_rn(xv.w, -k0)), k2);
+        if (relu) { o.x = o.x > 0.f ? o.x : 0.f; o.y = o.y > 0.f ? o.y : 0.f; o.z = o.z > 0.f ? o.z : 0.f; o.w = o.w > 0.f ? o.w : 0.f; }
       } else {
         float4 dv = *reinterpret_cast<float4 const*>(dy + off);
         o.x = __fadd_rn(__fmul_rn(k2, __fadd_rn(dv.x, -k1)), -__fmul_rn(k3, __fadd_rn(xv.x, -k0)));
@@ -257,7 +258,7 @@ bnorm_fused_kernel(float* __restrict__ out,            // y or dx
       int n = (int)(i / WH);
       int q = (int)(i - (long long)n * WH);
       size_t off = ((size_t)n * C + c) * (size_t)WH + q;
-      if (kMode == 0) out[off] = __fadd_rn(__fmul_rn(k1, __fadd_rn(x[off], -k0)), k2);
+      if (kMode == 0) { float o = __fadd_rn(__fmul_rn(k1, __fadd_rn(x[off], -k0)), k2); out[off] = (relu && !(o > 0.f)) ? 0.f : o; }
       else out[off] = __fadd_rn(__fmul_rn(k2, __fadd_rn(dy[off], -k1)), -__fmul_rn(k3, __fadd_rn(x[off], -k0)));
     }
   }
@@ -265,11 +266,11 @@ bnorm_fused_kernel(float* __restrict__ out,            // y or dx
 
 template <int kMode>
 void launch_fused(vlb_ctx* ctx, bool vec, float* out, float* momOut, float* dg, float* db, float const* momIn,
-                  float const* x, float const* dy, float const* g, float const* b, int WH, int C, int N, float eps)
+                  float const* x, float const* dy, float const* g, float const* b, int WH, int C, int N, float eps, int relu = 0)
 {
   dim3 grid(C, kCluster);
-  if (vec) bnorm_fused_kernel<kMode, true><<<grid, kThreads, 0, ctx->stream>>>(out, momOut, dg, db, momIn, x, dy, g, b, WH, C, N, eps);
-  else     bnorm_fused_kernel<kMode, false><<<grid, kThreads, 0, ctx->stream>>>(out, momOut, dg, db, momIn, x, dy, g, b, WH, C, N, eps);
+  if (vec) bnorm_fused_kernel<kMode, true><<<grid, kThreads, 0, ctx->stream>>>(out, momOut, dg, db, momIn, x, dy, g, b, WH, C, N, eps, relu);
+  else     bnorm_fused_kernel<kMode, false><<<grid, kThreads, 0, ctx->stream>>>(out, momOut, dg, db, momIn, x, dy, g, b, WH, C, N, eps, relu);
   VLB_LAUNCHED(ctx, 1);
 }
 
@@ -387,7 +388,7 @@ static float* scratch(vlb_ctx* ctx, int C, float4** cf)
 }
 
 static int forward_common(vlb_ctx* ctx, float* Y, float* momOut, float const* momIn, float const* X, float const* g,
-                          float const* b, int H, int W, int C, int N, double eps, char const* where)
+                          float const* b, int H, int W, int C, int N, double eps, char const* where, int relu = 0)
 {
   int rc = validate(ctx, H, W, C, N);
   if (rc) return rc;
@@ -400,7 +401,7 @@ static int forward_common(vlb_ctx* ctx, float* Y, float* momOut, float const* mo
   if (!momIn) {
     // moments computed and applied by the same clusters (the reference computes them into the context
     // workspace when the caller does not ask for them, bits/nnbnorm.cu:233-240)
-    launch_fused<0>(ctx, vec_ok(WH, Y, X, X), Y, momOut, nullptr, nullptr, nullptr, X, nullptr, g, b, WH, C, N, (float)eps);
+    launch_fused<0>(ctx, vec_ok(WH, Y, X, X), Y, momOut, nullptr, nullptr, nullptr, X, nullptr, g, b, WH, C, N, (float)eps, relu);
     return vlb::check_launch(ctx, where);
   }
   bnorm_coef_kernel<<<vlb::ceil_div(C, 256), 256, 0, ctx->stream>>>(cf, mom, g, b, nullptr, nullptr, C, 0.f);
@@ -444,6 +445,13 @@ int vlb_bnorm_forward(vlb_ctx* ctx, float* Y, float* moments, float const* X, fl
 {
   if (!ctx) return VLB_IllegalArgument;
   return forward_common(ctx, Y, moments, nullptr, X, g, b, H, W, C, N, eps, "vlb_bnorm_forward");
+}
+
+int vlb_bnorm_relu_forward(vlb_ctx* ctx, float* Y, float* moments, float const* X, float const* g, float const* b,
+                           int H, int W, int C, int N, double eps)
+{
+  if (!ctx) return VLB_IllegalArgument;
+  return forward_common(ctx, Y, moments, nullptr, X, g, b, H, W, C, N, eps, "vlb_bnorm_relu_forward", 1);
 }
 
 int vlb_bnorm_backward(vlb_ctx* ctx, float* dX, float* dG, float* dB, float* moments, float const* X,

@@ -164,10 +164,11 @@ def vl_nnconvt(x, f, b, dzdy=None, upsample=1, crop=0, num_groups=1, no_der_data
 
 
 # --------------------------------------------------------------------- vl_nnbnorm
-def vl_nnbnorm(x, g, b, dzdy=None, epsilon=1e-4, moments=None, der_out=None, ctx=None):
+def vl_nnbnorm(x, g, b, dzdy=None, epsilon=1e-4, moments=None, der_out=None, relu=False, ctx=None):
     """[Y, MOMENTS] = VL_NNBNORM(X, G, B) / [DX, DG, DB, MOMENTS] = VL_NNBNORM(X, G, B, DZDY)
     (matlab/vl_nnbnorm.m; gateway matlab/src/vl_nnbnorm.cu:73-302).  MOMENTS is C x 2:
-    [mean, sigma] with sigma = sqrt(var + epsilon)."""
+    [mean, sigma] with sigma = sqrt(var + epsilon).  relu=True (forward, moments from the batch) returns max(Y, 0) from the
+    same kernel, bit-identical to vl_nnrelu(vl_nnbnorm(...))."""
     ctx = _ctx(ctx)
     x, g, b, dzdy, moments = _need(x, "x"), _need(g, "g"), _need(b, "b"), _need(dzdy, "dzdy"), _need(moments, "moments")
     H, W, Cc, N = mat.shape4(x)
@@ -184,8 +185,10 @@ def vl_nnbnorm(x, g, b, dzdy=None, epsilon=1e-4, moments=None, der_out=None, ctx
             ctx.check(lib.vlb_bnorm_forward_moment(ctx.handle, mat.ptr(y), mat.ptr(mom), mat.ptr(x), mat.ptr(g),
                                                    mat.ptr(b), H, W, Cc, N, float(epsilon)))
         else:
-            ctx.check(lib.vlb_bnorm_forward(ctx.handle, mat.ptr(y), mat.ptr(mom), mat.ptr(x), mat.ptr(g),
-                                            mat.ptr(b), H, W, Cc, N, float(epsilon)))
+            fwd = lib.vlb_bnorm_relu_forward if relu else lib.vlb_bnorm_forward
+            ctx.check(fwd(ctx.handle, mat.ptr(y), mat.ptr(mom), mat.ptr(x), mat.ptr(g), mat.ptr(b), H, W, Cc, N, float(epsilon)))
+        if relu and given:
+            ctx.check(lib.vlb_relu_forward(ctx.handle, mat.ptr(y), mat.ptr(y), y.numel()))
         return y, mom
     if mat.shape4(dzdy) != (H, W, Cc, N):
         raise ValueError("DZDY dimensions are incompatible with X.")

@@ -72,9 +72,15 @@ def vl_simplenn(net, x, dzdy=None, res=None, on_dzdw=None, ctx=None, skip_forwar
                 res[i + 1]["x"] = nn.vl_nnpool(xi, l["pool"], stride=_get(l, "stride", 1), pad=_get(l, "pad", 0),
                                                method=_get(l, "method", "max"), ctx=ctx)
             elif t == "bnorm":
-                # training mode: moments from the batch (vl_simplenn.m:345-351)
-                res[i + 1]["x"], res[i]["aux"] = nn.vl_nnbnorm(xi, l["weights"][0], l["weights"][1],
-                                                               epsilon=_get(l, "epsilon", 1e-4), ctx=ctx)
+                # training mode: moments from the batch (vl_simplenn.m:345-351); a ReLU that follows is applied by the
+                # same kernel under fuse_relu, as after a convolution
+                fused = fuse_relu and i + 1 < n and layers[i + 1]["type"] == "relu"
+                y, res[i]["aux"] = nn.vl_nnbnorm(xi, l["weights"][0], l["weights"][1], epsilon=_get(l, "epsilon", 1e-4),
+                                                 relu=fused, ctx=ctx)
+                if fused:
+                    res[i + 1]["x"], res[i + 2]["x"] = None, y
+                else:
+                    res[i + 1]["x"] = y
             elif t == "softmaxloss":
                 res[i + 1]["x"] = nn.vl_nnsoftmaxloss(xi, l["class"], ctx=ctx)
             elif t == "normalize":

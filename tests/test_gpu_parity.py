@@ -429,3 +429,36 @@ def test_alexnet_style_chain_with_lrn_and_dropout(gpu, oracle):
         assert rel_l2(got, y) < TOL_FAITHFUL, (i, l["type"])
         dx, _ = cpu_net.layer_backward(oracle, oracle, l, f64(res[i]["x"]), d)
         assert rel_l2(mat.to_numpy(res[i]["dzdx"]), dx) < TOL_FAITHFUL, (i, l["type"])
+
+
+def test_bnorm_relu_fused_forward_is_bit_identical(gpu):
+    """vl_nnbnorm(..., relu=True) against vl_nnrelu(vl_nnbnorm(...)), vector and scalar paths, and a small network with
+    conv -> bnorm -> relu blocks under fuse_relu against the plain schedule: same outputs and gradients bit for bit."""
+    import torch
+    from matconvnet_b200 import models, simplenn
+    nn, mat, ctx = gpu
+    ctx.set_precision(0)
+    g = torch.Generator(device="cuda").manual_seed(50)
+    for shape in [(28, 28, 128, 8), (7, 5, 6, 3)]:
+        x = mat.as_mat(torch.randn(*shape, device="cuda", generator=g))
+        gam = mat.as_mat(torch.rand(shape[2], 1, device="cuda", generator=g) + 0.5)
+        bet = mat.as_mat(torch.randn(shape[2], 1, device="cuda", generator=g))
+        y, mom = nn.vl_nnbnorm(x, gam, bet, epsilon=1e-5)
+        yr, momr = nn.vl_nnbnorm(x, gam, bet, epsilon=1e-5, relu=True)
+        assert torch.equal(yr, nn.vl_nnrelu(y)) and torch.equal(mom, momr)
+        yg, _ = nn.vl_nnbnorm(x, gam, bet, epsilon=1e-5, moments=mom, relu=True)
+        assert torch.equal(yg, nn.vl_nnrelu(nn.vl_nnbnorm(x, gam, bet, epsilon=1e-5, moments=mom)[0]))
+    rng = np.random.default_rng(51)
+    bn = lambda c: {"type": "bnorm", "weights": [mat.from_numpy(np.ones((c, 1), np.float32)), mat.from_numpy(np.zeros((c, 1), np.float32))],
+                    "epsilon": 1e-5}
+    layers = [models._conv(rng, 3, 3, 3, 32, 1, 1), bn(32), models._relu(), models._conv(rng, 3, 3, 32, 32, 1, 1), bn(32),
+              models._relu(), models._pool("max", 2, 2), models._conv(rng, 8, 8, 32, 4, 1, 0),
+              {"type": "softmaxloss", "class": torch.tensor([1, 2, 3, 4, 1], device="cuda").float()}]
+    net = {"layers": layers}
+    x = mat.as_mat(torch.randn(16, 16, 3, 5, device="cuda", generator=g))
+    plain = simplenn.vl_simplenn(net, x, 1.0, ctx=ctx)
+    fused = simplenn.vl_simplenn(net, x, 1.0, ctx=ctx, fuse_relu=True)
+    assert torch.equal(plain[-1]["x"], fused[-1]["x"]) and torch.equal(plain[0]["dzdx"], fused[0]["dzdx"])
+    for a, c in zip(plain, fused):
+        for u, v in zip(a["dzdw"] or [], c["dzdw"] or []):
+            assert (u is None and v is None) or torch.equal(u, v)
