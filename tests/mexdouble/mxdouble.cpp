@@ -93,6 +93,7 @@ mxArray* make(mwSize ndim, mwSize const* dims, mxClassID cls, bool gpu, bool zer
   for (mwSize i = 0; i < ndim && i < 16; ++i) a->dims[i] = dims[i];
   if (ndim == 1) { a->dims[0] = dims[0]; a->dims[1] = 1; }
   if (ndim == 0) { a->dims[0] = 0; a->dims[1] = 0; }
+  while (a->ndim > 2 && a->dims[a->ndim - 1] == 1) --a->ndim;      // MATLAB drops trailing singleton dimensions
   a->blk = new_block(count(a->ndim, a->dims) * element_size(cls), gpu, zero);
   return a;
 }
@@ -188,6 +189,7 @@ int mxSetDimensions(mxArray* pa, mwSize const* dims, mwSize ndim)
   pa->ndim = ndim < 2 ? 2 : ndim;
   for (mwSize i = 0; i < 16; ++i) pa->dims[i] = 1;
   for (mwSize i = 0; i < ndim && i < 16; ++i) pa->dims[i] = dims[i];
+  while (pa->ndim > 2 && pa->dims[pa->ndim - 1] == 1) --pa->ndim;
   pa->blk->bytes = count(pa->ndim, pa->dims) * element_size(pa->cls);
   return 0;
 }
