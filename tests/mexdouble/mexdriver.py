@@ -42,7 +42,7 @@ class MexDouble:
         common = os.path.join(OUT, "libmexdouble.so")
         if not os.path.exists(common):
             raise RuntimeError("the MEX test double is not built: run tests/mexdouble/build_mexdouble.py where the reference is")
-        self.lib = L = ctypes.CDLL(common, mode=ctypes.RTLD_GLOBAL)
+        self.lib = L = ctypes.CDLL(common)      # local scope: the checker loads the reference's CPU build of the same classes
         vp, sz = ctypes.c_void_p, ctypes.c_size_t
         L.mxd_from_host.restype = vp
         L.mxd_from_host.argtypes = [vp, ctypes.c_int, ctypes.POINTER(sz), ctypes.c_int, ctypes.c_int]
