@@ -68,7 +68,9 @@ int vlb_ctx_set_wait_limit(vlb_ctx* ctx, long long cycles);
  * wait behind it runs out: the kernel records its status word, releases its tensor memory and returns
  * (vlb_ctx_device_status then gives VLE_Timeout; the output of that call is undefined).  Nothing traps or spins.
  * Bit 1: the tensor-memory convolution kernel gathers its input windows with per-thread loads even where it could have
- * them delivered by tensor-map copies; the two routes give the same result bit for bit, which is what a test compares. */
+ * them delivered by tensor-map copies; the two routes give the same result bit for bit, which is what a test compares.
+ * Bit 2: the filter gradient of a convolution takes the kernel with both operands in shared memory even where the
+ * tensor-memory kernel applies (the two differ in the order of the sums; a test checks both against the CPU checker). */
 int vlb_ctx_set_test_switch(vlb_ctx* ctx, int switches);
 /* Measurement aid: between begin and end every tensor-core contraction (with the launches that prepare its operands
  * and finish its result) is bracketed by CUDA events on the context's stream.  end synchronises and returns the summed kernel time, the summed

@@ -169,11 +169,13 @@ def main():
     ap.add_argument("--precision", default="3xtf32", choices=["3xtf32", "tf32", "fp32"])
     ap.add_argument("--layers", default="")
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--test-switch", type=int, default=0, help="vlb_ctx_set_test_switch bits (2: no tensor-map windows, 4: filter gradient on the shared-memory kernel)")
     args = ap.parse_args()
     torch.cuda.set_device(0)
     ctx = nn.default_context()
     ctx.set_precision({"3xtf32": 0, "tf32": 1, "fp32": 2}[args.precision])
     ctx.reserve_workspace(3 << 30)
+    ctx.check(ctx.lib.vlb_ctx_set_test_switch(ctx.handle, args.test_switch))
     flush = None if args.no_flush else torch.empty(64 << 20, device="cuda")
     if args.kind == "conv":
         which = [s for s in args.layers.split(",") if s]

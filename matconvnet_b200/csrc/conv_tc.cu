@@ -112,6 +112,11 @@ struct Params {
   // 16-byte boundary) x boxW columns x 32 channels -- arrives in shared memory by one cp.async.bulk.tensor per channel block
   int tma, bh, bw, tilesH, tilesW, boxH, boxW, rowOff;
   int bStages;            // conv_ts_kernel: filter-tile stages in shared memory (4, or 3 where the input windows need the room)
+  // conv_ts_kernel computing a filter gradient (wg != 0): D[(tap, c)][k] = sum over output pixels of x(pixel + tap, c) * dY(pixel, k).
+  // A tile row is one channel of one filter tap: tapsPerTile taps x cPer channels = 128 rows, tapGroups x C/cPer row tiles; the
+  // reduction (output pixels of the whole batch, kbTot k-blocks in the dY tile images) is cut into `splits` ranges of kbPerSplit
+  // k-blocks, one work item per (range, row tile, column tile); the x runs arrive by tensor-map copies, xStages buffers.
+  int wg, cPer, tapsPerTile, tapGroups, kbTot, splits, xStages;
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -1014,6 +1019,17 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dstSmem, void const* map, i
                ::"r"(dstSmem), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar) : "memory");
 }
 
+__device__ __forceinline__ void tma_load_3d(uint32_t dstSmem, void const* map, int c0, int c1, int c2, uint32_t bar)
+{
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+               ::"r"(dstSmem), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void lds128(uint32_t addr, float (&v)[4])
+{
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]) : "r"(addr));
+}
+
 __device__ __forceinline__ float lds32(uint32_t addr)
 {
   float v;
@@ -1029,6 +1045,15 @@ struct RowPos { int img, pix; bool valid; };
 __device__ __forceinline__ RowPos row_pos(Params const& p, int tm, int row)
 {
   RowPos r;
+  if (p.wg) {
+    // tm = row tile + tilesM * reduction range; row tile = tap group + tapGroups * channel block; row = local tap * cPer + channel.
+    // The "pixel" is the element of dF the row belongs to, fh + FH*(fw + FW*c), plus the offset of the range's partial result.
+    int const split = tm / p.tilesM, t = tm - split * p.tilesM, cb = t / p.tapGroups, tg = t - cb * p.tapGroups;
+    int const tl = row / p.cPer, c = cb * p.cPer + (row - tl * p.cPer), tap = tg * p.tapsPerTile + tl, taps = p.a.FH * p.a.FW;
+    r.valid = tap < taps && c < p.a.C;
+    r.img = 0; r.pix = r.valid ? tap + taps * c + split * (int)p.e.splitStride : 0;
+    return r;
+  }
   if (!p.tma) {
     int const m = tm * BM + row;
     r.valid = m < p.M;
@@ -1110,12 +1135,20 @@ __device__ __forceinline__ void ts_store_tile(Params const& p, float const* P, i
 // (one box of boxH x boxW pixels x 32 channels per channel block and tile, zero-filled outside the image by the copy
 // engine, two buffers), instead of gathering them from global memory with per-thread loads.  xmap: the 4-D tensor map
 // (H, W, C, N) of the gathered tensor; unused otherwise.
-template <bool kSplit, bool kTma>
+// kMode 2 (filter gradient): rows are (tap, channel), the reduction runs over the output pixels; warp 16 has the run of 32
+// pixels (plus up to three in front, so that the copy starts on a 16-byte boundary) of every row delivered per k-block.
+constexpr int kWgRowWords = 36;                         // words per row of an x run in shared memory (144 bytes: 16-byte loads of 8 rows hit 32 banks)
+constexpr int kWgRowBytes = kWgRowWords * 4;
+constexpr int kWgStageBytes = BM * kWgRowBytes;         // 18432
+constexpr int kTsXStages = 4;                           // at most
+
+template <bool kSplit, int kMode>
 __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p, const __grid_constant__ CUtensorMap xmap)
 {
+  constexpr bool kTma = kMode == 1, kWg = kMode == 2;
   extern __shared__ uint8_t smemRaw[];
   __shared__ __align__(8) uint64_t fullA[kTsGroups], emptyA[kTsGroups], fullB[kTsBStages], emptyB[kTsBStages];
-  __shared__ __align__(8) uint64_t tFull[3], tFree[3], tileDone, turn[2], fullX[2], emptyX[2];
+  __shared__ __align__(8) uint64_t tFull[3], tFree[3], tileDone, turn[2], fullX[kTsXStages], emptyX[kTsXStages];
   __shared__ uint32_t tmemBase;
   __shared__ int2 tapLut[64];       // per filter tap fh + FH*fw: {element offset of the tap (in the input window when kTma), fh | fw << 5}
 
@@ -1128,13 +1161,13 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p, const 
   uint32_t const colA = (uint32_t)(3 * BN);
   float* const Psm = reinterpret_cast<float*>(smem + (size_t)nB * bBytes);      // [BN][BM]
   // input windows (kTma): two buffers of boxH*boxW*32 floats behind P
-  uint32_t const xPlane = (uint32_t)(p.boxH * p.boxW), xTileBytes = xPlane * 32u * 4u;
+  uint32_t const xPlane = (uint32_t)(p.boxH * p.boxW), xTileBytes = kWg ? (uint32_t)kWgStageBytes : xPlane * 32u * 4u;
   uint32_t const xTile0 = smem_u32(Psm) + (uint32_t)BN * BM * 4u;
 
   int const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int const numIter = p.numKb;                     // k-blocks per tile
+  int const numIter = kWg ? p.kbPerSplit : p.numKb;      // k-blocks per tile
   int const chunksPerTile = kSplit ? (numIter + kTsDrainEvery - 1) / kTsDrainEvery : 1;
-  int const numTiles = p.tilesM * p.tilesN;
+  int const numTiles = p.tilesM * p.tilesN * (kWg ? p.splits : 1);
   // this CTA's tiles: blockIdx.x, blockIdx.x + gridDim.x, ...; tile t = (row tile t / tilesN, column tile t % tilesN)
   int const myTiles = (int)blockIdx.x < numTiles ? (numTiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
   bool const singleTile = (int)gridDim.x == numTiles;      // launched with one CTA per tile (long reductions)
@@ -1147,14 +1180,16 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p, const 
     mbar_init(smem_u32(&tileDone), kEpilogueWarps);
     mbar_init(smem_u32(&turn[0]), 1); mbar_init(smem_u32(&turn[1]), 1);
     // an input window is full when its copy has landed (one arrival with the byte count), empty when all eight producer warps are done with it
-    for (int b = 0; b < 2; ++b) { mbar_init(smem_u32(&fullX[b]), 1); mbar_init(smem_u32(&emptyX[b]), 4 * kTsGroups); }
+    // (filter gradient: a run belongs to one k-block, so only the four warps of the group that owns it let go of it)
+    for (int b = 0; b < kTsXStages; ++b) { mbar_init(smem_u32(&fullX[b]), 1); mbar_init(smem_u32(&emptyX[b]), kWg ? 4 : 4 * kTsGroups); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == kEpilogueWarps) tmem_alloc(smem_u32(&tmemBase), tmemCols);
   if ((int)threadIdx.x < p.a.FH * p.a.FW) {
     int const fh = (int)threadIdx.x % p.a.FH, fw = (int)threadIdx.x / p.a.FH;
-    if (kTma) tapLut[threadIdx.x] = make_int2(fw * p.a.dx * p.boxH + fh * p.a.dy, fh | (fw << 5));
-    else      tapLut[threadIdx.x] = make_int2((fw * p.a.dx - p.a.pl) * p.a.H + fh * p.a.dy - p.a.pt, fh | (fw << 5));
+    if (kWg)       tapLut[threadIdx.x] = make_int2((fw * p.a.dx - p.a.pl) * p.a.H + fh * p.a.dy - p.a.pt, fh * p.a.dy - p.a.pt);   // {shift of the tap in the flattened plane, its row offset}
+    else if (kTma) tapLut[threadIdx.x] = make_int2(fw * p.a.dx * p.boxH + fh * p.a.dy, fh | (fw << 5));
+    else           tapLut[threadIdx.x] = make_int2((fw * p.a.dx - p.a.pl) * p.a.H + fh * p.a.dy - p.a.pt, fh | (fw << 5));
   }
   tc_fence_before();
   __syncthreads();
@@ -1340,8 +1375,10 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p, const 
       int sb = 0; uint32_t ph = 1;                       // first use of a stage: nothing to wait for
       bool ok = true;
       for (int ts = 0; ts < myTiles && ok; ++ts) {
-        int const nt = ((int)blockIdx.x + ts * (int)gridDim.x) % p.tilesN;
+        int const tile = (int)blockIdx.x + ts * (int)gridDim.x;
+        int const nt = tile % p.tilesN;
         float const* src = p.bTiles + (size_t)nt * p.numKb * (bBytes / 4);
+        if (kWg) src = p.bTiles + ((size_t)nt * p.kbTot + (size_t)(tile / p.tilesN / p.tilesM) * numIter) * (bBytes / 4);
         for (int it = 0; it < numIter; ++it) {
           if (!mbar_wait(smem_u32(&emptyB[sb]), ph)) { atomicExch(p.status, 8); ok = false; break; }
           mbar_arrive_expect_tx(smem_u32(&fullB[sb]), bBytes);
@@ -1372,6 +1409,30 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p, const 
     // ============================== input windows: tensor-map copies ==============================
     // Window xs (numbered over the CTA's life: one per tile and block of 32 channels) goes into buffer xs & 1 as soon as
     // the producers have let go of window xs - 2, i.e. as far ahead of its use as two buffers allow.
+    if (kWg && lane == 0) {
+      // One run of 36 pixels x cPer channels per k-block and tap of the tile, from the plane of image r / P starting at
+      // pixel r % P + shift of the tap, rounded down to four pixels.  Pixels before the plane's first or past its last one
+      // -- a tap that leaves the image to the left or right, a k-block past the end of the batch -- arrive as zeros.
+      int const taps = p.a.FH * p.a.FW, P = p.a.Ho * p.a.Wo, nX = p.xStages;
+      int buf = 0; uint32_t ph = 1;                        // first use of a buffer: nothing to wait for
+      bool ok = true;
+      for (int ts = 0; ts < myTiles && ok; ++ts) {
+        int const tmf = ((int)blockIdx.x + ts * (int)gridDim.x) / p.tilesN;
+        int const split = tmf / p.tilesM, t = tmf - split * p.tilesM, cb = t / p.tapGroups, tg = t - cb * p.tapGroups;
+        int const tap0 = tg * p.tapsPerTile, nTaps = min(p.tapsPerTile, taps - tap0);
+        long long r0 = (long long)split * numIter * BK;
+        int img = (int)(r0 / P), pix0 = (int)(r0 - (long long)img * P);
+        for (int it = 0; it < numIter; ++it) {
+          if (!mbar_wait(smem_u32(&emptyX[buf]), ph)) { atomicExch(p.status, 12); ok = false; break; }
+          mbar_arrive_expect_tx(smem_u32(&fullX[buf]), (uint32_t)(nTaps * p.cPer * kWgRowBytes));
+          for (int tl = 0; tl < nTaps; ++tl)
+            tma_load_3d(xTile0 + (uint32_t)buf * xTileBytes + (uint32_t)(tl * p.cPer * kWgRowBytes), &xmap,
+                        pix0 + (tapLut[tap0 + tl].x & ~3), cb * p.cPer, img, smem_u32(&fullX[buf]));
+          if (++buf == nX) { buf = 0; ph ^= 1u; }
+          pix0 += BK; if (pix0 >= P) { pix0 -= P; ++img; }
+        }
+      }
+    }
     if (kTma && lane == 0) {
       int const numCb = numIter / (p.a.FH * p.a.FW);
       int const per = p.tilesH * p.tilesW;
@@ -1427,7 +1488,63 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p, const 
       return true;
     };
 
-    if (kTma) {
+    if (kWg) {
+      // This thread's row: channel (row % cPer) of the tile's local tap row / cPer -- the same tap for the whole warp.  A k-block
+      // is 32 consecutive output pixels; the row's 36-pixel run lies in shared memory, the wanted 32 start `s` pixels in.
+      int const row = quarter * 32 + lane;
+      int const tl = (quarter * 32) / p.cPer;
+      int const H = p.a.H, P = p.a.Ho * p.a.Wo, nX = p.xStages;
+      for (int ts = 0; ts < myTiles && ok; ++ts) {
+        int const tmf = ((int)blockIdx.x + ts * (int)gridDim.x) / p.tilesN;
+        int const split = tmf / p.tilesM, t = tmf - split * p.tilesM, tg = t % p.tapGroups;
+        int const tap = tg * p.tapsPerTile + tl;
+        bool const active = tap < taps;                                   // a tap the filter does not have: rows of zeros, never stored
+        int2 const te = tapLut[active ? tap : 0];
+        int const s = te.x & 3, dh = te.y;
+        int const itFirst = (int)((gi ^ grp) & 1);
+        int pb = (int)(((long long)split * numIter + itFirst) * BK % P);      // first pixel of the k-block inside its image
+        for (int it = itFirst; it < numIter; it += kTsGroups) {
+          uint32_t const xs = (uint32_t)(gi + it);
+          int const buf = (int)(xs % (uint32_t)nX);
+          if (!mbar_wait(smem_u32(&fullX[buf]), (xs / (uint32_t)nX) & 1u)) { atomicExch(p.status, 11); ok = false; break; }
+          uint32_t const src = xTile0 + (uint32_t)buf * xTileBytes + (uint32_t)(row * kWgRowBytes);
+          float w[kWgRowWords];
+#pragma unroll
+          for (int j = 0; j < kWgRowWords / 4; ++j) lds128(src + 16u * j, *reinterpret_cast<float(*)[4]>(&w[4 * j]));
+          // pixels whose tap row leaves the image above or below: output row ho + dh outside [0, H) -- the same for every lane's row
+          int const ho = (pb + lane) % H;
+          pb += kTsGroups * BK; while (pb >= P) pb -= P;
+          uint32_t const zm = active ? __ballot_sync(0xffffffffu, (unsigned)(ho + dh) >= (unsigned)H) : 0xffffffffu;
+          float v[32];
+          switch (s) {
+            case 0:
+#pragma unroll
+              for (int k = 0; k < 32; ++k) v[k] = w[k];
+              break;
+            case 1:
+#pragma unroll
+              for (int k = 0; k < 32; ++k) v[k] = w[k + 1];
+              break;
+            case 2:
+#pragma unroll
+              for (int k = 0; k < 32; ++k) v[k] = w[k + 2];
+              break;
+            default:
+#pragma unroll
+              for (int k = 0; k < 32; ++k) v[k] = w[k + 3];
+              break;
+          }
+          if (zm) {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) v[k] = ((zm >> k) & 1u) ? 0.f : v[k];
+          }
+          if (!hand_over(v, it)) { ok = false; break; }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&emptyX[buf]));     // this warp's loads from the run have completed (their values were used above)
+        }
+        gi += numIter;
+      }
+    } else if (kTma) {
       // This thread's pixel inside the input window: row dh + rowOff, column dw (a lane beyond the box reads the window's
       // first element; its row is never stored).  A k-block is one filter tap and 32 channels: 32 loads from shared memory
       // one channel plane apart.
@@ -1872,19 +1989,19 @@ int launch_ts(vlb_ctx* ctx, Params& p, char const* where)
   }
   if (split3) {
     if (windows) {
-      e = allow_large_smem<conv_ts_kernel<true, true>>(ctx->device);
-      if (e == cudaSuccess) conv_ts_kernel<true, true><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p, map);
+      e = allow_large_smem<conv_ts_kernel<true, 1>>(ctx->device);
+      if (e == cudaSuccess) conv_ts_kernel<true, 1><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p, map);
     } else {
-      e = allow_large_smem<conv_ts_kernel<true, false>>(ctx->device);
-      if (e == cudaSuccess) conv_ts_kernel<true, false><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p, map);
+      e = allow_large_smem<conv_ts_kernel<true, 0>>(ctx->device);
+      if (e == cudaSuccess) conv_ts_kernel<true, 0><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p, map);
     }
   } else {
     if (windows) {
-      e = allow_large_smem<conv_ts_kernel<false, true>>(ctx->device);
-      if (e == cudaSuccess) conv_ts_kernel<false, true><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p, map);
+      e = allow_large_smem<conv_ts_kernel<false, 1>>(ctx->device);
+      if (e == cudaSuccess) conv_ts_kernel<false, 1><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p, map);
     } else {
-      e = allow_large_smem<conv_ts_kernel<false, false>>(ctx->device);
-      if (e == cudaSuccess) conv_ts_kernel<false, false><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p, map);
+      e = allow_large_smem<conv_ts_kernel<false, 0>>(ctx->device);
+      if (e == cudaSuccess) conv_ts_kernel<false, 0><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p, map);
     }
   }
   if (record) { cudaEventRecord(rec.stop, ctx->stream); ctx->prof.push_back(rec); }
@@ -1905,6 +2022,26 @@ int pick_splits(vlb_ctx* ctx, int tiles, int numKb, int minKbPerSplit)
   return s < 1 ? 1 : s;
 }
 
+// The cut of a filter gradient's reduction (numKb k-blocks, `tiles` output tiles) into ranges: the work items -- tiles x
+// ranges -- should fill whole waves of the persistent CTAs, with ranges long enough that a tile's fixed cost stays small.
+int pick_wg_splits(int smCount, int tiles, int numKb, int* kbPerSplit)
+{
+  int best = 1; double bestEff = 0.0;
+  for (int w = 1; w <= 6; ++w) {
+    int s = std::max(1, (w * smCount) / tiles);
+    s = std::min(s, std::max(1, numKb / 48));
+    int const per = vlb::ceil_div(numKb, s);
+    s = vlb::ceil_div(numKb, per);
+    long long const items = (long long)tiles * s;
+    long long const perCta = (items + smCount - 1) / smCount;          // items of the busiest CTA
+    // useful k-blocks per SM over the k-block slots the busiest CTA spends, a dozen k-blocks' worth of fixed cost per item
+    double const eff = ((double)tiles * numKb / smCount) / ((double)perCta * (per + 12));
+    if (eff > bestEff * 1.01) { bestEff = eff; best = s; }
+  }
+  *kbPerSplit = vlb::ceil_div(numKb, best);
+  return vlb::ceil_div(numKb, *kbPerSplit);
+}
+
 void conv_operand(Operand& o, ConvGeom const& g, float const* ptr, int channels)
 {
   o.ptr = ptr;
@@ -1921,6 +2058,91 @@ bool fits32(ConvGeom const& g)
 {
   long long in = (long long)g.H * g.W * g.C * g.N, out = (long long)g.Ho * g.Wo * g.K * g.N;
   return in < (1LL << 31) - 256 && out < (1LL << 31) - 256 && (long long)g.FH * g.FW * g.FC * g.K < (1LL << 31);
+}
+
+// Filter gradient of a stride-1 convolution whose output has the input's height (every VGG / ResNet 3x3 layer), through
+// conv_ts_kernel: rows (tap, channel) in tensor memory, dY as tile images.  Returns -1 when the layer is not eligible (the
+// caller then takes tc_gemm_kernel), else an error code.
+//   needs: Ho == H (a tap is then a constant shift of the flattened plane), planes of a multiple of 32 pixels (a k-block
+//   never straddles two images) -- which also gives the 16-byte strides the tensor map wants --, channels in blocks of 32.
+int conv_wgrad_ts(vlb_ctx* ctx, ConvGeom const& g, float* dF, float* db, float const* X, float const* dY, bool* dbDone)
+{
+  int const taps = g.FH * g.FW, P = g.Ho * g.Wo, HW = g.H * g.W;
+  if (ctx->testSwitch & 4) return -1;
+  if (g.sy != 1 || g.sx != 1 || g.Ho != g.H || P % 32 != 0 || HW % 4 != 0 || taps > 64 || g.FH > 32 || g.FW > 32) return -1;
+  if (g.C % 32 != 0 || (g.C > 128 && g.C % 128 != 0) || (g.C < 128 && 128 % g.C != 0)) return -1;
+  if (g.K > 4096 || !aligned16(X) || !aligned16(dY)) return -1;
+  if ((g.FH - 1) * g.dy - g.pt >= g.H || g.pt >= g.H) return -1;
+  EncodeTiledFn const encode = encode_tiled();
+  if (!encode) return -1;
+  bool const split3 = ctx->precision == VLB_PRECISION_3XTF32;
+  int const V = taps * g.C;
+  long long const R = (long long)P * g.N;
+  Params p = {};
+  p.wg = 1;
+  p.cPer = std::min(g.C, 128); p.tapsPerTile = 128 / p.cPer; p.tapGroups = vlb::ceil_div(taps, p.tapsPerTile);
+  p.M = V; p.N = g.K; p.R = (int)R;
+  p.BN = pick_bn(p.N);
+  p.tilesM = p.tapGroups * (g.C / p.cPer); p.tilesN = vlb::ceil_div(p.N, p.BN);
+  if (vlb::ceil_div(g.K, p.BN) * p.BN > 65535) return -1;
+  int const numKb = (int)(R / BK);
+  p.splits = pick_wg_splits(ctx->smCount, p.tilesM * p.tilesN, numKb, &p.kbPerSplit);
+  p.kbTot = p.splits * p.kbPerSplit;               // the tile images are padded with zeros to whole ranges
+  p.numKb = p.kbTot;
+  conv_operand(p.a, g, X, g.C);
+  p.a.rows = V;
+  size_t const nF = (size_t)V * g.K;
+  if ((long long)nF * p.splits >= (1LL << 31)) return -1;
+  size_t const partBytes = p.splits > 1 ? ((sizeof(float) * nF * p.splits + 255) & ~(size_t)255) : 0;
+  size_t const tileBytes = b_tiles_bytes(ctx, g.K, p.BN, p.kbTot);
+  // shared memory: filter-tile stages, the running sum, the x runs
+  size_t const bBytes = (size_t)(split3 ? 2 : 1) * p.BN * BK * 4, pBytes = sizeof(float) * (size_t)p.BN * BM;
+  size_t const limit = 227 * 1024 - 1536;
+  p.bStages = 0;
+  for (int nb = kTsBStages; nb >= 3 && !p.bStages; --nb)
+    for (int nx = kTsXStages; nx >= 3 && !p.bStages; --nx)
+      if ((size_t)nb * bBytes + pBytes + (size_t)nx * kWgStageBytes + 1024 <= limit) { p.bStages = nb; p.xStages = nx; }
+  if (!p.bStages) return -1;
+  size_t smemBytes = (size_t)p.bStages * bBytes + pBytes + (size_t)p.xStages * kWgStageBytes + 1024;
+  if (smemBytes < 120u * 1024u) smemBytes = 120u * 1024u;      // two CTAs (each allocating all 512 TMEM columns) never share an SM
+  CUtensorMap map;
+  memset(&map, 0, sizeof(map));
+  cuuint64_t const dims[3] = {(cuuint64_t)HW, (cuuint64_t)g.C, (cuuint64_t)g.N};
+  cuuint64_t const strides[2] = {(cuuint64_t)HW * 4, (cuuint64_t)HW * g.C * 4};
+  cuuint32_t const box[3] = {(cuuint32_t)kWgRowWords, (cuuint32_t)p.cPer, 1u};
+  cuuint32_t const estr[3] = {1u, 1u, 1u};
+  if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(X), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return -1;
+
+  ProfScope prof(ctx, kProfWgrad);      // includes the dY tile images (with the bias gradient) and the sum of the partial results
+  prof.rec.flops = 2.0 * (double)V * (double)g.K * (double)R;
+  p.bTiles = prep_dy_tiles(ctx, dY, g.K, (int)R, P, p.BN, p.kbTot, partBytes, db);
+  if (!p.bTiles) return ctx->lastError;
+  *dbDone = db != nullptr;
+  float* const part = p.splits > 1 ? (float*)((char*)p.bTiles + tileBytes) : nullptr;
+  p.e = Epilogue{};
+  p.e.out = part ? part : dF; p.e.splitStride = part ? (long long)nF : 0; p.e.inMult = 1.f; p.e.P = V; p.e.Ktot = g.K;
+  p.status = ctx->deviceStatus;
+  p.testSwitch = ctx->testSwitch;
+  p.chanFast = 1;
+  long long const numTiles = (long long)p.tilesM * p.tilesN * p.splits;
+  dim3 grid((unsigned)std::min<long long>(numTiles, ctx->smCount), 1, 1);
+  cudaError_t e;
+  if (split3) {
+    e = allow_large_smem<conv_ts_kernel<true, 2>>(ctx->device);
+    if (e == cudaSuccess) conv_ts_kernel<true, 2><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p, map);
+  } else {
+    e = allow_large_smem<conv_ts_kernel<false, 2>>(ctx->device);
+    if (e == cudaSuccess) conv_ts_kernel<false, 2><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p, map);
+  }
+  if (e != cudaSuccess) { cudaGetLastError(); return vlb::set_error(ctx, VLB_Cuda, cudaGetErrorString(e)); }
+  VLB_LAUNCHED(ctx, 1);
+  if (part) {
+    tc_splitk_reduce_kernel<<<vlb::grid_for(nF, 256, ctx->smCount * 8), 256, 0, ctx->stream>>>(dF, part, nF, nF, p.splits);
+    VLB_LAUNCHED(ctx, 1);
+  }
+  return vlb::check_launch(ctx, "conv_wgrad_ts");
 }
 
 bool is_fc(ConvGeom const& g)
@@ -2062,6 +2284,10 @@ int conv_wgrad_tc(vlb_ctx* ctx, ConvGeom const& g, float* dF, float* db, float c
     p.numKb = ceil_div(p.R, BK); p.kbPerSplit = p.numKb;
     p.e = Epilogue{}; p.e.out = dF; p.e.ldd = V;
     return launch<OP_DENSE_MN, OP_DENSE_MN, EPI_PLAIN>(ctx, p, 1, "fc_wgrad_tc");
+  }
+  {
+    int const rc = conv_wgrad_ts(ctx, g, dF, db, X, dY, dbDone);
+    if (rc >= 0) return rc;
   }
   long long R = (long long)g.Ho * g.Wo * g.N;
   ProfScope prof(ctx, kProfWgrad);      // includes the dY tile images (with the bias gradient) and the sum of the split partial results

@@ -1,0 +1,66 @@
+"""The filter gradient through the tensor-memory kernel: rows (filter tap, channel), reduction over the output pixels.
+
+For a stride-1 convolution whose output has the input's height, planes of a multiple of 32 pixels and channels in blocks of
+32, dF[(fh,fw,c), k] = sum over pixels of x(pixel shifted by the tap, c) * dY(pixel, k) runs with the x rows in tensor
+memory -- every row's run of 32 pixels is delivered per k-block by a tensor-map copy that zero-fills what lies left or right
+of the image; rows above or below it are masked by the producers -- and dY as pre-split tile images; the reduction is cut
+into ranges whose partial results are added in fixed order.  Checked here against the CPU checker (double precision) and
+against the kernel with both operands in shared memory (test switch bit 2), which every other layer shape still takes:
+small planes, 64- and 128-channel tiles with two or four taps per tile, a tap group that is not full, 5x5 and 1x1 filters,
+dilation, an output narrower than the input, several ranges, both tensor-core arithmetic modes, run-to-run identical.
+"""
+import numpy as np
+import pytest
+
+from conftest import rel_l2
+
+pytestmark = pytest.mark.gpu
+
+# (H, W, C, N), (FH, FW, C, K), options
+CASES = [((8, 4, 32, 3), (3, 3, 32, 16), dict(pad=1)),                # one k-block per image, four taps per tile, 9 taps = 2 1/4 groups
+         ((16, 16, 64, 5), (3, 3, 64, 48), dict(pad=1)),              # two taps per tile, the last group half empty
+         ((16, 8, 128, 4), (3, 3, 128, 130), dict(pad=1)),            # one tap per tile, two column tiles (the second nearly empty)
+         ((32, 32, 256, 2), (3, 3, 256, 64), dict(pad=1)),            # two channel blocks
+         ((16, 12, 32, 6), (5, 5, 32, 24), dict(pad=2)),              # 5 x 5: shifts of -2 .. 2 rows
+         ((16, 16, 32, 3), (3, 3, 32, 32), dict(pad=(1, 1, 0, 0))),   # no padding left and right: the output is narrower than the input
+         ((32, 8, 32, 3), (3, 3, 32, 16), dict(pad=2, dilate=2)),     # dilation
+         ((8, 8, 96, 5), (1, 1, 96, 40), dict()),                     # 96 channels: not a tile shape, stays on the other kernel
+         ((8, 8, 64, 9), (1, 1, 64, 40), dict()),                     # 1 x 1
+         ((56, 56, 64, 8), (3, 3, 64, 64), dict(pad=1)),              # a VGG-like plane, 64-column tiles, many ranges
+         ((28, 32, 128, 16), (3, 3, 128, 128), dict(pad=1))]          # rows of 28: row masks at changing places
+
+
+@pytest.mark.parametrize("precision,tol", [(0, 1e-5), (1, 2e-3)])
+@pytest.mark.parametrize("case", range(len(CASES)))
+def test_filter_gradient_rows_in_tensor_memory(gpu, oracle, case, precision, tol):
+    nn, mat, ctx = gpu
+    xs, fs, kw = CASES[case]
+    rng = np.random.default_rng(300 + case)
+    x = np.asfortranarray(rng.standard_normal(xs).astype(np.float32))
+    f = np.asfortranarray((rng.standard_normal(fs) * (2.0 / (fs[0] * fs[1] * fs[2])) ** 0.5).astype(np.float32))
+    pad = kw.get("pad", 0)
+    pad = (pad,) * 4 if np.isscalar(pad) else pad
+    dil = kw.get("dilate", 1)
+    Ho = xs[0] + pad[0] + pad[1] - (fs[0] - 1) * dil
+    Wo = xs[1] + pad[2] + pad[3] - (fs[1] - 1) * dil
+    dy = np.asfortranarray(rng.standard_normal((Ho, Wo, fs[3], xs[3])).astype(np.float32))
+    _, dfr, dbr = oracle.conv_backward(x.astype(np.float64), f.astype(np.float64), dy.astype(np.float64), (1, 1), pad, (dil, dil))
+    xd, fd, dyd = mat.from_numpy(x), mat.from_numpy(f), mat.from_numpy(dy)
+    bd = mat.from_numpy(np.zeros((1, fs[3]), np.float32))
+    ctx.set_precision(precision)
+    lib = ctx.lib
+    try:
+        got = {}
+        for switch in (0, 4):
+            ctx.check(lib.vlb_ctx_set_test_switch(ctx.handle, switch))
+            _, df, db = nn.vl_nnconv(xd, fd, bd, dyd, no_der_data=True, ctx=ctx, **kw)
+            assert ctx.device_status() == 0
+            got[switch] = (mat.to_numpy(df), mat.to_numpy(db))
+            assert rel_l2(got[switch][0], dfr) < tol, (switch, "df")
+            assert rel_l2(got[switch][1].ravel(), dbr.ravel()) < 1e-5, (switch, "db")
+        ctx.check(lib.vlb_ctx_set_test_switch(ctx.handle, 0))
+        _, df2, db2 = nn.vl_nnconv(xd, fd, bd, dyd, no_der_data=True, ctx=ctx, **kw)
+        assert np.array_equal(mat.to_numpy(df2), got[0][0]) and np.array_equal(mat.to_numpy(db2), got[0][1])     # no atomics: run to run identical
+    finally:
+        ctx.check(lib.vlb_ctx_set_test_switch(ctx.handle, 0))
+        ctx.set_precision(0)
