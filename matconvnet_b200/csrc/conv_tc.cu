@@ -1040,7 +1040,7 @@ __device__ __forceinline__ float lds32(uint32_t addr)
 // Where row `row` (0..127, = TMEM lane) of row tile `tm` lies in the output: image, pixel ho + Ho*wo, and whether it exists.
 // Linear mode: the tile is 128 consecutive output pixels (ho fastest, images following one another).  Box mode (p.tma):
 // the tile is a box of bh x bw pixels of one image, row = dh + bh*dw.
-struct RowPos { int img, pix; bool valid; };
+struct RowPos { int img, pix, split; bool valid; };
 
 __device__ __forceinline__ RowPos row_pos(Params const& p, int tm, int row)
 {
@@ -1051,9 +1051,11 @@ __device__ __forceinline__ RowPos row_pos(Params const& p, int tm, int row)
     int const split = tm / p.tilesM, t = tm - split * p.tilesM, cb = t / p.tapGroups, tg = t - cb * p.tapGroups;
     int const tl = row / p.cPer, c = cb * p.cPer + (row - tl * p.cPer), tap = tg * p.tapsPerTile + tl, taps = p.a.FH * p.a.FW;
     r.valid = tap < taps && c < p.a.C;
-    r.img = 0; r.pix = r.valid ? tap + taps * c + split * (int)p.e.splitStride : 0;
+    r.img = 0; r.pix = r.valid ? tap + taps * c : 0; r.split = split;
     return r;
   }
+  // tm = row tile + tilesM * reduction range (one range unless the caller cut the reduction)
+  r.split = tm / p.tilesM; tm -= r.split * p.tilesM;
   if (!p.tma) {
     int const m = tm * BM + row;
     r.valid = m < p.M;
@@ -1079,7 +1081,7 @@ __device__ __forceinline__ void ts_store_tile(Params const& p, float const* P, i
   RowPos const rp = row_pos(p, tm, row);
   if (!rp.valid) return;
   int const pix = rp.pix, img = rp.img;
-  float* const dst0 = p.e.out + ((long long)img * p.e.Ktot * p.e.P + pix);
+  float* const dst0 = p.e.out + ((long long)rp.split * p.e.splitStride + (long long)img * p.e.Ktot * p.e.P + pix);
   int const nEnd = min(p.BN, p.N - n0);
   if (maskBits) {
     // the mask of this row was fetched while the tile was being computed: bit c = the mask is positive in column c
@@ -1165,9 +1167,9 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p, const 
   uint32_t const xTile0 = smem_u32(Psm) + (uint32_t)BN * BM * 4u;
 
   int const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int const numIter = kWg ? p.kbPerSplit : p.numKb;      // k-blocks per tile
+  int const numIter = p.kbPerSplit;                      // k-blocks per tile (work item: one range of the reduction of one output tile)
   int const chunksPerTile = kSplit ? (numIter + kTsDrainEvery - 1) / kTsDrainEvery : 1;
-  int const numTiles = p.tilesM * p.tilesN * (kWg ? p.splits : 1);
+  int const numTiles = p.tilesM * p.tilesN * p.splits;
   // this CTA's tiles: blockIdx.x, blockIdx.x + gridDim.x, ...; tile t = (row tile t / tilesN, column tile t % tilesN)
   int const myTiles = (int)blockIdx.x < numTiles ? (numTiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
   bool const singleTile = (int)gridDim.x == numTiles;      // launched with one CTA per tile (long reductions)
@@ -1221,7 +1223,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p, const 
       float const* mkRow = p.e.mask;
       if (preMask) {
         RowPos const rp = row_pos(p, tm, warp * 32 + lane);     // a row that does not exist reads (and discards) the mask of a pixel that does
-        mkRow += ((long long)rp.img * p.e.Ktot + n0) * p.e.P + rp.pix;
+        mkRow += ((long long)rp.img * p.e.Ktot + n0) * p.e.P + rp.pix;      // (a masked data gradient is never cut into ranges)
       }
       int lc = 0;                                     // batches of sixteen mask columns fetched so far
       for (int c = 0; c < chainsF && ok; ++c) {
@@ -1377,8 +1379,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p, const 
       for (int ts = 0; ts < myTiles && ok; ++ts) {
         int const tile = (int)blockIdx.x + ts * (int)gridDim.x;
         int const nt = tile % p.tilesN;
-        float const* src = p.bTiles + (size_t)nt * p.numKb * (bBytes / 4);
-        if (kWg) src = p.bTiles + ((size_t)nt * p.kbTot + (size_t)(tile / p.tilesN / p.tilesM) * numIter) * (bBytes / 4);
+        float const* src = p.bTiles + ((size_t)nt * p.kbTot + (size_t)(tile / p.tilesN / p.tilesM) * numIter) * (bBytes / 4);
         for (int it = 0; it < numIter; ++it) {
           if (!mbar_wait(smem_u32(&emptyB[sb]), ph)) { atomicExch(p.status, 8); ok = false; break; }
           mbar_arrive_expect_tx(smem_u32(&fullB[sb]), bBytes);
@@ -1439,10 +1440,12 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p, const 
       long long xs = 0;
       bool ok = true;
       for (int ts = 0; ts < myTiles && ok; ++ts) {
-        int const tm = ((int)blockIdx.x + ts * (int)gridDim.x) / p.tilesN;
+        int const tmf = ((int)blockIdx.x + ts * (int)gridDim.x) / p.tilesN;
+        int const split = tmf / p.tilesM, tm = tmf - split * p.tilesM;
         int const n = tm / per, t = tm - n * per, wb = t / p.tilesH, hb = t - wb * p.tilesH;
         int const c0 = hb * p.bh - p.a.pt - p.rowOff, c1 = wb * p.bw - p.a.pl;      // c0 is a multiple of four: bh and pt + rowOff are
-        for (int cb = 0; cb < numCb; ++cb, ++xs) {
+        int const cbEnd = (split + 1) * numCb;                                      // a range of the reduction is whole channel blocks
+        for (int cb = split * numCb; cb < cbEnd; ++cb, ++xs) {
           int const buf = (int)(xs & 1);
           if (xs >= 2 && !mbar_wait(smem_u32(&emptyX[buf]), (uint32_t)(((xs >> 1) - 1) & 1))) { atomicExch(p.status, 12); ok = false; break; }
           mbar_arrive_expect_tx(smem_u32(&fullX[buf]), xTileBytes);
@@ -1578,7 +1581,8 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p, const 
     } else {
       for (int ts = 0; ts < myTiles && ok; ++ts) {
         int const tile = (int)blockIdx.x + ts * (int)gridDim.x;
-        int const m = (tile / p.tilesN) * BM + quarter * 32 + lane;
+        int const tmf = tile / p.tilesN, split = tmf / p.tilesM, kb0 = split * numIter;     // this item's range starts at k-block kb0
+        int const m = (tmf - split * p.tilesM) * BM + quarter * 32 + lane;
         uint32_t hm = 0, wm = 0;                          // tap rows / columns inside the image for this pixel
         float const* xq = p.a.ptr;
         if (m < p.M) {
@@ -1588,15 +1592,15 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p, const 
           for (int fw = 0; fw < p.a.FW; ++fw) { int w = wo * p.a.sx + fw * p.a.dx - p.a.pl; if (w >= 0 && w < p.a.W) wm |= 1u << fw; }
         }
         for (int it = (int)((gi ^ grp) & 1); it < numIter; it += kTsGroups) {
-          int const r = it * BK;
+          int const r = (kb0 + it) * BK;
           float v[32];
           if (p.chanFast) {
             // the whole k-block is one filter tap and 32 consecutive channels: one validity test, constant stride.  The taps
             // of a channel block follow one another, so that the lines fetched for one tap are still in L1 for the next.
-            int const tp = it % taps, c0 = (it / taps) * 32;
+            int const tp = (kb0 + it) % taps, c0 = ((kb0 + it) / taps) * 32;
             int2 const te = tapLut[tp];
             uint32_t const e = (uint32_t)te.y;
-            bool const on = ((hm >> (e & 31u)) & (wm >> (e >> 5)) & 1u) != 0;
+            bool const on = ((hm >> (e & 31u)) & (wm >> (e >> 5)) & 1u) != 0 && c0 < p.a.C;      // (c0 >= C: padding of the last range)
             // unconditional loads (a pixel outside the image reads the start of the tensor instead and discards it):
             // nothing for the compiler to predicate or branch around, all 32 in flight together
             float const* const q = on ? xq + ((long long)c0 * HW + te.x) : p.a.ptr;
@@ -1672,6 +1676,7 @@ __global__ void flip_filters_kernel(float* __restrict__ ft, float const* __restr
 // kb: [hi tile BN x 32][lo tile BN x 32], K-major with the 128-byte swizzle -- so that a producer
 // fetches a whole stage of B with one bulk copy.
 // modes 3 / 4: as 0 / 1 with the reduction index in blocks of 32 channels, all filter taps of a block one after the other.
+// mode 5: B(n, r) = F[n + N*r].
 // mode 0: B(n, r) = F[n*R + r].  mode 2: B(n, r) = dY[pixel, n, image] with r = pixel + P*image.  mode 1 (data gradient of a stride-1 convolution): n = channel c,
 // r = fh' + FH*(fw' + FW*k), B = F[FH-1-fh', FW-1-fw', c, k].
 template <bool kSplit>
@@ -1690,6 +1695,9 @@ __global__ void prep_b_tiles_kernel(float* __restrict__ out, float const* __rest
         // filter gradient: n = filter, r = pixel + P*image of dY (FH carries P here)
         int img = r / FH, pix = r - img * FH;
         val = f[((size_t)img * N + n) * FH + pix];
+      } else if (mode == 5) {
+        // B(n, r) = f[n + N*r]: rows contiguous (dY of a fully connected layer as the filters of its weight gradient)
+        val = f[(size_t)r * N + n];
       } else if (mode == 3) {
         // forward filters, reduction in blocks of 32 channels: r = c%32 + 32*(tap + taps*(c/32))
         int taps = FH * FW, t = r >> 5, tap = t % taps, c = (t / taps) * 32 + (r & 31);
@@ -1921,6 +1929,7 @@ bool plan_windows(vlb_ctx* ctx, Params& p, CUtensorMap* map, size_t* smemBytes, 
   Operand const& a = p.a;
   if (ctx->testSwitch & 2) return false;
   if (!p.chanFast || a.sy != 1 || a.sx != 1 || a.H % 4 != 0 || !aligned16(a.ptr)) return false;
+  if (p.splits > 1 && p.kbPerSplit % (a.FH * a.FW) != 0) return false;      // a range of the reduction must be whole channel blocks
   EncodeTiledFn const encode = encode_tiled();
   if (!encode) return false;
   int const Ho = a.Ho, Wo = a.Wo;
@@ -1969,11 +1978,13 @@ int launch_ts(vlb_ctx* ctx, Params& p, char const* where)
   size_t smemBytes = (size_t)kTsBStages * (split3 ? 2u : 1u) * (size_t)p.BN * BK * 4 + sizeof(float) * (size_t)p.BN * BM + 1024;
   p.bStages = kTsBStages;
   p.tilesM = vlb::ceil_div(p.M, BM); p.tilesN = vlb::ceil_div(p.N, p.BN);
+  if (p.splits < 1) { p.splits = 1; p.kbPerSplit = p.numKb; }
+  p.kbTot = p.splits * p.kbPerSplit;       // what the tile images hold per column tile
   CUtensorMap map;
   memset(&map, 0, sizeof(map));
   bool const windows = plan_windows(ctx, p, &map, &smemBytes, split3);
   if (smemBytes < 120u * 1024u) smemBytes = 120u * 1024u;
-  long long const numTiles = (long long)p.tilesM * p.tilesN;
+  long long const numTiles = (long long)p.tilesM * p.tilesN * p.splits;
   if (numTiles >= (1LL << 31)) return VLB_Unsupported;
   // Persistent: one CTA per SM walks the tiles, so that the pipeline never drains between tiles and a tile is stored
   // while the next one is computed.  With fewer tiles than SMs every CTA has one tile and all its warps share the stores.
@@ -2024,12 +2035,12 @@ int pick_splits(vlb_ctx* ctx, int tiles, int numKb, int minKbPerSplit)
 
 // The cut of a filter gradient's reduction (numKb k-blocks, `tiles` output tiles) into ranges: the work items -- tiles x
 // ranges -- should fill whole waves of the persistent CTAs, with ranges long enough that a tile's fixed cost stays small.
-int pick_wg_splits(int smCount, int tiles, int numKb, int* kbPerSplit)
+int pick_wg_splits(int smCount, int tiles, int numKb, int* kbPerSplit, int minKb = 48)
 {
   int best = 1; double bestEff = 0.0;
   for (int w = 1; w <= 6; ++w) {
     int s = std::max(1, (w * smCount) / tiles);
-    s = std::min(s, std::max(1, numKb / 48));
+    s = std::min(s, std::max(1, numKb / minKb));
     int const per = vlb::ceil_div(numKb, s);
     s = vlb::ceil_div(numKb, per);
     long long const items = (long long)tiles * s;
@@ -2060,6 +2071,56 @@ bool fits32(ConvGeom const& g)
   return in < (1LL << 31) - 256 && out < (1LL << 31) - 256 && (long long)g.FH * g.FW * g.FC * g.K < (1LL << 31);
 }
 
+// conv_ts_kernel in its row mode (kMode 2): rows whose reduction index is contiguous in memory, delivered by the 3-D tensor map `map`
+// (run of 36 elements x cPer rows x 1).  p holds the tiling (cPer, tapsPerTile, tapGroups, tilesM, tilesN, splits, kbPerSplit,
+// kbTot), the operand geometry, the tile images and the epilogue.
+int launch_rows(vlb_ctx* ctx, Params& p, CUtensorMap const& map, char const* where)
+{
+  bool const split3 = ctx->precision == VLB_PRECISION_3XTF32;
+  // shared memory: filter-tile stages, the running sum, the runs
+  size_t const bBytes = (size_t)(split3 ? 2 : 1) * p.BN * BK * 4, pBytes = sizeof(float) * (size_t)p.BN * BM;
+  size_t const limit = 227 * 1024 - 1536;
+  p.bStages = 0;
+  for (int nb = kTsBStages; nb >= 3 && !p.bStages; --nb)
+    for (int nx = kTsXStages; nx >= 3 && !p.bStages; --nx)
+      if ((size_t)nb * bBytes + pBytes + (size_t)nx * kWgStageBytes + 1024 <= limit) { p.bStages = nb; p.xStages = nx; }
+  if (!p.bStages) return vlb::set_error(ctx, VLB_Unsupported, where);
+  size_t smemBytes = (size_t)p.bStages * bBytes + pBytes + (size_t)p.xStages * kWgStageBytes + 1024;
+  if (smemBytes < 120u * 1024u) smemBytes = 120u * 1024u;      // two CTAs (each allocating all 512 TMEM columns) never share an SM
+  p.wg = 1;
+  p.status = ctx->deviceStatus;
+  p.testSwitch = ctx->testSwitch;
+  p.chanFast = 1;
+  long long const numTiles = (long long)p.tilesM * p.tilesN * p.splits;
+  if (numTiles >= (1LL << 31)) return VLB_Unsupported;
+  dim3 grid((unsigned)std::min<long long>(numTiles, ctx->smCount), 1, 1);
+  cudaError_t e;
+  if (split3) {
+    e = allow_large_smem<conv_ts_kernel<true, 2>>(ctx->device);
+    if (e == cudaSuccess) conv_ts_kernel<true, 2><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p, map);
+  } else {
+    e = allow_large_smem<conv_ts_kernel<false, 2>>(ctx->device);
+    if (e == cudaSuccess) conv_ts_kernel<false, 2><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p, map);
+  }
+  if (e != cudaSuccess) { cudaGetLastError(); return vlb::set_error(ctx, VLB_Cuda, cudaGetErrorString(e)); }
+  VLB_LAUNCHED(ctx, 1);
+  return vlb::check_launch(ctx, where);
+}
+
+// The 3-D tensor map (run, rows, planes) of launch_rows; false when the driver refuses it.
+bool rows_map(CUtensorMap* map, float const* ptr, long long run, long long rows, long long planes, int cPer)
+{
+  EncodeTiledFn const encode = encode_tiled();
+  if (!encode) return false;
+  memset(map, 0, sizeof(*map));
+  cuuint64_t const dims[3] = {(cuuint64_t)run, (cuuint64_t)rows, (cuuint64_t)planes};
+  cuuint64_t const strides[2] = {(cuuint64_t)run * 4, (cuuint64_t)run * rows * 4};
+  cuuint32_t const box[3] = {(cuuint32_t)kWgRowWords, (cuuint32_t)cPer, 1u};
+  cuuint32_t const estr[3] = {1u, 1u, 1u};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // Filter gradient of a stride-1 convolution whose output has the input's height (every VGG / ResNet 3x3 layer), through
 // conv_ts_kernel: rows (tap, channel) in tensor memory, dY as tile images.  Returns -1 when the layer is not eligible (the
 // caller then takes tc_gemm_kernel), else an error code.
@@ -2073,13 +2134,9 @@ int conv_wgrad_ts(vlb_ctx* ctx, ConvGeom const& g, float* dF, float* db, float c
   if (g.C % 32 != 0 || (g.C > 128 && g.C % 128 != 0) || (g.C < 128 && 128 % g.C != 0)) return -1;
   if (g.K > 4096 || !aligned16(X) || !aligned16(dY)) return -1;
   if ((g.FH - 1) * g.dy - g.pt >= g.H || g.pt >= g.H) return -1;
-  EncodeTiledFn const encode = encode_tiled();
-  if (!encode) return -1;
-  bool const split3 = ctx->precision == VLB_PRECISION_3XTF32;
   int const V = taps * g.C;
   long long const R = (long long)P * g.N;
   Params p = {};
-  p.wg = 1;
   p.cPer = std::min(g.C, 128); p.tapsPerTile = 128 / p.cPer; p.tapGroups = vlb::ceil_div(taps, p.tapsPerTile);
   p.M = V; p.N = g.K; p.R = (int)R;
   p.BN = pick_bn(p.N);
@@ -2095,25 +2152,8 @@ int conv_wgrad_ts(vlb_ctx* ctx, ConvGeom const& g, float* dF, float* db, float c
   if ((long long)nF * p.splits >= (1LL << 31)) return -1;
   size_t const partBytes = p.splits > 1 ? ((sizeof(float) * nF * p.splits + 255) & ~(size_t)255) : 0;
   size_t const tileBytes = b_tiles_bytes(ctx, g.K, p.BN, p.kbTot);
-  // shared memory: filter-tile stages, the running sum, the x runs
-  size_t const bBytes = (size_t)(split3 ? 2 : 1) * p.BN * BK * 4, pBytes = sizeof(float) * (size_t)p.BN * BM;
-  size_t const limit = 227 * 1024 - 1536;
-  p.bStages = 0;
-  for (int nb = kTsBStages; nb >= 3 && !p.bStages; --nb)
-    for (int nx = kTsXStages; nx >= 3 && !p.bStages; --nx)
-      if ((size_t)nb * bBytes + pBytes + (size_t)nx * kWgStageBytes + 1024 <= limit) { p.bStages = nb; p.xStages = nx; }
-  if (!p.bStages) return -1;
-  size_t smemBytes = (size_t)p.bStages * bBytes + pBytes + (size_t)p.xStages * kWgStageBytes + 1024;
-  if (smemBytes < 120u * 1024u) smemBytes = 120u * 1024u;      // two CTAs (each allocating all 512 TMEM columns) never share an SM
   CUtensorMap map;
-  memset(&map, 0, sizeof(map));
-  cuuint64_t const dims[3] = {(cuuint64_t)HW, (cuuint64_t)g.C, (cuuint64_t)g.N};
-  cuuint64_t const strides[2] = {(cuuint64_t)HW * 4, (cuuint64_t)HW * g.C * 4};
-  cuuint32_t const box[3] = {(cuuint32_t)kWgRowWords, (cuuint32_t)p.cPer, 1u};
-  cuuint32_t const estr[3] = {1u, 1u, 1u};
-  if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(X), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-    return -1;
+  if (!rows_map(&map, X, HW, g.C, g.N, p.cPer)) return -1;
 
   ProfScope prof(ctx, kProfWgrad);      // includes the dY tile images (with the bias gradient) and the sum of the partial results
   prof.rec.flops = 2.0 * (double)V * (double)g.K * (double)R;
@@ -2123,26 +2163,114 @@ int conv_wgrad_ts(vlb_ctx* ctx, ConvGeom const& g, float* dF, float* db, float c
   float* const part = p.splits > 1 ? (float*)((char*)p.bTiles + tileBytes) : nullptr;
   p.e = Epilogue{};
   p.e.out = part ? part : dF; p.e.splitStride = part ? (long long)nF : 0; p.e.inMult = 1.f; p.e.P = V; p.e.Ktot = g.K;
-  p.status = ctx->deviceStatus;
-  p.testSwitch = ctx->testSwitch;
-  p.chanFast = 1;
-  long long const numTiles = (long long)p.tilesM * p.tilesN * p.splits;
-  dim3 grid((unsigned)std::min<long long>(numTiles, ctx->smCount), 1, 1);
-  cudaError_t e;
-  if (split3) {
-    e = allow_large_smem<conv_ts_kernel<true, 2>>(ctx->device);
-    if (e == cudaSuccess) conv_ts_kernel<true, 2><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p, map);
-  } else {
-    e = allow_large_smem<conv_ts_kernel<false, 2>>(ctx->device);
-    if (e == cudaSuccess) conv_ts_kernel<false, 2><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p, map);
-  }
-  if (e != cudaSuccess) { cudaGetLastError(); return vlb::set_error(ctx, VLB_Cuda, cudaGetErrorString(e)); }
-  VLB_LAUNCHED(ctx, 1);
+  int const rc = launch_rows(ctx, p, map, "conv_wgrad_ts");
+  if (rc) return rc;
   if (part) {
     tc_splitk_reduce_kernel<<<vlb::grid_for(nF, 256, ctx->smCount * 8), 256, 0, ctx->stream>>>(dF, part, nF, nF, p.splits);
     VLB_LAUNCHED(ctx, 1);
   }
   return vlb::check_launch(ctx, "conv_wgrad_ts");
+}
+
+// The geometry of a 1 x 1 convolution over a "plane" of `pixels` elements with `channels` channels (channel stride = pixels).
+ConvGeom plane_geom(int pixels, int channels, int filters)
+{
+  ConvGeom t = {};
+  t.H = pixels; t.W = 1; t.C = channels; t.N = 1; t.FH = 1; t.FW = 1; t.FC = channels; t.K = filters; t.Ho = pixels; t.Wo = 1;
+  t.sy = 1; t.sx = 1; t.dy = 1; t.dx = 1; t.G = 1;
+  return t;
+}
+
+// Fully connected layers at small batch are bound by the one pass over the weights (fc6 of VGG-16: 411 MB against 13 GFLOP at
+// batch 64).  All three passes run through conv_ts_kernel, whose A operand goes from global memory to tensor memory without a
+// shared-memory tile of its own, each with the weights (or their gradient) as the operand that is read or written exactly once:
+//   forward   Y(K x N) = F'(K x V) X(V x N): rows = filters, the reduction index v is contiguous in a row -> row mode, X as tile images;
+//   data      dX(V x N) = F(V x K) dY(K x N): a 1 x 1 convolution over the "plane" of V elements with K channels, dY as its N filters;
+//   weights   dF(V x K) = X(V x N) dY'(N x K): a 1 x 1 convolution over the plane X (N channels) with the K rows of dY as filters.
+// Each returns -1 when the shape is not eligible (the caller then takes tc_gemm_kernel).
+int fc_fprop_ts(vlb_ctx* ctx, ConvGeom const& g, float* Y, float const* X, float const* F, float const* b)
+{
+  int const V = g.FH * g.FW * g.FC;
+  if ((ctx->testSwitch & 4) || V % 32 != 0 || V < 128 * 64 || g.K % 128 != 0 || g.N > 4096 || !aligned16(X) || !aligned16(F)) return -1;
+  Params p = {};
+  p.cPer = 128; p.tapsPerTile = 1; p.tapGroups = 1;
+  p.M = g.K; p.N = g.N; p.R = V;
+  p.BN = pick_bn(p.N);
+  p.tilesM = g.K / 128; p.tilesN = vlb::ceil_div(p.N, p.BN);
+  p.splits = pick_wg_splits(ctx->smCount, p.tilesM * p.tilesN, V / BK, &p.kbPerSplit);
+  p.kbTot = p.splits * p.kbPerSplit; p.numKb = p.kbTot;
+  conv_operand(p.a, plane_geom(V, g.K, g.N), F, g.K);
+  p.a.rows = g.K;
+  size_t const nOut = (size_t)g.K * g.N;
+  size_t const partBytes = p.splits > 1 ? ((sizeof(float) * nOut * p.splits + 255) & ~(size_t)255) : 0;
+  CUtensorMap map;
+  if (!rows_map(&map, F, V, g.K, 1, 128)) return -1;
+  ProfScope prof(ctx, kProfFc);
+  prof.rec.flops = 2.0 * (double)g.K * (double)g.N * (double)V;
+  p.bTiles = prep_dy_tiles(ctx, X, g.N, V, V, p.BN, p.kbTot, partBytes, nullptr);      // B(n, v) = X[v + V n]
+  if (!p.bTiles) return ctx->lastError;
+  float* const part = p.splits > 1 ? (float*)((char*)p.bTiles + b_tiles_bytes(ctx, g.N, p.BN, p.kbTot)) : nullptr;
+  p.e = Epilogue{};
+  p.e.out = part ? part : Y; p.e.splitStride = part ? (long long)nOut : 0; p.e.inMult = 1.f; p.e.P = g.K; p.e.Ktot = g.N;
+  int rc = launch_rows(ctx, p, map, "fc_fprop_ts");
+  if (rc) return rc;
+  if (part) {
+    tc_splitk_reduce_kernel<<<vlb::grid_for(nOut, 256, ctx->smCount * 8), 256, 0, ctx->stream>>>(Y, part, nOut, nOut, p.splits);
+    VLB_LAUNCHED(ctx, 1);
+  }
+  if (b) return vlb_bias_forward(ctx, Y, 1.0, nullptr, 0.0, b, 1.0, 1, 1, g.K, g.N);
+  return vlb::check_launch(ctx, "fc_fprop_ts");
+}
+
+int fc_dgrad_ts(vlb_ctx* ctx, ConvGeom const& g, float* dX, float const* F, float const* dY)
+{
+  int const V = g.FH * g.FW * g.FC;
+  if ((ctx->testSwitch & 4) || V % 4 != 0 || g.K % 32 != 0 || !aligned16(F) || !aligned16(dY) || V < 128 * 16) return -1;
+  Params p = {};
+  p.M = V; p.N = g.N; p.R = g.K;
+  ConvGeom const t = plane_geom(V, g.K, g.N);
+  conv_operand(p.a, t, F, g.K);
+  p.a.rows = V;
+  p.BN = pick_bn(p.N);
+  int const numKb = vlb::ceil_div(g.K, BK);
+  p.splits = pick_wg_splits(ctx->smCount, vlb::ceil_div(V, BM) * vlb::ceil_div(p.N, p.BN), numKb, &p.kbPerSplit, 16);
+  p.numKb = p.splits * p.kbPerSplit;
+  p.chanFast = 1; p.pipelined = 1;
+  size_t const nOut = (size_t)V * g.N;
+  size_t const partBytes = p.splits > 1 ? sizeof(float) * nOut * p.splits : 0;
+  ProfScope prof(ctx, kProfFc);
+  prof.rec.flops = 2.0 * (double)V * (double)g.N * (double)g.K;
+  p.bTiles = prep_b_tiles(ctx, dY, g.N, g.K, p.BN, p.numKb, 0, t, partBytes);            // B(n, k) = dY[k + K n]
+  if (!p.bTiles) return ctx->lastError;
+  float* const part = p.splits > 1 ? (float*)((char*)p.bTiles + b_tiles_bytes(ctx, g.N, p.BN, p.numKb)) : nullptr;
+  p.e = Epilogue{};
+  p.e.out = part ? part : dX; p.e.splitStride = part ? (long long)nOut : 0; p.e.inMult = 1.f; p.e.P = V; p.e.Ktot = g.N;
+  int rc = launch_ts(ctx, p, "fc_dgrad_ts");
+  if (rc || !part) return rc;
+  tc_splitk_reduce_kernel<<<vlb::grid_for(nOut, 256, ctx->smCount * 8), 256, 0, ctx->stream>>>(dX, part, nOut, nOut, p.splits);
+  VLB_LAUNCHED(ctx, 1);
+  return vlb::check_launch(ctx, "fc_dgrad_ts");
+}
+
+int fc_wgrad_ts(vlb_ctx* ctx, ConvGeom const& g, float* dF, float const* X, float const* dY)
+{
+  int const V = g.FH * g.FW * g.FC;
+  if ((ctx->testSwitch & 4) || V % 4 != 0 || g.N % 32 != 0 || !aligned16(X) || !aligned16(dY) || V < 128 * 64) return -1;
+  Params p = {};
+  p.M = V; p.N = g.K; p.R = g.N;
+  ConvGeom const t = plane_geom(V, g.N, g.K);
+  conv_operand(p.a, t, X, g.N);
+  p.a.rows = V;
+  p.BN = pick_bn(p.N);
+  p.numKb = vlb::ceil_div(g.N, BK); p.kbPerSplit = p.numKb; p.splits = 1;
+  p.chanFast = 1; p.pipelined = 1;
+  ProfScope prof(ctx, kProfFc);
+  prof.rec.flops = 2.0 * (double)V * (double)g.K * (double)g.N;
+  p.bTiles = prep_b_tiles(ctx, dY, g.K, g.N, p.BN, p.numKb, 5, t);                       // B(k, n) = dY[k + K n]
+  if (!p.bTiles) return ctx->lastError;
+  p.e = Epilogue{};
+  p.e.out = dF; p.e.inMult = 1.f; p.e.P = V; p.e.Ktot = g.K;
+  return launch_ts(ctx, p, "fc_wgrad_ts");
 }
 
 bool is_fc(ConvGeom const& g)
@@ -2164,6 +2292,10 @@ int conv_fprop_tc(vlb_ctx* ctx, ConvGeom const& g, float* Y, float outMult, floa
   if (is_fc(g)) {
     // Y(K x N) = F'(K x V) X(V x N) + b 1'  (reference bits/nnfullyconnected.cu:45-70): rows = filters
     if (outMult != 0.f || inMult != 1.f) return VLB_Unsupported;
+    {
+      int const rc = fc_fprop_ts(ctx, g, Y, X, F, b);
+      if (rc >= 0) return rc;
+    }
     ProfScope prof(ctx, kProfFc);
     prof.rec.flops = 2.0 * (double)g.K * (double)g.N * (double)V;
     p.M = g.K; p.N = g.N; p.R = V;
@@ -2220,6 +2352,10 @@ int conv_dgrad_tc(vlb_ctx* ctx, ConvGeom const& g, float* dX, float const* F, fl
   if (is_fc(g)) {
     // dX(V x N) = F(V x K) dY(K x N)  (reference bits/nnfullyconnected.cu:139-151): rows = input elements
     int const V = g.FH * g.FW * g.FC;
+    {
+      int const rc = fc_dgrad_ts(ctx, g, dX, F, dY);
+      if (rc >= 0) return rc;
+    }
     ProfScope prof(ctx, kProfFc);
     prof.rec.flops = 2.0 * (double)V * (double)g.N * (double)g.K;
     p.M = V; p.N = g.N; p.R = g.K;
@@ -2275,6 +2411,10 @@ int conv_wgrad_tc(vlb_ctx* ctx, ConvGeom const& g, float* dF, float* db, float c
   Params p = {};
   if (is_fc(g)) {
     // dF(V x K) = X(V x N) dY'(N x K)  (reference bits/nnfullyconnected.cu:126-137): reduction over the batch
+    {
+      int const rc = fc_wgrad_ts(ctx, g, dF, X, dY);
+      if (rc >= 0) return rc;
+    }
     ProfScope prof(ctx, kProfFc);
     prof.rec.flops = 2.0 * (double)V * (double)g.K * (double)g.N;
     p.M = V; p.N = g.K; p.R = g.N;

@@ -64,3 +64,47 @@ def test_filter_gradient_rows_in_tensor_memory(gpu, oracle, case, precision, tol
     finally:
         ctx.check(lib.vlb_ctx_set_test_switch(ctx.handle, 0))
         ctx.set_precision(0)
+
+
+# Fully connected layers with a large weight matrix take the same kernel for all three passes: the forward pass in the row
+# mode (rows = filters), the two backward passes as 1 x 1 convolutions over the weight matrix / the input seen as a plane.
+FC_CASES = [((4, 4, 512, 64), 256),       # V = 8192, two row tiles of filters, batch 64: 64-column tiles
+            ((8, 8, 128, 96), 128),       # batch 96: 128-column tiles, one of them partly empty
+            ((4, 4, 512, 40), 384),       # batch 40: the weight gradient (reduction over the batch, not a multiple of 32) stays on the other kernel
+            ((2, 2, 2048, 96), 1000)]     # 1000 filters: the forward pass (rows in blocks of 128) stays on the other kernel; two column tiles
+
+
+@pytest.mark.parametrize("precision,tol", [(0, 1e-5), (1, 2e-3)])
+@pytest.mark.parametrize("case", range(len(FC_CASES)))
+def test_fully_connected_through_the_tensor_memory_kernel(gpu, oracle, case, precision, tol):
+    nn, mat, ctx = gpu
+    xs, K = FC_CASES[case]
+    rng = np.random.default_rng(400 + case)
+    V = xs[0] * xs[1] * xs[2]
+    x = np.asfortranarray(rng.standard_normal(xs).astype(np.float32))
+    f = np.asfortranarray((rng.standard_normal(xs[:3] + (K,)) * (2.0 / V) ** 0.5).astype(np.float32))
+    b = rng.standard_normal(K).astype(np.float32)
+    dy = np.asfortranarray(rng.standard_normal((1, 1, K, xs[3])).astype(np.float32))
+    x64, f64, dy64 = x.astype(np.float64), f.astype(np.float64), dy.astype(np.float64)
+    yr = oracle.fc_forward(x64, f64, b.astype(np.float64))
+    dxr, dfr, dbr = oracle.fc_backward(x64, f64, dy64)
+    xd, fd, bd, dyd = mat.from_numpy(x), mat.from_numpy(f), mat.from_numpy(b.reshape(1, -1)), mat.from_numpy(dy)
+    ctx.set_precision(precision)
+    lib = ctx.lib
+    try:
+        first = None
+        for switch in (0, 4, 0):
+            ctx.check(lib.vlb_ctx_set_test_switch(ctx.handle, switch))
+            y = mat.to_numpy(nn.vl_nnconv(xd, fd, bd, ctx=ctx))
+            yrelu = mat.to_numpy(nn.vl_nnconv(xd, fd, bd, relu=True, ctx=ctx))
+            dx, df, db = (mat.to_numpy(a) for a in nn.vl_nnconv(xd, fd, bd, dyd, ctx=ctx))
+            assert ctx.device_status() == 0
+            assert rel_l2(y, yr) < tol and rel_l2(dx, dxr) < tol and rel_l2(df, dfr) < tol and rel_l2(db.ravel(), dbr.ravel()) < 1e-5, switch
+            assert np.array_equal(yrelu, np.maximum(y, 0))
+            if switch == 0 and first is None:
+                first = (y, dx, df)
+            elif switch == 0:
+                assert all(np.array_equal(a, c) for a, c in zip(first, (y, dx, df)))      # run to run identical
+    finally:
+        ctx.check(lib.vlb_ctx_set_test_switch(ctx.handle, 0))
+        ctx.set_precision(0)
