@@ -117,6 +117,7 @@ struct Params {
   // reduction (output pixels of the whole batch, kbTot k-blocks in the dY tile images) is cut into `splits` ranges of kbPerSplit
   // k-blocks, one work item per (range, row tile, column tile); the x runs arrive by tensor-map copies, xStages buffers.
   int wg, cPer, tapsPerTile, tapGroups, kbTot, splits, xStages;
+  int plane;              // row mode: reduction indices per image in the tile images -- the plane's pixels rounded up to whole k-blocks
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -1412,9 +1413,10 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p, const 
     // the producers have let go of window xs - 2, i.e. as far ahead of its use as two buffers allow.
     if (kWg && lane == 0) {
       // One run of 36 pixels x cPer channels per k-block and tap of the tile, from the plane of image r / P starting at
-      // pixel r % P + shift of the tap, rounded down to four pixels.  Pixels before the plane's first or past its last one
+      // pixel r % P + shift of the tap, rounded down to four pixels (P: the plane rounded up to whole k-blocks; the tile images
+      // hold zeros for the pixels added).  Pixels before the plane's first or past its last one
       // -- a tap that leaves the image to the left or right, a k-block past the end of the batch -- arrive as zeros.
-      int const taps = p.a.FH * p.a.FW, P = p.a.Ho * p.a.Wo, nX = p.xStages;
+      int const taps = p.a.FH * p.a.FW, P = p.plane, nX = p.xStages;
       int buf = 0; uint32_t ph = 1;                        // first use of a buffer: nothing to wait for
       bool ok = true;
       for (int ts = 0; ts < myTiles && ok; ++ts) {
@@ -1496,7 +1498,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p, const 
       // is 32 consecutive output pixels; the row's 36-pixel run lies in shared memory, the wanted 32 start `s` pixels in.
       int const row = quarter * 32 + lane;
       int const tl = (quarter * 32) / p.cPer;
-      int const H = p.a.H, P = p.a.Ho * p.a.Wo, nX = p.xStages;
+      int const H = p.a.H, P = p.plane, nX = p.xStages;
       for (int ts = 0; ts < myTiles && ok; ++ts) {
         int const tmf = ((int)blockIdx.x + ts * (int)gridDim.x) / p.tilesN;
         int const split = tmf / p.tilesM, t = tmf - split * p.tilesM, tg = t % p.tapGroups;
@@ -1734,7 +1736,7 @@ constexpr int kPrepThreads = 256, kPrepIters = 4;
 
 template <bool kSplit>
 __global__ void __launch_bounds__(kPrepThreads)
-prep_dy_tiles_kernel(float* __restrict__ out, float const* __restrict__ dy, int N, int R, int P, int BN, int numKb,
+prep_dy_tiles_kernel(float* __restrict__ out, float const* __restrict__ dy, int N, int R, int P, int Pp, int BN, int numKb,
                      float* __restrict__ db, float* __restrict__ dbPart, unsigned* __restrict__ tickets)
 {
   __shared__ float red[kPrepThreads / 32];
@@ -1747,10 +1749,9 @@ prep_dy_tiles_kernel(float* __restrict__ out, float const* __restrict__ dy, int 
     int const r = ((int)blockIdx.x * kPrepIters + u) * (kPrepThreads * 4) + (int)threadIdx.x * 4;
     if (r < Rp) {
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (n < N && r < R) {
-        int const img = r / P, pix = r - img * P;
-        v = *reinterpret_cast<float4 const*>(dy + ((size_t)img * N + n) * P + pix);
-      }
+      // reduction index r = pixel + Pp * image (Pp >= P: planes padded to whole k-blocks read as zeros); R = P * images
+      int const img = r / Pp, pix = r - img * Pp;
+      if (n < N && pix < P && img * P + pix < R) v = *reinterpret_cast<float4 const*>(dy + ((size_t)img * N + n) * P + pix);
       sum += (v.x + v.y) + (v.z + v.w);
       int const kb = r >> 5, kk = r & 31;
       size_t const base = ((size_t)tile * numKb + kb) * (kSplit ? 2 : 1) * (size_t)BN * 32;
@@ -1825,8 +1826,9 @@ float const* prep_b_tiles(vlb_ctx* ctx, float const* f, int N, int R, int BN, in
 
 // dY tile images with 16-byte accesses and, when db is given, the bias gradient from the same sweep.
 // Scratch layout: [tiles][extraBytes for the caller][per-block partial sums of db].
-float const* prep_dy_tiles(vlb_ctx* ctx, float const* dY, int K, int R, int P, int BN, int numKb, size_t extraBytes, float* db)
+float const* prep_dy_tiles(vlb_ctx* ctx, float const* dY, int K, int R, int P, int BN, int numKb, size_t extraBytes, float* db, int Pp = 0)
 {
+  if (Pp == 0) Pp = P;
   bool split3 = ctx->precision == VLB_PRECISION_3XTF32;
   size_t const tileBytes = b_tiles_bytes(ctx, K, BN, numKb);
   int const perBlock = kPrepThreads * 4 * kPrepIters;
@@ -1839,8 +1841,8 @@ float const* prep_dy_tiles(vlb_ctx* ctx, float const* dY, int K, int R, int P, i
   float* dbPart = db ? (float*)(ws + tileBytes + extraBytes) : nullptr;
   unsigned* tickets = (unsigned*)((char*)ctx->deviceStatus + 256);
   dim3 grid(bx, (unsigned)(vlb::ceil_div(K, BN) * BN));
-  if (split3) prep_dy_tiles_kernel<true><<<grid, kPrepThreads, 0, ctx->stream>>>(tiles, dY, K, R, P, BN, numKb, db, dbPart, tickets);
-  else        prep_dy_tiles_kernel<false><<<grid, kPrepThreads, 0, ctx->stream>>>(tiles, dY, K, R, P, BN, numKb, db, dbPart, tickets);
+  if (split3) prep_dy_tiles_kernel<true><<<grid, kPrepThreads, 0, ctx->stream>>>(tiles, dY, K, R, P, Pp, BN, numKb, db, dbPart, tickets);
+  else        prep_dy_tiles_kernel<false><<<grid, kPrepThreads, 0, ctx->stream>>>(tiles, dY, K, R, P, Pp, BN, numKb, db, dbPart, tickets);
   VLB_LAUNCHED(ctx, 1);
   return tiles;
 }
@@ -2124,13 +2126,14 @@ bool rows_map(CUtensorMap* map, float const* ptr, long long run, long long rows,
 // Filter gradient of a stride-1 convolution whose output has the input's height (every VGG / ResNet 3x3 layer), through
 // conv_ts_kernel: rows (tap, channel) in tensor memory, dY as tile images.  Returns -1 when the layer is not eligible (the
 // caller then takes tc_gemm_kernel), else an error code.
-//   needs: Ho == H (a tap is then a constant shift of the flattened plane), planes of a multiple of 32 pixels (a k-block
-//   never straddles two images) -- which also gives the 16-byte strides the tensor map wants --, channels in blocks of 32.
+//   needs: Ho == H (a tap is then a constant shift of the flattened plane), planes of a multiple of four pixels (the 16-byte
+//   strides the tensor map wants) that whole k-blocks cover with at most 1/16 to spare, channels in blocks of 32.
 int conv_wgrad_ts(vlb_ctx* ctx, ConvGeom const& g, float* dF, float* db, float const* X, float const* dY, bool* dbDone)
 {
   int const taps = g.FH * g.FW, P = g.Ho * g.Wo, HW = g.H * g.W;
   if (ctx->testSwitch & 4) return -1;
-  if (g.sy != 1 || g.sx != 1 || g.Ho != g.H || P % 32 != 0 || HW % 4 != 0 || taps > 64 || g.FH > 32 || g.FW > 32) return -1;
+  int const Pp = (P + BK - 1) / BK * BK;             // planes are padded to whole k-blocks (at most 1/16 more work), so that no k-block straddles two images
+  if (g.sy != 1 || g.sx != 1 || g.Ho != g.H || P % 4 != 0 || (Pp - P) * 16 > Pp || HW % 4 != 0 || taps > 64 || g.FH > 32 || g.FW > 32) return -1;
   if (g.C % 32 != 0 || (g.C > 128 && g.C % 128 != 0) || (g.C < 128 && 128 % g.C != 0)) return -1;
   if (g.K > 4096 || !aligned16(X) || !aligned16(dY)) return -1;
   if ((g.FH - 1) * g.dy - g.pt >= g.H || g.pt >= g.H) return -1;
@@ -2142,7 +2145,9 @@ int conv_wgrad_ts(vlb_ctx* ctx, ConvGeom const& g, float* dF, float* db, float c
   p.BN = pick_bn(p.N);
   p.tilesM = p.tapGroups * (g.C / p.cPer); p.tilesN = vlb::ceil_div(p.N, p.BN);
   if (vlb::ceil_div(g.K, p.BN) * p.BN > 65535) return -1;
-  int const numKb = (int)(R / BK);
+  if ((long long)Pp * g.N >= (1LL << 31) - 4096) return -1;
+  int const numKb = (int)((long long)Pp * g.N / BK);
+  p.plane = Pp;
   p.splits = pick_wg_splits(ctx->smCount, p.tilesM * p.tilesN, numKb, &p.kbPerSplit);
   p.kbTot = p.splits * p.kbPerSplit;               // the tile images are padded with zeros to whole ranges
   p.numKb = p.kbTot;
@@ -2157,7 +2162,7 @@ int conv_wgrad_ts(vlb_ctx* ctx, ConvGeom const& g, float* dF, float* db, float c
 
   ProfScope prof(ctx, kProfWgrad);      // includes the dY tile images (with the bias gradient) and the sum of the partial results
   prof.rec.flops = 2.0 * (double)V * (double)g.K * (double)R;
-  p.bTiles = prep_dy_tiles(ctx, dY, g.K, (int)R, P, p.BN, p.kbTot, partBytes, db);
+  p.bTiles = prep_dy_tiles(ctx, dY, g.K, (int)R, P, p.BN, p.kbTot, partBytes, db, Pp);
   if (!p.bTiles) return ctx->lastError;
   *dbDone = db != nullptr;
   float* const part = p.splits > 1 ? (float*)((char*)p.bTiles + tileBytes) : nullptr;
@@ -2199,6 +2204,7 @@ int fc_fprop_ts(vlb_ctx* ctx, ConvGeom const& g, float* Y, float const* X, float
   p.tilesM = g.K / 128; p.tilesN = vlb::ceil_div(p.N, p.BN);
   p.splits = pick_wg_splits(ctx->smCount, p.tilesM * p.tilesN, V / BK, &p.kbPerSplit);
   p.kbTot = p.splits * p.kbPerSplit; p.numKb = p.kbTot;
+  p.plane = V;
   conv_operand(p.a, plane_geom(V, g.K, g.N), F, g.K);
   p.a.rows = g.K;
   size_t const nOut = (size_t)g.K * g.N;

@@ -4,7 +4,8 @@ For a stride-1 convolution whose output has the input's height, planes of a mult
 32, dF[(fh,fw,c), k] = sum over pixels of x(pixel shifted by the tap, c) * dY(pixel, k) runs with the x rows in tensor
 memory -- every row's run of 32 pixels is delivered per k-block by a tensor-map copy that zero-fills what lies left or right
 of the image; rows above or below it are masked by the producers -- and dY as pre-split tile images; the reduction is cut
-into ranges whose partial results are added in fixed order.  Checked here against the CPU checker (double precision) and
+into ranges whose partial results are added in fixed order; planes that are not whole k-blocks are padded (zeros in the
+tile images).  Checked here against the CPU checker (double precision) and
 against the kernel with both operands in shared memory (test switch bit 2), which every other layer shape still takes:
 small planes, 64- and 128-channel tiles with two or four taps per tile, a tap group that is not full, 5x5 and 1x1 filters,
 dilation, an output narrower than the input, several ranges, both tensor-core arithmetic modes, run-to-run identical.
@@ -27,7 +28,10 @@ CASES = [((8, 4, 32, 3), (3, 3, 32, 16), dict(pad=1)),                # one k-bl
          ((8, 8, 96, 5), (1, 1, 96, 40), dict()),                     # 96 channels: not a tile shape, stays on the other kernel
          ((8, 8, 64, 9), (1, 1, 64, 40), dict()),                     # 1 x 1
          ((56, 56, 64, 8), (3, 3, 64, 64), dict(pad=1)),              # a VGG-like plane, 64-column tiles, many ranges
-         ((28, 32, 128, 16), (3, 3, 128, 128), dict(pad=1))]          # rows of 28: row masks at changing places
+         ((28, 32, 128, 16), (3, 3, 128, 128), dict(pad=1)),          # rows of 28: row masks at changing places
+         ((28, 28, 32, 5), (3, 3, 32, 32), dict(pad=1)),              # planes of 784 pixels: padded to 25 k-blocks per image
+         ((12, 20, 64, 3), (3, 3, 64, 16), dict(pad=1)),              # 240 pixels padded to 256: the most padding the route accepts
+         ((14, 14, 32, 4), (3, 3, 32, 32), dict(pad=1))]              # 196 pixels would need 224: stays on the other kernel
 
 
 @pytest.mark.parametrize("precision,tol", [(0, 1e-5), (1, 2e-3)])
