@@ -35,6 +35,7 @@
 #include <stdlib.h>
 #include <string.h>
 #include <algorithm>
+#include <type_traits>
 
 namespace {
 
@@ -117,6 +118,8 @@ struct Params {
   // reduction (output pixels of the whole batch, kbTot k-blocks in the dY tile images) is cut into `splits` ranges of kbPerSplit
   // k-blocks, one work item per (range, row tile, column tile); the x runs arrive by tensor-map copies, xStages buffers.
   int wg, cPer, tapsPerTile, tapGroups, kbTot, splits, xStages;
+  int smemSum;            // conv_ts_kernel, kMode 0 / 1: keep the running sum of a tile in shared memory even for the tile widths that fit the
+                          // drain warps' registers (tiles of a few k-blocks, where the stores dominate; test switch bit 3)
   int plane;              // row mode: reduction indices per image in the tile images -- the plane's pixels rounded up to whole k-blocks
 };
 
@@ -145,6 +148,24 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
       else if (now - t0 > gWaitCycles) return false;
     }
   }
+}
+
+// One try_wait: true when the phase has completed; otherwise the thread was suspended for about `ns` nanoseconds at most.
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity, uint32_t ns)
+{
+  uint32_t ok;
+  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}"
+               : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
+  return ok != 0;
+}
+
+// Has the phase completed?  No waiting.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity)
+{
+  uint32_t ok;
+  asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
 }
 
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
@@ -976,9 +997,10 @@ constexpr int kTsGroups = 2;
 constexpr int kTsLoaderWarp = kEpilogueWarps + 2;
 constexpr int kTsForwardWarp = kEpilogueWarps + 3;
 constexpr int kTsFirstProducer = kEpilogueWarps + 4;
-constexpr int kTsWindowWarp = kTsFirstProducer + 4 * kTsGroups;          // warp 16: input-window loader (tensor-map copies)
-constexpr int kTsThreads = (kTsWindowWarp + 1) * 32;                     // 544
-constexpr int kTsBStages = 4;           // at most; Params::bStages are in use
+constexpr int kTsThreads = (kTsFirstProducer + 4 * kTsGroups) * 32;      // 512: four warpgroups, 128 registers per thread at launch
+constexpr int kTsRunWarp = kTsFirstProducer + 4 * kTsGroups;             // row mode only: warp 16 issues the runs (tensor-map copies)
+constexpr int kTsThreadsRows = (kTsRunWarp + 1) * 32;                    // 544
+constexpr int kTsBStages = 6;           // at most; Params::bStages are in use
 constexpr int kTsDrainEvery = 4;        // own k-blocks per accumulation chain: 4 x 4 k-steps x 3 MMAs.  Measured relative error of one layer
                                         // at the full VGG sizes: 4 -> 9e-7, 8 -> 1.7e-6, 16 -> 3.3e-6 (8 is 5-8% faster, 16 another 0-7%), but with 8
                                         // the end-to-end gradients of the LeNet and ResNet configurations no longer stay within 1e-5
@@ -1075,19 +1097,21 @@ __device__ __forceinline__ RowPos row_pos(Params const& p, int tm, int row)
 
 // Epilogue of conv_ts_kernel: the finished tile sits in shared memory, P[column][row]; this warp stores the rows of its
 // TMEM lane quarter for the columns rank, rank + nranks, ...: out[(image*Ktot + n)*P + pixel] = inMult*acc + bias[n] + outMult*old.
+// P holds the columns cBeg .. cBeg + cCnt - 1 of the tile (cCnt = BN: all of it).
 __device__ __forceinline__ void ts_store_tile(Params const& p, float const* P, int quarter, int lane, int rank, int nranks, int tm, int n0,
-                                              uint32_t const* maskBits = nullptr)
+                                              uint32_t const* maskBits = nullptr, int cBeg = 0, int cCnt = 1 << 20)
 {
   int const row = quarter * 32 + lane;
   RowPos const rp = row_pos(p, tm, row);
   if (!rp.valid) return;
   int const pix = rp.pix, img = rp.img;
   float* const dst0 = p.e.out + ((long long)rp.split * p.e.splitStride + (long long)img * p.e.Ktot * p.e.P + pix);
-  int const nEnd = min(p.BN, p.N - n0);
+  int const nEnd = min(min(p.BN, cBeg + cCnt), p.N - n0);
+  P -= (size_t)cBeg * BM;                              // column c of the tile sits at P[(c - cBeg) * BM + row]
   if (maskBits) {
     // the mask of this row was fetched while the tile was being computed: bit c = the mask is positive in column c
     uint32_t const b0 = maskBits[0], b1 = maskBits[1], b2 = maskBits[2], b3 = maskBits[3];
-    for (int c = rank; c < nEnd; c += nranks) {
+    for (int c = cBeg + rank; c < nEnd; c += nranks) {
       float* dst = dst0 + (long long)(n0 + c) * p.e.P;
       float o = p.e.inMult * P[c * BM + row];
       if (p.e.bias) o += p.e.bias[n0 + c];
@@ -1102,7 +1126,7 @@ __device__ __forceinline__ void ts_store_tile(Params const& p, float const* P, i
     // sixteen columns at a time, so that the mask loads of a batch are in flight together (one load per store in a plain
     // loop leaves the warp waiting for memory once per column)
     float const* const mk0 = p.e.mask + (dst0 - p.e.out);
-    for (int c0 = rank; c0 < nEnd; c0 += 16 * nranks) {
+    for (int c0 = cBeg + rank; c0 < nEnd; c0 += 16 * nranks) {
       float mk[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
@@ -1124,7 +1148,7 @@ __device__ __forceinline__ void ts_store_tile(Params const& p, float const* P, i
     }
     return;
   }
-  for (int c = rank; c < nEnd; c += nranks) {
+  for (int c = cBeg + rank; c < nEnd; c += nranks) {
     float* dst = dst0 + (long long)(n0 + c) * p.e.P;
     float o = p.e.inMult * P[c * BM + row];
     if (p.e.bias) o += p.e.bias[n0 + c];
@@ -1134,19 +1158,24 @@ __device__ __forceinline__ void ts_store_tile(Params const& p, float const* P, i
   }
 }
 
-// kTma: the producers take the input windows from shared memory, where warp 16 has them delivered by tensor-map copies
+// kTma: the producers take the input windows from shared memory, where the loader thread has them delivered by tensor-map copies
 // (one box of boxH x boxW pixels x 32 channels per channel block and tile, zero-filled outside the image by the copy
 // engine, two buffers), instead of gathering them from global memory with per-thread loads.  xmap: the 4-D tensor map
 // (H, W, C, N) of the gathered tensor; unused otherwise.
-// kMode 2 (filter gradient): rows are (tap, channel), the reduction runs over the output pixels; warp 16 has the run of 32
+// kMode 2 (filter gradient): rows are (tap, channel), the reduction runs over the output pixels; the loader thread has the run of 32
 // pixels (plus up to three in front, so that the copy starts on a 16-byte boundary) of every row delivered per k-block.
 constexpr int kWgRowWords = 36;                         // words per row of an x run in shared memory (144 bytes: 16-byte loads of 8 rows hit 32 banks)
 constexpr int kWgRowBytes = kWgRowWords * 4;
 constexpr int kWgStageBytes = BM * kWgRowBytes;         // 18432
-constexpr int kTsXStages = 4;                           // at most
+constexpr int kTsXStages = 6;                           // at most
 
+// Registers (kMode 0, 1): 128 per thread at launch (512 threads: the whole register file, one CTA per SM); then the warps 4-7
+// keep 56 and the drain warps 0-3 take 200 (setmaxnreg: 128 of them hold the running sum of a tile).
+// kMode 2 runs with a seventeenth warp for its per-k-block tensor-map copies -- such a copy keeps the issuing warp busy for about
+// a microsecond, so it cannot share a warp with the forwarding, the filter tiles or a producer (measured: 35-50% slower each way)
+// -- which leaves 96 registers per thread and the running sum in shared memory.
 template <bool kSplit, int kMode>
-__global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p, const __grid_constant__ CUtensorMap xmap)
+__global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) conv_ts_kernel(Params p, const __grid_constant__ CUtensorMap xmap)
 {
   constexpr bool kTma = kMode == 1, kWg = kMode == 2;
   extern __shared__ uint8_t smemRaw[];
@@ -1165,7 +1194,8 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p, const 
   float* const Psm = reinterpret_cast<float*>(smem + (size_t)nB * bBytes);      // [BN][BM]
   // input windows (kTma): two buffers of boxH*boxW*32 floats behind P
   uint32_t const xPlane = (uint32_t)(p.boxH * p.boxW), xTileBytes = kWg ? (uint32_t)kWgStageBytes : xPlane * 32u * 4u;
-  uint32_t const xTile0 = smem_u32(Psm) + (uint32_t)BN * BM * 4u;
+  bool const regsP = !kWg && (BN == 128 || BN == 64) && !p.smemSum;      // the running sum of a tile lives in the drain warps' registers
+  uint32_t const xTile0 = smem_u32(Psm) + (regsP ? 32u : (uint32_t)BN) * BM * 4u;      // (registers: a patch of 32 columns for the stores)
 
   int const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int const numIter = p.kbPerSplit;                      // k-blocks per tile (work item: one range of the reduction of one output tile)
@@ -1201,97 +1231,142 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p, const 
 
   if (warp < kEpilogueWarps) {
     // ============================== fp32 drain and epilogue ==============================
-    // Chains are numbered over the whole life of the CTA: chain gc was accumulated in T[gc & 1].  Every chain
-    // of a tile is added to P and its T released at once; after the last one the tile is stored from P (one
-    // TMEM lane = one output row per thread, stores coalesced along the rows) while the tensor core is already
-    // two chains into the next tile.
+    // Chains are numbered over the whole life of the CTA: chain g was accumulated in T[g % 3].  Every chain of a tile is
+    // added to the tile's running sum and its T released at once.  The running sum lives in this thread's registers (one
+    // TMEM lane = one output row per thread, BN columns): the four drain warps take the registers the issuing / loading
+    // warps give up (setmaxnreg).  After the tile's last chain the sum goes to shared memory once, P[column][row], and is
+    // stored from there (coalesced along the rows) while the tensor core is already two chains into the next tile.  Tiles
+    // of other widths than 128 and 64 columns keep the running sum in shared memory.
+    if (!kWg) asm volatile("setmaxnreg.inc.sync.aligned.u32 200;" ::: "memory");
     uint32_t const lanes = tmemAcc + ((uint32_t)(warp * 32) << 16);
     float* const Prow = Psm + warp * 32 + lane;       // this thread's row of P: Prow[column * BM]
-    int g = 0;                                        // chains in the order they are drained, over the CTA's life: chain g sits in T[g % 3]
-    bool ok = true;
     bool const preMask = p.e.mask != nullptr && !singleTile;
-    for (int ts = 0; ts < myTiles && ok; ++ts) {
-      int const tile = (int)blockIdx.x + ts * (int)gridDim.x;
-      int const tm = tile / p.tilesN, n0 = (tile % p.tilesN) * BN;
-      int const qFirst = (int)(((long long)ts * numIter) & 1);          // the issuer that owns the tile's first k-block
-      int const chainsF = ts_chains<kSplit>(numIter, 0), chainsS = ts_chains<kSplit>(numIter, 1);   // of that issuer, of the other
-      bool fresh = true;                              // P holds nothing of this tile yet
-      (void)qFirst;
-      // ReLU mask of this thread's output row (persistent mode): sixteen columns are fetched before each of the tile's
-      // first chain waits, so that their latency passes while the chain is being computed, and kept as one bit each
-      uint32_t mbits[4] = {0u, 0u, 0u, 0u};
-      int const nEndT = min(BN, p.N - n0);
-      float const* mkRow = p.e.mask;
-      if (preMask) {
-        RowPos const rp = row_pos(p, tm, warp * 32 + lane);     // a row that does not exist reads (and discards) the mask of a pixel that does
-        mkRow += ((long long)rp.img * p.e.Ktot + n0) * p.e.P + rp.pix;      // (a masked data gradient is never cut into ranges)
-      }
-      int lc = 0;                                     // batches of sixteen mask columns fetched so far
-      for (int c = 0; c < chainsF && ok; ++c) {
-        for (int h = 0; h < 2 && ok; ++h) {
-          if (h == 1 && c >= chainsS) continue;
-          int const t = g % 3;
-          float mk[16];
-          bool const fetch = preMask && 16 * lc < nEndT;
-          if (fetch) {
+    auto drain = [&](auto kRegsTag) {
+      constexpr int kRegs = decltype(kRegsTag)::value;          // columns of the running sum held in registers (0: none, shared memory)
+      float Pr[kRegs > 0 ? kRegs : 1];
+      int g = 0;                                        // chains in the order they are drained, over the CTA's life: chain g sits in T[g % 3]
+      bool ok = true;
+      for (int ts = 0; ts < myTiles && ok; ++ts) {
+        int const tile = (int)blockIdx.x + ts * (int)gridDim.x;
+        int const tm = tile / p.tilesN, n0 = (tile % p.tilesN) * BN;
+        int const chainsF = ts_chains<kSplit>(numIter, 0), chainsS = ts_chains<kSplit>(numIter, 1);   // of the issuer that owns the tile's first k-block, of the other
+        bool fresh = true;                              // P holds nothing of this tile yet
+        if (kRegs > 0) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) mk[j] = __ldg(mkRow + (long long)min(16 * lc + j, nEndT - 1) * p.e.P);
-          }
-          ok = mbar_wait(smem_u32(&tFull[t]), (uint32_t)((g / 3) & 1));
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) { if (lane == 0) atomicExch(p.status, 5); break; }
-          ++g;
-          tc_fence_after();
-          // P = T (first chain of the tile) or P += T in fp32, then T[t] goes back to the issuers at once
-          for (int c0 = 0; c0 < BN; c0 += 32) {
-            uint32_t t0[16], t1[16];
-            bool const two = c0 + 16 < BN;
-            tmem_ld16_issue(lanes + (uint32_t)(t * BN + c0), t0);
-            if (two) tmem_ld16_issue(lanes + (uint32_t)(t * BN + c0 + 16), t1);
-            tmem_ld_wait();
-            float* pc = Prow + (size_t)c0 * BM;
+          for (int j = 0; j < kRegs; ++j) Pr[j] = 0.f;
+        }
+        // ReLU mask of this thread's output row (persistent mode): sixteen columns are fetched before each of the tile's
+        // first chain waits, so that their latency passes while the chain is being computed, and kept as one bit each
+        uint32_t mbits[4] = {0u, 0u, 0u, 0u};
+        int const nEndT = min(BN, p.N - n0);
+        float const* mkRow = p.e.mask;
+        if (preMask) {
+          RowPos const rp = row_pos(p, tm, warp * 32 + lane);     // a row that does not exist reads (and discards) the mask of a pixel that does
+          mkRow += ((long long)rp.img * p.e.Ktot + n0) * p.e.P + rp.pix;      // (a masked data gradient is never cut into ranges)
+        }
+        int lc = 0;                                     // batches of sixteen mask columns fetched so far
+        for (int c = 0; c < chainsF && ok; ++c) {
+          for (int h = 0; h < 2 && ok; ++h) {
+            if (h == 1 && c >= chainsS) continue;
+            int const t = g % 3;
+            float mk[16];
+            bool const fetch = preMask && 16 * lc < nEndT;
+            if (fetch) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              float v0 = __uint_as_float(t0[j]), v1 = __uint_as_float(t1[j]);
-              if (!fresh) { v0 += pc[j * BM]; if (two) v1 += pc[(16 + j) * BM]; }
-              pc[j * BM] = v0;
-              if (two) pc[(16 + j) * BM] = v1;
+              for (int j = 0; j < 16; ++j) mk[j] = __ldg(mkRow + (long long)min(16 * lc + j, nEndT - 1) * p.e.P);
+            }
+            ok = mbar_wait(smem_u32(&tFull[t]), (uint32_t)((g / 3) & 1));
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) { if (lane == 0) atomicExch(p.status, 5); break; }
+            ++g;
+            tc_fence_after();
+            if (kRegs > 0) {
+              // P += T in fp32, in registers
+#pragma unroll
+              for (int c0 = 0; c0 < kRegs; c0 += 32) {
+                uint32_t t0[16], t1[16];
+                tmem_ld16_issue(lanes + (uint32_t)(t * kRegs + c0), t0);
+                tmem_ld16_issue(lanes + (uint32_t)(t * kRegs + c0 + 16), t1);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) { Pr[c0 + j] += __uint_as_float(t0[j]); Pr[c0 + 16 + j] += __uint_as_float(t1[j]); }
+              }
+            } else {
+              // P = T (first chain of the tile) or P += T in fp32, in shared memory
+              for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t t0[16], t1[16];
+                bool const two = c0 + 16 < BN;
+                tmem_ld16_issue(lanes + (uint32_t)(t * BN + c0), t0);
+                if (two) tmem_ld16_issue(lanes + (uint32_t)(t * BN + c0 + 16), t1);
+                tmem_ld_wait();
+                float* pc = Prow + (size_t)c0 * BM;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  float v0 = __uint_as_float(t0[j]), v1 = __uint_as_float(t1[j]);
+                  if (!fresh) { v0 += pc[j * BM]; if (two) v1 += pc[(16 + j) * BM]; }
+                  pc[j * BM] = v0;
+                  if (two) pc[(16 + j) * BM] = v1;
+                }
+              }
+            }
+            fresh = false;
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&tFree[t]));     // T[t] may be overwritten
+            if (fetch) {
+              uint32_t b = 0;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) b |= (mk[j] > 0.f ? 1u : 0u) << j;
+              b <<= 16 * (lc & 1);
+              if (lc < 2) mbits[0] |= b; else if (lc < 4) mbits[1] |= b; else if (lc < 6) mbits[2] |= b; else mbits[3] |= b;
+              ++lc;
             }
           }
-          fresh = false;
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&tFree[t]));     // T[t] may be overwritten
-          if (fetch) {
-            uint32_t b = 0;
+        }
+        if (!ok) break;
+        for (; preMask && 16 * lc < nEndT; ++lc) {        // a tile of fewer chains than batches: the rest of the mask
+          uint32_t b = 0;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) b |= (mk[j] > 0.f ? 1u : 0u) << j;
-            b <<= 16 * (lc & 1);
-            if (lc < 2) mbits[0] |= b; else if (lc < 4) mbits[1] |= b; else if (lc < 6) mbits[2] |= b; else mbits[3] |= b;
-            ++lc;
+          for (int j = 0; j < 16; ++j) b |= (__ldg(mkRow + (long long)min(16 * lc + j, nEndT - 1) * p.e.P) > 0.f ? 1u : 0u) << j;
+          b <<= 16 * (lc & 1);
+          if (lc < 2) mbits[0] |= b; else if (lc < 4) mbits[1] |= b; else if (lc < 6) mbits[2] |= b; else mbits[3] |= b;
+        }
+        if (kRegs > 0) {
+          // The finished tile, 32 columns at a time: registers -> P[column][row] (a 16 KB patch of shared memory; every thread
+          // writes and reads back its own row only, so no barrier) -> global memory, coalesced along the rows, while the tensor
+          // core works on the next tile.  (The loop over the columns has to run over shared memory: registers cannot be indexed.)
+#pragma unroll
+          for (int c0 = 0; c0 < kRegs; c0 += 32) {
+            if (c0 < nEndT) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) Prow[j * BM] = Pr[c0 + j];
+              ts_store_tile(p, Psm, warp, lane, 0, 1, tm, n0, preMask ? mbits : nullptr, c0, 32);
+            }
           }
+        } else if (singleTile) {
+          // one tile per CTA: the producers have nothing left to do and share the stores
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&tileDone));
+          ts_store_tile(p, Psm, warp, lane, 0, 1 + kTsGroups, tm, n0);
+        } else {
+          // the tile is complete in P: store it while the tensor core works on the next tile (its chains wait in
+          // their T buffers until this is through)
+          ts_store_tile(p, Psm, warp, lane, 0, 1, tm, n0, preMask ? mbits : nullptr);
         }
       }
-      if (!ok) break;
-      for (; preMask && 16 * lc < nEndT; ++lc) {        // a tile of fewer chains than batches: the rest of the mask
-        uint32_t b = 0;
-#pragma unroll
-        for (int j = 0; j < 16; ++j) b |= (__ldg(mkRow + (long long)min(16 * lc + j, nEndT - 1) * p.e.P) > 0.f ? 1u : 0u) << j;
-        b <<= 16 * (lc & 1);
-        if (lc < 2) mbits[0] |= b; else if (lc < 4) mbits[1] |= b; else if (lc < 6) mbits[2] |= b; else mbits[3] |= b;
-      }
-      if (singleTile) {
-        // one tile per CTA: the producers have nothing left to do and share the stores
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&tileDone));
-        ts_store_tile(p, Psm, warp, lane, 0, 1 + kTsGroups, tm, n0);
-      } else {
-        // the tile is complete in P: store it while the tensor core works on the next tile (its chains wait in
-        // their T buffers until this is through)
-        ts_store_tile(p, Psm, warp, lane, 0, 1, tm, n0, preMask ? mbits : nullptr);
-      }
+    };
+    if constexpr (kWg) {
+      drain(std::integral_constant<int, 0>{});
+    } else {
+      if (regsP && BN == 128) drain(std::integral_constant<int, 128>{});
+      else if (regsP) drain(std::integral_constant<int, 64>{});
+      else drain(std::integral_constant<int, 0>{});
     }
-  } else if (warp == kEpilogueWarps || warp == kEpilogueWarps + 1) {
+  } else if (warp < 2 * kEpilogueWarps) {
+    // warps 4-7 (issuers, filter-tile loader, forwarder) work with one thread each and a handful of registers: the rest goes
+    // to the drain warps.  All four warps of the group execute this before anything else.
+    if (!kWg) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;" ::: "memory");
+    if (warp == kEpilogueWarps || warp == kEpilogueWarps + 1) {
     // ============================== MMA issue ==============================
     // Two issuing threads (in two warps, on two schedulers).  The tensor core's queue is about one MMA deep, so
     // while a thread waits on a barrier or commits, nothing of its own is in flight; with two threads the other
@@ -1333,6 +1408,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p, const 
           }
           ok = mbar_wait(smem_u32(&fullA[q]), phA);
           if (!ok) { atomicExch(p.status, 2); break; }
+
           // The issuers take turns: left to themselves they interleave their MMAs one by one, both k-blocks finish
           // together, both A stages are refilled together and the tensor core idles meanwhile.  In turns, the MMAs of
           // one k-block run while the other issuer's A stage (freed a whole k-block earlier) is being refilled.
@@ -1391,31 +1467,65 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p, const 
     }
     __syncwarp();
   } else if (warp == kTsForwardWarp) {
-    // ============================== forwarder ==============================
-    // k-block gi (numbered over the CTA's life) uses A stage gi & 1 in that barrier's phase gi >> 1.  The arrival
-    // for gi must fall into that phase, so the phase of gi - 2 has to be complete first (this thread arrived in
-    // it as well).
+    // ============================== forwarder; input windows / runs: tensor-map copies ==============================
+    // Forwarding: k-block gi (numbered over the CTA's life) uses A stage gi & 1 in that barrier's phase gi >> 1.  The arrival
+    // for gi must fall into that phase, so the phase of gi - 2 has to be complete first (this thread arrived in it as well).
+    // The windows of kTma (one per tile and block of 32 channels, xStages buffers) are numbered over the CTA's life and issued by
+    // the same thread.
     if (lane == 0) {
+      bool ok = true;
+      int const taps = p.a.FH * p.a.FW;
+      int const perTile = kTma ? numIter / taps : 0;                         // windows per tile
+      int const nXb = p.xStages;
+      long long const wTotal = (long long)myTiles * perTile;
+      long long wxs = 0;                                  // next window to issue
+      int wts = 0, wsub = 0;                              // its tile (in this CTA's sequence) and its index inside the tile
+      int wbuf = 0; uint32_t wph = 1;                     // its buffer; first use of a buffer: nothing to wait for
+      // Window w is issued when this thread has come to k-block wpos(w) (numbered over the CTA's life), after a wait for its buffer
+      // (the window nXb before it).  That buffer is let go of at the end of a hand-over whose arrival on the A-stage barrier this
+      // thread has already seen at wpos(w) -- the hand-over of k-block wpos(w) - 2 -- so the wait is short and depends on nothing
+      // that this thread has yet to do.  The first nXb at once.
+      auto windows = [&](long long gpos) -> bool {
+        while (wxs < wTotal) {
+          long long const wpos = wxs < nXb ? 0 : (wxs - nXb + 1) * taps + 1;
+          if (wpos > gpos) break;
+          if (!mbar_wait(smem_u32(&emptyX[wbuf]), wph)) { atomicExch(p.status, 12); return false; }
+          int const tmf = ((int)blockIdx.x + wts * (int)gridDim.x) / p.tilesN;
+          int const split = tmf / p.tilesM, tm = tmf - split * p.tilesM;
+          {
+            int const per = p.tilesH * p.tilesW;
+            int const n = tm / per, t = tm - n * per, wb = t / p.tilesH, hb = t - wb * p.tilesH;
+            int const c0 = hb * p.bh - p.a.pt - p.rowOff, c1 = wb * p.bw - p.a.pl;      // c0 is a multiple of four: bh and pt + rowOff are
+            mbar_arrive_expect_tx(smem_u32(&fullX[wbuf]), xTileBytes);
+            tma_load_4d(xTile0 + (uint32_t)wbuf * xTileBytes, &xmap, c0, c1, (split * perTile + wsub) * 32, n, smem_u32(&fullX[wbuf]));   // a range of the reduction is whole channel blocks
+          }
+          ++wxs;
+          if (++wbuf == nXb) { wbuf = 0; wph ^= 1u; }
+          if (++wsub == perTile) { wsub = 0; ++wts; }
+        }
+        return true;
+      };
       int sb = 0; uint32_t phB = 0;
       long long const total = (long long)myTiles * numIter;
-      for (long long gi = 0; gi < total; ++gi) {
+      for (long long gi = 0; gi < total && ok; ++gi) {
         int const sa = (int)(gi & 1);
-        if (!mbar_wait(smem_u32(&fullB[sb]), phB)) { atomicExch(p.status, 7); break; }
         if (gi >= kTsGroups && !mbar_wait(smem_u32(&fullA[sa]), (uint32_t)(((gi >> 1) - 1) & 1))) { atomicExch(p.status, 9); break; }
+        if (kTma && !windows(gi)) break;
+        if (!mbar_wait(smem_u32(&fullB[sb]), phB)) { atomicExch(p.status, 7); break; }
         mbar_arrive(smem_u32(&fullA[sa]));
         if (++sb == nB) { sb = 0; phB ^= 1u; }
       }
     }
     __syncwarp();
-  } else if (warp == kTsWindowWarp) {
-    // ============================== input windows: tensor-map copies ==============================
-    // Window xs (numbered over the CTA's life: one per tile and block of 32 channels) goes into buffer xs & 1 as soon as
-    // the producers have let go of window xs - 2, i.e. as far ahead of its use as two buffers allow.
+    }
+  } else if (warp == kTsRunWarp) {
+    // ============================== row mode: runs by tensor-map copies ==============================
     if (kWg && lane == 0) {
-      // One run of 36 pixels x cPer channels per k-block and tap of the tile, from the plane of image r / P starting at
-      // pixel r % P + shift of the tap, rounded down to four pixels (P: the plane rounded up to whole k-blocks; the tile images
-      // hold zeros for the pixels added).  Pixels before the plane's first or past its last one
-      // -- a tap that leaves the image to the left or right, a k-block past the end of the batch -- arrive as zeros.
+      // The run of k-block j (numbered over the CTA's life) -- 36 pixels x cPer channels per
+      // tap of the tile, from the plane of image r / P starting at pixel r % P + shift of the tap, rounded down to four pixels (P:
+      // the plane rounded up to whole k-blocks; the tile images hold zeros for the pixels added; pixels before the plane's first
+      // or past its last one -- a tap that leaves the image to the left or right, a k-block past the end of the batch -- arrive as
+      // zeros) -- goes into buffer j % xStages as soon as the producers have let go of the run of k-block j - xStages.
       int const taps = p.a.FH * p.a.FW, P = p.plane, nX = p.xStages;
       int buf = 0; uint32_t ph = 1;                        // first use of a buffer: nothing to wait for
       bool ok = true;
@@ -1423,7 +1533,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p, const 
         int const tmf = ((int)blockIdx.x + ts * (int)gridDim.x) / p.tilesN;
         int const split = tmf / p.tilesM, t = tmf - split * p.tilesM, cb = t / p.tapGroups, tg = t - cb * p.tapGroups;
         int const tap0 = tg * p.tapsPerTile, nTaps = min(p.tapsPerTile, taps - tap0);
-        long long r0 = (long long)split * numIter * BK;
+        long long const r0 = (long long)split * numIter * BK;
         int img = (int)(r0 / P), pix0 = (int)(r0 - (long long)img * P);
         for (int it = 0; it < numIter; ++it) {
           if (!mbar_wait(smem_u32(&emptyX[buf]), ph)) { atomicExch(p.status, 12); ok = false; break; }
@@ -1433,25 +1543,6 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p, const 
                         pix0 + (tapLut[tap0 + tl].x & ~3), cb * p.cPer, img, smem_u32(&fullX[buf]));
           if (++buf == nX) { buf = 0; ph ^= 1u; }
           pix0 += BK; if (pix0 >= P) { pix0 -= P; ++img; }
-        }
-      }
-    }
-    if (kTma && lane == 0) {
-      int const numCb = numIter / (p.a.FH * p.a.FW);
-      int const per = p.tilesH * p.tilesW;
-      long long xs = 0;
-      bool ok = true;
-      for (int ts = 0; ts < myTiles && ok; ++ts) {
-        int const tmf = ((int)blockIdx.x + ts * (int)gridDim.x) / p.tilesN;
-        int const split = tmf / p.tilesM, tm = tmf - split * p.tilesM;
-        int const n = tm / per, t = tm - n * per, wb = t / p.tilesH, hb = t - wb * p.tilesH;
-        int const c0 = hb * p.bh - p.a.pt - p.rowOff, c1 = wb * p.bw - p.a.pl;      // c0 is a multiple of four: bh and pt + rowOff are
-        int const cbEnd = (split + 1) * numCb;                                      // a range of the reduction is whole channel blocks
-        for (int cb = split * numCb; cb < cbEnd; ++cb, ++xs) {
-          int const buf = (int)(xs & 1);
-          if (xs >= 2 && !mbar_wait(smem_u32(&emptyX[buf]), (uint32_t)(((xs >> 1) - 1) & 1))) { atomicExch(p.status, 12); ok = false; break; }
-          mbar_arrive_expect_tx(smem_u32(&fullX[buf]), xTileBytes);
-          tma_load_4d(xTile0 + (uint32_t)buf * xTileBytes, &xmap, c0, c1, cb * 32, n, smem_u32(&fullX[buf]));
         }
       }
     }
@@ -1562,10 +1653,10 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p, const 
       for (int ts = 0; ts < myTiles && ok; ++ts) {
         int const par = (int)((gi ^ grp) & 1);              // this group's k-blocks of the tile: it % 2 == par
         for (int cb = 0; cb < numCb && ok; ++cb, ++xs) {
-          int const buf = (int)(xs & 1);
+          int const buf = (int)(xs % p.xStages);
           // every producer warp waits for and lets go of every window, whether or not one of its k-blocks falls into it:
           // a warp can then never arrive twice in one phase of the window's barrier
-          if (!mbar_wait(smem_u32(&fullX[buf]), (uint32_t)((xs >> 1) & 1))) { atomicExch(p.status, 11); ok = false; break; }
+          if (!mbar_wait(smem_u32(&fullX[buf]), (uint32_t)((xs / p.xStages) & 1))) { atomicExch(p.status, 11); ok = false; break; }
           uint32_t const base = xTile0 + (uint32_t)buf * xTileBytes + laneOff;
           int const itBeg = cb * taps;
           for (int it = itBeg + ((itBeg ^ par) & 1); it < itBeg + taps; it += kTsGroups) {
@@ -1630,7 +1721,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) conv_ts_kernel(Params p, const 
         gi += numIter;
       }
     }
-    if (singleTile && ok && myTiles > 0) {
+    if (singleTile && !regsP && ok && myTiles > 0) {
       bool done = mbar_wait(smem_u32(&tileDone), 0);
       done = __all_sync(0xffffffffu, done);
       tc_fence_after();
@@ -1852,6 +1943,13 @@ int pick_bn(int N) { return N > 64 ? 128 : (N > 32 ? 64 : (N > 16 ? 32 : 16)); }
 
 bool aligned16(void const* p) { return (((uintptr_t)p) & 15) == 0; }
 
+// Registers per thread a kernel must have been compiled with (0: no requirement).
+template <auto kKernel> constexpr int kRegsAtLaunch() { return 0; }
+template <> constexpr int kRegsAtLaunch<conv_ts_kernel<true, 0>>() { return 128; }
+template <> constexpr int kRegsAtLaunch<conv_ts_kernel<true, 1>>() { return 128; }
+template <> constexpr int kRegsAtLaunch<conv_ts_kernel<false, 0>>() { return 128; }
+template <> constexpr int kRegsAtLaunch<conv_ts_kernel<false, 1>>() { return 128; }
+
 // The opt-in to more than 48 KB of dynamic shared memory, once per kernel and device instead of before every launch.
 template <auto kKernel>
 cudaError_t allow_large_smem(int device)
@@ -1859,6 +1957,13 @@ cudaError_t allow_large_smem(int device)
   static bool done[64] = {};
   if (device >= 0 && device < 64 && done[device]) return cudaSuccess;
   cudaError_t e = vlb::allow_max_dynamic_smem(kKernel);
+  if (e == cudaSuccess && kRegsAtLaunch<kKernel>() > 0) {
+    // conv_ts_kernel redistributes registers between its warps (setmaxnreg) on the premise that every thread starts with
+    // exactly this many; a build that gave it another count must not run (the hand-over would wait for registers for ever)
+    cudaFuncAttributes attr;
+    e = cudaFuncGetAttributes(&attr, kKernel);
+    if (e == cudaSuccess && attr.numRegs != kRegsAtLaunch<kKernel>()) e = cudaErrorInvalidDeviceFunction;
+  }
   if (e == cudaSuccess && device >= 0 && device < 64) done[device] = true;
   return e;
 }
@@ -1926,6 +2031,9 @@ EncodeTiledFn encode_tiled()
 // cover with at least 95% of the tile rows in use (measured: with 112 of 128 rows in use, as on 56 x 56 and 28 x 28 maps,
 // the per-thread gather is the faster route by 10-15%; on 224 x 224 and 112 x 112 maps the copies win by up to 20% on
 // 64-column tiles and draw level on 128-column tiles), and room in shared memory for two windows.
+// Shared memory of conv_ts_kernel for the running sum of a tile: a patch of 32 columns for the tile widths whose sum lives in registers.
+size_t p_bytes(int BN, int smemSum) { return sizeof(float) * (size_t)(((BN == 128 || BN == 64) && !smemSum) ? 32 : BN) * BM; }
+
 bool plan_windows(vlb_ctx* ctx, Params& p, CUtensorMap* map, size_t* smemBytes, bool split3)
 {
   Operand const& a = p.a;
@@ -1948,11 +2056,14 @@ bool plan_windows(vlb_ctx* ctx, Params& p, CUtensorMap* map, size_t* smemBytes, 
   int const boxH = (rowOff + bestBh + (a.FH - 1) * a.dy + 3) / 4 * 4, boxW = bestBw + (a.FW - 1) * a.dx;
   if (boxH > 256 || boxW > 256) return false;
   size_t const xTileBytes = (size_t)boxH * boxW * 32 * 4;
-  size_t const bBytes = (size_t)(split3 ? 2 : 1) * p.BN * BK * 4, pBytes = sizeof(float) * (size_t)p.BN * BM;
+  size_t const bBytes = (size_t)(split3 ? 2 : 1) * p.BN * BK * 4, pBytes = p_bytes(p.BN, p.smemSum);
   size_t const limit = 227 * 1024 - 1536;      // what one block may have, less the kernel's static shared memory
+  // window buffers: two where a window serves a whole channel block of several taps; four for 1 x 1 filters, whose windows are
+  // single k-blocks and must be on their way well before their turn.  Filter-tile stages: what is left, at least three.
+  int const nX = a.FH * a.FW == 1 ? 4 : 2;
   int nB = 0;
   for (int n = kTsBStages; n >= 3 && !nB; --n)
-    if ((size_t)n * bBytes + pBytes + 2 * xTileBytes + 1024 <= limit) nB = n;
+    if ((size_t)n * bBytes + pBytes + nX * xTileBytes + 1024 <= limit) nB = n;
   if (!nB) return false;
   long long const images = (long long)p.M / ((long long)Ho * Wo);
   cuuint64_t const dims[4] = {(cuuint64_t)a.H, (cuuint64_t)a.W, (cuuint64_t)a.C, (cuuint64_t)images};
@@ -1964,9 +2075,9 @@ bool plan_windows(vlb_ctx* ctx, Params& p, CUtensorMap* map, size_t* smemBytes, 
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return false;
   p.tma = 1; p.bh = bestBh; p.bw = bestBw; p.tilesH = vlb::ceil_div(Ho, bestBh); p.tilesW = vlb::ceil_div(Wo, bestBw);
-  p.boxH = boxH; p.boxW = boxW; p.rowOff = rowOff; p.bStages = nB;
+  p.boxH = boxH; p.boxW = boxW; p.rowOff = rowOff; p.bStages = nB; p.xStages = nX;
   p.tilesM = (int)(images * p.tilesH * p.tilesW);
-  *smemBytes = (size_t)nB * bBytes + pBytes + 2 * xTileBytes + 1024;
+  *smemBytes = (size_t)nB * bBytes + pBytes + nX * xTileBytes + 1024;
   return true;
 }
 
@@ -1977,10 +2088,13 @@ int launch_ts(vlb_ctx* ctx, Params& p, char const* where)
   p.status = ctx->deviceStatus;
   p.testSwitch = ctx->testSwitch;
   // at least 120 KB, so that two CTAs (each allocating all 512 TMEM columns) never share an SM
-  size_t smemBytes = (size_t)kTsBStages * (split3 ? 2u : 1u) * (size_t)p.BN * BK * 4 + sizeof(float) * (size_t)p.BN * BM + 1024;
-  p.bStages = kTsBStages;
-  p.tilesM = vlb::ceil_div(p.M, BM); p.tilesN = vlb::ceil_div(p.N, p.BN);
+  // filter-tile stages: as many as fit beside the running sum's patch, six at most
   if (p.splits < 1) { p.splits = 1; p.kbPerSplit = p.numKb; }
+  p.smemSum = ((ctx->testSwitch & 8) || p.kbPerSplit < 8) ? 1 : 0;
+  size_t const stageBytes = (split3 ? 2u : 1u) * (size_t)p.BN * BK * 4, sumBytes = p_bytes(p.BN, p.smemSum);
+  p.bStages = (int)std::min<size_t>(kTsBStages, (227 * 1024 - 1536 - 1024 - sumBytes) / stageBytes);
+  size_t smemBytes = (size_t)p.bStages * stageBytes + sumBytes + 1024;
+  p.tilesM = vlb::ceil_div(p.M, BM); p.tilesN = vlb::ceil_div(p.N, p.BN);
   p.kbTot = p.splits * p.kbPerSplit;       // what the tile images hold per column tile
   CUtensorMap map;
   memset(&map, 0, sizeof(map));
@@ -2083,8 +2197,9 @@ int launch_rows(vlb_ctx* ctx, Params& p, CUtensorMap const& map, char const* whe
   size_t const bBytes = (size_t)(split3 ? 2 : 1) * p.BN * BK * 4, pBytes = sizeof(float) * (size_t)p.BN * BM;
   size_t const limit = 227 * 1024 - 1536;
   p.bStages = 0;
-  for (int nb = kTsBStages; nb >= 3 && !p.bStages; --nb)
-    for (int nx = kTsXStages; nx >= 3 && !p.bStages; --nx)
+  int const capStages = (ctx->testSwitch & 16) ? 3 : 99;
+  for (int nb = std::min(kTsBStages, capStages); nb >= 3 && !p.bStages; --nb)
+    for (int nx = std::min(kTsXStages, capStages); nx >= 3 && !p.bStages; --nx)
       if ((size_t)nb * bBytes + pBytes + (size_t)nx * kWgStageBytes + 1024 <= limit) { p.bStages = nb; p.xStages = nx; }
   if (!p.bStages) return vlb::set_error(ctx, VLB_Unsupported, where);
   size_t smemBytes = (size_t)p.bStages * bBytes + pBytes + (size_t)p.xStages * kWgStageBytes + 1024;
@@ -2099,10 +2214,10 @@ int launch_rows(vlb_ctx* ctx, Params& p, CUtensorMap const& map, char const* whe
   cudaError_t e;
   if (split3) {
     e = allow_large_smem<conv_ts_kernel<true, 2>>(ctx->device);
-    if (e == cudaSuccess) conv_ts_kernel<true, 2><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p, map);
+    if (e == cudaSuccess) conv_ts_kernel<true, 2><<<grid, kTsThreadsRows, smemBytes, ctx->stream>>>(p, map);
   } else {
     e = allow_large_smem<conv_ts_kernel<false, 2>>(ctx->device);
-    if (e == cudaSuccess) conv_ts_kernel<false, 2><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p, map);
+    if (e == cudaSuccess) conv_ts_kernel<false, 2><<<grid, kTsThreadsRows, smemBytes, ctx->stream>>>(p, map);
   }
   if (e != cudaSuccess) { cudaGetLastError(); return vlb::set_error(ctx, VLB_Cuda, cudaGetErrorString(e)); }
   VLB_LAUNCHED(ctx, 1);
