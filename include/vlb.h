@@ -70,7 +70,10 @@ int vlb_ctx_set_wait_limit(vlb_ctx* ctx, long long cycles);
  * Bit 1: the tensor-memory convolution kernel gathers its input windows with per-thread loads even where it could have
  * them delivered by tensor-map copies; the two routes give the same result bit for bit, which is what a test compares.
  * Bit 2: the filter gradient of a convolution takes the kernel with both operands in shared memory even where the
- * tensor-memory kernel applies (the two differ in the order of the sums; a test checks both against the CPU checker). */
+ * tensor-memory kernel applies (the two differ in the order of the sums; a test checks both against the CPU checker).
+ * Bit 3: the tensor-memory convolution kernel keeps the running sum of an output tile in shared memory even for the tile
+ * widths (64 and 128 columns) whose sum fits the registers of its drain warps; same additions in the same order, so the
+ * results are equal, which is what a test compares. */
 int vlb_ctx_set_test_switch(vlb_ctx* ctx, int switches);
 /* Measurement aid: between begin and end every tensor-core contraction (with the launches that prepare its operands
  * and finish its result) is bracketed by CUDA events on the context's stream.  end synchronises and returns the summed kernel time, the summed

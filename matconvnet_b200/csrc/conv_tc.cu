@@ -1179,8 +1179,8 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
 {
   constexpr bool kTma = kMode == 1, kWg = kMode == 2;
   extern __shared__ uint8_t smemRaw[];
-  __shared__ __align__(8) uint64_t fullA[kTsGroups], emptyA[kTsGroups], fullB[kTsBStages], emptyB[kTsBStages];
-  __shared__ __align__(8) uint64_t tFull[3], tFree[3], tileDone, turn[2], fullX[kTsXStages], emptyX[kTsXStages];
+  __shared__ __align__(8) uint64_t fullA[4], emptyA[4], fullB[kTsBStages], emptyB[kTsBStages];
+  __shared__ __align__(8) uint64_t tFull[4], tFree[4], tileDone, turn[2], fullX[kTsXStages], emptyX[kTsXStages];
   __shared__ uint32_t tmemBase;
   __shared__ int2 tapLut[64];       // per filter tap fh + FH*fw: {element offset of the tap (in the input window when kTma), fh | fw << 5}
 
@@ -1190,7 +1190,15 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
   uint32_t const bTileBytes = (uint32_t)BN * BK * 4;
   uint32_t const bBytes = (kSplit ? 2u : 1u) * bTileBytes;
   uint32_t const tmemCols = 512;
-  uint32_t const colA = (uint32_t)(3 * BN);
+  // Tensor memory: kNT chain accumulators of BN columns (T[g % kNT] for chain g), then kNA A stages of 64 columns (32 hi, 32 lo).
+  // 128-column tiles: three accumulators (two chains being accumulated while the third is drained and, at the end of a tile,
+  // stored) and one A stage per issuer -- 512 columns.  Tiles of 64 columns or fewer have room for four accumulators and two
+  // A stages per issuer: a stage is refilled while the MMAs of the issuer's other stage run, which is what these tiles, whose
+  // MMAs are short, gain most from.  (Measured on 128-column tiles, same GPU, whole VGG-16 step: two accumulators + four stages is
+  // level with three + two -- the refill of an A stage is not what bounds those tiles.)
+  int const kNA = (!kWg && BN <= 64) ? 4 : 2, kAPer = kNA / 2;
+  int const kNT = (!kWg && BN <= 64) ? 4 : 3;
+  uint32_t const colA = (uint32_t)(kNT * BN);
   float* const Psm = reinterpret_cast<float*>(smem + (size_t)nB * bBytes);      // [BN][BM]
   // input windows (kTma): two buffers of boxH*boxW*32 floats behind P
   uint32_t const xPlane = (uint32_t)(p.boxH * p.boxW), xTileBytes = kWg ? (uint32_t)kWgStageBytes : xPlane * 32u * 4u;
@@ -1207,9 +1215,9 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
 
   if (threadIdx.x == 0) {
     // an A stage is full when its four producer warps and the forwarder (filter tile landed) have arrived
-    for (int s = 0; s < kTsGroups; ++s) { mbar_init(smem_u32(&fullA[s]), 5); mbar_init(smem_u32(&emptyA[s]), 1); }
+    for (int s = 0; s < 4; ++s) { mbar_init(smem_u32(&fullA[s]), 5); mbar_init(smem_u32(&emptyA[s]), 1); }
     for (int s = 0; s < kTsBStages; ++s) { mbar_init(smem_u32(&fullB[s]), 1); mbar_init(smem_u32(&emptyB[s]), 1); }
-    for (int b = 0; b < 3; ++b) { mbar_init(smem_u32(&tFull[b]), 1); mbar_init(smem_u32(&tFree[b]), kEpilogueWarps); }
+    for (int b = 0; b < 4; ++b) { mbar_init(smem_u32(&tFull[b]), 1); mbar_init(smem_u32(&tFree[b]), kEpilogueWarps); }
     mbar_init(smem_u32(&tileDone), kEpilogueWarps);
     mbar_init(smem_u32(&turn[0]), 1); mbar_init(smem_u32(&turn[1]), 1);
     // an input window is full when its copy has landed (one arrival with the byte count), empty when all eight producer warps are done with it
@@ -1268,14 +1276,14 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
         for (int c = 0; c < chainsF && ok; ++c) {
           for (int h = 0; h < 2 && ok; ++h) {
             if (h == 1 && c >= chainsS) continue;
-            int const t = g % 3;
+            int const t = g % kNT;
             float mk[16];
             bool const fetch = preMask && 16 * lc < nEndT;
             if (fetch) {
 #pragma unroll
               for (int j = 0; j < 16; ++j) mk[j] = __ldg(mkRow + (long long)min(16 * lc + j, nEndT - 1) * p.e.P);
             }
-            ok = mbar_wait(smem_u32(&tFull[t]), (uint32_t)((g / 3) & 1));
+            ok = mbar_wait(smem_u32(&tFull[t]), (uint32_t)((g / kNT) & 1));
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) { if (lane == 0) atomicExch(p.status, 5); break; }
             ++g;
@@ -1382,10 +1390,10 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
       uint32_t const idesc = make_idesc(false, false, BN);
       uint64_t const descB0 = make_desc(smem_u32(smem), 16, 1024);
       uint32_t const stageStep = bBytes >> 4, loStep = bTileBytes >> 4;
-      uint32_t const aHi = tmemAcc + colA + (uint32_t)(q * 64), aLo = aHi + 32u;
       bool ok = true;
       int sb = q, gBase = 0, g = 0;
-      uint32_t phA = 0, tAcc = tmemAcc;
+      uint32_t tAcc = tmemAcc;
+      uint32_t own = 0;                              // this issuer's k-blocks so far: k-block `own` sits in A stage q + 2*(own % kAPer)
       uint32_t phTurn = q == 0 ? 1u : 0u;            // issuer 0 has the first turn (nothing to wait for)
       // measured: +4-8% on 128-column tiles, -5% on 64-column tiles (their MMAs are short and the extra wait shows)
       bool const takeTurns = BN > 64;
@@ -1400,13 +1408,15 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
             // this chain's place in the drain order (first issuer's chain c, second issuer's chain c, first's c+1, ...)
             int const c = kSplit ? j / kTsDrainEvery : 0;
             g = gBase + min(c, chainsF) + min(c, chainsS) + (first == 1 && c < chainsF ? 1 : 0);
-            tAcc = tmemAcc + (uint32_t)((g % 3) * BN);
-            if (g >= 3) {                             // the chain that sat in this T before must have been added to P
-              ok = mbar_wait(smem_u32(&tFree[g % 3]), (uint32_t)(((g / 3) - 1) & 1));
+            tAcc = tmemAcc + (uint32_t)((g % kNT) * BN);
+            if (g >= kNT) {                           // the chain that sat in this T before must have been added to P
+              ok = mbar_wait(smem_u32(&tFree[g % kNT]), (uint32_t)(((g / kNT) - 1) & 1));
               if (!ok) { atomicExch(p.status, 6); break; }
             }
           }
-          ok = mbar_wait(smem_u32(&fullA[q]), phA);
+          int const sa = q + 2 * (int)(own % kAPer);
+          uint32_t const aHi = tmemAcc + colA + (uint32_t)(sa * 64), aLo = aHi + 32u;
+          ok = mbar_wait(smem_u32(&fullA[sa]), (own / kAPer) & 1u);
           if (!ok) { atomicExch(p.status, 2); break; }
 
           // The issuers take turns: left to themselves they interleave their MMAs one by one, both k-blocks finish
@@ -1438,10 +1448,11 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
             if (takeTurns && k8 == BK / 8 - 2) mbar_arrive(smem_u32(&turn[q ^ 1]));
           }
           if (!ok) break;
-          umma_commit(smem_u32(&emptyA[q]));      // frees the A stage; its producers pass the news on for the B stage
-          phA ^= 1u;
+          umma_commit(smem_u32(&emptyA[sa]));     // when these MMAs are through: the A stage goes back to its producers,
+          umma_commit(smem_u32(&emptyB[sb]));     // the filter stage to the loader
+          ++own;
           sb += 2; if (sb >= nB) sb -= nB;
-          if (chunkEnd) umma_commit(smem_u32(&tFull[g % 3]));   // chain complete: hand it to the drain warps
+          if (chunkEnd) umma_commit(smem_u32(&tFull[g % kNT]));   // chain complete: hand it to the drain warps
         }
         gBase += chainsF + chainsS;
       }
@@ -1508,8 +1519,8 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
       int sb = 0; uint32_t phB = 0;
       long long const total = (long long)myTiles * numIter;
       for (long long gi = 0; gi < total && ok; ++gi) {
-        int const sa = (int)(gi & 1);
-        if (gi >= kTsGroups && !mbar_wait(smem_u32(&fullA[sa]), (uint32_t)(((gi >> 1) - 1) & 1))) { atomicExch(p.status, 9); break; }
+        int const sa = (int)(gi % kNA);
+        if (gi >= kNA && !mbar_wait(smem_u32(&fullA[sa]), (uint32_t)(((gi / kNA) - 1) & 1))) { atomicExch(p.status, 9); break; }
         if (kTma && !windows(gi)) break;
         if (!mbar_wait(smem_u32(&fullB[sb]), phB)) { atomicExch(p.status, 7); break; }
         mbar_arrive(smem_u32(&fullA[sa]));
@@ -1551,11 +1562,9 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
     // ============================== producers ==============================
     int const grp = (warp - kTsFirstProducer) >> 2;
     int const quarter = warp & 3;                       // the TMEM lanes this warp may access
-    bool const herald = (warp - kTsFirstProducer) % 4 == 0 && lane == 0;   // tells the loader about freed filter stages
     int const HW = p.a.H * p.a.W, taps = p.a.FH * p.a.FW;
-    uint32_t const aAddr = tmemAcc + ((uint32_t)(quarter * 32) << 16) + colA + (uint32_t)(grp * 64);
-    uint32_t phE = 1;                                   // first use of the stage: nothing to wait for
-    int sbFree = grp;                                   // filter stage of the k-block whose MMAs this group sees complete next
+    uint32_t const aBase = tmemAcc + ((uint32_t)(quarter * 32) << 16) + colA;
+    uint32_t own = 0;                                   // this group's k-blocks so far: k-block `own` goes into A stage grp + 2*(own % kAPer)
     long long gi = 0;                                   // k-blocks numbered over the CTA's life; this group takes gi % 2 == grp
     bool ok = true;
 
@@ -1568,19 +1577,17 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
         hi[k] = __float_as_uint(tf32_hi(v[k]));
         if (kSplit) lo[k] = __float_as_uint(v[k] - __uint_as_float(hi[k]));
       }
-      if (!mbar_wait(smem_u32(&emptyA[grp]), phE)) { atomicExch(p.status, 1); return false; }
-      phE ^= 1u;
+      int const sa = grp + 2 * (int)(own % kAPer);
+      uint32_t const aAddr = aBase + (uint32_t)(sa * 64);
+      if (!mbar_wait(smem_u32(&emptyA[sa]), ((own / kAPer) & 1u) ^ 1u)) { atomicExch(p.status, 1); return false; }      // (first use of a stage: nothing to wait for)
+      ++own;
       tc_fence_after();
       tmem_st32(aAddr, hi);
       if (kSplit) tmem_st32(aAddr + 32u, lo);
-      if (herald && gi + it >= kTsGroups) {                      // the MMAs of the k-block two before this one are complete: its filter stage is free too
-        mbar_arrive(smem_u32(&emptyB[sbFree]));
-        sbFree += kTsGroups; if (sbFree >= nB) sbFree -= nB;
-      }
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&fullA[grp]));
+      if (lane == 0) mbar_arrive(smem_u32(&fullA[sa]));
       return true;
     };
 
@@ -2197,9 +2204,8 @@ int launch_rows(vlb_ctx* ctx, Params& p, CUtensorMap const& map, char const* whe
   size_t const bBytes = (size_t)(split3 ? 2 : 1) * p.BN * BK * 4, pBytes = sizeof(float) * (size_t)p.BN * BM;
   size_t const limit = 227 * 1024 - 1536;
   p.bStages = 0;
-  int const capStages = (ctx->testSwitch & 16) ? 3 : 99;
-  for (int nb = std::min(kTsBStages, capStages); nb >= 3 && !p.bStages; --nb)
-    for (int nx = std::min(kTsXStages, capStages); nx >= 3 && !p.bStages; --nx)
+  for (int nb = kTsBStages; nb >= 3 && !p.bStages; --nb)
+    for (int nx = kTsXStages; nx >= 3 && !p.bStages; --nx)
       if ((size_t)nb * bBytes + pBytes + (size_t)nx * kWgStageBytes + 1024 <= limit) { p.bStages = nb; p.xStages = nx; }
   if (!p.bStages) return vlb::set_error(ctx, VLB_Unsupported, where);
   size_t smemBytes = (size_t)p.bStages * bBytes + pBytes + (size_t)p.xStages * kWgStageBytes + 1024;

@@ -56,3 +56,33 @@ def test_tensor_map_route_equals_the_per_thread_gather(gpu, case, precision):
     finally:
         ctx.check(lib.vlb_ctx_set_test_switch(ctx.handle, 0))
         ctx.set_precision(0)
+
+
+@pytest.mark.parametrize("case", [0, 1, 2, 7])
+def test_running_sum_in_registers_equals_running_sum_in_shared_memory(gpu, case):
+    """The drain warps keep the fp32 running sum of a 64- or 128-column tile in registers (taken over from the issuing warps
+    with setmaxnreg); test switch bit 3 keeps it in shared memory, as narrower tiles and very short tiles do.  Same additions in
+    the same order: equal results, forward, data gradient (with the fused ReLU mask) and filter gradient."""
+    import torch
+    nn, mat, ctx = gpu
+    xs, fs, kw = CASES[case]
+    g = torch.Generator(device="cuda").manual_seed(200 + case)
+    x = mat.as_mat(torch.randn(*xs, device="cuda", generator=g))
+    f = mat.as_mat(torch.randn(*fs, device="cuda", generator=g) * (2.0 / (fs[0] * fs[1] * fs[2])) ** 0.5)
+    b = mat.as_mat(torch.randn(1, fs[3], device="cuda", generator=g))
+    lib = ctx.lib
+    try:
+        out = {}
+        for switch in (8, 0):
+            ctx.check(lib.vlb_ctx_set_test_switch(ctx.handle, switch))
+            y = nn.vl_nnconv(x, f, b, ctx=ctx, **kw)
+            dy = mat.as_mat(torch.randn(*y.shape, device="cuda", generator=torch.Generator(device="cuda").manual_seed(9)))
+            dx, df, db = nn.vl_nnconv(x, f, b, dy, ctx=ctx, **kw)
+            xr = nn.vl_nnrelu(x, ctx=ctx)
+            dxm, _, _ = nn.vl_nnconv(xr, f, b, dy, through_relu=True, no_der_filters=True, no_der_biases=True, ctx=ctx, **kw)
+            assert ctx.device_status() == 0
+            out[switch] = (y, dx, df, dxm)
+        for a, c in zip(out[8], out[0]):
+            assert torch.equal(a, c)
+    finally:
+        ctx.check(lib.vlb_ctx_set_test_switch(ctx.handle, 0))
