@@ -1174,7 +1174,8 @@ constexpr int kTsXStages = 6;                           // at most
 // kMode 2 runs with a seventeenth warp for its per-k-block tensor-map copies -- such a copy keeps the issuing warp busy for about
 // a microsecond, so it cannot share a warp with the forwarding, the filter tiles or a producer (measured: 35-50% slower each way)
 // -- which leaves 96 registers per thread and the running sum in shared memory.
-template <bool kSplit, int kMode>
+// kNarrow: tiles of 64 columns or fewer (kMode 0, 1), which get more accumulators and A stages (below).
+template <bool kSplit, int kMode, bool kNarrow>
 __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) conv_ts_kernel(Params p, const __grid_constant__ CUtensorMap xmap)
 {
   constexpr bool kTma = kMode == 1, kWg = kMode == 2;
@@ -1196,8 +1197,13 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
   // A stages per issuer: a stage is refilled while the MMAs of the issuer's other stage run, which is what these tiles, whose
   // MMAs are short, gain most from.  (Measured on 128-column tiles, same GPU, whole VGG-16 step: two accumulators + four stages is
   // level with three + two -- the refill of an A stage is not what bounds those tiles.)
-  int const kNA = (!kWg && BN <= 64) ? 4 : 2, kAPer = kNA / 2;
-  int const kNT = (!kWg && BN <= 64) ? 4 : 3;
+  constexpr int kNA = kNarrow ? 4 : 2, kAPer = kNA / 2, kAShift = kNA == 4 ? 1 : 0;      // kAPer = 1 << kAShift
+  constexpr int kNT = kNarrow ? 4 : 3;
+  // Who tells the loader that a filter stage is free.  The issuer, with a second commit per k-block: narrow tiles (whose
+  // producers learn of a finished k-block only two of their own k-blocks later) and the row mode (measured 3-11% faster on
+  // 64-channel row tiles, level elsewhere).  Or the producers, when they find their A stage free again: 128-column tiles
+  // of the other modes, where the second commit cost the issuers 2-5% (forward) to 10% (data gradient with the ReLU mask).
+  constexpr bool issuerFreesB = kWg || kNarrow;
   uint32_t const colA = (uint32_t)(kNT * BN);
   float* const Psm = reinterpret_cast<float*>(smem + (size_t)nB * bBytes);      // [BN][BM]
   // input windows (kTma): two buffers of boxH*boxW*32 floats behind P
@@ -1414,9 +1420,9 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
               if (!ok) { atomicExch(p.status, 6); break; }
             }
           }
-          int const sa = q + 2 * (int)(own % kAPer);
+          int const sa = q + 2 * (int)(own & (uint32_t)(kAPer - 1));
           uint32_t const aHi = tmemAcc + colA + (uint32_t)(sa * 64), aLo = aHi + 32u;
-          ok = mbar_wait(smem_u32(&fullA[sa]), (own / kAPer) & 1u);
+          ok = mbar_wait(smem_u32(&fullA[sa]), (own >> kAShift) & 1u);
           if (!ok) { atomicExch(p.status, 2); break; }
 
           // The issuers take turns: left to themselves they interleave their MMAs one by one, both k-blocks finish
@@ -1449,7 +1455,7 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
           }
           if (!ok) break;
           umma_commit(smem_u32(&emptyA[sa]));     // when these MMAs are through: the A stage goes back to its producers,
-          umma_commit(smem_u32(&emptyB[sb]));     // the filter stage to the loader
+          if (issuerFreesB) umma_commit(smem_u32(&emptyB[sb]));     // the filter stage to the loader
           ++own;
           sb += 2; if (sb >= nB) sb -= nB;
           if (chunkEnd) umma_commit(smem_u32(&tFull[g % kNT]));   // chain complete: hand it to the drain warps
@@ -1519,8 +1525,8 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
       int sb = 0; uint32_t phB = 0;
       long long const total = (long long)myTiles * numIter;
       for (long long gi = 0; gi < total && ok; ++gi) {
-        int const sa = (int)(gi % kNA);
-        if (gi >= kNA && !mbar_wait(smem_u32(&fullA[sa]), (uint32_t)(((gi / kNA) - 1) & 1))) { atomicExch(p.status, 9); break; }
+        int const sa = (int)(gi & (kNA - 1));
+        if (gi >= kNA && !mbar_wait(smem_u32(&fullA[sa]), (uint32_t)(((gi >> (kAShift + 1)) - 1) & 1))) { atomicExch(p.status, 9); break; }
         if (kTma && !windows(gi)) break;
         if (!mbar_wait(smem_u32(&fullB[sb]), phB)) { atomicExch(p.status, 7); break; }
         mbar_arrive(smem_u32(&fullA[sa]));
@@ -1565,6 +1571,8 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
     int const HW = p.a.H * p.a.W, taps = p.a.FH * p.a.FW;
     uint32_t const aBase = tmemAcc + ((uint32_t)(quarter * 32) << 16) + colA;
     uint32_t own = 0;                                   // this group's k-blocks so far: k-block `own` goes into A stage grp + 2*(own % kAPer)
+    bool const herald = !issuerFreesB && (warp - kTsFirstProducer) % 4 == 0 && lane == 0;   // tells the loader about freed filter stages
+    int sbFree = grp;                                   // filter stage of the k-block whose MMAs this group sees complete next
     long long gi = 0;                                   // k-blocks numbered over the CTA's life; this group takes gi % 2 == grp
     bool ok = true;
 
@@ -1577,9 +1585,13 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
         hi[k] = __float_as_uint(tf32_hi(v[k]));
         if (kSplit) lo[k] = __float_as_uint(v[k] - __uint_as_float(hi[k]));
       }
-      int const sa = grp + 2 * (int)(own % kAPer);
+      int const sa = grp + 2 * (int)(own & (uint32_t)(kAPer - 1));
       uint32_t const aAddr = aBase + (uint32_t)(sa * 64);
-      if (!mbar_wait(smem_u32(&emptyA[sa]), ((own / kAPer) & 1u) ^ 1u)) { atomicExch(p.status, 1); return false; }      // (first use of a stage: nothing to wait for)
+      if (!mbar_wait(smem_u32(&emptyA[sa]), ((own >> kAShift) & 1u) ^ 1u)) { atomicExch(p.status, 1); return false; }      // (first use of a stage: nothing to wait for)
+      if (herald && own >= 1) {          // (one A stage per issuer here:) the MMAs of this group's previous k-block are complete: its filter stage is free too
+        mbar_arrive(smem_u32(&emptyB[sbFree]));
+        sbFree += kTsGroups; if (sbFree >= nB) sbFree -= nB;
+      }
       ++own;
       tc_fence_after();
       tmem_st32(aAddr, hi);
@@ -1952,10 +1964,14 @@ bool aligned16(void const* p) { return (((uintptr_t)p) & 15) == 0; }
 
 // Registers per thread a kernel must have been compiled with (0: no requirement).
 template <auto kKernel> constexpr int kRegsAtLaunch() { return 0; }
-template <> constexpr int kRegsAtLaunch<conv_ts_kernel<true, 0>>() { return 128; }
-template <> constexpr int kRegsAtLaunch<conv_ts_kernel<true, 1>>() { return 128; }
-template <> constexpr int kRegsAtLaunch<conv_ts_kernel<false, 0>>() { return 128; }
-template <> constexpr int kRegsAtLaunch<conv_ts_kernel<false, 1>>() { return 128; }
+template <> constexpr int kRegsAtLaunch<conv_ts_kernel<true, 0, true>>() { return 128; }
+template <> constexpr int kRegsAtLaunch<conv_ts_kernel<true, 0, false>>() { return 128; }
+template <> constexpr int kRegsAtLaunch<conv_ts_kernel<true, 1, true>>() { return 128; }
+template <> constexpr int kRegsAtLaunch<conv_ts_kernel<true, 1, false>>() { return 128; }
+template <> constexpr int kRegsAtLaunch<conv_ts_kernel<false, 0, true>>() { return 128; }
+template <> constexpr int kRegsAtLaunch<conv_ts_kernel<false, 0, false>>() { return 128; }
+template <> constexpr int kRegsAtLaunch<conv_ts_kernel<false, 1, true>>() { return 128; }
+template <> constexpr int kRegsAtLaunch<conv_ts_kernel<false, 1, false>>() { return 128; }
 
 // The opt-in to more than 48 KB of dynamic shared memory, once per kernel and device instead of before every launch.
 template <auto kKernel>
@@ -2121,23 +2137,20 @@ int launch_ts(vlb_ctx* ctx, Params& p, char const* where)
     rec.flops = 2.0 * (double)p.M * (double)p.N * (double)p.R; rec.kind = -1;
     cudaEventRecord(rec.start, ctx->stream);
   }
+  bool const narrow = p.BN <= 64;
+  auto go = [&](auto kernel) {
+    e = allow_large_smem<decltype(kernel)::value>(ctx->device);
+    if (e == cudaSuccess) decltype(kernel)::value<<<grid, kTsThreads, smemBytes, ctx->stream>>>(p, map);
+  };
+#define VLB_TS(split, mode, nar) go(std::integral_constant<decltype(&conv_ts_kernel<split, mode, nar>), &conv_ts_kernel<split, mode, nar>>{})
   if (split3) {
-    if (windows) {
-      e = allow_large_smem<conv_ts_kernel<true, 1>>(ctx->device);
-      if (e == cudaSuccess) conv_ts_kernel<true, 1><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p, map);
-    } else {
-      e = allow_large_smem<conv_ts_kernel<true, 0>>(ctx->device);
-      if (e == cudaSuccess) conv_ts_kernel<true, 0><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p, map);
-    }
+    if (windows) { if (narrow) VLB_TS(true, 1, true); else VLB_TS(true, 1, false); }
+    else         { if (narrow) VLB_TS(true, 0, true); else VLB_TS(true, 0, false); }
   } else {
-    if (windows) {
-      e = allow_large_smem<conv_ts_kernel<false, 1>>(ctx->device);
-      if (e == cudaSuccess) conv_ts_kernel<false, 1><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p, map);
-    } else {
-      e = allow_large_smem<conv_ts_kernel<false, 0>>(ctx->device);
-      if (e == cudaSuccess) conv_ts_kernel<false, 0><<<grid, kTsThreads, smemBytes, ctx->stream>>>(p, map);
-    }
+    if (windows) { if (narrow) VLB_TS(false, 1, true); else VLB_TS(false, 1, false); }
+    else         { if (narrow) VLB_TS(false, 0, true); else VLB_TS(false, 0, false); }
   }
+#undef VLB_TS
   if (record) { cudaEventRecord(rec.stop, ctx->stream); ctx->prof.push_back(rec); }
   if (e != cudaSuccess) { cudaGetLastError(); return vlb::set_error(ctx, VLB_Cuda, cudaGetErrorString(e)); }
   VLB_LAUNCHED(ctx, 1);
@@ -2219,11 +2232,11 @@ int launch_rows(vlb_ctx* ctx, Params& p, CUtensorMap const& map, char const* whe
   dim3 grid((unsigned)std::min<long long>(numTiles, ctx->smCount), 1, 1);
   cudaError_t e;
   if (split3) {
-    e = allow_large_smem<conv_ts_kernel<true, 2>>(ctx->device);
-    if (e == cudaSuccess) conv_ts_kernel<true, 2><<<grid, kTsThreadsRows, smemBytes, ctx->stream>>>(p, map);
+    e = allow_large_smem<conv_ts_kernel<true, 2, false>>(ctx->device);
+    if (e == cudaSuccess) conv_ts_kernel<true, 2, false><<<grid, kTsThreadsRows, smemBytes, ctx->stream>>>(p, map);
   } else {
-    e = allow_large_smem<conv_ts_kernel<false, 2>>(ctx->device);
-    if (e == cudaSuccess) conv_ts_kernel<false, 2><<<grid, kTsThreadsRows, smemBytes, ctx->stream>>>(p, map);
+    e = allow_large_smem<conv_ts_kernel<false, 2, false>>(ctx->device);
+    if (e == cudaSuccess) conv_ts_kernel<false, 2, false><<<grid, kTsThreadsRows, smemBytes, ctx->stream>>>(p, map);
   }
   if (e != cudaSuccess) { cudaGetLastError(); return vlb::set_error(ctx, VLB_Cuda, cudaGetErrorString(e)); }
   VLB_LAUNCHED(ctx, 1);
