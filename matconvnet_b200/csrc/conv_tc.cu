@@ -1401,8 +1401,9 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
       uint32_t tAcc = tmemAcc;
       uint32_t own = 0;                              // this issuer's k-blocks so far: k-block `own` sits in A stage q + 2*(own % kAPer)
       uint32_t phTurn = q == 0 ? 1u : 0u;            // issuer 0 has the first turn (nothing to wait for)
-      // measured: +4-8% on 128-column tiles, -5% on 64-column tiles (their MMAs are short and the extra wait shows)
-      bool const takeTurns = BN > 64;
+      // measured: +5-13% on 128-column tiles, -5% on 64-column tiles (their MMAs are short and the extra wait shows), -1-5% in the
+      // row mode (whose producers read shared memory and are never late)
+      bool const takeTurns = BN > 64 && !kWg;
       for (int ts = 0; ts < myTiles && ok; ++ts) {
         int const first = (int)((((long long)ts * numIter) ^ q) & 1);      // 0: this issuer owns the tile's first k-block
         int const chainsF = ts_chains<kSplit>(numIter, 0), chainsS = ts_chains<kSplit>(numIter, 1);
