@@ -9,6 +9,8 @@
 // dimension of the MATLAB layout), with the filters in shared memory read as broadcasts.  Exact fp32 FMAs:
 // the results are at least as accurate as the 3xTF32 arithmetic of the tensor-core path.
 #include "conv_internal.cuh"
+#include <stdint.h>
+#include <algorithm>
 
 namespace {
 
@@ -109,6 +111,82 @@ __global__ void __launch_bounds__(kThreads) conv_small_r_kernel(SmallParams p)
   }
 }
 
+// ---- few inputs per pixel, unit stride and dilation, output columns a multiple of four pixels high: four vertically adjacent
+// pixels x KC filters per thread.  The FH + 3 input values of a (channel, filter column) serve all FH filter rows of the four
+// pixels, and a filter value read from shared memory (a broadcast) feeds four FMAs instead of one: the kernel above spends as
+// many shared-memory wavefronts as FMA issue slots, this one a quarter.  Stores are 16 bytes per thread and filter.
+template <int KC, int FH>
+__global__ void __launch_bounds__(kThreads) conv_small_r4_kernel(SmallParams p)
+{
+  extern __shared__ float4 smem4[];
+  float* fs = reinterpret_cast<float*>(smem4);                 // [R][KC], r = fh + FH*(fw + FW*c)
+  int const taps = FH * p.FW, R = taps * p.Cin;
+  int const k0 = blockIdx.y * KC;
+  for (int i = threadIdx.x; i < R * KC; i += kThreads) {
+    int const r = i / KC, k = i % KC;
+    int const fh = r % FH, fw = (r / FH) % p.FW, c = r / taps;
+    fs[i] = (k0 + k < p.Kout) ? filter_at(p, fh, fw, c, k0 + k) : 0.f;
+  }
+  __syncthreads();
+  int const quadsPerCol = p.Ho >> 2;
+  long long const m4 = (long long)blockIdx.x * kThreads + threadIdx.x;
+  long long const Q = (long long)quadsPerCol * p.Wo * p.N;
+  if (m4 >= Q) return;
+  int const ho0 = (int)(m4 % quadsPerCol) * 4;
+  long long const t = m4 / quadsPerCol;
+  int const wo = (int)(t % p.Wo), n = (int)(t / p.Wo);
+  float acc[4][KC];
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int k = 0; k < KC; ++k) acc[j][k] = 0.f;
+  int const h0 = ho0 - p.pt;                                   // input row of window element 0
+  float const* const xn = p.x + (long long)n * p.H * p.W * p.Cin;
+  for (int c = 0; c < p.Cin; ++c) {
+    for (int fw = 0; fw < p.FW; ++fw) {
+      int const w = wo + fw - p.pl;
+      bool const wOk = w >= 0 && w < p.W;
+      float const* const col = xn + ((long long)c * p.W + (wOk ? w : 0)) * p.H;
+      float xs[FH + 3];
+#pragma unroll
+      for (int i = 0; i < FH + 3; ++i) {
+        int const h = h0 + i;
+        bool const ok = wOk && h >= 0 && h < p.H;
+        xs[i] = ok ? __ldg(col + h) : 0.f;
+      }
+      float4 const* f4 = reinterpret_cast<float4 const*>(fs + (size_t)(FH * (fw + p.FW * c)) * KC);
+#pragma unroll
+      for (int fh = 0; fh < FH; ++fh) {
+#pragma unroll
+        for (int k4 = 0; k4 < KC / 4; ++k4) {
+          float4 const wv = f4[fh * (KC / 4) + k4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float const xv = xs[j + fh];
+            acc[j][4 * k4 + 0] = fmaf(xv, wv.x, acc[j][4 * k4 + 0]);
+            acc[j][4 * k4 + 1] = fmaf(xv, wv.y, acc[j][4 * k4 + 1]);
+            acc[j][4 * k4 + 2] = fmaf(xv, wv.z, acc[j][4 * k4 + 2]);
+            acc[j][4 * k4 + 3] = fmaf(xv, wv.w, acc[j][4 * k4 + 3]);
+          }
+        }
+      }
+    }
+  }
+  long long const P = (long long)p.Ho * p.Wo;
+  float* const dst0 = p.out + (long long)n * p.Kout * P + (long long)wo * p.Ho + ho0;
+#pragma unroll
+  for (int k = 0; k < KC; ++k) {
+    if (k0 + k < p.Kout) {
+      float4* dst = reinterpret_cast<float4*>(dst0 + (long long)(k0 + k) * P);
+      float const b = p.bias ? p.bias[k0 + k] : 0.f;
+      float4 o = make_float4(p.inMult * acc[0][k] + b, p.inMult * acc[1][k] + b, p.inMult * acc[2][k] + b, p.inMult * acc[3][k] + b);
+      if (p.outMult != 0.f) { float4 const old = *dst; o.x += p.outMult * old.x; o.y += p.outMult * old.y; o.z += p.outMult * old.z; o.w += p.outMult * old.w; }
+      if (p.relu) { o.x = o.x > 0.f ? o.x : 0.f; o.y = o.y > 0.f ? o.y : 0.f; o.z = o.z > 0.f ? o.z : 0.f; o.w = o.w > 0.f ? o.w : 0.f; }
+      *dst = o;
+    }
+  }
+}
+
 // ---- few output channels: NC accumulators per thread, filters [tap][cin][NC] in shared memory
 template <int NC>
 __global__ void __launch_bounds__(kThreads) conv_small_n_kernel(SmallParams p)
@@ -189,6 +267,16 @@ int conv_fprop_small(vlb_ctx* ctx, ConvGeom const& g, float* Y, float outMult, f
   p.flip = 0; p.Cf = g.FC;
   p.relu = ctx->fuseRelu; ctx->reluDone = ctx->fuseRelu;
   long long const M = (long long)g.Ho * g.Wo * g.N;
+  if (g.sy == 1 && g.sx == 1 && g.dy == 1 && g.dx == 1 && g.Ho % 4 == 0 && (g.FH == 3 || g.FH == 5) && g.K % 4 == 0 &&
+      (((uintptr_t)Y) & 15) == 0) {
+    constexpr int KC = 16;
+    dim3 grid4((unsigned)ceil_div(M / 4, kThreads), (unsigned)ceil_div(g.K, KC));
+    size_t const smem4 = sizeof(float) * (size_t)R * KC;
+    if (g.FH == 3) conv_small_r4_kernel<KC, 3><<<grid4, kThreads, smem4, ctx->stream>>>(p);
+    else           conv_small_r4_kernel<KC, 5><<<grid4, kThreads, smem4, ctx->stream>>>(p);
+    VLB_LAUNCHED(ctx, 1);
+    return check_launch(ctx, "conv_fprop_small");
+  }
   int const KC = g.K > 32 ? 64 : (g.K > 16 ? 32 : 16);
   dim3 grid((unsigned)ceil_div(M, kThreads), (unsigned)ceil_div(g.K, KC));
   size_t const smem = sizeof(float) * (size_t)R * KC + sizeof(int2) * (size_t)R;
