@@ -151,7 +151,7 @@ bnorm_fused_kernel(float* __restrict__ out,            // y or dx
   long long const items = kVec ? (long long)N * WH4 : (long long)N * WH;
   long long const first = (long long)rank * kThreads + threadIdx.x, step = (long long)kCluster * kThreads;
 
-#pragma unroll 4
+#pragma unroll 8
   for (long long i = first; i < items; i += step) {
     if (kVec) {
       int n = (int)(i / WH4);
@@ -193,12 +193,18 @@ bnorm_fused_kernel(float* __restrict__ out,            // y or dx
     part[threadIdx.x] = s;
   }
   cluster.sync();
+  // rank 0 gathers the partial sums of all ranks through distributed shared memory -- 32 threads fetch one value each, so that
+  // the remote reads are one round trip instead of 32 -- and thread 0 adds them in rank order
+  __shared__ float gath[kCluster][4];
+  if (rank == 0 && threadIdx.x < kCluster * 4) {
+    int const r = threadIdx.x >> 2, j = threadIdx.x & 3;
+    gath[r][j] = cluster.map_shared_rank(part, r)[j];
+  }
+  if (rank == 0) __syncwarp();
   if (rank == 0 && threadIdx.x == 0) {
     float tot[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int r = 0; r < kCluster; ++r) {
-      float const* remote = cluster.map_shared_rank(part, r);
-      for (int j = 0; j < 4; ++j) tot[j] += remote[j];
-    }
+    for (int r = 0; r < kCluster; ++r)
+      for (int j = 0; j < 4; ++j) tot[j] += gath[r][j];
     float const mass = (float)((long long)WH * N);
     float mean, sigma;
     if (kMode == 2) { mean = momentsIn[c]; sigma = momentsIn[c + C]; }
@@ -230,9 +236,9 @@ bnorm_fused_kernel(float* __restrict__ out,            // y or dx
     float const* rc = cluster.map_shared_rank(coef, 0);
     k0 = rc[0]; k1 = rc[1]; k2 = rc[2]; k3 = rc[3];
   }
-  cluster.sync();   // rank 0's shared memory has been read by everyone
+  // (rank 0's shared memory has to outlive these reads: the cluster meets once more at the very end, where nobody waits long)
 
-#pragma unroll 4
+#pragma unroll 8
   for (long long i = first; i < items; i += step) {
     if (kVec) {
       int n = (int)(i / WH4);
@@ -262,6 +268,7 @@ bnorm_fused_kernel(float* __restrict__ out,            // y or dx
       else out[off] = __fadd_rn(__fmul_rn(k2, __fadd_rn(dy[off], -k1)), -__fmul_rn(k3, __fadd_rn(x[off], -k0)));
     }
   }
+  cluster.sync();   // every CTA has read rank 0's coefficients long ago; rank 0 may exit
 }
 
 template <int kMode>
