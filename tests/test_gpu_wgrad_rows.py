@@ -30,8 +30,9 @@ CASES = [((8, 4, 32, 3), (3, 3, 32, 16), dict(pad=1)),                # one k-bl
          ((56, 56, 64, 8), (3, 3, 64, 64), dict(pad=1)),              # a VGG-like plane, 64-column tiles, many ranges
          ((28, 32, 128, 16), (3, 3, 128, 128), dict(pad=1)),          # rows of 28: row masks at changing places
          ((28, 28, 32, 5), (3, 3, 32, 32), dict(pad=1)),              # planes of 784 pixels: padded to 25 k-blocks per image
-         ((12, 20, 64, 3), (3, 3, 64, 16), dict(pad=1)),              # 240 pixels padded to 256: the most padding the route accepts
-         ((14, 14, 32, 4), (3, 3, 32, 32), dict(pad=1))]              # 196 pixels would need 224: stays on the other kernel
+         ((12, 20, 64, 3), (3, 3, 64, 16), dict(pad=1)),              # 240 pixels padded to 256
+         ((14, 14, 32, 4), (3, 3, 32, 32), dict(pad=1)),              # 196 pixels padded to 224: the most padding the route accepts (1/8)
+         ((10, 10, 32, 4), (3, 3, 32, 32), dict(pad=1))]              # 100 pixels would need 128: stays on the other kernel
 
 
 @pytest.mark.parametrize("precision,tol", [(0, 1e-5), (1, 2e-3)])
