@@ -154,7 +154,7 @@ def contraction_kernels(ctx, passes, peak_tf32):
     """The per-kind sums of the last profile as entries of the bench line's `kernels` list."""
     names = ["conv fprop (conv_ts_kernel; conv1_1 runs on CUDA cores and is not in this sum)",
              "conv dgrad (conv_ts_kernel, ReLU mask fused)",
-             "conv wgrad + dbias (dY tile images + conv_ts_kernel in its row mode, conv1_1 on tc_gemm_kernel, + sum of the reduction ranges)",
+             "conv wgrad + dbias (dY tile images + conv_ts_kernel in its row mode + sum of the reduction ranges; conv1_1 on CUDA cores)",
              "fully connected fprop/dgrad/wgrad (fc6 on conv_ts_kernel: weights read or written once; fc7, fc8 on tc_gemm_kernel)"]
     out = []
     for kind, name in enumerate(names):
@@ -354,7 +354,7 @@ def main():
                 "traffic": None,
                 "traffic_note": "DRAM bytes are captured per kernel on single layers (one kernel, a few launches) and kept under "
                                 "profiles/; no whole-step counter capture is made",
-                "kernel": "conv_ts_kernel (conv fprop / dgrad / wgrad, fc6) + tc_gemm_kernel (conv1_1 wgrad, fc7, fc8), operand "
+                "kernel": "conv_ts_kernel (conv fprop / dgrad / wgrad, fc6) + tc_gemm_kernel (fc7, fc8), operand "
                           "preparation and the sums over reduction ranges included",
                 "contractions_per_step": tc_count, "ms_per_step": tc_ms, "mma_passes": passes,
                 "tensor_work_frac": passes * achieved / peak, "peak_source": peak_src,

@@ -185,7 +185,8 @@ int vlb_conv_backward(vlb_ctx* ctx, float* dX, float* dF, float* db, float const
   bool tc = ctx->precision != VLB_PRECISION_FP32;
   bool dbDone = false;
   if (dF) {
-    rc = tc ? vlb::conv_wgrad_tc(ctx, g, dF, db, X, dY, &dbDone) : VLB_Unsupported;
+    rc = vlb::conv_wgrad_small(ctx, g, dF, db, X, dY, &dbDone);
+    if (rc == VLB_Unsupported) rc = tc ? vlb::conv_wgrad_tc(ctx, g, dF, db, X, dY, &dbDone) : VLB_Unsupported;
     if (rc == VLB_Unsupported) rc = vlb::conv_wgrad_simt(ctx, g, dF, X, dY);
     if (rc) return vlb::pass_error(ctx, rc, "vlb_conv_backward");
   }

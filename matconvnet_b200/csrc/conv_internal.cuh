@@ -24,6 +24,7 @@ int conv_wgrad_simt(vlb_ctx* ctx, ConvGeom const& g, float* dF, float const* X, 
 int conv_fprop_small(vlb_ctx* ctx, ConvGeom const& g, float* Y, float outMult, float const* X, float inMult,
                      float const* F, float const* b);
 int conv_dgrad_small(vlb_ctx* ctx, ConvGeom const& g, float* dX, float const* F, float const* dY);
+int conv_wgrad_small(vlb_ctx* ctx, ConvGeom const& g, float* dF, float* db, float const* X, float const* dY, bool* dbDone);
 
 // tcgen05 implicit GEMM (conv_tc.cu).  Each returns VLB_Unsupported -- without touching
 // the context's error state -- when the configuration is outside what the tensor-core
