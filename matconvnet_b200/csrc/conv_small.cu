@@ -244,6 +244,76 @@ __global__ void __launch_bounds__(kThreads) conv_small_n_kernel(SmallParams p)
   }
 }
 
+// ---- few output channels, 3-row filters with one row of padding above, unit stride and dilation, columns a multiple of four
+// pixels high: four vertically adjacent output pixels per thread.  The six input rows h0-1 .. h0+4 of a (filter column, input
+// channel) -- one 16-byte load and two scalars -- serve all three filter rows of the four pixels, and a filter value read from
+// shared memory feeds four FMAs: 2.3 times fewer load instructions per FMA than one pixel per thread.
+template <int NC>
+__global__ void __launch_bounds__(kThreads) conv_small_n4_kernel(SmallParams p)
+{
+  extern __shared__ float4 smem4[];
+  float* fs = reinterpret_cast<float*>(smem4);                 // [tap][cin][4]
+  int const taps = 3 * p.FW;
+  for (int i = threadIdx.x; i < taps * p.Cin * 4; i += kThreads) {
+    int const k = i & 3, c = (i >> 2) % p.Cin, tap = (i >> 2) / p.Cin;
+    fs[i] = k < p.Kout ? filter_at(p, tap % 3, tap / 3, c, k) : 0.f;
+  }
+  __syncthreads();
+  int const quadsPerCol = p.Ho >> 2;
+  long long const m4 = (long long)blockIdx.x * kThreads + threadIdx.x;
+  if (m4 >= (long long)quadsPerCol * p.Wo * p.N) return;
+  int const ho0 = (int)(m4 % quadsPerCol) * 4;
+  long long const t = m4 / quadsPerCol;
+  int const wo = (int)(t % p.Wo), n = (int)(t / p.Wo);
+  float acc[4][NC];
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int k = 0; k < NC; ++k) acc[j][k] = 0.f;
+  long long const HW = (long long)p.H * p.W;
+  float const* const xn = p.x + (long long)n * HW * p.Cin;
+  bool const up = ho0 - 1 >= 0, down = ho0 + 4 < p.H, mid = ho0 + 3 < p.H;      // (input and output have the same height here)
+  for (int fw = 0; fw < p.FW; ++fw) {
+    int const w = wo + fw - p.pl;
+    if (w < 0 || w >= p.W) continue;
+    float const* col = xn + (long long)w * p.H + ho0;
+    float4 const* ft = reinterpret_cast<float4 const*>(fs) + (size_t)(3 * fw) * p.Cin;
+#pragma unroll 4
+    for (int c = 0; c < p.Cin; ++c, col += HW) {
+      float xs[6];
+      float4 const v = mid ? __ldg(reinterpret_cast<float4 const*>(col)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      xs[0] = up ? __ldg(col - 1) : 0.f;
+      xs[1] = v.x; xs[2] = v.y; xs[3] = v.z; xs[4] = v.w;
+      xs[5] = down ? __ldg(col + 4) : 0.f;
+#pragma unroll
+      for (int fh = 0; fh < 3; ++fh) {
+        float4 const wv = ft[(size_t)fh * p.Cin + c];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float const xv = xs[j + fh];
+          acc[j][0] = fmaf(xv, wv.x, acc[j][0]);
+          if (NC > 1) acc[j][1] = fmaf(xv, wv.y, acc[j][1]);
+          if (NC > 2) acc[j][2] = fmaf(xv, wv.z, acc[j][2]);
+          if (NC > 3) acc[j][3] = fmaf(xv, wv.w, acc[j][3]);
+        }
+      }
+    }
+  }
+  long long const P = (long long)p.Ho * p.Wo;
+  float* const dst0 = p.out + (long long)n * p.Kout * P + (long long)wo * p.Ho + ho0;
+#pragma unroll
+  for (int k = 0; k < NC; ++k) {
+    if (k < p.Kout) {
+      float4* dst = reinterpret_cast<float4*>(dst0 + (long long)k * P);
+      float const b = p.bias ? p.bias[k] : 0.f;
+      float4 o = make_float4(p.inMult * acc[0][k] + b, p.inMult * acc[1][k] + b, p.inMult * acc[2][k] + b, p.inMult * acc[3][k] + b);
+      if (p.outMult != 0.f) { float4 const old = *dst; o.x += p.outMult * old.x; o.y += p.outMult * old.y; o.z += p.outMult * old.z; o.w += p.outMult * old.w; }
+      if (p.relu) { o.x = o.x > 0.f ? o.x : 0.f; o.y = o.y > 0.f ? o.y : 0.f; o.z = o.z > 0.f ? o.z : 0.f; o.w = o.w > 0.f ? o.w : 0.f; }
+      *dst = o;
+    }
+  }
+}
+
 // ---- filter (and bias) gradient with few inputs per pixel (R = FH*FW*C <= 27): dF[r][k] = sum over output pixels of
 // x(pixel, r) * dY(pixel, k).  A block walks chunks of 256 consecutive output pixels: it stages the chunk's input windows
 // (256 x R values, gathered once and then shared by all filters) and its 64 x 256 tile of dY in shared memory, both loaded
@@ -450,6 +520,13 @@ int conv_dgrad_small(vlb_ctx* ctx, ConvGeom const& g, float* dX, float const* F,
   p.pt = (g.FH - 1) * g.dy - g.pt; p.pl = (g.FW - 1) * g.dx - g.pl;
   p.flip = 1; p.Cf = g.FC;
   long long const M = (long long)g.H * g.W * g.N;
+  // filter rows: fh' = 0..2 with pt' = 1 row of padding above; the input (dY) and the output (dX) have the same height
+  if (g.FH == 3 && p.pt == 1 && g.dy == 1 && g.dx == 1 && g.Ho == g.H && g.H % 4 == 0 && g.C <= 3 &&
+      (((uintptr_t)dX) & 15) == 0 && (((uintptr_t)dY) & 15) == 0) {
+    conv_small_n4_kernel<3><<<(unsigned)ceil_div(M / 4, kThreads), kThreads, smem, ctx->stream>>>(p);
+    VLB_LAUNCHED(ctx, 1);
+    return check_launch(ctx, "conv_dgrad_small");
+  }
   conv_small_n_kernel<4><<<(unsigned)ceil_div(M, kThreads), kThreads, smem, ctx->stream>>>(p);
   VLB_LAUNCHED(ctx, 1);
   return check_launch(ctx, "conv_dgrad_small");
