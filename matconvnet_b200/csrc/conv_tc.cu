@@ -999,7 +999,7 @@ constexpr int kTsForwardWarp = kEpilogueWarps + 3;
 constexpr int kTsFirstProducer = kEpilogueWarps + 4;
 constexpr int kTsThreads = (kTsFirstProducer + 4 * kTsGroups) * 32;      // 512: four warpgroups, 128 registers per thread at launch
 constexpr int kTsRunWarp = kTsFirstProducer + 4 * kTsGroups;             // row mode only: warp 16 issues the runs (tensor-map copies)
-constexpr int kTsThreadsRows = (kTsRunWarp + 1) * 32;                    // 544
+constexpr int kTsThreadsRows = (kTsRunWarp + 4) * 32;                    // 640: warp 16's warpgroup is launched whole (warps 17-19 idle), so that it can hand its registers over
 constexpr int kTsBStages = 6;           // at most; Params::bStages are in use
 constexpr int kTsDrainEvery = 4;        // own k-blocks per accumulation chain: 4 x 4 k-steps x 3 MMAs.  Measured relative error of one layer
                                         // at the full VGG sizes: 4 -> 9e-7, 8 -> 1.7e-6, 16 -> 3.3e-6 (8 is 5-8% faster, 16 another 0-7%), but with 8
@@ -1172,8 +1172,13 @@ constexpr int kTsXStages = 6;                           // at most
 // Registers (kMode 0, 1): 128 per thread at launch (512 threads: the whole register file, one CTA per SM); then the warps 4-7
 // keep 56 and the drain warps 0-3 take 200 (setmaxnreg: 128 of them hold the running sum of a tile).
 // kMode 2 runs with a seventeenth warp for its per-k-block tensor-map copies -- such a copy keeps the issuing warp busy for about
-// a microsecond, so it cannot share a warp with the forwarding, the filter tiles or a producer (measured: 35-50% slower each way)
-// -- which leaves 96 registers per thread and the running sum in shared memory.
+// a microsecond, so it cannot share a warp with the forwarding, the filter tiles or a producer (measured: 35-50% slower each way).
+// Registers are handed over by whole warpgroups, so the kernel is launched with five of them (640 threads, 96 registers each; the
+// warps 17-19 have nothing to do): the warps 4-7 and 16-19 keep 40, the producers their 96, and the drain warps take 200 here
+// too -- what the two groups give up (2 x 128 x 56) covers what the drain warps take (128 x 104), so the hand-over stays inside
+// the registers the block was launched with and never waits.  With the running sum in shared memory this mode was
+// bound by shared-memory bandwidth (per k-block about 150 KB of tile copies, operand reads by the tensor core, runs read by the
+// producers and 32 KB of running sum read and rewritten, against 128 bytes per clock).
 // kNarrow: tiles of 64 columns or fewer (kMode 0, 1), which get more accumulators and A stages (below).
 template <bool kSplit, int kMode, bool kNarrow>
 __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) conv_ts_kernel(Params p, const __grid_constant__ CUtensorMap xmap)
@@ -1208,7 +1213,7 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
   float* const Psm = reinterpret_cast<float*>(smem + (size_t)nB * bBytes);      // [BN][BM]
   // input windows (kTma): two buffers of boxH*boxW*32 floats behind P
   uint32_t const xPlane = (uint32_t)(p.boxH * p.boxW), xTileBytes = kWg ? (uint32_t)kWgStageBytes : xPlane * 32u * 4u;
-  bool const regsP = !kWg && (BN == 128 || BN == 64) && !p.smemSum;      // the running sum of a tile lives in the drain warps' registers
+  bool const regsP = (BN == 128 || BN == 64) && !p.smemSum;      // the running sum of a tile lives in the drain warps' registers
   uint32_t const xTile0 = smem_u32(Psm) + (regsP ? 32u : (uint32_t)BN) * BM * 4u;      // (registers: a patch of 32 columns for the stores)
 
   int const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1251,7 +1256,7 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
     // warps give up (setmaxnreg).  After the tile's last chain the sum goes to shared memory once, P[column][row], and is
     // stored from there (coalesced along the rows) while the tensor core is already two chains into the next tile.  Tiles
     // of other widths than 128 and 64 columns keep the running sum in shared memory.
-    if (!kWg) asm volatile("setmaxnreg.inc.sync.aligned.u32 200;" ::: "memory");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;" ::: "memory");
     uint32_t const lanes = tmemAcc + ((uint32_t)(warp * 32) << 16);
     float* const Prow = Psm + warp * 32 + lane;       // this thread's row of P: Prow[column * BM]
     bool const preMask = p.e.mask != nullptr && !singleTile;
@@ -1369,17 +1374,14 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
         }
       }
     };
-    if constexpr (kWg) {
-      drain(std::integral_constant<int, 0>{});
-    } else {
-      if (regsP && BN == 128) drain(std::integral_constant<int, 128>{});
-      else if (regsP) drain(std::integral_constant<int, 64>{});
-      else drain(std::integral_constant<int, 0>{});
-    }
+    if (regsP && BN == 128) drain(std::integral_constant<int, 128>{});
+    else if (regsP) drain(std::integral_constant<int, 64>{});
+    else drain(std::integral_constant<int, 0>{});
   } else if (warp < 2 * kEpilogueWarps) {
     // warps 4-7 (issuers, filter-tile loader, forwarder) work with one thread each and a handful of registers: the rest goes
     // to the drain warps.  All four warps of the group execute this before anything else.
-    if (!kWg) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;" ::: "memory");
+    if (kWg) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
+    else     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;" ::: "memory");
     if (warp == kEpilogueWarps || warp == kEpilogueWarps + 1) {
     // ============================== MMA issue ==============================
     // Two issuing threads (in two warps, on two schedulers).  The tensor core's queue is about one MMA deep, so
@@ -1536,9 +1538,11 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
     }
     __syncwarp();
     }
-  } else if (warp == kTsRunWarp) {
+  } else if (warp >= kTsRunWarp) {
     // ============================== row mode: runs by tensor-map copies ==============================
-    if (kWg && lane == 0) {
+    // (the warpgroup of warps 16-19 exists in the row mode only and keeps a handful of registers, like the warps 4-7)
+    if (kWg) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
+    if (kWg && warp == kTsRunWarp && lane == 0) {
       // The run of k-block j (numbered over the CTA's life) -- 36 pixels x cPer channels per
       // tap of the tile, from the plane of image r / P starting at pixel r % P + shift of the tap, rounded down to four pixels (P:
       // the plane rounded up to whole k-blocks; the tile images hold zeros for the pixels added; pixels before the plane's first
@@ -1973,6 +1977,8 @@ template <> constexpr int kRegsAtLaunch<conv_ts_kernel<false, 0, true>>() { retu
 template <> constexpr int kRegsAtLaunch<conv_ts_kernel<false, 0, false>>() { return 128; }
 template <> constexpr int kRegsAtLaunch<conv_ts_kernel<false, 1, true>>() { return 128; }
 template <> constexpr int kRegsAtLaunch<conv_ts_kernel<false, 1, false>>() { return 128; }
+template <> constexpr int kRegsAtLaunch<conv_ts_kernel<true, 2, false>>() { return 96; }
+template <> constexpr int kRegsAtLaunch<conv_ts_kernel<false, 2, false>>() { return 96; }
 
 // The opt-in to more than 48 KB of dynamic shared memory, once per kernel and device instead of before every launch.
 template <auto kKernel>
@@ -2215,7 +2221,8 @@ int launch_rows(vlb_ctx* ctx, Params& p, CUtensorMap const& map, char const* whe
 {
   bool const split3 = ctx->precision == VLB_PRECISION_3XTF32;
   // shared memory: filter-tile stages, the running sum, the runs
-  size_t const bBytes = (size_t)(split3 ? 2 : 1) * p.BN * BK * 4, pBytes = sizeof(float) * (size_t)p.BN * BM;
+  p.smemSum = ((ctx->testSwitch & 8) || p.kbPerSplit < 8) ? 1 : 0;
+  size_t const bBytes = (size_t)(split3 ? 2 : 1) * p.BN * BK * 4, pBytes = p_bytes(p.BN, p.smemSum);
   size_t const limit = 227 * 1024 - 1536;
   p.bStages = 0;
   for (int nb = kTsBStages; nb >= 3 && !p.bStages; --nb)

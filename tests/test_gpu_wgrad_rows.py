@@ -56,13 +56,15 @@ def test_filter_gradient_rows_in_tensor_memory(gpu, oracle, case, precision, tol
     lib = ctx.lib
     try:
         got = {}
-        for switch in (0, 4):
+        for switch in (0, 8, 4):
             ctx.check(lib.vlb_ctx_set_test_switch(ctx.handle, switch))
             _, df, db = nn.vl_nnconv(xd, fd, bd, dyd, no_der_data=True, ctx=ctx, **kw)
             assert ctx.device_status() == 0
             got[switch] = (mat.to_numpy(df), mat.to_numpy(db))
             assert rel_l2(got[switch][0], dfr) < tol, (switch, "df")
             assert rel_l2(got[switch][1].ravel(), dbr.ravel()) < 1e-5, (switch, "db")
+        # the running sum of a tile in the drain warps' registers (default) or in shared memory (switch bit 3): same additions
+        assert np.array_equal(got[0][0], got[8][0]) and np.array_equal(got[0][1], got[8][1])
         ctx.check(lib.vlb_ctx_set_test_switch(ctx.handle, 0))
         _, df2, db2 = nn.vl_nnconv(xd, fd, bd, dyd, no_der_data=True, ctx=ctx, **kw)
         assert np.array_equal(mat.to_numpy(df2), got[0][0]) and np.array_equal(mat.to_numpy(db2), got[0][1])     # no atomics: run to run identical
