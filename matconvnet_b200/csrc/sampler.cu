@@ -12,13 +12,16 @@
 // (bits/impl/nnbilinearsampler_gpu.cu:38-118).  Which output pixels touch an input pixel depends
 // on the grid alone, not on the channel, so one CTA per image first inverts the grid in shared
 // memory: it counts the taps that land on every input pixel, prefix-sums the counts, fills one
-// list (output pixel, tap weight) per input pixel and sorts each list by output pixel.  Then every
-// input pixel adds up its list, for eight channels at a time, in ascending output-pixel order --
-// the order in which the CPU loop reaches that element (bits/nnbilinearsampler.cu:72-131) -- and
-// writes dX once: no atomics, no zero fill, the CPU's result bit for bit, identical from run to
-// run.  dy is read once from HBM (the grid derivative, computed by the same CTA afterwards, finds
-// it in L2).  A grid that sends more than kMaxList taps to one input pixel, and planes too large
-// for the lists, take the atomic scatter instead.
+// list (output pixel, tap) per input pixel and sorts each list by output pixel.  Then every
+// input pixel adds up its list in ascending output-pixel order -- the order in which the CPU loop
+// reaches that element (bits/nnbilinearsampler.cu:72-131) -- for four channels per walk of the
+// list (the dY planes of four channels wait in shared memory, the next four travel meanwhile;
+// decoding an entry and forming its weight is paid once for the four), and writes dX once: no
+// atomics, no zero fill, the CPU's result bit for bit, identical from run to run.  The grid
+// derivative is a second sweep of the same CTA over the channels, two at a time, with the x
+// planes staged beside the dY planes (dY comes from L2 this time), every output pixel adding its
+// channels' terms in ascending channel order.  A grid that sends more than kMaxList taps to one
+// input pixel, and planes too large for the lists, take the atomic scatter instead.
 //
 // Boundary rule of the CPU reference, kept as it is: the taps are guarded by
 // `-1 <= sy && sy < inHeight` with inHeight a size_t (bits/nnbilinearsampler.cu:92), so
@@ -127,21 +130,26 @@ __global__ void sampler_kernel(float* __restrict__ y, float* __restrict__ dx, fl
 constexpr int kGatherThreads = 1024;
 constexpr int kMaxList = 48;          // taps of one grid on one input pixel beyond which the scatter path is used
 constexpr int kMaxQPerThread = 4;     // output pixels per thread whose taps and grid derivative are kept in registers
+constexpr int kCB = 4;                // channels per stage: one walk of a pixel's list serves four channels
 
-// Shared memory (bytes): cur int[HW] | entW float[4Q] | stage float[2][HW + Q] (x plane and dy plane of a channel, double
-// buffered) | entQ uint16[4Q]
+// Shared memory (bytes): the stage buffers -- float[2][4][Q] (dY planes of four channels, double buffered) for the data gradient,
+// float[2][2 x HW + 2 x Q] (x and dY planes of two channels, double buffered) for the grid derivative -- | wq float2[Q] (the two
+// fractions of every output pixel) | cur int[HW] | ent uint16[4Q] (list entries: output pixel << 2 | tap)
 __host__ __device__ inline size_t gather_smem(int HW, int Q)
 {
-  return sizeof(int) * (size_t)HW + (sizeof(float) + sizeof(uint16_t)) * 4 * (size_t)Q + sizeof(float) * 2 * ((size_t)HW + Q) + 64;
+  size_t const stageFloats = 8 * (size_t)Q > 4 * ((size_t)HW + Q) ? 8 * (size_t)Q : 4 * ((size_t)HW + Q);
+  return sizeof(float) * stageFloats + sizeof(int) * (size_t)HW + (sizeof(float2) + 4 * sizeof(uint16_t)) * (size_t)Q + 64;
 }
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, void const* src)
-{ asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory"); }
 __device__ __forceinline__ void cp_async4(uint32_t dst, void const* src)
 { asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.commit_group;\n cp.async.wait_group 0;" ::: "memory"); }
 
-// n floats global -> shared by the whole block, asynchronously (16-byte pieces when both sides allow)
+__device__ __forceinline__ void cp_async16(uint32_t dst, void const* src)
+{ asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory"); }
+
+// n floats global -> shared by the whole block, asynchronously (16-byte pieces when both sides allow; copies of four bytes
+// keep the load/store unit busy four times as long and were measured to slow the whole stage down)
 __device__ __forceinline__ void stage_plane(float* dst, float const* src, int n)
 {
   uint32_t const d = (uint32_t)__cvta_generic_to_shared(dst);
@@ -150,6 +158,12 @@ __device__ __forceinline__ void stage_plane(float* dst, float const* src, int n)
   } else {
     for (int i = threadIdx.x; i < n; i += kGatherThreads) cp_async4(d + 4u * i, src + i);
   }
+}
+
+// dY of the channels c .. c + nst - 1 (nst <= 4) of one grid, Q floats per channel, as nst planes of Q floats
+__device__ __forceinline__ void stage_dy4(float* dst, float const* src, int Q, int nst)
+{
+  for (int j = 0; j < nst; ++j) stage_plane(dst + (size_t)Q * j, src + (size_t)Q * j, Q);
 }
 
 template <bool kWantGrid>
@@ -161,27 +175,28 @@ sampler_bwd_gather_kernel(float* __restrict__ dx, float* __restrict__ dgrid, flo
   extern __shared__ __align__(16) uint8_t sm[];
   __shared__ int warpSums[32];
   int const HW = H * W, tid = threadIdx.x;
-  int* cur = reinterpret_cast<int*>(sm);                                   // [HW]  list ends (starts before the fill)
-  float* entW = reinterpret_cast<float*>(cur + HW);                       // [4Q]  tap weight wwx*wwy
-  float* stage = entW + 4 * (size_t)Q;                                    // [2][HW + Q]
-  uint16_t* entQ = reinterpret_cast<uint16_t*>(stage + 2 * ((size_t)HW + Q));   // [4Q]  output pixel
+  float* dy4 = reinterpret_cast<float*>(sm);                              // [2][4][Q]
+  float2* wq = reinterpret_cast<float2*>(dy4 + (2 * kCB * (size_t)Q > 4 * ((size_t)HW + Q) ? 2 * kCB * (size_t)Q : 4 * ((size_t)HW + Q)));            // [Q]   (wx, wy) of every output pixel
+  int* cur = reinterpret_cast<int*>(wq + Q);                              // [HW]  list ends (starts before the fill)
+  uint16_t* ent = reinterpret_cast<uint16_t*>(cur + HW);                  // [4Q]  output pixel << 2 | tap (tap = 2*column offset + row offset)
   int const group = Ng / N;
   int const img = blockIdx.x / chunks, c0 = (blockIdx.x % chunks) * CH, nch = min(CH, C - c0);
+  int const nStages = (nch + kCB - 1) / kCB;
   size_t const imgOff = (size_t)HW * C * (size_t)img;
 
   for (int gi = 0; gi < group; ++gi) {
     int const n = img * group + gi;
     float2 const* gr = reinterpret_cast<float2 const*>(grid) + (size_t)Q * n;
     float const* const dyn = dy + (size_t)Q * C * (size_t)n;
-    // the first channel's planes start travelling while the grid is inverted
-    stage_plane(stage, x + imgOff + (size_t)HW * c0, HW);
-    stage_plane(stage + HW, dyn + (size_t)Q * c0, Q);
+    // the first stage's dY starts travelling while the grid is inverted
+    stage_dy4(dy4, dyn + (size_t)Q * c0, Q, min(kCB, nch));
     // ---- invert the grid: count, scan, fill, sort
     for (int i = tid; i < HW; i += kGatherThreads) cur[i] = 0;
     __syncthreads();
     for (int q = tid; q < Q; q += kGatherThreads) {
       float2 const gv = gr[q];
       Taps t = make_taps(gv.x, gv.y, H, W);
+      wq[q] = make_float2(t.wx, t.wy);
       if (t.inside) {
 #pragma unroll
         for (int j = 0; j < 2; ++j)
@@ -202,8 +217,6 @@ sampler_bwd_gather_kernel(float* __restrict__ dx, float* __restrict__ dgrid, flo
         float2 const gv = gr[q];
         Taps t = make_taps(gv.x, gv.y, H, W);
         if (t.inside) {
-          float const wwx[2] = {__fadd_rn(1.f, -t.wx), t.wx};
-          float const wwy[2] = {__fadd_rn(1.f, -t.wy), t.wy};
 #pragma unroll
           for (int j = 0; j < 2; ++j)
 #pragma unroll
@@ -211,100 +224,144 @@ sampler_bwd_gather_kernel(float* __restrict__ dx, float* __restrict__ dgrid, flo
               int const ssy = t.sy + ii, ssx = t.sx + j;
               if (ssy < H && ssx < W) {
                 int const pos = atomicAdd(&cur[ssy + ssx * H], 1);
-                entQ[pos] = (uint16_t)q;
-                entW[pos] = __fmul_rn(wwx[j], wwy[ii]);
+                ent[pos] = (uint16_t)((q << 2) | (2 * j + ii));
               }
             }
         }
       }
       __syncthreads();
-      // every input pixel sorts its list by output pixel
+      // every input pixel sorts its list by output pixel (an output pixel reaches an input pixel with one tap at most)
       for (int pix = tid; pix < HW; pix += kGatherThreads) {
         int const beg = pix == 0 ? 0 : cur[pix - 1], end = cur[pix];
         for (int a = beg + 1; a < end; ++a) {
-          uint16_t const kq = entQ[a];
-          float const kw = entW[a];
+          uint16_t const kq = ent[a];
           int b = a - 1;
-          while (b >= beg && entQ[b] > kq) { entQ[b + 1] = entQ[b]; entW[b + 1] = entW[b]; --b; }
-          entQ[b + 1] = kq; entW[b + 1] = kw;
+          while (b >= beg && ent[b] > kq) { ent[b + 1] = ent[b]; --b; }
+          ent[b + 1] = kq;
         }
       }
-      // ---- channel by channel from shared memory: the planes of channel cc + 1 travel while channel cc is computed
-      float accGy[kMaxQPerThread], accGx[kMaxQPerThread];
-      // this thread's output pixels: first tap's offset in the plane, which of the four taps exist, the two fractions
-      int tapBase[kMaxQPerThread], tapOk[kMaxQPerThread];
-      float tapWx[kMaxQPerThread], tapWy[kMaxQPerThread];
-#pragma unroll
-      for (int k = 0; k < kMaxQPerThread; ++k) {
-        accGy[k] = 0.f; accGx[k] = 0.f;
-        tapBase[k] = 0; tapOk[k] = 0; tapWx[k] = 0.f; tapWy[k] = 0.f;
-        int const q = tid + k * kGatherThreads;
-        if (kWantGrid && q < Q) {
-          float2 const gv = gr[q];
-          Taps t = make_taps(gv.x, gv.y, H, W);
-          tapWx[k] = t.wx; tapWy[k] = t.wy;
-          if (t.inside) {
-            tapBase[k] = t.sy + t.sx * H;
-            tapOk[k] = 1 | (t.sy + 1 < H ? 2 : 0) | (t.sx + 1 < W ? 4 : 0) | ((t.sy + 1 < H && t.sx + 1 < W) ? 8 : 0);   // bit ii + 2*j
-          }
-        }
-      }
-      float const sclY = __fmul_rn(0.5f, (float)(H - 1)), sclX = __fmul_rn(0.5f, (float)(W - 1));
-      for (int cc = 0; cc < nch; ++cc) {
-        float const* const xs = stage + (size_t)(cc & 1) * (HW + Q);
-        float const* const ds = xs + HW;
+      // ---- data gradient, four channels at a time from shared memory: the dY of stage s + 1 travels while stage s is computed
+      for (int st = 0; st < nStages; ++st) {
+        int const cs = c0 + st * kCB, nst = min(kCB, c0 + nch - cs);
+        float const* const ds = dy4 + (size_t)(st & 1) * kCB * Q;
         cp_async_wait_all();
-        __syncthreads();                    // this channel's planes have landed; the other buffer is no longer read
-        if (cc + 1 < nch) {
-          float* const nx = stage + (size_t)((cc + 1) & 1) * (HW + Q);
-          stage_plane(nx, x + imgOff + (size_t)HW * (c0 + cc + 1), HW);
-          stage_plane(nx + HW, dyn + (size_t)Q * (c0 + cc + 1), Q);
-        }
-        // data gradient: every input pixel adds up its list in output-pixel order
-        float* const dxc = dx + imgOff + (size_t)HW * (c0 + cc);
+        __syncthreads();                    // this stage's dY has landed (and the lists are sorted); the other buffer is no longer read
+        if (st + 1 < nStages) stage_dy4(dy4 + (size_t)((st + 1) & 1) * kCB * Q, dyn + (size_t)Q * (cs + kCB), Q, min(kCB, c0 + nch - cs - kCB));
+        // every input pixel adds up its list in output-pixel order, four channels per walk.  The weight of an entry
+        // is wwx[j] * wwy[i] as the CPU loop forms it (bits/nnbilinearsampler.cu:108-110), from the output pixel's two fractions.
+        float* const dxc = dx + imgOff + (size_t)HW * cs;
         for (int pix = tid; pix < HW; pix += kGatherThreads) {
           int const beg = pix == 0 ? 0 : cur[pix - 1], end = cur[pix];
-          float acc = gi > 0 ? dxc[pix] : 0.f;
-          for (int e = beg; e < end; ++e) acc = __fadd_rn(acc, __fmul_rn(entW[e], ds[entQ[e]]));
-          dxc[pix] = acc;
+          float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+          if (gi > 0) {
+            a0 = dxc[pix];
+            if (nst > 1) a1 = dxc[pix + (size_t)HW];
+            if (nst > 2) a2 = dxc[pix + 2 * (size_t)HW];
+            if (nst > 3) a3 = dxc[pix + 3 * (size_t)HW];
+          }
+          for (int e = beg; e < end; ++e) {
+            unsigned const en = ent[e];
+            unsigned const q = en >> 2;
+            float2 const f = wq[q];
+            float const wx = (en & 2u) ? f.x : __fadd_rn(1.f, -f.x), wy = (en & 1u) ? f.y : __fadd_rn(1.f, -f.y);
+            float const w = __fmul_rn(wx, wy);
+            float const* const d = ds + q;
+            a0 = __fadd_rn(a0, __fmul_rn(w, d[0])); a1 = __fadd_rn(a1, __fmul_rn(w, d[Q]));
+            a2 = __fadd_rn(a2, __fmul_rn(w, d[2 * Q])); a3 = __fadd_rn(a3, __fmul_rn(w, d[3 * Q]));
+          }
+          dxc[pix] = a0;
+          if (nst > 1) dxc[pix + (size_t)HW] = a1;
+          if (nst > 2) dxc[pix + 2 * (size_t)HW] = a2;
+          if (nst > 3) dxc[pix + 3 * (size_t)HW] = a3;
         }
-        // grid derivative: this channel's term of every output pixel, the taps in the CPU loop's order (column offset j
-        // outer, row offset i inner; bits/nnbilinearsampler.cu:98-128).  (2j-1)*wwy*dy*x is evaluated left to right there;
-        // a negation is exact, so the two magnitudes wwy0*dy and wwy1*dy serve all four taps.
-        if (kWantGrid) {
+      }
+      // ---- grid derivative: a second sweep over the channels, two at a time, with the x planes beside the dY planes in the
+      // stage buffers (dY comes from L2 this time).  Every output pixel adds its channels' terms in ascending channel order, the
+      // taps in the CPU loop's order (column offset j outer, row offset i inner; bits/nnbilinearsampler.cu:98-128).
+      // (2j-1)*wwy*dy*x is evaluated left to right there; a negation is exact, so the two magnitudes wwy0*dy and wwy1*dy serve
+      // all four taps.
+      if (kWantGrid) {
+        float accGy[kMaxQPerThread], accGx[kMaxQPerThread];
+        // this thread's output pixels: first tap's offset in the plane | which of the four taps exist << 28, the two fractions
+        int tapInfo[kMaxQPerThread];
+        float tapWx[kMaxQPerThread], tapWy[kMaxQPerThread];
+#pragma unroll
+        for (int k = 0; k < kMaxQPerThread; ++k) {
+          accGy[k] = 0.f; accGx[k] = 0.f;
+          tapInfo[k] = 0; tapWx[k] = 0.f; tapWy[k] = 0.f;
+          int const q = tid + k * kGatherThreads;
+          if (q < Q) {
+            float2 const gv = gr[q];
+            Taps t = make_taps(gv.x, gv.y, H, W);
+            tapWx[k] = t.wx; tapWy[k] = t.wy;
+            if (t.inside)
+              tapInfo[k] = (t.sy + t.sx * H) |
+                           ((1 | (t.sy + 1 < H ? 2 : 0) | (t.sx + 1 < W ? 4 : 0) | ((t.sy + 1 < H && t.sx + 1 < W) ? 8 : 0)) << 28);   // bit ii + 2*j
+          }
+        }
+        float const sclY = __fmul_rn(0.5f, (float)(H - 1)), sclX = __fmul_rn(0.5f, (float)(W - 1));
+        // buffer b: x planes of two channels, then their dY planes
+        size_t const bufFloats = 2 * ((size_t)HW + Q);
+        auto stage2 = [&](int b, int cs, int n2) {
+          float* const base = dy4 + (size_t)b * bufFloats;
+          for (int j = 0; j < n2; ++j) {
+            stage_plane(base + (size_t)HW * j, x + imgOff + (size_t)HW * (cs + j), HW);
+            stage_plane(base + 2 * (size_t)HW + (size_t)Q * j, dyn + (size_t)Q * (cs + j), Q);
+          }
+        };
+        int const nStages2 = (nch + 1) / 2;
+        __syncthreads();                    // the last stage's dY is no longer read
+        stage2(0, c0, min(2, nch));
+        for (int st = 0; st < nStages2; ++st) {
+          int const cs = c0 + 2 * st, n2 = min(2, c0 + nch - cs);
+          float const* const xs = dy4 + (size_t)(st & 1) * bufFloats;
+          float const* const ds = xs + 2 * (size_t)HW;
+          cp_async_wait_all();
+          __syncthreads();
+          if (st + 1 < nStages2) stage2((st + 1) & 1, cs + 2, min(2, c0 + nch - cs - 2));
 #pragma unroll
           for (int k = 0; k < kMaxQPerThread; ++k) {
             int const q = tid + k * kGatherThreads;
-            if (q < Q && tapOk[k]) {
-              float const d = ds[q];
+            int const ok = (int)((unsigned)tapInfo[k] >> 28);
+            if (q < Q && ok) {
               float const wx1 = tapWx[k], wy1 = tapWy[k], wx0 = __fadd_rn(1.f, -wx1), wy0 = __fadd_rn(1.f, -wy1);
-              float const ty0 = __fmul_rn(wy0, d), ty1 = __fmul_rn(wy1, d), tx0 = __fmul_rn(wx0, d), tx1 = __fmul_rn(wx1, d);
-              float const* const xp = xs + tapBase[k];
-              int const ok = tapOk[k];
-              float dgx = 0.f, dgy = 0.f;
-              {                                         // j = 0, i = 0: dgx -= wwy0*d*x, dgy -= wwx0*d*x
-                float const xv = xp[0];
-                dgx = __fsub_rn(dgx, __fmul_rn(ty0, xv)); dgy = __fsub_rn(dgy, __fmul_rn(tx0, xv));
+              float const* p0 = xs + (tapInfo[k] & 0x0fffffff);      // taps (i = 0, 1; j = 0), and H further on (j = 1)
+              float const* dq = ds + q;
+              for (int j = 0; j < n2; ++j) {
+                float const d = dq[0];
+                float const ty0 = __fmul_rn(wy0, d), ty1 = __fmul_rn(wy1, d), tx0 = __fmul_rn(wx0, d), tx1 = __fmul_rn(wx1, d);
+                float dgx, dgy;
+                if (ok == 15) {
+                  float const x00 = p0[0], x10 = p0[1], x01 = p0[H], x11 = p0[H + 1];
+                  dgx = __fsub_rn(0.f, __fmul_rn(ty0, x00)); dgy = __fsub_rn(0.f, __fmul_rn(tx0, x00));
+                  dgx = __fsub_rn(dgx, __fmul_rn(ty1, x10)); dgy = __fadd_rn(dgy, __fmul_rn(tx0, x10));
+                  dgx = __fadd_rn(dgx, __fmul_rn(ty0, x01)); dgy = __fsub_rn(dgy, __fmul_rn(tx1, x01));
+                  dgx = __fadd_rn(dgx, __fmul_rn(ty1, x11)); dgy = __fadd_rn(dgy, __fmul_rn(tx1, x11));
+                } else {
+                  {                                         // j = 0, i = 0: dgx -= wwy0*d*x, dgy -= wwx0*d*x
+                    float const xv = p0[0];
+                    dgx = __fsub_rn(0.f, __fmul_rn(ty0, xv)); dgy = __fsub_rn(0.f, __fmul_rn(tx0, xv));
+                  }
+                  if (ok & 2) {                             // j = 0, i = 1: dgx -= wwy1*d*x, dgy += wwx0*d*x
+                    float const xv = p0[1];
+                    dgx = __fsub_rn(dgx, __fmul_rn(ty1, xv)); dgy = __fadd_rn(dgy, __fmul_rn(tx0, xv));
+                  }
+                  if (ok & 4) {                             // j = 1, i = 0: dgx += wwy0*d*x, dgy -= wwx1*d*x
+                    float const xv = p0[H];
+                    dgx = __fadd_rn(dgx, __fmul_rn(ty0, xv)); dgy = __fsub_rn(dgy, __fmul_rn(tx1, xv));
+                  }
+                  if (ok & 8) {                             // j = 1, i = 1: dgx += wwy1*d*x, dgy += wwx1*d*x
+                    float const xv = p0[H + 1];
+                    dgx = __fadd_rn(dgx, __fmul_rn(ty1, xv)); dgy = __fadd_rn(dgy, __fmul_rn(tx1, xv));
+                  }
+                }
+                accGy[k] = __fadd_rn(accGy[k], __fmul_rn(sclY, dgy));
+                accGx[k] = __fadd_rn(accGx[k], __fmul_rn(sclX, dgx));
+                p0 += HW; dq += Q;
               }
-              if (ok & 2) {                             // j = 0, i = 1: dgx -= wwy1*d*x, dgy += wwx0*d*x
-                float const xv = xp[1];
-                dgx = __fsub_rn(dgx, __fmul_rn(ty1, xv)); dgy = __fadd_rn(dgy, __fmul_rn(tx0, xv));
-              }
-              if (ok & 4) {                             // j = 1, i = 0: dgx += wwy0*d*x, dgy -= wwx1*d*x
-                float const xv = xp[H];
-                dgx = __fadd_rn(dgx, __fmul_rn(ty0, xv)); dgy = __fsub_rn(dgy, __fmul_rn(tx1, xv));
-              }
-              if (ok & 8) {                             // j = 1, i = 1: dgx += wwy1*d*x, dgy += wwx1*d*x
-                float const xv = xp[H + 1];
-                dgx = __fadd_rn(dgx, __fmul_rn(ty1, xv)); dgy = __fadd_rn(dgy, __fmul_rn(tx1, xv));
-              }
-              accGy[k] = __fadd_rn(accGy[k], __fmul_rn(sclY, dgy));
-              accGx[k] = __fadd_rn(accGx[k], __fmul_rn(sclX, dgx));
             }
           }
         }
-      }
-      if (kWantGrid) {
 #pragma unroll
         for (int k = 0; k < kMaxQPerThread; ++k) {
           int const q = tid + k * kGatherThreads;
@@ -398,7 +455,7 @@ int vlb_sampler_backward(vlb_ctx* ctx, float* dX, float* dGrid, float const* X, 
   VLB_REQUIRE(ctx, ((((uintptr_t)grid) | ((uintptr_t)dGrid)) & 7) == 0, "sampler_backward: grid must be 8-byte aligned");
   if (!dX && !dGrid) return VLB_Success;
   int const Qo = Ho * Wo, HWi = H * W;
-  if (dX && Qo <= 65535 && Qo <= kMaxQPerThread * kGatherThreads && gather_smem(HWi, Qo) <= 200 * 1024) {
+  if (dX && Qo <= kMaxQPerThread * kGatherThreads && HWi < (1 << 28) && gather_smem(HWi, Qo) <= 226 * 1024) {
     // gather: one CTA per image; with fewer images than SMs the channels are shared out among several CTAs per image,
     // and the grid derivative (which runs over all channels of an output pixel in order) is left to the other kernel
     int chunks = 1;
