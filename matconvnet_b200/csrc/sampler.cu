@@ -19,7 +19,7 @@
 // decoding an entry and forming its weight is paid once for the four), and writes dX once: no
 // atomics, no zero fill, the CPU's result bit for bit, identical from run to run.  The grid
 // derivative is a second sweep of the same CTA over the channels, two at a time, with the x
-// planes staged beside the dY planes (dY comes from L2 this time), every output pixel adding its
+// planes staged beside the dY planes (dY is read a second time), every output pixel adding its
 // channels' terms in ascending channel order.  A grid that sends more than kMaxList taps to one
 // input pixel, and planes too large for the lists, take the atomic scatter instead.
 //
@@ -276,7 +276,7 @@ sampler_bwd_gather_kernel(float* __restrict__ dx, float* __restrict__ dgrid, flo
         }
       }
       // ---- grid derivative: a second sweep over the channels, two at a time, with the x planes beside the dY planes in the
-      // stage buffers (dY comes from L2 this time).  Every output pixel adds its channels' terms in ascending channel order, the
+      // stage buffers (dY is read a second time).  Every output pixel adds its channels' terms in ascending channel order, the
       // taps in the CPU loop's order (column offset j outer, row offset i inner; bits/nnbilinearsampler.cu:98-128).
       // (2j-1)*wwy*dy*x is evaluated left to right there; a negation is exact, so the two magnitudes wwy0*dy and wwy1*dy serve
       // all four taps.
