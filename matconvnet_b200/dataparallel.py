@@ -46,11 +46,12 @@ def _dense(tensor):
 
 
 class GradientExchange:
-    def __init__(self, world_size=None, average=False, scale_fn=None, bucket_bytes=32 << 20):
+    def __init__(self, world_size=None, average=False, scale_fn=None, bucket_bytes=32 << 20, tail_bytes=2 << 20):
         self.world = world_size if world_size is not None else (dist.get_world_size() if dist.is_initialized() else 1)
         self.average = bool(average)
         self.scale_fn = scale_fn      # (tensor, alpha) -> None, in place; defaults to tensor.mul_
         self.bucket_bytes = int(bucket_bytes)
+        self.tail_bytes = int(tail_bytes)      # the most the last bucket may hold (its collective cannot overlap anything)
         self.pending = []             # (names, tensors, flat buffer or None, work)
         self.bytes = 0                # bytes handed to push since the counter was last reset
         self.collectives = 0          # all-reduce calls issued since the counter was last reset
@@ -62,35 +63,48 @@ class GradientExchange:
     def plan(self, specs, device, dtype=torch.float32):
         """specs: [(name, MATLAB shape)] in the order the backward pass will push them.  Returns {name: tensor}, each a
         column-major tensor of its shape that lives inside a flat bucket; consecutive tensors share a bucket until it
-        holds bucket_bytes.  Pushing exactly these tensors triggers one collective per bucket."""
+        holds bucket_bytes.  Pushing exactly these tensors triggers one collective per bucket.
+
+        The last bucket's collective starts when the backward pass ends, so all of it is waited for.  It is therefore
+        kept small: if it would hold more than tail_bytes, its trailing members that fit in tail_bytes (the first layers'
+        small filters, produced last) become a bucket of their own and the rest is reduced while those layers are still
+        being computed."""
         self._bucket_of, self._buckets = {}, []
         out = {}
-        group, size = [], 0
-
-        def close():
-            nonlocal group, size
-            if not group:
-                return
+        sized = []
+        for name, shape in specs:
+            numel = 1
+            for s in shape:
+                numel *= int(s)
+            sized.append((name, shape, numel, (numel + 63) // 64 * 64))     # members start on 256-byte boundaries (vector accesses)
+        groups, group, size = [], [], 0
+        for item in sized:
+            group.append(item)
+            size += item[3]
+            if size * 4 >= self.bucket_bytes:
+                groups.append(group)
+                group, size = [], 0
+        if group:
+            groups.append(group)
+        if groups and sum(i[3] for i in groups[-1]) * 4 > self.tail_bytes and len(groups[-1]) > 1:
+            last, tail, tsize = groups[-1], [], 0
+            while len(last) > 1 and (tsize + last[-1][3]) * 4 <= self.tail_bytes:
+                tsize += last[-1][3]
+                tail.insert(0, last.pop())
+            if tail:
+                groups.append(tail)
+        for group in groups:
+            size = sum(i[3] for i in group)
             flat = torch.zeros(size, device=device, dtype=dtype)
-            names = []
-            for name, shape, off, numel in group:
+            names, off = [], 0
+            for name, shape, numel, padded in group:
                 shape = tuple(int(s) for s in shape)
                 view = flat.narrow(0, off, numel).view(shape[::-1]).permute(*range(len(shape) - 1, -1, -1))
                 out[name] = view
                 self._bucket_of[name] = len(self._buckets)
                 names.append(name)
+                off += padded
             self._buckets.append(dict(flat=flat, names=names, missing=set(names), tensors={n: out[n] for n in names}))
-            group, size = [], 0
-
-        for name, shape in specs:
-            numel = 1
-            for s in shape:
-                numel *= int(s)
-            group.append((name, shape, size, numel))
-            size += (numel + 63) // 64 * 64          # members start on 256-byte boundaries (vector accesses)
-            if size * 4 >= self.bucket_bytes:
-                close()
-        close()
         return out
 
     # ------------------------------------------------------------------ push / pull

@@ -137,3 +137,30 @@ def test_single_worker_is_identity():
     exa = GradientExchange(1, average=True)
     exa.push("w", t)
     assert torch.equal(exa.pull_all()["w"], ref)
+
+
+def test_the_last_bucket_is_kept_small():
+    """The collective of the last bucket starts when the backward pass ends and is waited for in full, so the planner
+    splits the trailing small tensors (at most tail_bytes) off a last bucket that would hold more."""
+    sys.path.insert(0, ROOT)
+    from matconvnet_b200.dataparallel import GradientExchange
+    specs = [("a", (1000,)), ("b", (1000,)), ("c", (300,)), ("d", (40,)), ("e", (10,))]
+    ex = GradientExchange(1, bucket_bytes=6000, tail_bytes=1600)
+    views = ex.plan(specs, "cpu")
+    assert [b["names"] for b in ex._buckets] == [["a", "b"], ["c"], ["d", "e"]]
+    assert all(tuple(views[n].shape) == s for n, s in specs)
+    # a last bucket that is small enough stays whole; one whose last member alone is too large is not split
+    ex = GradientExchange(1, bucket_bytes=6000, tail_bytes=4000)
+    ex.plan(specs, "cpu")
+    assert [b["names"] for b in ex._buckets] == [["a", "b"], ["c", "d", "e"]]
+    ex = GradientExchange(1, bucket_bytes=1 << 20, tail_bytes=100)
+    ex.plan(specs, "cpu")
+    assert [b["names"] for b in ex._buckets] == [["a", "b", "c", "d", "e"]]
+    # every tensor still lands where it was planned and comes back from pull_all
+    ex = GradientExchange(1, bucket_bytes=6000, tail_bytes=1600)
+    views = ex.plan(specs, "cpu")
+    for i, (n, s) in enumerate(specs):
+        views[n].fill_(float(i + 1))
+        ex.push(n, views[n])
+    got = ex.pull_all()
+    assert all(torch.equal(got[n], torch.full(s, float(i + 1))) for i, (n, s) in enumerate(specs))
