@@ -296,6 +296,17 @@ def test_sampler_backward_gather_paths(gpu, oracle):
     assert bit_equal(mat.to_numpy(dx), dxr) and bit_equal(mat.to_numpy(dgrid), dgr)
     dx2, _ = nn.vl_nnbilinearsampler(xd, gd, dyd)
     assert torch.equal(dx, dx2)
+    # 1b: planes whose sizes are not multiples of four (the stages are filled with 4-byte copies), five channels (a full
+    # stage of four and a stage of one for the data gradient; two stages of two and one of one for the grid derivative),
+    # more input than output pixels
+    H, W, C, N, Ng, Ho, Wo = 7, 9, 5, 150, 150, 5, 7
+    xb = np.asfortranarray(rng.standard_normal((H, W, C, N)).astype(np.float32))
+    gridb = np.asfortranarray(rng.uniform(-1.05, 1.05, (2, Ho, Wo, Ng)).astype(np.float32))
+    dyb = np.asfortranarray(rng.standard_normal((Ho, Wo, C, Ng)).astype(np.float32))
+    dx, dgrid = nn.vl_nnbilinearsampler(*_up(mat, xb, gridb, dyb))
+    dxr, dgr = oracle.sampler_backward(xb, gridb, dyb)
+    assert bit_equal(mat.to_numpy(dx), dxr) and bit_equal(mat.to_numpy(dgrid), dgr)
+    H, W, C, N, Ng, Ho, Wo = 12, 20, 13, 3, 6, 16, 8
     # 2: every output pixel samples around one point
     grid2 = np.asfortranarray((0.013 * rng.standard_normal((2, Ho, Wo, Ng)) + 0.2).astype(np.float32))
     dyi = np.asfortranarray(rng.integers(-3, 4, (Ho, Wo, C, Ng)).astype(np.float32))
