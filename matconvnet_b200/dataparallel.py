@@ -56,7 +56,7 @@ class GradientExchange:
         self.bytes = 0                # bytes handed to push since the counter was last reset
         self.collectives = 0          # all-reduce calls issued since the counter was last reset
         self._bucket_of = {}          # name -> bucket index
-        self._buckets = []            # dicts: flat, names, missing (set of names not yet pushed this round)
+        self._buckets = []            # dicts: flat, names, missing (set of names not yet pushed in this step)
         self._native_avg = None
 
     # ------------------------------------------------------------------ planning
