@@ -1213,7 +1213,7 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
   float* const Psm = reinterpret_cast<float*>(smem + (size_t)nB * bBytes);      // [BN][BM]
   // input windows (kTma): two buffers of boxH*boxW*32 floats behind P
   uint32_t const xPlane = (uint32_t)(p.boxH * p.boxW), xTileBytes = kWg ? (uint32_t)kWgStageBytes : xPlane * 32u * 4u;
-  bool const regsP = (BN == 128 || BN == 64) && !p.smemSum;      // the running sum of a tile lives in the drain warps' registers
+  bool const regsP = (kWg ? (BN == 128 || BN == 64) : (kNarrow ? BN == 64 : BN == 128)) && !p.smemSum;      // the running sum of a tile lives in the drain warps' registers
   uint32_t const xTile0 = smem_u32(Psm) + (regsP ? 32u : (uint32_t)BN) * BM * 4u;      // (registers: a patch of 32 columns for the stores)
 
   int const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1374,9 +1374,19 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
         }
       }
     };
-    if (regsP && BN == 128) drain(std::integral_constant<int, 128>{});
-    else if (regsP) drain(std::integral_constant<int, 64>{});
-    else drain(std::integral_constant<int, 0>{});
+    // (each variant is compiled with the drain loops it can need only: the kernel's code has to stay small -- the variants for
+    // 64-column tiles lost 10-30% whenever a few instructions were added to their roles)
+    if constexpr (kWg) {
+      if (regsP && BN == 128) drain(std::integral_constant<int, 128>{});
+      else if (regsP) drain(std::integral_constant<int, 64>{});
+      else drain(std::integral_constant<int, 0>{});
+    } else if constexpr (kNarrow) {
+      if (regsP && BN == 64) drain(std::integral_constant<int, 64>{});
+      else drain(std::integral_constant<int, 0>{});
+    } else {
+      if (regsP && BN == 128) drain(std::integral_constant<int, 128>{});
+      else drain(std::integral_constant<int, 0>{});
+    }
   } else if (warp < 2 * kEpilogueWarps) {
     // warps 4-7 (issuers, filter-tile loader, forwarder) work with one thread each and a handful of registers: the rest goes
     // to the drain warps.  All four warps of the group execute this before anything else.
