@@ -1209,9 +1209,6 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
   // 64-channel row tiles, level elsewhere).  Or the producers, when they find their A stage free again: 128-column tiles
   // of the other modes, where the second commit cost the issuers 2-5% (forward) to 10% (data gradient with the ReLU mask).
   constexpr bool issuerFreesB = kWg || kNarrow;
-  // Narrow tiles: no second commit either -- the loader waits on the barrier of the k-block's A stage, which reports the same
-  // event (3-4% faster on the 64-column layers; the row mode lost 8% on its 64-column tiles that way and keeps the second commit).
-  constexpr bool loaderWaitsA = kNarrow;
   uint32_t const colA = (uint32_t)(kNT * BN);
   float* const Psm = reinterpret_cast<float*>(smem + (size_t)nB * bBytes);      // [BN][BM]
   // input windows (kTma): two buffers of boxH*boxW*32 floats behind P
@@ -1471,7 +1468,7 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
           }
           if (!ok) break;
           umma_commit(smem_u32(&emptyA[sa]));     // when these MMAs are through: the A stage goes back to its producers,
-          if (issuerFreesB && !loaderWaitsA) umma_commit(smem_u32(&emptyB[sb]));     // the filter stage to the loader
+          if (issuerFreesB) umma_commit(smem_u32(&emptyB[sb]));     // the filter stage to the loader
           ++own;
           sb += 2; if (sb >= nB) sb -= nB;
           if (chunkEnd) umma_commit(smem_u32(&tFull[g % kNT]));   // chain complete: hand it to the drain warps
@@ -1486,20 +1483,11 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
     if (lane == 0 && !(p.testSwitch & 1)) {
       int sb = 0; uint32_t ph = 1;                       // first use of a stage: nothing to wait for
       bool ok = true;
-      long long gk = 0;                                  // k-blocks numbered over the CTA's life
       for (int ts = 0; ts < myTiles && ok; ++ts) {
         int const tile = (int)blockIdx.x + ts * (int)gridDim.x;
         int const nt = tile % p.tilesN;
         float const* src = p.bTiles + ((size_t)nt * p.kbTot + (size_t)(tile / p.tilesN / p.tilesM) * numIter) * (bBytes / 4);
-        for (int it = 0; it < numIter; ++it, ++gk) {
-          if (loaderWaitsA) {
-            // The stage held the filter tile of k-block gk - nB, which is free when that k-block's MMAs are through -- the event
-            // its A stage's barrier already reports (k-block j: stage j % kNA, phase j / kNA), so the issuer need not commit twice.
-            // (This thread comes by every k-block and waits for nothing else, so it cannot miss a phase: the same stage
-            // completes again kNA k-blocks later at the earliest.)
-            long long const j = gk - nB;
-            if (j >= 0 && !mbar_wait(smem_u32(&emptyA[j & (kNA - 1)]), (uint32_t)((j >> (kAShift + 1)) & 1))) { atomicExch(p.status, 8); ok = false; break; }
-          } else
+        for (int it = 0; it < numIter; ++it) {
           if (!mbar_wait(smem_u32(&emptyB[sb]), ph)) { atomicExch(p.status, 8); ok = false; break; }
           mbar_arrive_expect_tx(smem_u32(&fullB[sb]), bBytes);
           bulk_copy_g2s(smem_u32(smem + (size_t)sb * bBytes), src + (size_t)it * (bBytes / 4), bBytes, smem_u32(&fullB[sb]));
