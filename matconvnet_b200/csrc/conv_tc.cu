@@ -1168,6 +1168,16 @@ constexpr int kWgRowWords = 36;                         // words per row of an x
 constexpr int kWgRowBytes = kWgRowWords * 4;
 constexpr int kWgStageBytes = BM * kWgRowBytes;         // 18432
 constexpr int kTsXStages = 6;                           // at most
+// "The MMAs of k-block j (numbered over the CTA's life) are through" is reported on barrier j % kTsDoneRing, phase j / kTsDoneRing,
+// by the issuer's one commit per k-block.  Two parties wait for it: the producers of the A stage (for k-block j + kNA) and, in the
+// forward / data-gradient modes, the filter-tile loader (for k-block j + bStages) -- the filter stage is free at the same moment,
+// so the issuer needs no second commit and the producers need not tell the loader.  The ring is longer than either party can
+// fall behind (at most bStages - 1 <= 5 k-blocks can complete before the loader has looked, at most kNA - 1 before a producer
+// has), so a waiter never meets a barrier that is already a phase further.  (Waiting on the barriers of the kNA A stages instead
+// was tried first: with six filter stages and four A stages the loader fell a whole phase behind on conv1_2 at batch 64 and then
+// waited for a completion that needed its own copies -- the bounded wait ran out.)
+constexpr int kTsDoneRing = 8;
+static_assert(kTsBStages < kTsDoneRing, "the loader must not be able to fall a whole ring behind");
 
 // Registers (kMode 0, 1): 128 per thread at launch (512 threads: the whole register file, one CTA per SM); then the warps 4-7
 // keep 56 and the drain warps 0-3 take 200 (setmaxnreg: 128 of them hold the running sum of a tile).
@@ -1185,7 +1195,7 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
 {
   constexpr bool kTma = kMode == 1, kWg = kMode == 2;
   extern __shared__ uint8_t smemRaw[];
-  __shared__ __align__(8) uint64_t fullA[4], emptyA[4], fullB[kTsBStages], emptyB[kTsBStages];
+  __shared__ __align__(8) uint64_t fullA[4], doneK[kTsDoneRing], fullB[kTsBStages], emptyB[kTsBStages];
   __shared__ __align__(8) uint64_t tFull[4], tFree[4], tileDone, turn[2], fullX[kTsXStages], emptyX[kTsXStages];
   __shared__ uint32_t tmemBase;
   __shared__ int2 tapLut[64];       // per filter tap fh + FH*fw: {element offset of the tap (in the input window when kTma), fh | fw << 5}
@@ -1204,11 +1214,12 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
   // level with three + two -- the refill of an A stage is not what bounds those tiles.)
   constexpr int kNA = kNarrow ? 4 : 2, kAPer = kNA / 2, kAShift = kNA == 4 ? 1 : 0;      // kAPer = 1 << kAShift
   constexpr int kNT = kNarrow ? 4 : 3;
-  // Who tells the loader that a filter stage is free.  The issuer, with a second commit per k-block: narrow tiles (whose
-  // producers learn of a finished k-block only two of their own k-blocks later) and the row mode (measured 3-11% faster on
-  // 64-channel row tiles, level elsewhere).  Or the producers, when they find their A stage free again: 128-column tiles
-  // of the other modes, where the second commit cost the issuers 2-5% (forward) to 10% (data gradient with the ReLU mask).
-  constexpr bool issuerFreesB = kWg || kNarrow;
+  // Who tells the loader that a filter stage is free: the k-block's completion barrier (doneK, above) in the forward and
+  // data-gradient modes (against a second commit per k-block on the narrow tiles and an arrival by the producers on the wide
+  // ones: 3-4% faster on the 64-column layers, 1-3% on the 128-column layers); the row mode keeps a second commit by the issuer
+  // on a barrier per filter stage (it lost 8% on its 64-column tiles without it and was level elsewhere).
+  constexpr bool issuerFreesB = kWg;
+  constexpr int kRing = kWg ? kNA : kTsDoneRing;      // (row mode: only the producers wait, a barrier per A stage is enough)
   uint32_t const colA = (uint32_t)(kNT * BN);
   float* const Psm = reinterpret_cast<float*>(smem + (size_t)nB * bBytes);      // [BN][BM]
   // input windows (kTma): two buffers of boxH*boxW*32 floats behind P
@@ -1226,7 +1237,8 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
 
   if (threadIdx.x == 0) {
     // an A stage is full when its four producer warps and the forwarder (filter tile landed) have arrived
-    for (int s = 0; s < 4; ++s) { mbar_init(smem_u32(&fullA[s]), 5); mbar_init(smem_u32(&emptyA[s]), 1); }
+    for (int s = 0; s < 4; ++s) mbar_init(smem_u32(&fullA[s]), 5);
+    for (int s = 0; s < kTsDoneRing; ++s) mbar_init(smem_u32(&doneK[s]), 1);
     for (int s = 0; s < kTsBStages; ++s) { mbar_init(smem_u32(&fullB[s]), 1); mbar_init(smem_u32(&emptyB[s]), 1); }
     for (int b = 0; b < 4; ++b) { mbar_init(smem_u32(&tFull[b]), 1); mbar_init(smem_u32(&tFree[b]), kEpilogueWarps); }
     mbar_init(smem_u32(&tileDone), kEpilogueWarps);
@@ -1467,8 +1479,8 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
             if (takeTurns && k8 == BK / 8 - 2) mbar_arrive(smem_u32(&turn[q ^ 1]));
           }
           if (!ok) break;
-          umma_commit(smem_u32(&emptyA[sa]));     // when these MMAs are through: the A stage goes back to its producers,
-          if (issuerFreesB) umma_commit(smem_u32(&emptyB[sb]));     // the filter stage to the loader
+          umma_commit(smem_u32(&doneK[(2u * own + (uint32_t)q) & (uint32_t)(kRing - 1)]));     // when these MMAs are through: the A stage goes back to its producers and (forward, data gradient) the filter stage to the loader
+          if (issuerFreesB) umma_commit(smem_u32(&emptyB[sb]));     // (row mode) the filter stage to the loader
           ++own;
           sb += 2; if (sb >= nB) sb -= nB;
           if (chunkEnd) umma_commit(smem_u32(&tFull[g % kNT]));   // chain complete: hand it to the drain warps
@@ -1483,11 +1495,17 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
     if (lane == 0 && !(p.testSwitch & 1)) {
       int sb = 0; uint32_t ph = 1;                       // first use of a stage: nothing to wait for
       bool ok = true;
+      long long gk = 0;                                  // k-blocks numbered over the CTA's life
       for (int ts = 0; ts < myTiles && ok; ++ts) {
         int const tile = (int)blockIdx.x + ts * (int)gridDim.x;
         int const nt = tile % p.tilesN;
         float const* src = p.bTiles + ((size_t)nt * p.kbTot + (size_t)(tile / p.tilesN / p.tilesM) * numIter) * (bBytes / 4);
-        for (int it = 0; it < numIter; ++it) {
+        for (int it = 0; it < numIter; ++it, ++gk) {
+          if (!issuerFreesB) {
+            // the stage held the filter tile of k-block gk - nB
+            long long const j = gk - nB;
+            if (j >= 0 && !mbar_wait(smem_u32(&doneK[j & (kRing - 1)]), (uint32_t)((j / kRing) & 1))) { atomicExch(p.status, 8); ok = false; break; }
+          } else
           if (!mbar_wait(smem_u32(&emptyB[sb]), ph)) { atomicExch(p.status, 8); ok = false; break; }
           mbar_arrive_expect_tx(smem_u32(&fullB[sb]), bBytes);
           bulk_copy_g2s(smem_u32(smem + (size_t)sb * bBytes), src + (size_t)it * (bBytes / 4), bBytes, smem_u32(&fullB[sb]));
@@ -1586,8 +1604,6 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
     int const HW = p.a.H * p.a.W, taps = p.a.FH * p.a.FW;
     uint32_t const aBase = tmemAcc + ((uint32_t)(quarter * 32) << 16) + colA;
     uint32_t own = 0;                                   // this group's k-blocks so far: k-block `own` goes into A stage grp + 2*(own % kAPer)
-    bool const herald = !issuerFreesB && (warp - kTsFirstProducer) % 4 == 0 && lane == 0;   // tells the loader about freed filter stages
-    int sbFree = grp;                                   // filter stage of the k-block whose MMAs this group sees complete next
     long long gi = 0;                                   // k-blocks numbered over the CTA's life; this group takes gi % 2 == grp
     bool ok = true;
 
@@ -1602,10 +1618,9 @@ __global__ void __launch_bounds__(kMode == 2 ? kTsThreadsRows : kTsThreads, 1) c
       }
       int const sa = grp + 2 * (int)(own & (uint32_t)(kAPer - 1));
       uint32_t const aAddr = aBase + (uint32_t)(sa * 64);
-      if (!mbar_wait(smem_u32(&emptyA[sa]), ((own >> kAShift) & 1u) ^ 1u)) { atomicExch(p.status, 1); return false; }      // (first use of a stage: nothing to wait for)
-      if (herald && own >= 1) {          // (one A stage per issuer here:) the MMAs of this group's previous k-block are complete: its filter stage is free too
-        mbar_arrive(smem_u32(&emptyB[sbFree]));
-        sbFree += kTsGroups; if (sbFree >= nB) sbFree -= nB;
+      if (own >= (uint32_t)kAPer) {      // (first use of a stage: nothing to wait for) the stage's previous k-block, kNA before this one, must be through
+        uint32_t const jp = 2u * (own - (uint32_t)kAPer) + (uint32_t)grp;
+        if (!mbar_wait(smem_u32(&doneK[jp & (uint32_t)(kRing - 1)]), (jp / (uint32_t)kRing) & 1u)) { atomicExch(p.status, 1); return false; }
       }
       ++own;
       tc_fence_after();
