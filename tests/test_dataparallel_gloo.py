@@ -164,3 +164,24 @@ def test_the_last_bucket_is_kept_small():
         ex.push(n, views[n])
     got = ex.pull_all()
     assert all(torch.equal(got[n], torch.full(s, float(i + 1))) for i, (n, s) in enumerate(specs))
+
+
+def test_vgg16_gradients_are_planned_into_five_buckets_with_a_small_last_one():
+    """The benchmark's network: filters and biases of fc8 ... conv1_1 in the order the backward pass produces them."""
+    sys.path.insert(0, ROOT)
+    from matconvnet_b200.dataparallel import GradientExchange
+    convs = [(3, 64), (64, 64), (64, 128), (128, 128), (128, 256), (256, 256), (256, 256), (256, 512), (512, 512), (512, 512),
+             (512, 512), (512, 512), (512, 512)]
+    fcs = [((7, 7, 512, 4096), 4096), ((1, 1, 4096, 4096), 4096), ((1, 1, 4096, 1000), 1000)]
+    specs = []
+    for i, (shape, k) in enumerate(reversed(fcs)):
+        specs += [("fc%d_f" % i, shape), ("fc%d_b" % i, (1, k))]
+    for i, (c, k) in enumerate(reversed(convs)):
+        specs += [("conv%d_f" % i, (3, 3, c, k)), ("conv%d_b" % i, (1, k))]
+    ex = GradientExchange(2, average=True)
+    ex.plan(specs, "meta")
+    sizes = [b["flat"].numel() * 4 for b in ex._buckets]
+    assert len(sizes) == 5
+    assert sizes[-1] <= 2 << 20 and sizes[-2] > 8 << 20          # the tail is small; what was cut off it goes out earlier
+    assert sum(len(b["names"]) for b in ex._buckets) == len(specs)
+    assert ex._buckets[-1]["names"][-1] == "conv12_b"            # the first layer's bias is produced last
